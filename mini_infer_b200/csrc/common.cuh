@@ -1,0 +1,108 @@
+// Shared helpers of the kernel libraries.
+//
+// Every library is a plain shared object with `extern "C"` entry points that take
+// device pointers, sizes and a CUDA stream, launch on that stream and return a
+// status: 0 = launched, > 0 = a cudaError_t, < 0 = the arguments were refused
+// (the reason is then available from mi_error_message()).  Nothing here allocates
+// device memory and nothing synchronises.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define MI_DTYPE_F32 0
+#define MI_DTYPE_BF16 1
+
+#define MI_REFUSED (-1)
+
+#define MI_DEFINE_ERROR_API()                                              \
+  static thread_local char g_mi_error[512] = "";                           \
+  extern "C" const char* mi_error_message() { return g_mi_error; }
+
+#define MI_REFUSE(...)                                                     \
+  do {                                                                     \
+    snprintf(g_mi_error, sizeof(g_mi_error), __VA_ARGS__);                 \
+    return MI_REFUSED;                                                     \
+  } while (0)
+
+#define MI_RETURN_LAUNCH_STATUS()                                          \
+  do {                                                                     \
+    cudaError_t e__ = cudaGetLastError();                                  \
+    if (e__ != cudaSuccess) {                                              \
+      snprintf(g_mi_error, sizeof(g_mi_error), "CUDA: %s",                 \
+               cudaGetErrorString(e__));                                   \
+      return (int)e__;                                                     \
+    }                                                                      \
+    return 0;                                                              \
+  } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float mi_to_float(float x) { return x; }
+__device__ __forceinline__ float mi_to_float(bf16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T mi_from_float(float x);
+template <>
+__device__ __forceinline__ float mi_from_float<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ bf16 mi_from_float<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+// Four consecutive elements, loaded/stored as one access where T allows.
+template <typename T>
+struct Vec4;
+template <>
+struct Vec4<float> {
+  float4 v;
+  __device__ __forceinline__ void load(const float* p) { v = *reinterpret_cast<const float4*>(p); }
+  __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }
+  __device__ __forceinline__ void get(float (&f)[4]) const { f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w; }
+  __device__ __forceinline__ void set(const float (&f)[4]) { v = make_float4(f[0], f[1], f[2], f[3]); }
+};
+template <>
+struct Vec4<bf16> {
+  uint2 v;
+  __device__ __forceinline__ void load(const bf16* p) { v = *reinterpret_cast<const uint2*>(p); }
+  __device__ __forceinline__ void store(bf16* p) const { *reinterpret_cast<uint2*>(p) = v; }
+  __device__ __forceinline__ void get(float (&f)[4]) const {
+    __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+    __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+    float2 fa = __bfloat1622float2(a), fb = __bfloat1622float2(b);
+    f[0] = fa.x; f[1] = fa.y; f[2] = fb.x; f[3] = fb.y;
+  }
+  __device__ __forceinline__ void set(const float (&f)[4]) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]);
+    __nv_bfloat162 b = __floats2bfloat162_rn(f[2], f[3]);
+    v.x = *reinterpret_cast<uint32_t*>(&a);
+    v.y = *reinterpret_cast<uint32_t*>(&b);
+  }
+};
+
+__device__ __forceinline__ float mi_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float mi_warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over the block; `scratch` holds 32 floats.  Every thread gets the result.
+// The order of additions depends only on blockDim, never on the data.
+__device__ __forceinline__ float mi_block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = mi_warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : 0.f;
+  t = mi_warp_sum(t);
+  return t;
+}
+
+static inline bool mi_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

@@ -1,0 +1,316 @@
+// Row-wise kernels of the decoder: token embedding, (residual add +) RMS norm,
+// rotary position encoding fused with the key/value page write, SiLU-and-multiply.
+//
+// All arithmetic is fp32; T is the storage type of activations (float or bf16).
+// The residual stream is always stored in fp32.  Each kernel accepts any width;
+// widths that are a multiple of 4 with 16-byte aligned rows take the vector path.
+#include "common.cuh"
+
+MI_DEFINE_ERROR_API()
+
+// ---------------------------------------------------------------------------
+// Embedding: out[t, :] = table[ids[t], :].  An id outside [0, V) writes NaN rows
+// (the step function validates ids on the host; this keeps a fault visible).
+// ---------------------------------------------------------------------------
+template <typename T, int VEC>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                 T* __restrict__ out, int H, int V) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  T* dst = out + (size_t)t * H;
+  if ((unsigned)id >= (unsigned)V) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = mi_from_float<T>(__int_as_float(0x7fc00000));
+    return;
+  }
+  const T* src = table + (size_t)id * H;
+  if (VEC == 4) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      Vec4<T> v;
+      v.load(src + i);
+      v.store(dst + i);
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+extern "C" int mi_embedding(const void* table, const int* ids, void* out, int M, int H, int V,
+                            int dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (H <= 0 || V <= 0) MI_REFUSE("embedding: bad sizes H=%d V=%d", H, V);
+  const size_t es = dtype == MI_DTYPE_F32 ? 4 : 2;
+  const bool vec = (H % 4 == 0) && mi_aligned(table, 16) && mi_aligned(out, 16) && ((H * es) % 16 == 0 || es == 4);
+  int threads = H / 4 >= 256 ? 256 : (H / 4 >= 128 ? 128 : 64);
+  if (dtype == MI_DTYPE_F32) {
+    if (vec) embedding_kernel<float, 4><<<M, threads, 0, stream>>>((const float*)table, ids, (float*)out, H, V);
+    else embedding_kernel<float, 1><<<M, threads, 0, stream>>>((const float*)table, ids, (float*)out, H, V);
+  } else if (dtype == MI_DTYPE_BF16) {
+    const bool vecb = vec && (H % 8 == 0);
+    if (vecb) embedding_kernel<bf16, 4><<<M, threads, 0, stream>>>((const bf16*)table, ids, (bf16*)out, H, V);
+    else embedding_kernel<bf16, 1><<<M, threads, 0, stream>>>((const bf16*)table, ids, (bf16*)out, H, V);
+  } else {
+    MI_REFUSE("embedding: unknown dtype %d", dtype);
+  }
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// (Residual add +) RMS norm.
+//   r      = float(x[src]) + (res_in ? res_in[src] : 0)        src = rows ? rows[i] : i
+//   res_out[i] = r                                              (if res_out)
+//   out[i] = T( w * r * rsqrt(mean(r^2) + eps) )
+// One block per output row.  r is kept in shared memory when the row fits,
+// else it is recomputed from the inputs in the second pass (same value).
+// ---------------------------------------------------------------------------
+template <typename T, typename WT, int VEC>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ x, const float* __restrict__ res_in,
+                                   float* __restrict__ res_out, const WT* __restrict__ w,
+                                   T* __restrict__ out, const int* __restrict__ rows, int H,
+                                   float eps, int cache_row) {
+  extern __shared__ float smem[];
+  float* red = smem;         // 32 floats
+  float* rbuf = smem + 32;   // H floats when cache_row
+  const int i = blockIdx.x;
+  const int src = rows ? rows[i] : i;
+  const T* xr = x + (size_t)src * H;
+  const float* rr = res_in ? res_in + (size_t)src * H : nullptr;
+  float* ro = res_out ? res_out + (size_t)i * H : nullptr;
+  T* orow = out + (size_t)i * H;
+
+  float ss = 0.f;
+  if (VEC == 4) {
+    for (int k = threadIdx.x * 4; k < H; k += blockDim.x * 4) {
+      Vec4<T> xv;
+      xv.load(xr + k);
+      float f[4];
+      xv.get(f);
+      if (rr) {
+        float4 rv = *reinterpret_cast<const float4*>(rr + k);
+        f[0] += rv.x; f[1] += rv.y; f[2] += rv.z; f[3] += rv.w;
+      }
+      ss += f[0] * f[0];
+      ss += f[1] * f[1];
+      ss += f[2] * f[2];
+      ss += f[3] * f[3];
+      if (ro) *reinterpret_cast<float4*>(ro + k) = make_float4(f[0], f[1], f[2], f[3]);
+      if (cache_row) *reinterpret_cast<float4*>(rbuf + k) = make_float4(f[0], f[1], f[2], f[3]);
+    }
+  } else {
+    for (int k = threadIdx.x; k < H; k += blockDim.x) {
+      float f = mi_to_float(xr[k]);
+      if (rr) f += rr[k];
+      ss += f * f;
+      if (ro) ro[k] = f;
+      if (cache_row) rbuf[k] = f;
+    }
+  }
+  const float total = mi_block_sum(ss, red);
+  const float inv = rsqrtf(total / (float)H + eps);
+  // (the block sum's __syncthreads also orders the rbuf writes before these reads)
+  if (VEC == 4) {
+    for (int k = threadIdx.x * 4; k < H; k += blockDim.x * 4) {
+      float f[4];
+      if (cache_row) {
+        float4 rv = *reinterpret_cast<const float4*>(rbuf + k);
+        f[0] = rv.x; f[1] = rv.y; f[2] = rv.z; f[3] = rv.w;
+      } else {
+        Vec4<T> xv;
+        xv.load(xr + k);
+        xv.get(f);
+        if (rr) {
+          float4 rv = *reinterpret_cast<const float4*>(rr + k);
+          f[0] += rv.x; f[1] += rv.y; f[2] += rv.z; f[3] += rv.w;
+        }
+      }
+      float o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = mi_to_float(w[k + j]) * (f[j] * inv);
+      Vec4<T> ov;
+      ov.set(o);
+      ov.store(orow + k);
+    }
+  } else {
+    for (int k = threadIdx.x; k < H; k += blockDim.x) {
+      float f;
+      if (cache_row) {
+        f = rbuf[k];
+      } else {
+        f = mi_to_float(xr[k]);
+        if (rr) f += rr[k];
+      }
+      orow[k] = mi_from_float<T>(mi_to_float(w[k]) * (f * inv));
+    }
+  }
+}
+
+template <typename T, typename WT>
+static int launch_add_rmsnorm(const void* x, const float* res_in, float* res_out, const void* w,
+                              void* out, const int* rows, int M, int H, float eps,
+                              cudaStream_t stream) {
+  const size_t es = sizeof(T);
+  bool vec = (H % 4 == 0) && ((H * es) % (es == 2 ? 8 : 16) == 0) && mi_aligned(x, 16) &&
+             mi_aligned(out, 16) && (!res_in || mi_aligned(res_in, 16)) &&
+             (!res_out || mi_aligned(res_out, 16));
+  int threads = 32;
+  while (threads < 512 && threads * 8 < H) threads <<= 1;
+  const size_t row_bytes = (size_t)H * sizeof(float);
+  const int cache_row = row_bytes <= 160 * 1024 ? 1 : 0;
+  const size_t smem = 32 * sizeof(float) + (cache_row ? row_bytes : 0);
+  auto kern = vec ? add_rmsnorm_kernel<T, WT, 4> : add_rmsnorm_kernel<T, WT, 1>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  kern<<<M, threads, smem, stream>>>((const T*)x, res_in, res_out, (const WT*)w, (T*)out, rows, H, eps,
+                                     cache_row);
+  return 0;
+}
+
+// w_dtype: dtype of the gain vector (a gain stored in 32-bit stays 32-bit even when
+// activations are bf16).
+extern "C" int mi_add_rmsnorm(const void* x, const float* res_in, float* res_out, const void* w,
+                              void* out, const int* rows, int M, int H, float eps, int dtype,
+                              int w_dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (H <= 0) MI_REFUSE("rmsnorm: bad width %d", H);
+  int rc;
+  if (dtype == MI_DTYPE_F32 && w_dtype == MI_DTYPE_F32)
+    rc = launch_add_rmsnorm<float, float>(x, res_in, res_out, w, out, rows, M, H, eps, stream);
+  else if (dtype == MI_DTYPE_BF16 && w_dtype == MI_DTYPE_BF16)
+    rc = launch_add_rmsnorm<bf16, bf16>(x, res_in, res_out, w, out, rows, M, H, eps, stream);
+  else if (dtype == MI_DTYPE_BF16 && w_dtype == MI_DTYPE_F32)
+    rc = launch_add_rmsnorm<bf16, float>(x, res_in, res_out, w, out, rows, M, H, eps, stream);
+  else
+    MI_REFUSE("rmsnorm: unsupported dtype pair (%d, %d)", dtype, w_dtype);
+  if (rc) return rc;
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// Rotary position encoding of q and k (half layout: dim j pairs with j + rot/2),
+// fused with the write of k and v into cache pages.
+//   qkv      [M, (nq + 2 nkv) * d]   q heads, then k heads, then v heads
+//   pos      [M]  absolute positions;  inv_freq [rot/2] fp32
+//   slot     [M]  flat cache slot (page * page_size + offset) of each token, < 0: no write
+//   kcache, vcache  [slots, nkv, d]  (may be null: rotate only)
+// q is rotated in place.  k is rotated in place too (so that a later reader of the
+// buffer sees what the cache holds) and stored; v is copied.  Angles, sine and cosine
+// are fp32; each output is rounded once.  rot = 0 means no rotation (store only).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_write_kernel(T* __restrict__ qkv, const int* __restrict__ pos,
+                                  const float* __restrict__ inv_freq, const int* __restrict__ slot,
+                                  T* __restrict__ kcache, T* __restrict__ vcache, int nq, int nkv,
+                                  int d, int rot) {
+  const int t = blockIdx.x;
+  const int width = (nq + 2 * nkv) * d;
+  T* row = qkv + (size_t)t * width;
+  const int sl = (slot && kcache) ? slot[t] : -1;
+  const int half = rot >> 1;
+  const int nrot_heads = nq + nkv;
+  if (half > 0) {
+    const float p = (float)pos[t];
+    int cached_i = -1;
+    float c = 1.f, s = 0.f;
+    for (int idx = threadIdx.x; idx < nrot_heads * half; idx += blockDim.x) {
+      const int h = idx / half, i = idx - h * half;
+      if (i != cached_i) {
+        sincosf(p * inv_freq[i], &s, &c);
+        cached_i = i;
+      }
+      T* head = row + (size_t)h * d;
+      const float x1 = mi_to_float(head[i]);
+      const float x2 = mi_to_float(head[i + half]);
+      const T y1 = mi_from_float<T>(x1 * c - x2 * s);
+      const T y2 = mi_from_float<T>(x2 * c + x1 * s);
+      head[i] = y1;
+      head[i + half] = y2;
+      if (h >= nq && sl >= 0) {
+        T* dst = kcache + ((size_t)sl * nkv + (h - nq)) * d;
+        dst[i] = y1;
+        dst[i + half] = y2;
+      }
+    }
+  }
+  if (sl >= 0) {
+    // un-rotated tail of k (rot < d) and all of v
+    const int tail = d - rot;
+    for (int idx = threadIdx.x; idx < nkv * tail; idx += blockDim.x) {
+      const int h = idx / tail, i = rot + (idx - h * tail);
+      kcache[((size_t)sl * nkv + h) * d + i] = row[(size_t)(nq + h) * d + i];
+    }
+    const T* vsrc = row + (size_t)(nq + nkv) * d;
+    T* vdst = vcache + (size_t)sl * nkv * d;
+    for (int idx = threadIdx.x; idx < nkv * d; idx += blockDim.x) vdst[idx] = vsrc[idx];
+  }
+}
+
+extern "C" int mi_rope_write(void* qkv, const int* pos, const float* inv_freq, const int* slot,
+                             void* kcache, void* vcache, int M, int nq, int nkv, int d, int rot,
+                             int dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (nq < 0 || nkv < 0 || d <= 0) MI_REFUSE("rope: bad sizes nq=%d nkv=%d d=%d", nq, nkv, d);
+  if (rot < 0 || rot > d || (rot & 1)) MI_REFUSE("rope: rotary width %d must be even and <= head size %d", rot, d);
+  if (rot > 0 && (!pos || !inv_freq)) MI_REFUSE("rope: positions and frequencies are required");
+  if ((kcache == nullptr) != (vcache == nullptr)) MI_REFUSE("rope: key and value cache go together");
+  int work = (nq + nkv) * (rot / 2);
+  int threads = 64;
+  while (threads < 256 && threads < work) threads <<= 1;
+  if (dtype == MI_DTYPE_F32)
+    rope_write_kernel<float><<<M, threads, 0, stream>>>((float*)qkv, pos, inv_freq, slot, (float*)kcache,
+                                                        (float*)vcache, nq, nkv, d, rot);
+  else if (dtype == MI_DTYPE_BF16)
+    rope_write_kernel<bf16><<<M, threads, 0, stream>>>((bf16*)qkv, pos, inv_freq, slot, (bf16*)kcache,
+                                                       (bf16*)vcache, nq, nkv, d, rot);
+  else
+    MI_REFUSE("rope: unknown dtype %d", dtype);
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// SiLU-and-multiply: out[m, i] = silu(gu[m, i]) * gu[m, I + i], silu(g) = g / (1 + e^-g).
+// ---------------------------------------------------------------------------
+template <typename T, int VEC>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+  const int m = blockIdx.x;
+  const T* g = gu + (size_t)m * 2 * I;
+  const T* u = g + I;
+  T* o = out + (size_t)m * I;
+  const int i0 = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+  if (i0 >= I) return;
+  if (VEC == 4) {
+    Vec4<T> gv, uv, ov;
+    gv.load(g + i0);
+    uv.load(u + i0);
+    float gf[4], uf[4], of[4];
+    gv.get(gf);
+    uv.get(uf);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) of[j] = (gf[j] / (1.f + expf(-gf[j]))) * uf[j];
+    ov.set(of);
+    ov.store(o + i0);
+  } else {
+    const float gf = mi_to_float(g[i0]), uf = mi_to_float(u[i0]);
+    o[i0] = mi_from_float<T>((gf / (1.f + expf(-gf))) * uf);
+  }
+}
+
+extern "C" int mi_silu_mul(const void* gu, void* out, int M, int I, int dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (I <= 0) MI_REFUSE("silu_mul: bad width %d", I);
+  const size_t es = dtype == MI_DTYPE_F32 ? 4 : 2;
+  const bool vec = (I % 4 == 0) && ((I * es) % (es == 2 ? 8 : 16) == 0) && mi_aligned(gu, 16) && mi_aligned(out, 16);
+  const int threads = 256;
+  if (vec) {
+    dim3 grid(M, (I / 4 + threads - 1) / threads);
+    if (dtype == MI_DTYPE_F32) silu_mul_kernel<float, 4><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, I);
+    else if (dtype == MI_DTYPE_BF16) silu_mul_kernel<bf16, 4><<<grid, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I);
+    else MI_REFUSE("silu_mul: unknown dtype %d", dtype);
+  } else {
+    dim3 grid(M, (I + threads - 1) / threads);
+    if (dtype == MI_DTYPE_F32) silu_mul_kernel<float, 1><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, I);
+    else if (dtype == MI_DTYPE_BF16) silu_mul_kernel<bf16, 1><<<grid, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I);
+    else MI_REFUSE("silu_mul: unknown dtype %d", dtype);
+  }
+  MI_RETURN_LAUNCH_STATUS();
+}

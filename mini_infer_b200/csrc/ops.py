@@ -1,0 +1,382 @@
+"""Python faces of the CUDA kernels.
+
+Each function checks its tensors (device, dtype, layout), passes raw pointers and the
+current CUDA stream to an ``extern "C"`` entry point, and raises ``KernelError`` with the
+library's message if the arguments were refused or the launch failed.  There is no CPU
+path: a tensor that is not on a CUDA device is an error.
+
+``launch_count`` counts the kernels launched through this module (the bench reports it).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from . import build
+
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+launch_count = 0
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _cuda(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels run on CUDA tensors only (got a tensor on %s)" % t.device)
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {dtype}; kernels take float32 or bfloat16") from None
+
+
+def _finish(lib: ctypes.CDLL, rc: int, what: str) -> None:
+    global launch_count
+    if rc != 0:
+        msg = lib.mi_error_message().decode("utf-8", "replace")
+        raise KernelError(f"{what}: {msg or ('status %d' % rc)}")
+    launch_count += 1
+
+
+_configured: set[str] = set()
+
+
+def _lib(name: str) -> ctypes.CDLL:
+    lib = build.library(name)
+    if name not in _configured:
+        _SIGNATURES[name](lib)
+        _configured.add(name)
+    return lib
+
+
+def _sig_elementwise(lib: ctypes.CDLL) -> None:
+    lib.mi_embedding.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    lib.mi_add_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_int, c_int, c_float, c_int, c_int, c_void_p]
+    lib.mi_rope_write.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    lib.mi_silu_mul.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+
+
+def _sig_gemm_f32(lib: ctypes.CDLL) -> None:
+    lib.mi_gemm_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                c_int, c_void_p]
+
+
+def _sig_attention_generic(lib: ctypes.CDLL) -> None:
+    lib.mi_attention_generic.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+        c_float, c_int, c_int, c_void_p]
+    lib.mi_attention_generic_tile_tokens.restype = c_int
+
+
+def _sig_sampling(lib: ctypes.CDLL) -> None:
+    lib.mi_sample.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+
+
+_SIGNATURES = {
+    "elementwise": _sig_elementwise,
+    "gemm_f32": _sig_gemm_f32,
+    "attention_generic": _sig_attention_generic,
+    "sampling": _sig_sampling,
+}
+
+
+def register_signatures(name: str, fn) -> None:
+    _SIGNATURES[name] = fn
+
+
+# ---------------------------------------------------------------------------------------
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[t] = table[ids[t]]``; ``ids`` int32 ``[M]``, ``table`` ``[V, H]``."""
+    _cuda(table, ids, out)
+    if ids.dtype != torch.int32 or ids.dim() != 1 or not ids.is_contiguous():
+        raise KernelError("embedding: ids must be a contiguous int32 vector")
+    if table.dim() != 2 or not table.is_contiguous():
+        raise KernelError("embedding: table must be a contiguous [V, H] matrix")
+    V, H = table.shape
+    M = ids.shape[0]
+    if out is None:
+        out = torch.empty((M, H), dtype=table.dtype, device=table.device)
+    elif out.shape != (M, H) or out.dtype != table.dtype or not out.is_contiguous():
+        raise KernelError("embedding: bad output tensor")
+    lib = _lib("elementwise")
+    rc = lib.mi_embedding(_ptr(table), _ptr(ids), _ptr(out), M, H, V, _code(table.dtype), _stream())
+    _finish(lib, rc, "embedding")
+    return out
+
+
+def add_rmsnorm(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    eps: float,
+    *,
+    residual_in: torch.Tensor | None = None,
+    residual_out: torch.Tensor | None = None,
+    rows: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """RMS norm of ``x (+ residual_in)`` with fp32 statistics.
+
+    ``r = float(x[src]) + residual_in[src]`` (``src = rows[i]`` if ``rows`` is given, else
+    ``i``); ``residual_out[i] = r`` if given (fp32; may alias ``residual_in`` when no
+    ``rows``); returns ``weight * r * rsqrt(mean(r*r) + eps)`` in ``x``'s dtype.
+    """
+    _cuda(x, weight, residual_in, residual_out, rows, out)
+    if x.dim() != 2 or not x.is_contiguous():
+        raise KernelError("rmsnorm: x must be a contiguous [M, H] matrix")
+    H = x.shape[1]
+    M = x.shape[0] if rows is None else rows.shape[0]
+    if weight.shape != (H,) or not weight.is_contiguous():
+        raise KernelError(f"rmsnorm: weight must have shape ({H},)")
+    for name, r in (("residual_in", residual_in), ("residual_out", residual_out)):
+        if r is not None and (r.dtype != torch.float32 or r.dim() != 2 or r.shape[1] != H
+                              or not r.is_contiguous()):
+            raise KernelError(f"rmsnorm: {name} must be a contiguous fp32 [*, {H}] matrix")
+    if residual_in is not None and residual_in.shape[0] != x.shape[0]:
+        raise KernelError("rmsnorm: residual_in must have x's rows")
+    if residual_out is not None and residual_out.shape[0] != M:
+        raise KernelError("rmsnorm: residual_out must have one row per output row")
+    if rows is not None and (rows.dtype != torch.int32 or rows.dim() != 1 or not rows.is_contiguous()):
+        raise KernelError("rmsnorm: rows must be a contiguous int32 vector")
+    if out is None:
+        out = torch.empty((M, H), dtype=x.dtype, device=x.device)
+    elif out.shape != (M, H) or out.dtype != x.dtype or not out.is_contiguous():
+        raise KernelError("rmsnorm: bad output tensor")
+    lib = _lib("elementwise")
+    rc = lib.mi_add_rmsnorm(_ptr(x), _ptr(residual_in), _ptr(residual_out), _ptr(weight), _ptr(out),
+                            _ptr(rows), M, H, float(eps), _code(x.dtype), _code(weight.dtype), _stream())
+    _finish(lib, rc, "rmsnorm")
+    return out
+
+
+def rope_write(
+    qkv: torch.Tensor,
+    nq: int,
+    nkv: int,
+    head_dim: int,
+    *,
+    positions: torch.Tensor | None = None,
+    inv_freq: torch.Tensor | None = None,
+    rotary_dim: int = 0,
+    slots: torch.Tensor | None = None,
+    kcache: torch.Tensor | None = None,
+    vcache: torch.Tensor | None = None,
+) -> None:
+    """Rotate q and k inside ``qkv [M, (nq + 2 nkv) * d]`` (half layout, fp32 angles) and
+    store k and v at ``slots`` of ``kcache`` / ``vcache`` ``[n_slots, nkv, d]``."""
+    _cuda(qkv, positions, inv_freq, slots, kcache, vcache)
+    M = qkv.shape[0]
+    if qkv.dim() != 2 or qkv.shape[1] != (nq + 2 * nkv) * head_dim or not qkv.is_contiguous():
+        raise KernelError("rope: qkv must be contiguous [M, (nq + 2 nkv) * d]")
+    if rotary_dim:
+        if positions is None or positions.dtype != torch.int32 or positions.shape != (M,):
+            raise KernelError("rope: positions must be int32 [M]")
+        if inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.shape != (rotary_dim // 2,):
+            raise KernelError("rope: inv_freq must be fp32 [rotary_dim / 2]")
+    if kcache is not None:
+        if slots is None or slots.dtype != torch.int32 or slots.shape != (M,):
+            raise KernelError("rope: slots must be int32 [M]")
+        for c in (kcache, vcache):
+            if (c is None or c.dtype != qkv.dtype or c.dim() != 3 or c.shape[1:] != (nkv, head_dim)
+                    or not c.is_contiguous()):
+                raise KernelError("rope: caches must be contiguous [slots, nkv, d] in qkv's dtype")
+    lib = _lib("elementwise")
+    rc = lib.mi_rope_write(_ptr(qkv), _ptr(positions), _ptr(inv_freq), _ptr(slots), _ptr(kcache),
+                           _ptr(vcache), M, nq, nkv, head_dim, rotary_dim, _code(qkv.dtype), _stream())
+    _finish(lib, rc, "rope")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``silu(gate_up[:, :I]) * gate_up[:, I:]`` with fp32 arithmetic."""
+    _cuda(gate_up, out)
+    if gate_up.dim() != 2 or gate_up.shape[1] % 2 or not gate_up.is_contiguous():
+        raise KernelError("silu_mul: input must be contiguous [M, 2 I]")
+    M, I2 = gate_up.shape
+    I = I2 // 2
+    if out is None:
+        out = torch.empty((M, I), dtype=gate_up.dtype, device=gate_up.device)
+    elif out.shape != (M, I) or out.dtype != gate_up.dtype or not out.is_contiguous():
+        raise KernelError("silu_mul: bad output tensor")
+    lib = _lib("elementwise")
+    rc = lib.mi_silu_mul(_ptr(gate_up), _ptr(out), M, I, _code(gate_up.dtype), _stream())
+    _finish(lib, rc, "silu_mul")
+    return out
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``a [M, K] @ w [N, K]^T`` in true fp32 (CUDA cores, fixed summation order)."""
+    _cuda(a, w, out)
+    if a.dtype != torch.float32 or w.dtype != torch.float32:
+        raise KernelError("gemm_f32: operands must be float32")
+    if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1]:
+        raise KernelError(f"gemm_f32: shapes {tuple(a.shape)} x {tuple(w.shape)}^T do not match")
+    if a.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError("gemm_f32: operands must be K-contiguous")
+    M, K = a.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    elif out.shape != (M, N) or out.dtype != torch.float32 or out.stride(1) != 1:
+        raise KernelError("gemm_f32: bad output tensor")
+    lib = _lib("gemm_f32")
+    rc = lib.mi_gemm_f32(_ptr(a), _ptr(w), _ptr(out), M, N, K, a.stride(0) if M > 1 else K,
+                         w.stride(0) if N > 1 else K, out.stride(0) if M > 1 else N, _stream())
+    _finish(lib, rc, "gemm_f32")
+    return out
+
+
+# Query tokens per tile of the CUDA-core attention kernel (BQ in attention_generic.cu).
+ATTENTION_TILE_TOKENS = 16
+
+
+def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq: int, nkv: int,
+              head_dim: int, scale: float, window: int = 0) -> None:
+    """Attention of this step's queries over one cache layer.
+
+    ``cache`` is a ``LayerCache`` (its ``k``/``v`` pages and group index), ``ctx`` the
+    ``StepContext`` (block tables, lengths, query tiles).
+    """
+    group = ctx.groups[cache.group]
+    tile_req, tile_tok0, n_tiles = ctx.q_tiles(ATTENTION_TILE_TOKENS)
+    attention_generic(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
+                      ctx.q_start, ctx.q_len, ctx.kv_len, tile_req, tile_tok0, n_tiles,
+                      nq, nkv, head_dim, scale, window)
+
+
+def attention_generic(
+    q: torch.Tensor,
+    q_stride: int,
+    out: torch.Tensor,
+    kcache: torch.Tensor,
+    vcache: torch.Tensor,
+    block_table: torch.Tensor,
+    page_size: int,
+    q_start: torch.Tensor,
+    q_len: torch.Tensor,
+    kv_len: torch.Tensor,
+    tile_req: torch.Tensor,
+    tile_tok0: torch.Tensor,
+    n_tiles: int,
+    nq: int,
+    nkv: int,
+    head_dim: int,
+    scale: float,
+    window: int = 0,
+) -> None:
+    """Causal attention of query portions over the paged cache (see attention_generic.cu).
+
+    ``q`` is any tensor whose element ``(token t, head h, k)`` lies at
+    ``t * q_stride + h * head_dim + k`` from its first element.
+    """
+    _cuda(q, out, kcache, vcache, block_table, q_start, q_len, kv_len, tile_req, tile_tok0)
+    for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len),
+                    ("kv_len", kv_len), ("tile_req", tile_req), ("tile_tok0", tile_tok0)):
+        if t.dtype != torch.int32:
+            raise KernelError(f"attention: {name} must be int32")
+    if kcache.dtype != q.dtype or vcache.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: q, out and caches must share a dtype")
+    if kcache.dim() != 3 or kcache.shape[1:] != (nkv, head_dim) or not kcache.is_contiguous() \
+            or vcache.shape != kcache.shape or not vcache.is_contiguous():
+        raise KernelError("attention: caches must be contiguous [slots, nkv, d]")
+    if out.dim() != 2 or out.shape[1] != nq * head_dim or not out.is_contiguous():
+        raise KernelError("attention: out must be contiguous [tokens, nq * d]")
+    if block_table.dim() != 2 or block_table.stride(1) != 1:
+        raise KernelError("attention: block_table must be [requests, pages] with unit inner stride")
+    lib = _lib("attention_generic")
+    if lib.mi_attention_generic_tile_tokens() != ATTENTION_TILE_TOKENS:
+        raise KernelError("attention: the kernel's tile size differs from ATTENTION_TILE_TOKENS")
+    rc = lib.mi_attention_generic(
+        _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
+        _ptr(block_table), block_table.stride(0), int(page_size), _ptr(q_start), _ptr(q_len),
+        _ptr(kv_len), _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), nq, nkv, head_dim,
+        float(scale), int(window), _code(q.dtype), _stream())
+    _finish(lib, rc, "attention")
+
+
+def sample(
+    logits: torch.Tensor,
+    out: torch.Tensor,
+    *,
+    temperature: torch.Tensor | None = None,
+    top_k: torch.Tensor | None = None,
+    top_p: torch.Tensor | None = None,
+    seed_lo: torch.Tensor | None = None,
+    seed_hi: torch.Tensor | None = None,
+    draw_index: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """One token id per row of fp32 ``logits [B, V]`` into int32 ``out [B]`` (see sampling.cu)."""
+    _cuda(logits, out, temperature, top_k, top_p, seed_lo, seed_hi, draw_index)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be fp32 [B, V] with unit inner stride")
+    B, V = logits.shape
+    if out.dtype != torch.int32 or out.shape != (B,) or not out.is_contiguous():
+        raise KernelError("sample: out must be int32 [B]")
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                        ("top_p", top_p, torch.float32), ("seed_lo", seed_lo, torch.int32),
+                        ("seed_hi", seed_hi, torch.int32), ("draw_index", draw_index, torch.int32)):
+        if t is not None and (t.dtype != dt or t.shape != (B,) or not t.is_contiguous()):
+            raise KernelError(f"sample: {name} must be {dt} [B]")
+    lib = _lib("sampling")
+    rc = lib.mi_sample(_ptr(logits), logits.stride(0) if B > 1 else V, B, V, _ptr(temperature),
+                       _ptr(top_k), _ptr(top_p), _ptr(seed_lo), _ptr(seed_hi), _ptr(draw_index),
+                       _ptr(out), _stream())
+    _finish(lib, rc, "sample")
+    return out
+
+
+_MM_OUT_DTYPE: bool | None = None
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x [M, K] @ w [N, K]^T``.
+
+    float32 operands run the true-fp32 CUDA-core kernel (never a library product, which
+    could pick a reduced-precision mode).  bfloat16 operands use the library product with
+    fp32 accumulation, as the reference does for every linear layer
+    (``distributed/linear.py:167``); ``out_dtype=float32`` keeps the accumulator's
+    precision in the result (used for logits).
+    """
+    global _MM_OUT_DTYPE, launch_count
+    if x.dtype == torch.float32:
+        if w.dtype != torch.float32:
+            raise KernelError("linear: fp32 activations need fp32 weights")
+        return gemm_f32(x, w)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
+    _cuda(x, w)
+    launch_count += 1
+    if out_dtype in (None, torch.bfloat16):
+        return torch.mm(x, w.t())
+    if out_dtype != torch.float32:
+        raise KernelError(f"linear: unsupported output dtype {out_dtype}")
+    if _MM_OUT_DTYPE is None:
+        try:
+            torch.mm(x[:1], w[:1].t(), out_dtype=torch.float32)
+            _MM_OUT_DTYPE = True
+        except (TypeError, RuntimeError):
+            _MM_OUT_DTYPE = False
+    if _MM_OUT_DTYPE:
+        return torch.mm(x, w.t(), out_dtype=torch.float32)
+    return torch.mm(x, w.t()).float()

@@ -1,0 +1,243 @@
+// Next-token choice on the device, one block per logits row.
+//
+//   temperature == 0            greedy: the lowest index among the largest logits
+//   temperature  > 0            s_i = logit_i / temperature, optionally filtered by
+//       top_k  (0 = off): keep s_i >= the k-th largest s (ties kept)
+//       top_p  (1 = off): among those, keep token i while the probability mass of the
+//                         strictly larger tokens is <= top_p (the boundary token is kept)
+//     then draw from softmax over the kept set as argmax(s_i + g_i), g_i Gumbel noise.
+//
+// The noise is counter-based: g_i = -log(-log(u_i)), u_i from Philox4x32-10 with the
+// row's 64-bit seed as key and (i, draw index, 0, 0) as counter, so a request's draws do
+// not depend on which other rows share the batch or on the order of execution.  Filters
+// are found by radix selection over order-preserving 32-bit keys; probability masses are
+// accumulated in 64-bit fixed point (2^-40 of the largest probability), which makes the
+// selection independent of the order of atomic additions.
+#include "common.cuh"
+
+MI_DEFINE_ERROR_API()
+
+#define SAMPLE_THREADS 512
+
+__device__ __forceinline__ uint32_t order_key(float f) {
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ uint32_t philox_first_word(uint32_t c0, uint32_t c1, uint32_t k0, uint32_t k1) {
+  uint32_t c2 = 0u, c3 = 0u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return c0;
+}
+
+__device__ __forceinline__ float gumbel_noise(uint32_t i, uint32_t draw, uint32_t k0, uint32_t k1) {
+  const uint32_t x = philox_first_word(i, draw, k0, k1);
+  const float u = ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f);  // (0, 1), 24 bits
+  return -logf(-logf(u));
+}
+
+struct ArgBest {
+  float v;
+  int i;
+};
+__device__ __forceinline__ ArgBest better(ArgBest a, ArgBest b) {
+  if (b.i >= 0 && (a.i < 0 || b.v > a.v || (b.v == a.v && b.i < a.i))) return b;
+  return a;
+}
+__device__ __forceinline__ ArgBest block_best(ArgBest x, ArgBest* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgBest y;
+    y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+    y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+    x = better(x, y);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = x;
+  __syncthreads();
+  ArgBest r;
+  r.v = 0.f;
+  r.i = -1;
+  if (lane < (blockDim.x >> 5)) r = scratch[lane];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgBest y;
+    y.v = __shfl_xor_sync(0xffffffffu, r.v, o);
+    y.i = __shfl_xor_sync(0xffffffffu, r.i, o);
+    r = better(r, y);
+  }
+  return r;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const uint32_t* __restrict__ seed_lo, const uint32_t* __restrict__ seed_hi,
+              const uint32_t* __restrict__ draw_index, int* __restrict__ out) {
+  __shared__ ArgBest best_scratch[32];
+  __shared__ unsigned int hist_cnt[256];
+  __shared__ unsigned long long hist_mass[256];
+  __shared__ uint32_t sh_prefix;
+  __shared__ unsigned int sh_krem;
+  __shared__ unsigned long long sh_above, sh_total;
+  __shared__ int sh_flag;
+
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const float* lg = logits + (size_t)row * ld;
+  const float T = temperature ? temperature[row] : 0.f;
+
+  if (!(T > 0.f)) {
+    ArgBest b;
+    b.v = 0.f;
+    b.i = -1;
+    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+      ArgBest c;
+      c.v = lg[i];
+      c.i = i;
+      if (c.v == c.v) b = better(b, c);  // NaN never wins
+    }
+    b = block_best(b, best_scratch);
+    if (tid == 0) out[row] = b.i;
+    return;
+  }
+
+  const int k = top_k ? top_k[row] : 0;
+  const float p = top_p ? top_p[row] : 1.f;
+  uint32_t kmin = 0u;
+
+  if (k > 0 && k < V) {
+    uint32_t prefix = 0u, mask = 0u;
+    if (tid == 0) sh_krem = (unsigned int)k;
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      for (int b = tid; b < 256; b += SAMPLE_THREADS) hist_cnt[b] = 0u;
+      __syncthreads();
+      for (int i = tid; i < V; i += SAMPLE_THREADS) {
+        const uint32_t key = order_key(lg[i] / T);
+        if ((key & mask) == prefix) atomicAdd(&hist_cnt[(key >> shift) & 255u], 1u);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        unsigned int rem = sh_krem, cum = 0u;
+        int sel = 0;
+        for (int b = 255; b >= 0; --b) {
+          if (cum + hist_cnt[b] >= rem) {
+            sel = b;
+            break;
+          }
+          cum += hist_cnt[b];
+        }
+        sh_krem = rem - cum;
+        sh_prefix = prefix | ((uint32_t)sel << shift);
+      }
+      __syncthreads();
+      prefix = sh_prefix;
+      mask |= 255u << shift;
+    }
+    kmin = prefix;
+  }
+
+  if (p < 1.f) {
+    // largest s for a stable exponent
+    float mx = -INFINITY;
+    for (int i = tid; i < V; i += SAMPLE_THREADS) mx = fmaxf(mx, lg[i] / T);
+    mx = mi_warp_max(mx);
+    __shared__ float sh_max[32];
+    __syncthreads();
+    if ((tid & 31) == 0) sh_max[tid >> 5] = mx;
+    __syncthreads();
+    mx = sh_max[0];
+    for (int w = 1; w < SAMPLE_THREADS / 32; ++w) mx = fmaxf(mx, sh_max[w]);
+
+    uint32_t prefix = 0u, mask = 0u;
+    if (tid == 0) {
+      sh_above = 0ull;
+      sh_total = 0ull;
+      sh_flag = 0;
+    }
+    __syncthreads();
+    // total mass of the kept set
+    unsigned long long part = 0ull;
+    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+      const float s = lg[i] / T;
+      if (order_key(s) >= kmin) part += __float2ull_rd(expf(s - mx) * 1099511627776.f);
+    }
+    atomicAdd(&sh_total, part);
+    __syncthreads();
+    const unsigned long long target = (unsigned long long)((double)p * (double)sh_total);
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      for (int b = tid; b < 256; b += SAMPLE_THREADS) hist_mass[b] = 0ull;
+      __syncthreads();
+      for (int i = tid; i < V; i += SAMPLE_THREADS) {
+        const float s = lg[i] / T;
+        const uint32_t key = order_key(s);
+        if (key >= kmin && (key & mask) == prefix)
+          atomicAdd(&hist_mass[(key >> shift) & 255u], __float2ull_rd(expf(s - mx) * 1099511627776.f));
+      }
+      __syncthreads();
+      if (tid == 0) {
+        unsigned long long above = sh_above;
+        int sel = -1;
+        for (int b = 255; b >= 0; --b) {
+          if (above + hist_mass[b] > target) {
+            sel = b;
+            break;
+          }
+          above += hist_mass[b];
+        }
+        if (sel < 0) {
+          sh_flag = 1;  // the whole set stays
+          sel = 0;
+        }
+        sh_above = above;
+        sh_prefix = prefix | ((uint32_t)sel << shift);
+      }
+      __syncthreads();
+      prefix = sh_prefix;
+      mask |= 255u << shift;
+      if (sh_flag) break;
+    }
+    if (!sh_flag && prefix > kmin) kmin = prefix;
+  }
+
+  const uint32_t k0 = seed_lo[row], k1 = seed_hi[row], draw = draw_index[row];
+  ArgBest b;
+  b.v = 0.f;
+  b.i = -1;
+  for (int i = tid; i < V; i += SAMPLE_THREADS) {
+    const float s = lg[i] / T;
+    if (s == s && order_key(s) >= kmin) {
+      ArgBest c;
+      c.v = s + gumbel_noise((uint32_t)i, draw, k0, k1);
+      c.i = i;
+      b = better(b, c);
+    }
+  }
+  b = block_best(b, best_scratch);
+  if (tid == 0) out[row] = b.i;
+}
+
+// Any of temperature / top_k / top_p may be null (greedy / off / off).  seed_* and
+// draw_index are required when any temperature may be positive.
+extern "C" int mi_sample(const float* logits, int ld, int B, int V, const float* temperature,
+                         const int* top_k, const float* top_p, const uint32_t* seed_lo,
+                         const uint32_t* seed_hi, const uint32_t* draw_index, int* out,
+                         cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (V <= 0 || ld < V) MI_REFUSE("sample: bad vocabulary %d (row stride %d)", V, ld);
+  if (temperature && (!seed_lo || !seed_hi || !draw_index))
+    MI_REFUSE("sample: seeds and draw indices are required with a temperature");
+  sample_kernel<<<B, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, seed_lo,
+                                                  seed_hi, draw_index, out);
+  MI_RETURN_LAUNCH_STATUS();
+}

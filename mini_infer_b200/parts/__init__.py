@@ -1,0 +1,28 @@
+"""Parts a decoder is put together from (see ``base`` for the interfaces)."""
+
+from .base import (  # noqa: F401
+    Arrangement,
+    FeedForward,
+    GroupView,
+    KVNeed,
+    LayerCache,
+    Mixer,
+    Norm,
+    ParamDecl,
+    Part,
+    PlanNeeds,
+    Position,
+    StateNeed,
+    StepContext,
+    build_part,
+    lookup,
+    register_arrangement,
+    register_embedding,
+    register_feed_forward,
+    register_head,
+    register_mixer,
+    register_norm,
+    register_position,
+)
+from .model import DecoderModel  # noqa: F401
+from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry  # noqa: F401

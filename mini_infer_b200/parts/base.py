@@ -1,0 +1,305 @@
+"""Interfaces of the parts a decoder is put together from, and their registries.
+
+A *part* is built from a :class:`~.spec.PartSpec` alone (its sizes and constants); it
+declares the tensors it needs under local names, receives them in ``bind`` and does its
+work in ``forward``.  Four families exist, each with a registry keyed by ``kind``:
+
+``Mixer``         mixes information across the tokens of a request (attention here).
+                  Declares what it keeps between steps: per-token keys/values in pages
+                  (``cache_need``) and/or a fixed-size per-request state (``state_need``).
+``FeedForward``   per-token transformation (dense SwiGLU here; routed experts fit the
+                  same interface).
+``Norm``          ``forward(x, residual) -> (normed, new_residual)``; the residual stream
+                  is fp32.
+``Position``      how positions enter a mixer's queries and keys.
+
+An *arrangement* says where the norms and the residual additions of a layer stand.
+
+No part knows which model it is in: everything it needs is in its spec, in the tensors it
+is bound to, and in the :class:`StepContext` of the step.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, ClassVar
+
+import torch
+
+from .spec import PartSpec
+
+
+# ----------------------------------------------------------------------------- declarations
+
+
+@dataclass(frozen=True)
+class ParamDecl:
+    """A tensor a part needs.  ``role`` guides random initialisation and dtype policy:
+
+    ``matrix``  operand of a matrix product; converted to the compute dtype when bound
+    ``gain``    multiplicative vector of a norm; a 32-bit stored gain stays 32-bit
+    ``table``   anything else (kept as loaded)
+    """
+
+    shape: tuple[int, ...]
+    role: str = "matrix"
+
+
+@dataclass(frozen=True)
+class KVNeed:
+    """Per-token keys and values kept in pages: ``kv_heads * head_dim`` numbers each per
+    token.  ``window``: only the last ``window`` positions are ever read (None: all)."""
+
+    kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A per-request state of fixed size (zeroed when a request is admitted)."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class PlanNeeds:
+    """What a mixer wants the step planner to prepare each step.
+
+    ``q_tile_tokens``: for each value n, a list of tiles of at most n consecutive query
+    tokens of one request (``StepContext.q_tiles(n)``).
+    """
+
+    q_tile_tokens: frozenset[int] = frozenset()
+
+
+# ----------------------------------------------------------------------------- step context
+
+
+@dataclass
+class GroupView:
+    """One cache group as a step sees it (device tensors are int32)."""
+
+    page_size: int
+    window: int | None
+    block_table: torch.Tensor          # [requests, max_pages] page ids of this group
+    slots: torch.Tensor                # [tokens] flat slot (page * page_size + offset) per new token
+
+
+@dataclass
+class LayerCache:
+    """What one schedule entry's mixer gets from the cache manager."""
+
+    group: int | None = None           # index into StepContext.groups
+    k: torch.Tensor | None = None      # [slots, kv_heads, head_dim]
+    v: torch.Tensor | None = None
+    state: torch.Tensor | None = None  # [request slots, *StateNeed.shape]
+    writes: bool = True
+
+
+@dataclass
+class StepContext:
+    """Everything a part may know about the batch of one step.
+
+    Host lists and their device copies describe the same thing; kernels read the device
+    tensors, Python code that must loop over requests (a toy mixer) reads the lists.
+    """
+
+    dtype: torch.dtype
+    device: torch.device
+    n_tokens: int
+    n_requests: int
+    token_ids: torch.Tensor            # [tokens] int32
+    positions: torch.Tensor            # [tokens] int32 absolute position of each token
+    q_start: torch.Tensor              # [requests] int32 first row of each request's portion
+    q_len: torch.Tensor                # [requests] int32
+    kv_len: torch.Tensor               # [requests] int32 tokens held after this step
+    state_slot: torch.Tensor           # [requests] int32 row of each request in state arenas
+    host_q_start: list[int] = field(default_factory=list)
+    host_q_len: list[int] = field(default_factory=list)
+    host_kv_len: list[int] = field(default_factory=list)
+    host_state_slot: list[int] = field(default_factory=list)
+    groups: list[GroupView] = field(default_factory=list)
+    tiles: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = field(default_factory=dict)
+    decode_only: bool = False          # every request brings exactly one token
+    max_kv_len: int = 0
+
+    def q_tiles(self, tokens: int) -> tuple[torch.Tensor, torch.Tensor, int]:
+        """``(tile_request, tile_first_token, n_tiles)`` for tiles of ``tokens`` tokens."""
+        try:
+            return self.tiles[tokens]
+        except KeyError:
+            raise KeyError(
+                f"no query tiles of {tokens} tokens were planned; a mixer must announce "
+                "the tile sizes it uses in plan_needs()"
+            ) from None
+
+
+# ----------------------------------------------------------------------------- part families
+
+
+class Part:
+    kind: ClassVar[str] = ""
+
+    def __init__(self, spec: PartSpec) -> None:
+        self.spec = spec
+
+    def param_decls(self) -> dict[str, ParamDecl]:
+        return {}
+
+    def bind(self, tensors: dict[str, torch.Tensor], dtype: torch.dtype,
+             device: torch.device) -> None:
+        """Receive the declared tensors (already on ``device``); ``dtype`` is the compute
+        dtype of activations (float32 or bfloat16)."""
+
+    def param(self, name: str, default: Any = None) -> Any:
+        if name in self.spec.params:
+            return self.spec.params[name]
+        if default is not None:
+            return default
+        raise KeyError(f"part {self.spec.kind!r} needs parameter {name!r}")
+
+
+class Position(Part):
+    """Position encoding applied to the queries and keys of a mixer.
+
+    ``rotate_and_store`` receives the packed projection ``qkv [tokens, (nq + 2 nkv) * d]``
+    and must leave encoded queries and keys in it and, when ``cache.writes``, store the
+    encoded keys and the values at ``ctx.groups[cache.group].slots``.  The default does
+    the two halves separately through ``encode`` and the store kernel; a part with a
+    fused kernel overrides ``rotate_and_store``.
+    """
+
+    def encode(self, qkv: torch.Tensor, nq: int, nkv: int, head_dim: int, ctx: StepContext) -> None:
+        raise NotImplementedError
+
+    def rotate_and_store(self, qkv: torch.Tensor, nq: int, nkv: int, head_dim: int,
+                         ctx: StepContext, cache: LayerCache) -> None:
+        from ..csrc import ops
+
+        self.encode(qkv, nq, nkv, head_dim, ctx)
+        if cache.writes and cache.k is not None:
+            ops.rope_write(qkv, nq, nkv, head_dim, slots=ctx.groups[cache.group].slots,
+                           kcache=cache.k, vcache=cache.v)
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None,
+                rows: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
+        """``(normed, new_residual)``; ``residual`` is the fp32 stream or None (first norm).
+
+        With ``rows`` (int32 indices) only those rows are normalised and no residual is
+        returned."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_need(self) -> KVNeed | None:
+        return None
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def plan_needs(self) -> PlanNeeds:
+        return PlanNeeds()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache,
+                position: Position | None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Arrangement:
+    """A layer: a mixer and a feed-forward behind their norms.
+
+    ``forward(x, residual, ctx, cache) -> (x, residual)`` where ``x`` is the last branch
+    output not yet added to the fp32 ``residual`` stream (``residual`` is None before the
+    first layer, when ``x`` is the embedding).
+    """
+
+    kind: ClassVar[str] = ""
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
+                 feed_forward_norm: Norm, position: Position | None) -> None:
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = mixer_norm
+        self.feed_forward_norm = feed_forward_norm
+        self.position = position
+
+    def parts(self) -> list[Part]:
+        ps: list[Part] = [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        if self.position is not None:
+            ps.append(self.position)
+        return ps
+
+    def forward(self, x, residual, ctx: StepContext, cache: LayerCache):
+        raise NotImplementedError
+
+
+# ----------------------------------------------------------------------------- registries
+
+_REGISTRIES: dict[str, dict[str, Callable[..., Any]]] = {
+    "mixer": {},
+    "feed_forward": {},
+    "norm": {},
+    "position": {},
+    "arrangement": {},
+    "embedding": {},
+    "head": {},
+}
+
+
+def _register(family: str, kind: str, cls, replace: bool) -> None:
+    reg = _REGISTRIES[family]
+    if kind in reg and not replace:
+        raise ValueError(f"{family} kind {kind!r} is already registered")
+    reg[kind] = cls
+
+
+def register_mixer(kind: str, cls, *, replace: bool = False) -> None:
+    _register("mixer", kind, cls, replace)
+
+
+def register_feed_forward(kind: str, cls, *, replace: bool = False) -> None:
+    _register("feed_forward", kind, cls, replace)
+
+
+def register_norm(kind: str, cls, *, replace: bool = False) -> None:
+    _register("norm", kind, cls, replace)
+
+
+def register_position(kind: str, cls, *, replace: bool = False) -> None:
+    _register("position", kind, cls, replace)
+
+
+def register_arrangement(kind: str, cls, *, replace: bool = False) -> None:
+    _register("arrangement", kind, cls, replace)
+
+
+def register_embedding(kind: str, cls, *, replace: bool = False) -> None:
+    _register("embedding", kind, cls, replace)
+
+
+def register_head(kind: str, cls, *, replace: bool = False) -> None:
+    _register("head", kind, cls, replace)
+
+
+def lookup(family: str, kind: str):
+    from . import builtin  # noqa: F401  (registers the parts that ship with the package)
+
+    try:
+        return _REGISTRIES[family][kind]
+    except KeyError:
+        raise ValueError(
+            f"unknown {family} kind {kind!r}; registered: {sorted(_REGISTRIES[family])}"
+        ) from None
+
+
+def build_part(family: str, spec: PartSpec):
+    return lookup(family, spec.kind)(spec)

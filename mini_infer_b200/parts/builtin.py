@@ -1,0 +1,311 @@
+"""The parts that ship with the package: RMS norm, rotary position encoding, grouped-query
+attention, SwiGLU feed-forward, token embedding, output head, the pre-norm arrangement.
+
+Each class takes its sizes and constants from its ``PartSpec.params`` and its tensors from
+``bind``.  The formulas follow the reference's blocks, cited per class.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..csrc import ops
+from .base import (
+    Arrangement,
+    FeedForward,
+    KVNeed,
+    LayerCache,
+    Mixer,
+    Norm,
+    ParamDecl,
+    Part,
+    PlanNeeds,
+    Position,
+    StepContext,
+    register_arrangement,
+    register_embedding,
+    register_feed_forward,
+    register_head,
+    register_mixer,
+    register_norm,
+    register_position,
+)
+
+
+def _as_compute(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """A matrix operand in the compute dtype (a no-op when it is stored that way)."""
+    return t if t.dtype == dtype else t.to(dtype)
+
+
+class Linear:
+    """``y = x W^T`` with ``W [out, in]`` kept in the compute dtype."""
+
+    def __init__(self, weight: torch.Tensor) -> None:
+        if weight.dim() != 2 or not weight.is_contiguous():
+            raise ValueError("Linear needs a contiguous [out, in] matrix")
+        self.weight = weight
+
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        return ops.linear(x, self.weight, out_dtype)
+
+
+# ----------------------------------------------------------------------------- norm
+
+
+class RMSNorm(Norm):
+    """``w * r * rsqrt(mean(r^2) + eps)`` with ``r = x + residual`` in fp32
+    (reference ``models/blocks/rmsnorm.py:63-93``; the residual sum is kept in fp32 here
+    instead of being rounded to the model dtype).
+
+    params: ``hidden_size``, ``eps``.  tensors: ``weight [hidden_size]``.
+    """
+
+    def param_decls(self):
+        return {"weight": ParamDecl((int(self.param("hidden_size")),), "gain")}
+
+    def bind(self, tensors, dtype, device):
+        w = tensors["weight"]
+        # a gain stored in 32-bit stays 32-bit; anything else follows the compute dtype
+        self.weight = w if w.dtype == torch.float32 else w.to(dtype)
+        self.eps = float(self.param("eps"))
+
+    def forward(self, x, residual, rows=None):
+        if rows is not None:
+            return ops.add_rmsnorm(x, self.weight, self.eps, residual_in=residual, rows=rows), None
+        new_residual = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        out = ops.add_rmsnorm(x, self.weight, self.eps, residual_in=residual,
+                              residual_out=new_residual)
+        return out, new_residual
+
+
+# ----------------------------------------------------------------------------- position
+
+
+def rotary_inv_freq(head_dim: int, theta: float, rotary_dim: int | None = None,
+                    scaling: dict | None = None) -> torch.Tensor:
+    """fp32 inverse frequencies ``theta^(-2i/d)``, optionally with the llama3 rescale.
+
+    The rescale keeps short wavelengths, divides long ones by ``factor`` and blends in
+    between (reference ``models/blocks/rope.py:200-225``); operations are applied in that
+    file's order so the fp32 table comes out bit-equal.
+    """
+    rot = head_dim if rotary_dim is None else rotary_dim
+    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / head_dim))
+    if scaling is None:
+        return inv
+    factor = float(scaling["factor"])
+    low = float(scaling["low_freq_factor"])
+    high = float(scaling["high_freq_factor"])
+    old_len = int(scaling["original_max_position_embeddings"])
+    low_wavelen = old_len / low
+    high_wavelen = old_len / high
+    wavelen = 2 * math.pi / inv
+    scaled = torch.where(wavelen > low_wavelen, inv / factor, inv)
+    smooth = (old_len / wavelen - low) / (high - low)
+    smoothed = (1 - smooth) * scaled / factor + smooth * scaled
+    medium = ~(wavelen < high_wavelen) * ~(wavelen > low_wavelen)
+    return torch.where(medium, smoothed, scaled)
+
+
+class RotaryPosition(Position):
+    """Rotary encoding, half layout: dim ``j`` pairs with ``j + rotary_dim/2``
+    (reference ``models/blocks/rope.py:392-431``).  Angles ``p * inv_freq`` and their sine
+    and cosine are fp32 and computed in the kernel; each rotated value is rounded once.
+
+    params: ``head_dim``, ``theta``, optional ``rotary_dim`` (default ``head_dim``),
+    optional ``scaling`` (the llama3 mapping).
+    """
+
+    def bind(self, tensors, dtype, device):
+        d = int(self.param("head_dim"))
+        self.rotary_dim = int(self.spec.params.get("rotary_dim") or d)
+        self.inv_freq = rotary_inv_freq(
+            d, float(self.param("theta")), self.rotary_dim, self.spec.params.get("scaling")
+        ).to(device)
+
+    def encode(self, qkv, nq, nkv, head_dim, ctx):
+        ops.rope_write(qkv, nq, nkv, head_dim, positions=ctx.positions, inv_freq=self.inv_freq,
+                       rotary_dim=self.rotary_dim)
+
+    def rotate_and_store(self, qkv, nq, nkv, head_dim, ctx, cache):
+        if cache.writes and cache.k is not None:
+            ops.rope_write(qkv, nq, nkv, head_dim, positions=ctx.positions,
+                           inv_freq=self.inv_freq, rotary_dim=self.rotary_dim,
+                           slots=ctx.groups[cache.group].slots, kcache=cache.k, vcache=cache.v)
+        else:
+            self.encode(qkv, nq, nkv, head_dim, ctx)
+
+
+# ----------------------------------------------------------------------------- mixer
+
+
+class GroupedQueryAttention(Mixer):
+    """Causal attention with ``num_heads`` query heads sharing ``num_kv_heads`` key/value
+    heads over the paged cache (reference ``models/blocks/gqa.py:111-155`` and
+    ``cache/packed_attention.py:242-340``): one merged q/k/v projection, position encoding
+    of q and k, k/v written to pages, softmax(q k^T * scale + causal [+ window]) v in fp32,
+    output projection.
+
+    params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``; optional
+    ``window`` (keys older than ``window - 1`` positions are not seen), ``scale``
+    (default ``head_dim ** -0.5``).
+    tensors: ``q_proj.weight``, ``k_proj.weight``, ``v_proj.weight``, ``o_proj.weight``.
+    """
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.param("hidden_size"))
+        self.nq = int(self.param("num_heads"))
+        self.nkv = int(self.param("num_kv_heads"))
+        self.d = int(self.param("head_dim"))
+        w = self.spec.params.get("window")
+        self.window = int(w) if w else None
+        s = self.spec.params.get("scale")
+        self.scale = float(s) if s else self.d ** -0.5
+        if self.nq % self.nkv:
+            raise ValueError(f"{self.nq} query heads cannot share {self.nkv} key/value heads")
+        if self.d % 16 or not 16 <= self.d <= 256:
+            raise ValueError(f"head_dim {self.d} is not a multiple of 16 in [16, 256]")
+
+    def param_decls(self):
+        H, nq, nkv, d = self.hidden, self.nq, self.nkv, self.d
+        return {
+            "q_proj.weight": ParamDecl((nq * d, H)),
+            "k_proj.weight": ParamDecl((nkv * d, H)),
+            "v_proj.weight": ParamDecl((nkv * d, H)),
+            "o_proj.weight": ParamDecl((H, nq * d)),
+        }
+
+    def cache_need(self):
+        return KVNeed(self.nkv, self.d, self.window)
+
+    def plan_needs(self):
+        return PlanNeeds(frozenset({ops.ATTENTION_TILE_TOKENS}))
+
+    def bind(self, tensors, dtype, device):
+        qkv = torch.cat(
+            [_as_compute(tensors[n], dtype) for n in ("q_proj.weight", "k_proj.weight", "v_proj.weight")],
+            dim=0,
+        ).contiguous()
+        self.qkv_proj = Linear(qkv)
+        self.o_proj = Linear(_as_compute(tensors["o_proj.weight"], dtype).contiguous())
+
+    def forward(self, x, ctx: StepContext, cache: LayerCache, position):
+        nq, nkv, d = self.nq, self.nkv, self.d
+        qkv = self.qkv_proj(x)
+        if position is not None:
+            position.rotate_and_store(qkv, nq, nkv, d, ctx, cache)
+        elif cache.writes:
+            ops.rope_write(qkv, nq, nkv, d, slots=ctx.groups[cache.group].slots,
+                           kcache=cache.k, vcache=cache.v)
+        out = torch.empty((ctx.n_tokens, nq * d), dtype=x.dtype, device=x.device)
+        ops.attention(qkv, qkv.stride(0), out, cache, ctx, nq, nkv, d, self.scale, self.window or 0)
+        return self.o_proj(out)
+
+
+# ----------------------------------------------------------------------------- feed-forward
+
+
+class SwiGLU(FeedForward):
+    """``down(silu(gate(x)) * up(x))``, no biases (reference ``models/blocks/swiglu.py:35-46``,
+    ``models/blocks/activations.py:36-45``).  gate and up are one merged product; SiLU and
+    the product are fp32 per element.
+
+    params: ``hidden_size``, ``intermediate_size``.
+    tensors: ``gate_proj.weight``, ``up_proj.weight``, ``down_proj.weight``.
+    """
+
+    def param_decls(self):
+        H, I = int(self.param("hidden_size")), int(self.param("intermediate_size"))
+        return {
+            "gate_proj.weight": ParamDecl((I, H)),
+            "up_proj.weight": ParamDecl((I, H)),
+            "down_proj.weight": ParamDecl((H, I)),
+        }
+
+    def bind(self, tensors, dtype, device):
+        gate_up = torch.cat(
+            [_as_compute(tensors["gate_proj.weight"], dtype), _as_compute(tensors["up_proj.weight"], dtype)],
+            dim=0,
+        ).contiguous()
+        self.gate_up_proj = Linear(gate_up)
+        self.down_proj = Linear(_as_compute(tensors["down_proj.weight"], dtype).contiguous())
+
+    def forward(self, x, ctx):
+        return self.down_proj(ops.silu_mul(self.gate_up_proj(x)))
+
+
+# ----------------------------------------------------------------------------- embedding / head
+
+
+class TokenEmbedding(Part):
+    """``h0 = E[token]``, no scale (reference ``models/llama/llama.py:104,159``).
+
+    params: ``vocab_size``, ``hidden_size``.  tensors: ``weight [vocab, hidden]``.
+    """
+
+    def param_decls(self):
+        return {"weight": ParamDecl((int(self.param("vocab_size")), int(self.param("hidden_size"))))}
+
+    def bind(self, tensors, dtype, device):
+        self.weight = _as_compute(tensors["weight"], dtype).contiguous()
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        return ops.embedding(self.weight, ctx.token_ids)
+
+
+class OutputHead(Part):
+    """``logits = z W^T`` in fp32 (reference ``models/llama/llama.py:169-172``).  With
+    ``tied`` the embedding's table is the weight and no tensor of its own is expected.
+
+    params: ``vocab_size``, ``hidden_size``, ``tied``.  tensors: ``weight`` unless tied.
+    """
+
+    @property
+    def tied(self) -> bool:
+        return bool(self.spec.params.get("tied", False))
+
+    def param_decls(self):
+        if self.tied:
+            return {}
+        return {"weight": ParamDecl((int(self.param("vocab_size")), int(self.param("hidden_size"))))}
+
+    def bind(self, tensors, dtype, device, tied_weight: torch.Tensor | None = None):
+        if self.tied:
+            if tied_weight is None:
+                raise ValueError("a tied head needs the embedding's table")
+            self.proj = Linear(tied_weight)
+        else:
+            self.proj = Linear(_as_compute(tensors["weight"], dtype).contiguous())
+
+    def forward(self, z: torch.Tensor) -> torch.Tensor:
+        return self.proj(z, out_dtype=torch.float32)
+
+
+# ----------------------------------------------------------------------------- arrangement
+
+
+class PreNormBlock(Arrangement):
+    """``h += mixer(norm1(h)); h += ffn(norm2(h))`` with every addition folded into the
+    following norm (reference ``models/blocks/transformer_block.py:107-120,140-153``): the
+    block receives the previous branch output ``x`` and the fp32 stream ``residual``, and
+    returns its feed-forward output with the stream that does not yet include it.
+    """
+
+    def forward(self, x, residual, ctx, cache):
+        a, residual = self.mixer_norm.forward(x, residual)
+        h = self.mixer.forward(a, ctx, cache, self.position)
+        b, residual = self.feed_forward_norm.forward(h, residual)
+        f = self.feed_forward.forward(b, ctx)
+        return f, residual
+
+
+register_norm("rmsnorm", RMSNorm, replace=True)
+register_position("rotary", RotaryPosition, replace=True)
+register_mixer("gqa_attention", GroupedQueryAttention, replace=True)
+register_feed_forward("swiglu", SwiGLU, replace=True)
+register_embedding("token_embedding", TokenEmbedding, replace=True)
+register_head("linear_head", OutputHead, replace=True)
+register_arrangement("prenorm", PreNormBlock, replace=True)
