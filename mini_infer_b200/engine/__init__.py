@@ -1,0 +1,4 @@
+"""The step function, the runner, the scheduler and the entry points."""
+
+from .runner import ModelRunner  # noqa: F401
+from .step import StepEntry, StepError, StepResult, StepRunner  # noqa: F401

@@ -1,0 +1,98 @@
+"""``ModelRunner``: a loaded model, its cache and its step function in one object.
+
+``ModelRunner.from_pretrained(model_dir, dtype=..., num_blocks=..., block_size=...)`` follows
+the reference's constructor of the same name (``engine/model_runner.py:84-175``; the option
+names ``num_blocks`` and ``block_size`` and their defaults 1024 and 16 are the reference's),
+reduced to what a single-GPU engine for local model folders needs.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Any, Mapping, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.registry import load_config
+from ..parts.model import DecoderModel
+from ..weights.loader import bind_state_dict, load_weights
+from .step import StepEntry, StepResult, StepRunner
+
+DTYPES = {
+    "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+    "float32": torch.float32, "fp32": torch.float32,
+    torch.bfloat16: torch.bfloat16, torch.float32: torch.float32,
+}
+
+DEFAULT_NUM_BLOCKS = 1024
+DEFAULT_BLOCK_SIZE = 16
+
+
+def resolve_dtype(dtype) -> torch.dtype:
+    try:
+        return DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}") from None
+
+
+def require_cuda(device) -> torch.device:
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError(f"the engine runs on a CUDA device only, got {device}")
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device is available; the engine has no CPU path")
+    return device
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, config: Any, *, num_blocks: int = DEFAULT_NUM_BLOCKS,
+                 block_size: int = DEFAULT_BLOCK_SIZE, max_requests: int = 64) -> None:
+        self.model = model
+        self.config = config
+        self.dtype = model.dtype
+        self.device = model.device
+        self.cache = CacheManager(
+            model.cache_needs(), page_size=block_size, num_pages=num_blocks,
+            max_requests=max_requests, dtype=self.dtype, device=self.device,
+        )
+        self.stepper = StepRunner(model, self.cache)
+        self.vocab_size = model.spec.vocab_size
+        self.max_positions = model.spec.max_positions
+        self.num_blocks = num_blocks
+        self.block_size = block_size
+
+    @classmethod
+    def from_pretrained(cls, model_dir: str | os.PathLike, *, device="cuda:0", dtype="bfloat16",
+                        num_blocks: int = DEFAULT_NUM_BLOCKS, block_size: int = DEFAULT_BLOCK_SIZE,
+                        max_requests: int = 64) -> "ModelRunner":
+        """Load ``config.json`` and the safetensors of a local model folder."""
+        device = require_cuda(device)
+        tdtype = resolve_dtype(dtype)
+        arch, cfg = load_config(model_dir)
+        model = DecoderModel(arch.assemble(cfg))
+        load_weights(model, model_dir, tdtype, device)
+        return cls(model, cfg, num_blocks=num_blocks, block_size=block_size, max_requests=max_requests)
+
+    @classmethod
+    def from_state_dict(cls, raw_config: Mapping[str, Any], state: Mapping[str, torch.Tensor], *,
+                        device="cuda:0", dtype="bfloat16", num_blocks: int = DEFAULT_NUM_BLOCKS,
+                        block_size: int = DEFAULT_BLOCK_SIZE, max_requests: int = 64) -> "ModelRunner":
+        """Build from a raw configuration mapping and tensors already in memory."""
+        device = require_cuda(device)
+        tdtype = resolve_dtype(dtype)
+        arch, cfg = load_config(raw_config)
+        model = DecoderModel(arch.assemble(cfg))
+        bind_state_dict(model, dict(state), tdtype, device)
+        return cls(model, cfg, num_blocks=num_blocks, block_size=block_size, max_requests=max_requests)
+
+    # -- requests -----------------------------------------------------------------------
+
+    def add_request(self, rid) -> int:
+        return self.cache.add_request(rid)
+
+    def free_request(self, rid) -> None:
+        self.cache.free_request(rid)
+
+    def step(self, entries: Sequence[StepEntry]) -> StepResult:
+        return self.stepper.step(entries)

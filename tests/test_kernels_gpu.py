@@ -1,0 +1,319 @@
+"""Each CUDA kernel alone against its plain reference, at sizes other than the engine's."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_impl as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from mini_infer_b200.csrc import ops as _ops
+
+    return _ops
+
+
+def tol(dtype, fp32=2e-6, bf16=1.0 / 128):
+    """Relative bound: a few fp32 roundings, or one bf16 rounding (2^-8) with margin."""
+    return fp32 if dtype == torch.float32 else bf16
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+# ----------------------------------------------------------------------------- embedding
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [40, 96, 1030])
+def test_embedding(dtype, H):
+    table = rnd(77, H, dtype=dtype).to(DEV)
+    ids = torch.tensor([0, 76, 5, 5, 33], dtype=torch.int32, device=DEV)
+    out = ops().embedding(table, ids)
+    assert torch.equal(out, table[ids.long()])
+
+
+def test_embedding_bad_id_is_loud():
+    table = rnd(10, 16).to(DEV)
+    out = ops().embedding(table, torch.tensor([3, 10], dtype=torch.int32, device=DEV))
+    assert torch.equal(out[0], table[3]) and torch.isnan(out[1]).all()
+
+
+# ----------------------------------------------------------------------------- rms norm
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,H", [(5, 100), (3, 4096), (2, 50001), (7, 192)])
+def test_add_rmsnorm(dtype, M, H):
+    x = rnd(M, H, dtype=dtype, seed=1)
+    res = rnd(M, H, seed=2)
+    w = (1 + 0.1 * rnd(H, seed=3)).to(dtype)
+    eps = 1e-5
+    r64 = x.double() + res.double()
+    want = P.rms_norm(r64, w.double(), eps)
+    res_out = torch.empty(M, H, device=DEV)
+    out = ops().add_rmsnorm(x.to(DEV), w.to(DEV), eps, residual_in=res.to(DEV), residual_out=res_out)
+    assert torch.allclose(res_out.cpu().double(), r64, rtol=1e-6, atol=1e-6)
+    err = (out.cpu().double() - want).abs().max().item()
+    assert err <= tol(dtype, fp32=5e-6) * want.abs().max().item()
+    # without a residual the stream starts as float(x)
+    res_out2 = torch.empty(M, H, device=DEV)
+    out2 = ops().add_rmsnorm(x.to(DEV), w.to(DEV), eps, residual_out=res_out2)
+    assert torch.equal(res_out2.cpu(), x.float())
+    want2 = P.rms_norm(x.double(), w.double(), eps)
+    assert (out2.cpu().double() - want2).abs().max().item() <= tol(dtype, fp32=5e-6) * want2.abs().max().item()
+
+
+def test_add_rmsnorm_rows_and_fp32_gain():
+    M, H = 9, 136
+    x = rnd(M, H, dtype=torch.bfloat16, seed=4)
+    res = rnd(M, H, seed=5)
+    w32 = 1 + 0.1 * rnd(H, seed=6)          # a gain stored in 32-bit stays 32-bit
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32)
+    out = ops().add_rmsnorm(x.to(DEV), w32.to(DEV), 1e-6, residual_in=res.to(DEV), rows=rows.to(DEV))
+    want = P.rms_norm(x.double() + res.double(), w32.double(), 1e-6)[rows.long()]
+    assert out.shape == (3, H)
+    assert (out.cpu().double() - want).abs().max().item() <= want.abs().max().item() / 128
+
+
+# ----------------------------------------------------------------------------- rope + store
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,rot", [(6, 2, 32, 32), (5, 5, 48, 48), (4, 1, 64, 32), (8, 2, 128, 128)])
+def test_rope_write(dtype, nq, nkv, d, rot):
+    M, n_slots = 11, 40
+    qkv = rnd(M, (nq + 2 * nkv) * d, dtype=dtype, seed=7)
+    pos = torch.tensor([0, 1, 2, 50, 51, 7, 1000, 30000, 3, 4, 131071], dtype=torch.int32)
+    slots = torch.tensor([5, 6, 7, 39, 0, 17, 18, 19, 20, 33, 2], dtype=torch.int32)
+    inv = P.rope_inv_freq(rot, 500000.0, None) if rot == d else (
+        1.0 / (500000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / d)))
+    kc = torch.zeros(n_slots, nkv, d, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    buf = qkv.to(DEV).clone()
+    ops().rope_write(buf, nq, nkv, d, positions=pos.to(DEV), inv_freq=inv.to(DEV), rotary_dim=rot,
+                     slots=slots.to(DEV), kcache=kc, vcache=vc)
+    x = qkv.double().view(M, nq + 2 * nkv, d)
+    cos, sin = P.rope_cos_sin(pos.tolist(), inv, torch.float64)
+    want = x.clone()
+    want[:, : nq + nkv, :rot] = P.apply_rope(x[:, : nq + nkv, :rot], cos, sin)
+    got = buf.cpu().double().view(M, nq + 2 * nkv, d)
+    bound = tol(dtype, fp32=3e-5) * 4.0     # sine/cosine of angles up to 1.3e5 rad in fp32
+    assert (got - want).abs().max().item() <= bound
+    # the cache holds exactly what the buffer holds, at the given slots, and nothing else
+    for t in range(M):
+        assert torch.equal(kc[slots[t]].cpu(), buf[t].view(nq + 2 * nkv, d)[nq:nq + nkv].cpu())
+        assert torch.equal(vc[slots[t]].cpu(), qkv[t].view(nq + 2 * nkv, d)[nq + nkv:])
+    untouched = sorted(set(range(n_slots)) - set(slots.tolist()))
+    assert kc[untouched].abs().sum().item() == 0 and vc[untouched].abs().sum().item() == 0
+
+
+def test_rope_write_refuses_bad_rotary_width():
+    buf = torch.zeros(2, 4 * 16, device=DEV)
+    with pytest.raises(Exception):
+        ops().rope_write(buf, 2, 1, 16, positions=torch.zeros(2, dtype=torch.int32, device=DEV),
+                         inv_freq=torch.zeros(9, device=DEV), rotary_dim=18)
+
+
+# ----------------------------------------------------------------------------- silu * up
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,I", [(3, 176), (5, 50), (2, 14336), (4, 33)])
+def test_silu_mul(dtype, M, I):
+    gu = rnd(M, 2 * I, dtype=dtype, seed=8, scale=3.0)
+    gu[0, 0], gu[0, 1] = 60.0, -60.0      # large and tiny gates stay finite
+    out = ops().silu_mul(gu.to(DEV))
+    g, u = gu.double()[:, :I], gu.double()[:, I:]
+    want = P.silu(g) * u
+    assert torch.isfinite(out).all()
+    assert (out.cpu().double() - want).abs().max().item() <= tol(dtype, fp32=3e-6) * want.abs().max().item()
+
+
+# ----------------------------------------------------------------------------- fp32 product
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 300, 77), (17, 130, 64), (200, 190, 1000), (64, 512, 176), (3, 5, 2)])
+def test_gemm_f32(M, N, K):
+    a, w = rnd(M, K, seed=9), rnd(N, K, seed=10)
+    out = ops().gemm_f32(a.to(DEV), w.to(DEV))
+    want = a.double() @ w.double().T
+    assert (out.cpu().double() - want).abs().max().item() <= 1e-6 * math.sqrt(K) * want.abs().max().item() + 1e-6
+
+
+def test_gemm_f32_rows_do_not_depend_on_the_batch():
+    a, w = rnd(150, 333, seed=11), rnd(257, 333, seed=12)
+    full = ops().gemm_f32(a.to(DEV), w.to(DEV))
+    for rows in ([0], [5, 6, 7], list(range(40)), list(range(149, 70, -1))):
+        part = ops().gemm_f32(a[rows].contiguous().to(DEV), w.to(DEV))
+        assert torch.equal(part, full[rows])
+
+
+def test_gemm_f32_is_not_reduced_precision():
+    # products that a 10-bit (TF32) or 8-bit (bf16) mantissa would lose
+    a = torch.tensor([[1.0 + 2.0 ** -20, 1.0]], device=DEV)
+    w = torch.tensor([[1.0, -1.0]], device=DEV)
+    assert ops().gemm_f32(a, w).item() == 2.0 ** -20
+
+
+# ----------------------------------------------------------------------------- attention
+
+
+def build_paged(kv_lens, nkv, d, page, dtype, seed, n_extra_pages=3):
+    """Random keys/values of several requests scattered over shuffled pages."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages = sum(-(-L // page) for L in kv_lens) + n_extra_pages
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kc = torch.full((n_pages * page, nkv, d), float("nan"), dtype=dtype)
+    vc = torch.full((n_pages * page, nkv, d), float("nan"), dtype=dtype)
+    tables, ks, vs = [], [], []
+    for L in kv_lens:
+        k = torch.randn(L, nkv, d, generator=g).to(dtype)
+        v = torch.randn(L, nkv, d, generator=g).to(dtype)
+        t = [perm.pop() for _ in range(-(-L // page))]
+        for p in range(L):
+            kc[t[p // page] * page + p % page] = k[p]
+            vc[t[p // page] * page + p % page] = v[p]
+        tables.append(t)
+        ks.append(k)
+        vs.append(v)
+    width = max(len(t) for t in tables)
+    bt = torch.tensor([t + [-1] * (width - len(t)) for t in tables], dtype=torch.int32)
+    return kc, vc, bt, ks, vs
+
+
+def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, boost=None):
+    o = ops()
+    kc, vc, bt, ks, vs = build_paged(kv_lens, nkv, d, page, dtype, seed)
+    M = sum(q_lens)
+    g = torch.Generator().manual_seed(seed + 1)
+    q = torch.randn(M, nq, d, generator=g).to(dtype)
+    if boost is not None:
+        boost(q, ks, kc, bt)
+    q_start = [sum(q_lens[:i]) for i in range(len(q_lens))]
+    T_ = o.ATTENTION_TILE_TOKENS
+    treq = [i for i, n in enumerate(q_lens) for _ in range(0, n, T_)]
+    ttok = [t0 for n in q_lens for t0 in range(0, n, T_)]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    # q lives inside a wider buffer, as it does in the engine (row stride > nq * d)
+    wide = torch.zeros(M, nq * d + 24, dtype=dtype)
+    wide[:, : nq * d] = q.view(M, nq * d)
+    wide = wide.to(DEV)
+    out = torch.full((M, nq * d), float("nan"), dtype=dtype, device=DEV)
+    o.attention_generic(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), page, i32(q_start),
+                        i32(q_lens), i32(kv_lens), i32(treq), i32(ttok), len(treq), nq, nkv, d,
+                        1.0 / math.sqrt(d), window)
+    want = torch.empty(M, nq, d, dtype=torch.float64)
+    for i, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
+        want[q_start[i]:q_start[i] + ql] = P.causal_attention(
+            q[q_start[i]:q_start[i] + ql].double(), ks[i].double(), vs[i].double(), 1.0 / math.sqrt(d),
+            window or None, q_offset=kl - ql)
+    return out.cpu().double().view(M, nq, d), want
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page", [(6, 2, 48, 8), (4, 4, 16, 16), (8, 1, 128, 16), (3, 1, 256, 4), (10, 5, 80, 32)])
+def test_attention_mixed_batch(dtype, nq, nkv, d, page):
+    q_lens = [1, 5, 37, 1, 16]
+    kv_lens = [1, 5, 100, 131, 16]
+    got, want = run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, seed=nq)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max().item() <= tol(dtype, fp32=2e-5, bf16=1 / 64)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 7, 20, 64])
+def test_attention_window(dtype, window):
+    got, want = run_attention([1, 40, 3], [90, 70, 3], 4, 2, 32, 8, dtype, window=window, seed=3)
+    assert (got - want).abs().max().item() <= tol(dtype, fp32=2e-5, bf16=1 / 64)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_a_far_key_among_hundreds(dtype):
+    """One key far back is made to match the last query strongly; the output must be its
+    value.  A kernel that skips, repeats or misplaces a page cannot pass."""
+    nq, nkv, d, page = 2, 1, 32, 16
+    for target in (0, 15, 16, 257, 700, 703):
+        def boost(q, ks, kc, bt, target=target):
+            ks[0][target] = 0
+            ks[0][target, 0, 0] = 8.0
+            kc[bt[0, target // page] * page + target % page] = ks[0][target]
+            q[-1] = 0
+            q[-1, :, 0] = 40.0
+        got, want = run_attention([1], [704], nq, nkv, d, page, dtype, seed=5, boost=boost)
+        assert (got - want).abs().max().item() <= tol(dtype, fp32=2e-5, bf16=1 / 64)
+
+
+def test_attention_refuses_bad_head_size():
+    with pytest.raises(Exception):
+        run_attention([1], [4], 2, 1, 24, 4, torch.float32)
+
+
+# ----------------------------------------------------------------------------- sampling
+
+
+def sample_rows(logits, temperature=None, top_k=None, top_p=None, seeds=None, draws=None):
+    B = logits.shape[0]
+    f32 = lambda x: torch.tensor(x, dtype=torch.float32, device=DEV)
+    i32 = lambda x: torch.tensor(np.array(x, dtype=np.int64).astype(np.uint32).view(np.int32).tolist() if x is not None else [],
+                                 dtype=torch.int32, device=DEV)
+    out = torch.empty(B, dtype=torch.int32, device=DEV)
+    kw = {}
+    if temperature is not None:
+        kw = dict(temperature=f32(temperature), top_k=i32(top_k if top_k is not None else [0] * B),
+                  top_p=f32(top_p if top_p is not None else [1.0] * B),
+                  seed_lo=i32([s & 0xFFFFFFFF for s in seeds]), seed_hi=i32([(s >> 32) & 0xFFFFFFFF for s in seeds]),
+                  draw_index=i32(draws))
+    ops().sample(logits.to(DEV), out, **kw)
+    return out.cpu().tolist()
+
+
+def test_sample_greedy_is_argmax_with_lowest_index():
+    logits = rnd(6, 1000, seed=13)
+    logits[2, 17] = logits[2, 900] = 50.0
+    got = sample_rows(logits)
+    want = logits.argmax(dim=-1).tolist()
+    want[2] = 17
+    assert got == want
+
+
+def test_sample_matches_reference_draws():
+    V = 1000
+    logits = rnd(8, V, seed=14, scale=2.0)
+    temps = [0.7, 1.0, 0.0, 1.3, 0.8, 0.8, 1.0, 0.5]
+    top_k = [0, 5, 0, 50, 0, 3, 1, 0]
+    top_p = [1.0, 1.0, 1.0, 1.0, 0.6, 0.9, 1.0, 0.05]
+    seeds = [1, 2, 3, (7 << 32) | 9, 5, 6, 7, 8]
+    draws = [0, 1, 2, 3, 4, 5, 6, 100000]
+    got = sample_rows(logits, temps, top_k, top_p, seeds, draws)
+    for b in range(8):
+        tok, score, keep = P.sample_reference(logits[b].numpy(), temps[b], top_k[b], top_p[b], seeds[b], draws[b])
+        if temps[b] == 0.0:
+            assert got[b] == tok
+            continue
+        assert keep[got[b]], f"row {b}: token {got[b]} is outside the kept set"
+        # the chosen token maximises the perturbed score up to fp32 rounding of the noise
+        assert score[got[b]] >= score.max() - 1e-4 * max(1.0, abs(score.max()))
+
+
+def test_sample_draws_follow_softmax_and_ignore_the_batch():
+    logits_row = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0, -30.0, 1.5, 0.2])
+    B = 4000
+    logits = logits_row.repeat(B, 1)
+    got = sample_rows(logits, [0.9] * B, None, None, [42] * B, list(range(B)))
+    freq = np.bincount(got, minlength=8) / B
+    probs = torch.softmax(logits_row.double() / 0.9, dim=-1).numpy()
+    assert np.abs(freq - probs).max() < 0.03
+    # the same (seed, draw index) gives the same token whatever else is in the batch
+    alone = sample_rows(logits[:1], [0.9], None, None, [42], [1234])
+    mixed = sample_rows(logits[:3], [0.9, 0.0, 0.9], None, None, [7, 8, 42], [0, 0, 1234])
+    assert alone[0] == mixed[2]

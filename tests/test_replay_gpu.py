@@ -1,0 +1,141 @@
+"""The engine against the plain implementation under every way of cutting the work,
+in 32-bit and in bfloat16, for two tiny configurations."""
+
+import numpy as np
+import pytest
+import torch
+
+import trace_util as T
+from tiny_configs import PAGE_SIZE, TINY, load_state, prompt_ids
+
+pytestmark = pytest.mark.gpu
+
+# Largest allowed |logit difference| as a fraction of max(1, largest |reference logit|).
+# float32: rounding of a few hundred fp32 operations.  bfloat16: activations are rounded
+# to 8 bits of mantissa about six times per layer; that predicts errors below one percent
+# of the logit scale for these depths, a wrong key or position gives tens of percent.
+TOL = {"float32": 1e-4, "bfloat16": 3e-2}
+
+LENGTHS = {
+    "A": [17, 33, 64, 5, 70, 90],        # prompts 1/17/48 plus 16 decoded, and three more
+    "B": [25, 31, 87, 154, 224, 3],      # prompts 1/7/63/130/200 plus 24 decoded, and one more
+}
+
+
+def requests_for(which):
+    return {f"r{i}": prompt_ids(which, n, salt=i) for i, n in enumerate(LENGTHS[which])}
+
+
+@pytest.fixture(scope="module")
+def plain(model_dirs):
+    out = {}
+    for which in ("A", "B"):
+        state = load_state(model_dirs[which])
+        out[which] = T.plain_logits(state, TINY[which], requests_for(which))
+    return out
+
+
+def make_runner(model_dir, which, dtype, steps):
+    from mini_infer_b200.engine import ModelRunner
+
+    ps = PAGE_SIZE[which]
+    runner = ModelRunner.from_pretrained(model_dir, dtype=dtype, block_size=ps,
+                                         num_blocks=T.max_tokens_needed(steps) // ps, max_requests=4)
+    for st in runner.cache.storage:
+        st.fill_(float("nan"))       # a slot that was never written must never be read
+    return runner
+
+
+CUTTINGS = {
+    "whole": T.cut_whole,
+    "last_decoded": T.cut_last_decoded,
+    "portions": T.cut_portions,
+    "mixed": T.cut_mixed,
+}
+
+
+@pytest.mark.parametrize("cutting", list(CUTTINGS))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_replay_matches_plain(which, dtype, cutting, model_dirs, plain):
+    requests = requests_for(which)
+    steps = CUTTINGS[cutting](requests)
+    if cutting == "mixed":
+        assert max(len(s["entries"]) for s in steps) == 4
+        assert any(len(e["tokens"]) > 1 for s in steps for e in s["entries"] if len(s["entries"]) > 1)
+    runner = make_runner(model_dirs[which], which, dtype, steps)
+    got = T.collect(steps, T.replay_in_process(runner, steps), TINY[which]["vocab_size"])
+    runner.cache.check()
+    assert runner.cache.num_requests == 0
+    assert runner.cache.num_free_pages() == runner.cache.pools[0].num_pages
+    want = plain[which]
+    scale = max(1.0, max(float(np.abs(want[r]).max()) for r in want))
+    for rid in requests:
+        assert got[rid].shape == want[rid].shape
+        assert np.isfinite(got[rid]).all(), f"{rid}: non-finite logits"
+        bad = T.first_bad(got[rid], want[rid], TOL[dtype] * scale)
+        assert bad is None, (
+            f"{which}/{dtype}/{cutting}: request {rid} first differs at position {bad} "
+            f"(page size {PAGE_SIZE[which]}), |diff| = {np.abs(got[rid][bad] - want[rid][bad]).max():.3e}"
+        )
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_fp32_cuttings_agree_closely(which, model_dirs):
+    """In 32-bit every cutting gives the same logits bit for bit: every sum in the fp32
+    kernels runs in an order that depends on the position alone."""
+    requests = requests_for(which)
+    results = {}
+    for name, cut in CUTTINGS.items():
+        steps = cut(requests)
+        runner = make_runner(model_dirs[which], which, "float32", steps)
+        results[name] = T.collect(steps, T.replay_in_process(runner, steps), TINY[which]["vocab_size"])
+    for name in ("last_decoded", "portions", "mixed"):
+        err, scale = T.max_err(results[name], results["whole"])
+        assert err == 0.0, f"{name} vs whole: {err:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, model_dirs, plain, tmp_path):
+    """The program itself, as a user runs it: mixed cutting with pages used again."""
+    which = "A"
+    requests = requests_for(which)
+    steps = T.cut_mixed(requests)
+    per_step = T.replay_program(model_dirs[which], dtype, steps, str(tmp_path / "out"),
+                                block_size=PAGE_SIZE[which])
+    got = T.collect(steps, per_step, TINY[which]["vocab_size"])
+    err, scale = T.max_err(got, plain[which])
+    assert err <= TOL[dtype] * max(1.0, scale)
+
+
+def test_first_tokens_and_long_decoding(model_dirs, plain):
+    """The first tokens of a sequence (positions 0, 1, 2 alone in their steps) and a long
+    run of single-token steps crossing many page edges."""
+    which = "B"
+    toks = prompt_ids(which, 224, salt=4)
+    steps = [{"step": i, "entries": [{"id": "x", "tokens": [t], "want": [0]}], "end": []}
+             for i, t in enumerate(toks)]
+    steps[-1]["end"] = ["x"]
+    for dtype in ("float32", "bfloat16"):
+        runner = make_runner(model_dirs[which], which, dtype, steps)
+        got = T.collect(steps, T.replay_in_process(runner, steps), TINY[which]["vocab_size"])["x"]
+        want = plain[which]["r4"]
+        scale = max(1.0, float(np.abs(want).max()))
+        bad = T.first_bad(got, want, TOL[dtype] * scale)
+        assert bad is None, f"{dtype}: token-by-token decoding first differs at position {bad}"
+
+
+def test_out_of_pages_changes_nothing(model_dirs):
+    from mini_infer_b200.cache import OutOfPages
+    from mini_infer_b200.engine import ModelRunner, StepEntry
+
+    runner = ModelRunner.from_pretrained(model_dirs["A"], dtype="float32", block_size=16, num_blocks=3,
+                                         max_requests=2)
+    runner.add_request("a")
+    runner.add_request("b")
+    runner.step([StepEntry("a", prompt_ids("A", 30), [29])])
+    with pytest.raises(OutOfPages):
+        runner.step([StepEntry("a", [1], [0]), StepEntry("b", prompt_ids("A", 40), [])])
+    assert runner.cache.length("a") == 30 and runner.cache.length("b") == 0
+    assert runner.cache.num_free_pages() == 1
+    runner.cache.check()

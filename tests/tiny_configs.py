@@ -58,7 +58,14 @@ SEED = {"A": 11, "B": 23}
 # Attention that is almost uniform hides position and cache faults; q and k projections
 # drawn this wide make single keys stand out (the reference's own rope test widens them
 # too, tests/unit/models/llama/test_llama_rope_scaling.py:83-92).
-PEAKED = {"q_proj": 0.35, "k_proj": 0.35}
+# The width is sqrt(2.5 / hidden_size): attention scores then have a standard deviation of
+# about 2.5, peaked enough to show a wrong key, mild enough for bfloat16 to follow.
+def peaked(which: str) -> dict:
+    s = (2.5 / TINY[which]["hidden_size"]) ** 0.5
+    return {"q_proj": s, "k_proj": s}
+
+
+PEAKED = {"A": peaked("A"), "B": peaked("B")}
 
 
 def make_model_dir(which: str, root: str | None = None, peaked: bool = True) -> str:
@@ -67,7 +74,7 @@ def make_model_dir(which: str, root: str | None = None, peaked: bool = True) -> 
     root = root or tempfile.mkdtemp(prefix="mini_infer_test_")
     out = os.path.join(root, f"tiny_{which}{'_peaked' if peaked else ''}")
     if not os.path.isfile(os.path.join(out, "model.safetensors")):
-        write_random_model(TINY[which], out, SEED[which], std_overrides=PEAKED if peaked else None)
+        write_random_model(TINY[which], out, SEED[which], std_overrides=PEAKED[which] if peaked else None)
     return out
 
 
