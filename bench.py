@@ -1,0 +1,353 @@
+"""Benchmark: decode and prefill throughput at Llama 3.1 8B layer sizes, random bf16 weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+A "step" is one decode step of a batch of 8 requests, each holding 2,048 tokens of context
+(growing by one per step).  The one JSON line printed at the end carries:
+
+``value``      decoded tokens per second at batch 8, timed on the device with CUDA events
+               around exactly K steps (after W warm-up steps);
+``e2e``        the same through the Python entry point (``ContinuousScheduler.step``): host
+               token ids in (pinned staging, one host-to-device copy per step) and sampled
+               ids read back to the host every step;
+``prefill``    one 2,048-token prompt in one step: tokens/s, ms, and flops / time / peak;
+``roofline``   bytes the decode step must read (every weight once, plus the cache of the
+               live requests) / time, against the measured copy bandwidth;
+``points``     decode tokens/s at batch 1 and 64;
+``clocks``     SM clocks and throttle reasons sampled during the timed regions.
+
+Weights are far larger than L2, so nothing is flushed between timed iterations
+(``config.l2``).  The engine is single-GPU: ``--gpus N`` with N > 1 prints one line and
+exits with status 2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# Layer sizes of Llama 3.1 8B (the benchmark's model; the engine itself reads sizes from
+# config.json only).
+LLAMA_8B = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "vocab_size": 128256,
+    "hidden_size": 4096,
+    "intermediate_size": 14336,
+    "num_hidden_layers": 32,
+    "num_attention_heads": 32,
+    "num_key_value_heads": 8,
+    "head_dim": 128,
+    "rms_norm_eps": 1e-5,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "max_position_embeddings": 131072,
+    "tie_word_embeddings": False,
+}
+CONTEXT = 2048
+PREFILL_TOKENS = 2048
+PAGE = 16
+BASELINE_DECODE_TOK_S = 276.0   # the reference's published single-request decode speed on a B200
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p.get("bf16_tflops_sustained") or p["bf16_tflops"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi while a timed region runs (reads settings only)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.samples: list[list[str]] = []
+        self._proc = None
+        self._thread = None
+
+    def start(self) -> None:
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self._proc = None
+            return
+
+        def pump() -> None:
+            for line in self._proc.stdout:
+                self.samples.append([c.strip() for c in line.split(",")])
+
+        self._thread = threading.Thread(target=pump, daemon=True)
+        self._thread.start()
+
+    def stop(self) -> dict:
+        if self._proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self._proc.terminate()
+        try:
+            self._proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self._proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx.append(float(s[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, s[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def matmul_params(cfg: dict, layers: int) -> int:
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I
+    return layers * per_layer + V * H
+
+
+def decode_bytes(cfg: dict, layers: int, batch: int, context: int) -> float:
+    nkv, d, H = cfg["num_key_value_heads"], cfg["head_dim"], cfg["hidden_size"]
+    weights = 2.0 * (matmul_params(cfg, layers) + (2 * layers + 1) * H)
+    cache = 2.0 * batch * context * 2 * nkv * d * layers
+    return weights + cache + 2.0 * batch * H      # + the embedding rows read
+
+
+def prefill_flops(cfg: dict, layers: int, tokens: int) -> float:
+    nq, d, V, H = cfg["num_attention_heads"], cfg["head_dim"], cfg["vocab_size"], cfg["hidden_size"]
+    gemm = 2.0 * tokens * (matmul_params(cfg, layers) - V * H) + 2.0 * V * H     # the head runs on one row
+    attention = layers * 2.0 * tokens * tokens * nq * d                            # causal half of 4 T^2 nq d
+    return gemm + attention
+
+
+def build_runner(cfg: dict, layers: int, num_blocks: int, max_requests: int):
+    import torch
+
+    from mini_infer_b200.engine import ModelRunner
+    from mini_infer_b200.weights import random_state_dict
+
+    raw = dict(cfg, num_hidden_layers=layers)
+    state = random_state_dict(raw, seed=0, gain_std=0.0, device="cuda")
+    runner = ModelRunner.from_state_dict(raw, state, device="cuda:0", dtype="bfloat16",
+                                         num_blocks=num_blocks, block_size=PAGE, max_requests=max_requests)
+    del state
+    torch.cuda.empty_cache()
+    return runner
+
+
+def fill_cache(runner, batch: int, context: int) -> list[str]:
+    """Admit ``batch`` requests that already hold ``context`` tokens of (random) keys and
+    values: a decode step's cost does not depend on what the cache holds."""
+    import torch
+
+    for st in runner.cache.storage:
+        st.normal_(0.0, 1.0)
+    rids = []
+    for i in range(batch):
+        rid = f"bench{i}"
+        runner.add_request(rid)
+        runner.cache.plan_append([(rid, context)])
+        rids.append(rid)
+    torch.cuda.synchronize()
+    return rids
+
+
+def time_decode(runner, batch: int, context: int, steps: int, warmup: int) -> tuple[float, int]:
+    """(milliseconds per decode step, kernels launched in the timed region), device-timed."""
+    import torch
+
+    from mini_infer_b200.csrc import ops
+    from mini_infer_b200.engine import StepEntry
+    from mini_infer_b200.sampling import DeviceSampler, SamplingParams
+
+    rids = fill_cache(runner, batch, context)
+    sampler = DeviceSampler(runner.device)
+    params = [SamplingParams()] * batch
+    gen = torch.Generator().manual_seed(1)
+    tokens = torch.randint(0, runner.vocab_size, (steps + warmup, batch), generator=gen).tolist()
+
+    def one(i: int) -> None:
+        res = runner.step([StepEntry(r, [tokens[i][j]], [0]) for j, r in enumerate(rids)])
+        sampler.sample(res.logits, params, [0] * batch, [i] * batch)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    launches0 = ops.launch_count
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    launches = ops.launch_count - launches0
+    for r in rids:
+        runner.free_request(r)
+    return ms, launches
+
+
+def time_prefill(runner, tokens: int, repeats: int, warmup: int) -> float:
+    import torch
+
+    from mini_infer_b200.engine import StepEntry
+
+    gen = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, runner.vocab_size, (tokens,), generator=gen).tolist()
+    times = []
+    for i in range(warmup + repeats):
+        runner.add_request("prefill")
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([StepEntry("prefill", ids, [tokens - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        runner.free_request("prefill")
+        if i >= warmup:
+            times.append(start.elapsed_time(end))
+    return statistics.median(times)
+
+
+def time_e2e(runner, batch: int, context: int, steps: int, warmup: int) -> dict:
+    """Decode through the scheduler: real prompts are prefilled (untimed), then K engine steps
+    are timed by the wall clock with a device synchronise on both sides; every step copies its
+    token ids from pinned host memory and reads the sampled ids back."""
+    import torch
+
+    from mini_infer_b200.engine import ContinuousScheduler, Request
+    from mini_infer_b200.sampling import SamplingParams
+
+    gen = torch.Generator().manual_seed(3)
+    sched = ContinuousScheduler(runner, max_concurrent=batch, chunk_size=context,
+                                max_tokens_per_step=max(context, batch), decode_headroom_blocks=0)
+    for _ in range(batch):
+        prompt = torch.randint(0, runner.vocab_size, (context,), generator=gen).tolist()
+        sched.submit(Request(prompt, SamplingParams(), max_tokens=steps + warmup + 4))
+    while sched.has_prefill_work():
+        sched.step()
+    for _ in range(warmup):
+        sched.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        sched.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    sched.stop()
+    return {"value": batch * steps / dt, "unit": "tokens/s", "ms_per_step": 1000.0 * dt / steps,
+            "h2d_bytes_per_step": runner.stepper.last_h2d_bytes, "d2h_bytes_per_step": 4 * batch}
+
+
+def reference_arm(args) -> int:
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    line = {"impl": "reference"}
+    if not os.path.isdir(os.path.join(ref, "mini_infer")):
+        line["unavailable"] = ("the reference is not installed under baseline/_ref: its build backend "
+                               "(hatchling) is not in the offline wheelhouse")
+        print(json.dumps(line))
+        return 0
+    line["unavailable"] = "the reference arm is not wired up yet"
+    print(json.dumps(line))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=LLAMA_8B["num_hidden_layers"],
+                    help="fewer layers than the model has (sizes unchanged), for small memory")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 and e2e measurements")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.impl == "reference":
+        return reference_arm(args)
+    warmup = max(3, args.warmup)
+
+    import torch
+
+    from mini_infer_b200.csrc import build as kernel_build
+
+    cfg, layers, batch = LLAMA_8B, args.layers, args.batch
+    peaks = load_peaks()
+    max_batch = batch if args.skip_points else max(batch, 64)
+    tokens_cap = max_batch * (CONTEXT + args.steps + warmup + 64)
+    runner = build_runner(cfg, layers, num_blocks=tokens_cap // PAGE + 8, max_requests=max_batch)
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches = time_decode(runner, batch, CONTEXT, args.steps, warmup)
+    points, e2e, prefill = {}, None, None
+    prefill_ms = time_prefill(runner, PREFILL_TOKENS, repeats=3, warmup=2)
+    if not args.skip_points:
+        for b in (1, 64):
+            pms, _ = time_decode(runner, b, CONTEXT, args.steps, warmup)
+            points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+        e2e = time_e2e(runner, batch, CONTEXT, args.steps, warmup)
+    clock_summary = clocks.stop()
+
+    value = batch * 1000.0 / ms
+    mean_ctx = CONTEXT + warmup + args.steps / 2.0
+    achieved = decode_bytes(cfg, layers, batch, mean_ctx) / (ms * 1e-3) / 1e9
+    flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
+    line = {
+        "metric": "decode tok/s @ batch 8, 2048-token context (Llama 3.1 8B layer sizes)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(value / BASELINE_DECODE_TOK_S, 3), "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {
+            "model": "Llama-3.1-8B sizes, random weights", "layers": layers,
+            "layers_of_model": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"],
+            "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "global_batch": batch, "seq_len": CONTEXT, "context_cap": 4096, "page_size": PAGE,
+            "prefill_tokens": PREFILL_TOKENS, "kv_dtype": "bf16", "parallelism": "single GPU",
+            "l2": "inputs (weights) larger than L2, no flush", "peaks": peaks["source"],
+        },
+        "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "gpu_launches": launches,
+        "clocks": clock_summary,
+        "kernel_libraries": sorted(os.path.basename(kernel_build.library_path(n)) for n in kernel_build._loaded),
+    }
+    if e2e is not None:
+        line["e2e"] = {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()}
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -253,6 +253,11 @@ class ContinuousScheduler:
             with open(self.trace_out, "w", encoding="utf-8") as f:
                 json.dump({"traceEvents": self._trace}, f)
 
+    def has_prefill_work(self) -> bool:
+        """True while a request waits for admission or still has prompt tokens to feed."""
+        with self._lock:
+            return bool(self._waiting) or any(r.state is RequestState.PREFILLING for r in self._live)
+
     def load_stats(self) -> SchedulerLoad:
         with self._lock:
             return SchedulerLoad(

@@ -51,6 +51,7 @@ class StepRunner:
         self.tile_sizes = sorted(model.plan_needs().q_tile_tokens)
         self.max_positions = model.spec.max_positions
         self.steps_run = 0
+        self.last_h2d_bytes = 0
 
     # ------------------------------------------------------------------ planning
 
@@ -135,6 +136,7 @@ class StepRunner:
             if n:
                 host_np[o:o + n] = lst
         dev = host.to(self.device, non_blocking=True)
+        self.last_h2d_bytes = host.numel() * 4
 
         def view(name: str) -> torch.Tensor:
             o, n = offsets[name]

@@ -1,0 +1,234 @@
+"""The scheduler's decisions, with a scripted step function over a real cache manager
+(no GPU): admission, the token budget, portions, finishing, and what happens when pages
+run out.  The fake logits name the request and position they came from, so the tests see
+which row every request read (the reference tests its scheduler the same way,
+tests/unit/scheduler/test_scheduler_variable_tokens.py:44-110)."""
+
+from types import SimpleNamespace
+
+import pytest
+
+from mini_infer_b200.cache import CacheManager
+from mini_infer_b200.engine.scheduler import ContinuousScheduler, Request, RequestState
+from mini_infer_b200.parts import KVNeed
+from mini_infer_b200.sampling import SamplingParams
+
+VOCAB = 1000
+
+
+def token_for(rid, position):
+    return (rid * 131 + position * 7 + 3) % (VOCAB - 1) + 1      # never 0 (0 is the end id in one test)
+
+
+class FakeRunner:
+    """Keeps the fed tokens per request and answers each wanted row with (rid, position)."""
+
+    def __init__(self, num_pages, page_size=4, max_requests=8, max_positions=None):
+        needs = [SimpleNamespace(index=0, kv=KVNeed(1, 16), state=None)]
+        self.cache = CacheManager(needs, page_size=page_size, num_pages=num_pages, max_requests=max_requests)
+        self.device = None
+        self.max_positions = max_positions
+        self.fed = {}            # rid -> tokens currently in the cache
+        self.log = []            # per step: [(rid, n_tokens, start_position, wants)]
+
+    def step(self, entries):
+        plan = self.cache.plan_append([(e.rid, len(e.tokens)) for e in entries])
+        rows, rec = [], []
+        for e, start in zip(entries, plan.start):
+            if start == 0:
+                self.fed[e.rid] = []
+            assert len(self.fed[e.rid]) == start
+            self.fed[e.rid].extend(e.tokens)
+            rec.append((e.rid, len(e.tokens), start, list(e.want)))
+            for w in e.want:
+                rows.append((e.rid, start + w))
+        self.log.append(rec)
+        self.cache.check()
+        return SimpleNamespace(logits=rows, rows=rows)
+
+
+class FakeSampler:
+    def __init__(self, eos_at=None):
+        self.eos_at = eos_at or {}
+        self.calls = []
+
+    def sample(self, logits, params, seeds, draw_index):
+        self.calls.append((list(logits), list(draw_index)))
+        out = []
+        for (rid, pos), n in zip(logits, draw_index):
+            out.append(0 if self.eos_at.get(rid) == n else token_for(rid, pos))
+        return out
+
+
+def make(num_pages=64, **kw):
+    runner = FakeRunner(num_pages, page_size=kw.pop("page_size", 4), max_requests=kw.pop("max_requests", 8),
+                        max_positions=kw.pop("max_positions", None))
+    sampler = kw.pop("sampler", FakeSampler())
+    sched = ContinuousScheduler(runner, sampler=sampler, **kw)
+    return runner, sched
+
+
+def expected_tokens(rid, prompt_len, n):
+    return [token_for(rid, prompt_len - 1 + i) for i in range(n)]
+
+
+def prompt(n, base=100):
+    return [(base + i) % VOCAB for i in range(n)]
+
+
+def test_generates_and_frees_everything():
+    runner, sched = make(max_tokens_per_step=64, chunk_size=64)
+    results = sched.generate([Request(prompt(n), SamplingParams(), 5) for n in (1, 17, 48)])
+    for rid, (res, n) in enumerate(zip(results, (1, 17, 48))):
+        assert res.finish_reason == "length" and res.prompt_tokens == n
+        assert res.tokens == expected_tokens(rid, n, 5)
+    assert runner.cache.num_requests == 0 and runner.cache.num_free_pages() == 64
+    # what was fed is the prompt followed by the generated tokens but the last
+    for rid, n in enumerate((1, 17, 48)):
+        assert runner.fed[rid] == prompt(n) + results[rid].tokens[:-1]
+
+
+def test_token_budget_decoders_first_then_portions_in_order():
+    runner, sched = make(max_tokens_per_step=10, chunk_size=6, decode_headroom_blocks=0)
+    sched.generate([Request(prompt(3), max_tokens=30), Request(prompt(20), max_tokens=2),
+                    Request(prompt(9), max_tokens=2)])
+    for rec in runner.log:
+        assert sum(n for _, n, _, _ in rec) <= 10
+        assert all(n <= 6 for _, n, _, _ in rec)
+        kinds = ["d" if (n == 1 and start > 0 and start >= {0: 3, 1: 20, 2: 9}[rid]) else "p"
+                 for rid, n, start, _ in rec]
+        assert kinds == sorted(kinds), "decoding tokens come before prompt portions"
+    # step 0: request 0 whole (3), request 1 gets min(chunk, budget left) = 6, request 2 the last token of budget
+    assert [(r, n) for r, n, _, _ in runner.log[0]] == [(0, 3), (1, 6), (2, 1)]
+    # step 1: request 0 decodes (1), then 1 gets 6, then 2 is cut to what is left (3)
+    assert [(r, n) for r, n, _, _ in runner.log[1]] == [(0, 1), (1, 6), (2, 3)]
+    # logits are wanted only where a prompt ends or a token is decoded
+    for rec in runner.log:
+        for rid, n, start, want in rec:
+            ends_prompt = start + n == {0: 3, 1: 20, 2: 9}[rid]
+            decoding = start >= {0: 3, 1: 20, 2: 9}[rid]
+            assert want == ([n - 1] if (ends_prompt or decoding) else [])
+
+
+def test_portions_can_be_as_small_as_one_token():
+    runner, sched = make(max_tokens_per_step=3, chunk_size=2)
+    res = sched.generate([Request(prompt(7), max_tokens=3), Request(prompt(5), max_tokens=3)])
+    assert [r.tokens for r in res] == [expected_tokens(0, 7, 3), expected_tokens(1, 5, 3)]
+    sizes = {n for rec in runner.log for _, n, _, _ in rec}
+    assert sizes == {1, 2}
+
+
+def test_admission_is_fifo_and_bounded():
+    runner, sched = make(num_pages=64, max_concurrent=2, max_tokens_per_step=64)
+    handles = [sched.submit(Request(prompt(4), max_tokens=3)) for _ in range(5)]
+    sched.step()
+    assert sched.load_stats().num_running == 2 and sched.load_stats().num_waiting == 3
+    assert {rid for rid, *_ in runner.log[0]} == {0, 1}
+    sched.run_until_done()
+    first_seen = {}
+    for i, rec in enumerate(runner.log):
+        for rid, *_ in rec:
+            first_seen.setdefault(rid, i)
+    assert [first_seen[r] for r in range(5)] == sorted(first_seen[r] for r in range(5))
+    assert all(h.wait().finish_reason == "length" for h in handles)
+    stats = sched.load_stats()
+    assert (stats.num_running, stats.num_waiting, stats.kv_cache_usage) == (0, 0, 0.0)
+    assert (stats.block_size, stats.num_blocks) == (4, 64)
+
+
+def test_admission_waits_for_pages_and_keeps_headroom():
+    runner, sched = make(num_pages=10, max_tokens_per_step=64, chunk_size=64, decode_headroom_blocks=2)
+    sched.submit(Request(prompt(20), max_tokens=4))       # 6 pages with its first decoded token
+    sched.submit(Request(prompt(12), max_tokens=4))       # 4 pages + 2 headroom: must wait
+    sched.step()
+    assert sched.load_stats().num_running == 1 and sched.load_stats().num_waiting == 1
+    sched.run_until_done()
+    assert runner.cache.num_free_pages() == 10
+
+
+def test_finish_reasons():
+    sampler = FakeSampler(eos_at={0: 2})
+    runner, sched = make(sampler=sampler, eos_token_ids=[0])
+    a = sched.submit(Request(prompt(5), max_tokens=10))
+    b = sched.submit(Request([], max_tokens=10))
+    c = sched.submit(Request(prompt(500), max_tokens=10))          # 126 pages > pool of 64
+    sched.run_until_done()
+    ra, rb, rc = a.wait(), b.wait(), c.wait()
+    assert ra.finish_reason == "stop" and ra.tokens == expected_tokens(0, 5, 2)   # the end id is not emitted
+    assert rb.finish_reason == "stop" and rb.tokens == []
+    assert rc.finish_reason == "cancelled" and rc.tokens == []
+    with pytest.raises(ValueError):
+        sched.submit(Request(prompt(3), max_tokens=0))
+
+
+def test_last_position_of_the_model_ends_a_request():
+    runner, sched = make(max_positions=12)
+    res = sched.run(Request(prompt(9), max_tokens=50))
+    assert res.finish_reason == "length" and len(res.tokens) == 4     # tokens at positions 9, 10, 11 fed; 12th position never
+    assert max(start + n for rec in runner.log for _, n, start, _ in rec) <= 12
+    assert sched.run(Request(prompt(12), max_tokens=5)).finish_reason == "cancelled"
+
+
+def test_when_pages_run_out_portions_shrink_then_the_youngest_is_recomputed():
+    # 8 pages of 4 tokens.  Two requests decode until the pool is full; then the youngest is
+    # preempted, recomputed later, and still produces exactly the tokens it would have.
+    runner, sched = make(num_pages=8, max_tokens_per_step=64, chunk_size=64, decode_headroom_blocks=0)
+    res = sched.generate([Request(prompt(10), max_tokens=14), Request(prompt(9), max_tokens=14)])
+    assert sched.preemptions >= 1
+    assert res[0].tokens == expected_tokens(0, 10, 14) and res[0].finish_reason == "length"
+    assert res[1].tokens == expected_tokens(1, 9, 14) and res[1].finish_reason == "length"
+    assert runner.cache.num_free_pages() == 8 and runner.cache.num_requests == 0
+    # the preempted request was fed its prompt plus what it had generated, from position 0
+    restarts = [rec for rec in runner.log for rid, n, start, _ in rec if rid == 1 and start == 0]
+    assert len(restarts) >= 2
+    # no token was emitted twice: draw indices per request are 0, 1, 2, ... without repeats
+    draws = {}
+    for rows, idx in sched.sampler.calls:
+        for (rid, _), n in zip(rows, idx):
+            draws.setdefault(rid, []).append(n)
+    assert draws[0] == list(range(14)) and draws[1] == list(range(14))
+
+
+def test_prompt_portions_shrink_to_the_pages_that_are_left():
+    runner, sched = make(num_pages=6, max_tokens_per_step=64, chunk_size=64, decode_headroom_blocks=0)
+    a = sched.submit(Request(prompt(14), max_tokens=3))
+    sched.step()                                    # a: 14 tokens, 4 pages
+    b = sched.submit(Request(prompt(7), max_tokens=2))
+    sched.run_until_done()
+    assert a.wait().tokens == expected_tokens(0, 14, 3)
+    assert b.wait().tokens == expected_tokens(1, 7, 2)
+    assert runner.cache.num_free_pages() == 6
+
+
+def test_a_request_that_cannot_fit_alone_is_cancelled():
+    runner, sched = make(num_pages=3, max_tokens_per_step=64, chunk_size=64, decode_headroom_blocks=0)
+    res = sched.run(Request(prompt(10), max_tokens=20))       # needs a 4th page at token 13
+    assert res.finish_reason == "cancelled" and res.tokens == expected_tokens(0, 10, len(res.tokens))
+    assert runner.cache.num_free_pages() == 3
+
+
+def test_cancel_and_engine_thread():
+    runner, sched = make()
+    h = sched.submit(Request(prompt(6), max_tokens=1000))
+    sched.step()
+    h.cancel()
+    assert h.wait().finish_reason == "cancelled" and runner.cache.num_free_pages() == 64
+    sched.start()
+    try:
+        out = sched.submit(Request(prompt(5), max_tokens=4)).wait(timeout=20)
+        assert out.tokens == expected_tokens(1, 5, 4)
+    finally:
+        sched.stop()
+
+
+def test_trace_out(tmp_path):
+    import json
+
+    path = tmp_path / "trace.json"
+    runner, sched = make(trace_out=str(path), max_tokens_per_step=8, chunk_size=8)
+    sched.generate([Request(prompt(12), max_tokens=2), Request(prompt(2), max_tokens=4)])
+    sched.stop()
+    events = json.loads(path.read_text())["traceEvents"]
+    assert len(events) == len(runner.log)
+    assert {e["args"]["phase"] for e in events} <= {"prefill", "decode", "mixed"}
+    assert events[0]["args"]["total_q"] == 8 and events[0]["args"]["B"] == 1
