@@ -151,7 +151,8 @@ def build_runner(cfg: dict, layers: int, num_blocks: int, max_requests: int):
     raw = dict(cfg, num_hidden_layers=layers)
     state = random_state_dict(raw, seed=0, gain_std=0.0, device="cuda")
     runner = ModelRunner.from_state_dict(raw, state, device="cuda:0", dtype="bfloat16",
-                                         num_blocks=num_blocks, block_size=PAGE, max_requests=max_requests)
+                                         num_blocks=num_blocks, block_size=PAGE, max_requests=max_requests,
+                                         cuda_graph=True)
     del state
     torch.cuda.empty_cache()
     return runner

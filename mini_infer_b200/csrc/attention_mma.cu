@@ -1,0 +1,638 @@
+// bfloat16 attention over the paged cache on tensor cores (mma.sync m16n8k16, fp32
+// accumulation, fp32 online softmax), keys and values staged in shared memory with
+// cp.async (two buffers) and read with ldmatrix.
+//
+// Two kernels share the machinery:
+//
+//   decode   every request brings one query token.  A block takes one request, one group
+//            of up to 16 query heads that share a key/value head, and one slice of the
+//            keys ("split"); its 4 warps take 16 keys each of every 64-key chunk, keep an
+//            online softmax of their own and are merged at the end.  With more than one
+//            split the block writes an unnormalised partial result (fp32) and its
+//            (max, sum) to scratch memory, and a second kernel merges the splits.
+//   prefill  query portions of any length.  A block takes a tile of tokens of one request
+//            and up to 128 rows (token, head-in-group) that share a key/value head; each
+//            warp owns 16 rows and walks all keys up to the causal limit.
+//
+// A query at absolute position p sees keys j with max(0, p - window + 1) <= j <= p.
+// Layouts are those of attention_generic.cu.
+#include "common.cuh"
+
+MI_DEFINE_ERROR_API()
+
+#define KCHUNK 64
+#define NTHREADS 128
+#define LOG2E 1.4426950408889634f
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copy the 64 keys and the 64 values of chunk `chunk` of one request into `kdst` / `vdst`
+// ([64][sd] bf16 each).  Keys outside [lo, hi) are zero-filled and their pages never touched.
+// When the thread count is a multiple of the 16-byte units per row (head sizes 16, 32, 64,
+// 128, 256) every thread keeps one unit column and walks rows, so the page lookup is done
+// once per row; other head sizes take the general path.
+template <int THREADS>
+__device__ __forceinline__ void load_kv_chunk(bf16* kdst, bf16* vdst, const bf16* __restrict__ kcache,
+                                              const bf16* __restrict__ vcache, const int* __restrict__ table,
+                                              int page_size, int page_shift, int chunk, int lo, int hi,
+                                              int nkv, int kvh, int d, int sd) {
+  const int units = d >> 3;  // 16-byte units per row
+  const int jbase = chunk * KCHUNK;
+  if (THREADS % units == 0) {
+    const int u = threadIdx.x % units, rstep = THREADS / units;
+    for (int r = threadIdx.x / units; r < KCHUNK; r += rstep) {
+      const int j = jbase + r;
+      bf16* ks = kdst + r * sd + u * 8;
+      bf16* vs = vdst + r * sd + u * 8;
+      if (j >= lo && j < hi) {
+        int page, inpage;
+        if (page_shift >= 0) {
+          page = table[j >> page_shift];
+          inpage = j & (page_size - 1);
+        } else {
+          page = table[j / page_size];
+          inpage = j % page_size;
+        }
+        const size_t off = ((size_t)(page * page_size + inpage) * nkv + kvh) * d + u * 8;
+        cp_async16(ks, kcache + off);
+        cp_async16(vs, vcache + off);
+      } else {
+        *reinterpret_cast<uint4*>(ks) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(vs) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < KCHUNK * units; idx += THREADS) {
+      const int r = idx / units, u = idx - r * units;
+      const int j = jbase + r;
+      bf16* ks = kdst + r * sd + u * 8;
+      bf16* vs = vdst + r * sd + u * 8;
+      if (j >= lo && j < hi) {
+        const int page = table[j / page_size];
+        const size_t off = ((size_t)(page * page_size + j % page_size) * nkv + kvh) * d + u * 8;
+        cp_async16(ks, kcache + off);
+        cp_async16(vs, vcache + off);
+      } else {
+        *reinterpret_cast<uint4*>(ks) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(vs) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------- decode
+
+template <int DMAX>
+__global__ void __launch_bounds__(NTHREADS)
+attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+                        const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                        const int* __restrict__ block_table, int bt_stride, int page_size, int page_shift,
+                        const int* __restrict__ q_start, const int* __restrict__ kv_len, int nq, int nkv,
+                        int d, float scale, int window, int n_splits, float* __restrict__ part_o,
+                        float* __restrict__ part_ml) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int sd = d + 8;  // row stride in elements: 16 bytes of padding keep ldmatrix conflict-free
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [16][sd]
+  bf16* Ks = Qs + 16 * sd;                               // [2][64][sd]
+  bf16* Vs = Ks + 2 * KCHUNK * sd;                       // [2][64][sd]
+  float* merge_o = reinterpret_cast<float*>(Ks);         // [4][16][d] after the main loop
+  __shared__ float merge_m[4][16], merge_l[4][16];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int qd = lane >> 2, t4 = lane & 3;
+  const int g = nq / nkv;
+  const int hblocks = (g + 15) >> 4;
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y / hblocks, hb = blockIdx.y - kvh * hblocks;
+  const int b = blockIdx.z;
+  const int kl = kv_len[b];
+  const int tok = q_start[b];
+  const int lo = window > 0 ? max(0, kl - window) : 0;  // the query sits at position kl - 1
+  const int c_first = lo / KCHUNK, c_end = (kl + KCHUNK - 1) / KCHUNK;
+  const int per_split = (c_end - c_first + n_splits - 1) / n_splits;
+  const int c0 = c_first + split * per_split;
+  const int c1 = min(c_end, c0 + per_split);
+  const int heads_here = min(16, g - hb * 16);
+  const int head0 = kvh * g + hb * 16;
+  const int* table = block_table + (size_t)b * bt_stride;
+
+  if (c0 >= c1) {  // nothing for this split (only possible with n_splits > 1)
+    for (int r = tid; r < heads_here; r += NTHREADS) {
+      float* ml = part_ml + ((size_t)(b * nq + head0 + r) * n_splits + split) * 2;
+      ml[0] = -INFINITY;
+      ml[1] = 0.f;
+    }
+    return;
+  }
+
+  const int units = d >> 3;
+  for (int idx = tid; idx < 16 * units; idx += NTHREADS) {
+    const int r = idx / units, u = idx - r * units;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < heads_here) v = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (size_t)(head0 + r) * d + u * 8);
+    *reinterpret_cast<uint4*>(Qs + r * sd + u * 8) = v;
+  }
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[DMAX / 8][4];
+#pragma unroll
+  for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const float sc = scale * LOG2E;
+  const int ksteps = d >> 4;
+
+  load_kv_chunk<NTHREADS>(Ks, Vs, kcache, vcache, table, page_size, page_shift, c0, lo, kl, nkv, kvh, d, sd);
+  cp_async_commit();
+
+  for (int c = c0; c < c1; ++c) {
+    const int buf = (c - c0) & 1;
+    if (c + 1 < c1) {
+      load_kv_chunk<NTHREADS>(Ks + (buf ^ 1) * KCHUNK * sd, Vs + (buf ^ 1) * KCHUNK * sd, kcache, vcache, table,
+                              page_size, page_shift, c + 1, lo, kl, nkv, kvh, d, sd);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const bf16* Kb = Ks + buf * KCHUNK * sd + (warp * 16) * sd;
+    const bf16* Vb = Vs + buf * KCHUNK * sd + (warp * 16) * sd;
+    const int key0 = c * KCHUNK + warp * 16;
+    if (key0 < kl && key0 + 16 > lo) {  // warp-uniform: this warp's 16 keys hold something visible
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int ks = 0; ks < DMAX / 16; ++ks) {
+        if (ks < ksteps) {
+          uint32_t a[4], kb[4];
+          ldmatrix_x4(a, Qs + (lane & 15) * sd + ks * 16 + (lane >> 4) * 8);
+          ldmatrix_x4(kb, Kb + ((lane & 7) + (lane >> 4) * 8) * sd + ks * 16 + ((lane >> 3) & 1) * 8);
+          mma_bf16(s[0], a, kb[0], kb[1]);
+          mma_bf16(s[1], a, kb[2], kb[3]);
+        }
+      }
+      float mx = -INFINITY;  // every row of this block is the same query position: one mask
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = key0 + nt * 8 + 2 * t4 + (e & 1);
+          s[nt][e] = (j < kl && j >= lo) ? s[nt][e] * sc : -INFINITY;
+        }
+      uint32_t pa[4];
+#pragma unroll
+      for (int hr = 0; hr < 2; ++hr) {
+        mx = fmaxf(fmaxf(s[0][2 * hr], s[0][2 * hr + 1]), fmaxf(s[1][2 * hr], s[1][2 * hr + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[hr], mx);
+        float alpha = 1.f, p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+        if (m_new != -INFINITY) {
+          alpha = exp2f(m_run[hr] - m_new);
+          p0 = exp2f(s[0][2 * hr] - m_new);
+          p1 = exp2f(s[0][2 * hr + 1] - m_new);
+          p2 = exp2f(s[1][2 * hr] - m_new);
+          p3 = exp2f(s[1][2 * hr + 1] - m_new);
+        }
+        m_run[hr] = m_new;
+        l_run[hr] = l_run[hr] * alpha + ((p0 + p1) + (p2 + p3));
+        pa[hr] = pack_bf16(p0, p1);        // a0 / a1: keys 2t, 2t+1 of the first 8
+        pa[2 + hr] = pack_bf16(p2, p3);    // a2 / a3: keys 2t, 2t+1 of the second 8
+#pragma unroll
+        for (int i = 0; i < DMAX / 8; ++i) {
+          o[i][2 * hr] *= alpha;
+          o[i][2 * hr + 1] *= alpha;
+        }
+      }
+#pragma unroll
+      for (int dt = 0; dt < DMAX / 16; ++dt) {
+        if (dt < ksteps) {
+          uint32_t vb[4];
+          ldmatrix_x4_trans(vb, Vb + ((lane & 7) + ((lane >> 3) & 1) * 8) * sd + dt * 16 + (lane >> 4) * 8);
+          mma_bf16(o[2 * dt], pa, vb[0], vb[1]);
+          mma_bf16(o[2 * dt + 1], pa, vb[2], vb[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // merge the four warps (the last __syncthreads above freed the K/V buffers)
+#pragma unroll
+  for (int hr = 0; hr < 2; ++hr) {
+    float l = l_run[hr];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (t4 == 0) {
+      merge_m[warp][qd + 8 * hr] = m_run[hr];
+      merge_l[warp][qd + 8 * hr] = l;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < DMAX / 8; ++i) {
+    if (i * 8 < d) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        merge_o[((size_t)warp * 16 + qd + 8 * (e >> 1)) * d + i * 8 + 2 * t4 + (e & 1)] = o[i][e];
+    }
+  }
+  __syncthreads();
+  const int r = tid >> 3, cgrp = tid & 7;
+  if (r < heads_here) {
+    float m = merge_m[0][r];
+#pragma unroll
+    for (int w = 1; w < 4; ++w) m = fmaxf(m, merge_m[w][r]);
+    float f[4], L = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      f[w] = (m == -INFINITY) ? 0.f : exp2f(merge_m[w][r] - m);
+      L += merge_l[w][r] * f[w];
+    }
+    const int head = head0 + r;
+    if (n_splits == 1) {
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      bf16* orow = out + (size_t)tok * out_stride + (size_t)head * d;
+      for (int k = cgrp; k < d; k += 8) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) acc += f[w] * merge_o[((size_t)w * 16 + r) * d + k];
+        orow[k] = __float2bfloat16_rn(acc * inv);
+      }
+    } else {
+      const size_t slot = (size_t)(b * nq + head) * n_splits + split;
+      float* po = part_o + slot * d;
+      for (int k = cgrp; k < d; k += 8) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) acc += f[w] * merge_o[((size_t)w * 16 + r) * d + k];
+        po[k] = acc;
+      }
+      if (cgrp == 0) {
+        part_ml[slot * 2] = m;
+        part_ml[slot * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+// Merge the splits of one (request, head): out = sum_s f_s O_s / sum_s f_s l_s, f_s = 2^(m_s - m).
+// One block per (head, request); n_splits <= 64.
+__global__ void __launch_bounds__(128)
+attention_merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                              bf16* __restrict__ out, int out_stride, const int* __restrict__ q_start, int nq,
+                              int d, int n_splits) {
+  __shared__ float fs[64];
+  __shared__ float inv_l;
+  const int head = blockIdx.x, b = blockIdx.y;
+  const size_t base = (size_t)(b * nq + head) * n_splits;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    const float m0 = lane < n_splits ? part_ml[(base + lane) * 2] : -INFINITY;
+    const float m1 = lane + 32 < n_splits ? part_ml[(base + lane + 32) * 2] : -INFINITY;
+    const float m = mi_warp_max(fmaxf(m0, m1));
+    const float f0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - m);
+    const float f1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - m);
+    float l = 0.f;
+    if (lane < n_splits) l += f0 * part_ml[(base + lane) * 2 + 1];
+    if (lane + 32 < n_splits) l += f1 * part_ml[(base + lane + 32) * 2 + 1];
+    l = mi_warp_sum(l);
+    fs[lane] = f0;
+    fs[lane + 32] = f1;
+    if (lane == 0) inv_l = l > 0.f ? 1.f / l : 0.f;
+  }
+  __syncthreads();
+  bf16* orow = out + (size_t)q_start[b] * out_stride + (size_t)head * d;
+  for (int k = threadIdx.x; k < d; k += blockDim.x) {
+    float acc = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < n_splits; ++s) {
+      const float f = fs[s];
+      if (f != 0.f) acc += f * part_o[(base + s) * d + k];
+    }
+    orow[k] = __float2bfloat16_rn(acc * inv_l);
+  }
+}
+
+// ------------------------------------------------------------------------------- prefill
+
+#define PTHREADS 256
+#define PROWS 128   // rows (token, head in group) per block: 8 warps of 16
+
+template <int DMAX>
+__global__ void __launch_bounds__(PTHREADS)
+attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+                         const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                         const int* __restrict__ block_table, int bt_stride, int page_size, int page_shift,
+                         const int* __restrict__ q_start, const int* __restrict__ q_len,
+                         const int* __restrict__ kv_len, const int* __restrict__ tile_req,
+                         const int* __restrict__ tile_tok0, int nq, int nkv, int d, float scale, int window,
+                         int gb, int tt) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int sd = d + 8;
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);   // [PROWS][sd]
+  bf16* Ks = Qs + PROWS * sd;                        // [2][64][sd]
+  bf16* Vs = Ks + 2 * KCHUNK * sd;                // [2][64][sd]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int qd = lane >> 2, t4 = lane & 3;
+  const int g = nq / nkv;
+  const int hblocks = (g + gb - 1) / gb;
+  const int tile = blockIdx.x;
+  const int kvh = blockIdx.y / hblocks, hb = blockIdx.y - kvh * hblocks;
+  const int b = tile_req[tile], tok0 = tile_tok0[tile];
+  const int ql = q_len[b], kl = kv_len[b], qs = q_start[b];
+  const int ntok = min(tt, ql - tok0);
+  const int p_first = kl - ql + tok0;
+  const int hi = p_first + ntok;  // one past the last key any row of the tile sees
+  const int lo = window > 0 ? max(0, p_first - window + 1) : 0;
+  const int heads_here = min(gb, g - hb * gb);
+  const int* table = block_table + (size_t)b * bt_stride;
+
+  // row R of the tile: token tok0 + R / gb, head kvh * g + hb * gb + R % gb
+  const int units = d >> 3;
+  for (int idx = tid; idx < PROWS * units; idx += PTHREADS) {
+    const int R = idx / units, u = idx - R * units;
+    const int tk = R / gb, mem = R - tk * gb;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (tk < ntok && mem < heads_here)
+      v = *reinterpret_cast<const uint4*>(q + (size_t)(qs + tok0 + tk) * q_stride +
+                                          (size_t)(kvh * g + hb * gb + mem) * d + u * 8);
+    *reinterpret_cast<uint4*>(Qs + R * sd + u * 8) = v;
+  }
+
+  // this lane's two rows
+  int prow[2], lorow[2];
+  bool rvalid[2];
+#pragma unroll
+  for (int hr = 0; hr < 2; ++hr) {
+    const int R = warp * 16 + qd + 8 * hr;
+    const int tk = R / gb, mem = R - tk * gb;
+    rvalid[hr] = tk < ntok && mem < heads_here;
+    prow[hr] = p_first + tk;
+    lorow[hr] = window > 0 ? max(0, prow[hr] - window + 1) : 0;
+  }
+  // the warp's rows span tokens [wt0, wt1]
+  const int wt0 = (warp * 16) / gb, wt1 = min(ntok - 1, (warp * 16 + 15) / gb);
+  const bool warp_active = wt0 < ntok;
+  const int warp_hi = p_first + wt1 + 1;                                   // one past its last visible key
+  const int warp_lo = window > 0 ? max(0, p_first + wt0 - window + 1) : 0;  // its first visible key
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[DMAX / 8][4];
+#pragma unroll
+  for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const float sc = scale * LOG2E;
+  const int ksteps = d >> 4;
+  const int c0 = lo / KCHUNK, c1 = (hi + KCHUNK - 1) / KCHUNK;
+
+  load_kv_chunk<PTHREADS>(Ks, Vs, kcache, vcache, table, page_size, page_shift, c0, lo, hi, nkv, kvh, d, sd);
+  cp_async_commit();
+
+  for (int c = c0; c < c1; ++c) {
+    const int buf = (c - c0) & 1;
+    if (c + 1 < c1) {
+      load_kv_chunk<PTHREADS>(Ks + (buf ^ 1) * KCHUNK * sd, Vs + (buf ^ 1) * KCHUNK * sd, kcache, vcache, table,
+                              page_size, page_shift, c + 1, lo, hi, nkv, kvh, d, sd);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const bf16* Kb = Ks + buf * KCHUNK * sd;
+    const bf16* Vb = Vs + buf * KCHUNK * sd;
+    const int key0 = c * KCHUNK;
+    if (warp_active && key0 < warp_hi && key0 + KCHUNK > warp_lo) {
+      float s[8][4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < DMAX / 16; ++ks) {
+        if (ks < ksteps) {
+          uint32_t a[4];
+          ldmatrix_x4(a, Qs + (warp * 16 + (lane & 15)) * sd + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+          for (int kp = 0; kp < 4; ++kp) {
+            uint32_t kb[4];
+            ldmatrix_x4(kb, Kb + (kp * 16 + (lane & 7) + (lane >> 4) * 8) * sd + ks * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16(s[2 * kp], a, kb[0], kb[1]);
+            mma_bf16(s[2 * kp + 1], a, kb[2], kb[3]);
+          }
+        }
+      }
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int hr = e >> 1;
+          const int j = key0 + nt * 8 + 2 * t4 + (e & 1);
+          s[nt][e] = (rvalid[hr] && j <= prow[hr] && j >= lorow[hr]) ? s[nt][e] * sc : -INFINITY;
+        }
+      uint32_t pa[4][4];
+#pragma unroll
+      for (int hr = 0; hr < 2; ++hr) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) mx = fmaxf(mx, fmaxf(s[nt][2 * hr], s[nt][2 * hr + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[hr], mx);
+        float alpha = 1.f, sum = 0.f;
+        if (m_new != -INFINITY) {
+          alpha = exp2f(m_run[hr] - m_new);
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt) {
+            s[nt][2 * hr] = exp2f(s[nt][2 * hr] - m_new);
+            s[nt][2 * hr + 1] = exp2f(s[nt][2 * hr + 1] - m_new);
+            sum += s[nt][2 * hr] + s[nt][2 * hr + 1];
+          }
+        } else {
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt) s[nt][2 * hr] = s[nt][2 * hr + 1] = 0.f;
+        }
+        m_run[hr] = m_new;
+        l_run[hr] = l_run[hr] * alpha + sum;
+#pragma unroll
+        for (int i = 0; i < DMAX / 8; ++i) {
+          o[i][2 * hr] *= alpha;
+          o[i][2 * hr + 1] *= alpha;
+        }
+      }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        pa[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        pa[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        pa[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        pa[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      }
+#pragma unroll
+      for (int dt = 0; dt < DMAX / 16; ++dt) {
+        if (dt < ksteps) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            uint32_t vb[4];
+            ldmatrix_x4_trans(vb, Vb + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * sd + dt * 16 + (lane >> 4) * 8);
+            mma_bf16(o[2 * dt], pa[kk], vb[0], vb[1]);
+            mma_bf16(o[2 * dt + 1], pa[kk], vb[2], vb[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int hr = 0; hr < 2; ++hr) {
+    float l = l_run[hr];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (!rvalid[hr] || !(l > 0.f)) continue;
+    const float inv = 1.f / l;
+    const int R = warp * 16 + qd + 8 * hr;
+    const int tk = R / gb, mem = R - tk * gb;
+    bf16* orow = out + (size_t)(qs + tok0 + tk) * out_stride + (size_t)(kvh * g + hb * gb + mem) * d;
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; ++i) {
+      if (i * 8 < d) {
+        const uint32_t v = pack_bf16(o[i][2 * hr] * inv, o[i][2 * hr + 1] * inv);
+        *reinterpret_cast<uint32_t*>(orow + i * 8 + 2 * t4) = v;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------- host side
+
+static int check_common(const void* q, int q_stride, const void* out, int out_stride, const void* kcache,
+                        const void* vcache, int nq, int nkv, int d, int page_size, int window) {
+  if (d <= 0 || d % 16 != 0 || d > 256) MI_REFUSE("attention: head size %d is not a multiple of 16 in [16, 256]", d);
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0) MI_REFUSE("attention: %d query heads cannot share %d key/value heads", nq, nkv);
+  if (page_size <= 0 || window < 0) MI_REFUSE("attention: bad page size %d or window %d", page_size, window);
+  if (!mi_aligned(q, 16) || q_stride % 8 != 0) MI_REFUSE("attention: queries must be 16-byte aligned with a row stride that is a multiple of 8");
+  if (!mi_aligned(out, 4) || out_stride % 2 != 0) MI_REFUSE("attention: output rows must be 4-byte aligned");
+  if (!mi_aligned(kcache, 16) || !mi_aligned(vcache, 16)) MI_REFUSE("attention: cache must be 16-byte aligned");
+  return 0;
+}
+
+static size_t smem_bytes(int q_rows, int d) { return (size_t)(q_rows + 4 * KCHUNK) * (d + 8) * sizeof(bf16); }
+
+static int shift_of(int page_size) {  // log2 for powers of two, else -1
+  if (page_size & (page_size - 1)) return -1;
+  int s = 0;
+  while ((1 << s) < page_size) ++s;
+  return s;
+}
+
+// Scratch: part_o holds B * nq * n_splits * d floats, part_ml holds B * nq * n_splits * 2 floats
+// (both may be null when n_splits == 1).
+extern "C" int mi_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
+                                   const void* vcache, const int* block_table, int bt_stride, int page_size,
+                                   const int* q_start, const int* kv_len, int B, int nq, int nkv, int d,
+                                   float scale, int window, int n_splits, float* part_o, float* part_ml,
+                                   cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (int rc = check_common(q, q_stride, out, out_stride, kcache, vcache, nq, nkv, d, page_size, window)) return rc;
+  if (n_splits < 1 || n_splits > 64) MI_REFUSE("attention: n_splits must be in [1, 64], got %d", n_splits);
+  const int page_shift = shift_of(page_size);
+  if (n_splits > 1 && (!part_o || !part_ml)) MI_REFUSE("attention: split results need scratch memory");
+  const int g = nq / nkv, hblocks = (g + 15) / 16;
+  if (B > 65535 || nkv * hblocks > 65535) MI_REFUSE("attention: batch or head count too large for one launch");
+  const size_t smem = smem_bytes(16, d);
+  dim3 grid(n_splits, nkv * hblocks, B);
+#define MI_DECODE(DMAX)                                                                                 \
+  do {                                                                                                  \
+    auto kern = attention_decode_kernel<DMAX>;                                                          \
+    if (smem > 48 * 1024) {                                                                             \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return (int)e;                                                              \
+    }                                                                                                   \
+    kern<<<grid, NTHREADS, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride,            \
+                                           (const bf16*)kcache, (const bf16*)vcache, block_table,       \
+                                           bt_stride, page_size, page_shift, q_start, kv_len, nq, nkv,  \
+                                           d, scale, window, n_splits, part_o, part_ml);                \
+  } while (0)
+  if (d <= 64) MI_DECODE(64);
+  else if (d <= 128) MI_DECODE(128);
+  else MI_DECODE(256);
+#undef MI_DECODE
+  if (n_splits > 1) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      snprintf(g_mi_error, sizeof(g_mi_error), "CUDA: %s", cudaGetErrorString(e));
+      return (int)e;
+    }
+    dim3 mgrid(nq, B);
+    attention_merge_splits_kernel<<<mgrid, 128, 0, stream>>>(part_o, part_ml, (bf16*)out, out_stride, q_start, nq,
+                                                             d, n_splits);
+  }
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+// Tokens per tile the prefill kernel wants for a group of g query heads per key/value head.
+extern "C" int mi_attention_prefill_tile_tokens(int g) {
+  const int gb = g < PROWS ? g : PROWS;
+  return PROWS / gb;
+}
+
+extern "C" int mi_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
+                                    const void* vcache, const int* block_table, int bt_stride, int page_size,
+                                    const int* q_start, const int* q_len, const int* kv_len,
+                                    const int* tile_req, const int* tile_tok0, int n_tiles, int tile_tokens,
+                                    int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (int rc = check_common(q, q_stride, out, out_stride, kcache, vcache, nq, nkv, d, page_size, window)) return rc;
+  const int g = nq / nkv;
+  const int gb = g < PROWS ? g : PROWS;
+  if (tile_tokens != PROWS / gb) MI_REFUSE("attention: tiles of %d tokens, the kernel wants %d", tile_tokens, PROWS / gb);
+  const int hblocks = (g + gb - 1) / gb;
+  if (nkv * hblocks > 65535) MI_REFUSE("attention: too many heads for one launch");
+  const size_t smem = smem_bytes(PROWS, d);
+  const int page_shift = shift_of(page_size);
+  dim3 grid(n_tiles, nkv * hblocks);
+#define MI_PREFILL(DMAX)                                                                                \
+  do {                                                                                                  \
+    auto kern = attention_prefill_kernel<DMAX>;                                                         \
+    if (smem > 48 * 1024) {                                                                             \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return (int)e;                                                              \
+    }                                                                                                   \
+    kern<<<grid, PTHREADS, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride,            \
+                                           (const bf16*)kcache, (const bf16*)vcache, block_table,       \
+                                           bt_stride, page_size, page_shift, q_start, q_len, kv_len,    \
+                                           tile_req, tile_tok0, nq, nkv, d, scale, window, gb,          \
+                                           PROWS / gb);                                                 \
+  } while (0)
+  if (d <= 64) MI_PREFILL(64);
+  else if (d <= 128) MI_PREFILL(128);
+  else MI_PREFILL(256);
+#undef MI_PREFILL
+  MI_RETURN_LAUNCH_STATUS();
+}

@@ -202,46 +202,37 @@ __global__ void rope_write_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   const float* __restrict__ inv_freq, const int* __restrict__ slot,
                                   T* __restrict__ kcache, T* __restrict__ vcache, int nq, int nkv,
                                   int d, int rot) {
-  const int t = blockIdx.x;
+  // one block per (token, head); heads are q heads, then k heads, then v heads
+  const int t = blockIdx.x, h = blockIdx.y;
   const int width = (nq + 2 * nkv) * d;
-  T* row = qkv + (size_t)t * width;
+  T* head = qkv + (size_t)t * width + (size_t)h * d;
   const int sl = (slot && kcache) ? slot[t] : -1;
   const int half = rot >> 1;
-  const int nrot_heads = nq + nkv;
-  if (half > 0) {
-    const float p = (float)pos[t];
-    int cached_i = -1;
-    float c = 1.f, s = 0.f;
-    for (int idx = threadIdx.x; idx < nrot_heads * half; idx += blockDim.x) {
-      const int h = idx / half, i = idx - h * half;
-      if (i != cached_i) {
+  if (h < nq + nkv) {
+    const bool is_k = h >= nq;
+    T* dst = (is_k && sl >= 0) ? kcache + ((size_t)sl * nkv + (h - nq)) * d : nullptr;
+    if (half > 0) {
+      const float p = (float)pos[t];
+      for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
         sincosf(p * inv_freq[i], &s, &c);
-        cached_i = i;
-      }
-      T* head = row + (size_t)h * d;
-      const float x1 = mi_to_float(head[i]);
-      const float x2 = mi_to_float(head[i + half]);
-      const T y1 = mi_from_float<T>(x1 * c - x2 * s);
-      const T y2 = mi_from_float<T>(x2 * c + x1 * s);
-      head[i] = y1;
-      head[i + half] = y2;
-      if (h >= nq && sl >= 0) {
-        T* dst = kcache + ((size_t)sl * nkv + (h - nq)) * d;
-        dst[i] = y1;
-        dst[i + half] = y2;
+        const float x1 = mi_to_float(head[i]);
+        const float x2 = mi_to_float(head[i + half]);
+        const T y1 = mi_from_float<T>(x1 * c - x2 * s);
+        const T y2 = mi_from_float<T>(x2 * c + x1 * s);
+        head[i] = y1;
+        head[i + half] = y2;
+        if (dst) {
+          dst[i] = y1;
+          dst[i + half] = y2;
+        }
       }
     }
-  }
-  if (sl >= 0) {
-    // un-rotated tail of k (rot < d) and all of v
-    const int tail = d - rot;
-    for (int idx = threadIdx.x; idx < nkv * tail; idx += blockDim.x) {
-      const int h = idx / tail, i = rot + (idx - h * tail);
-      kcache[((size_t)sl * nkv + h) * d + i] = row[(size_t)(nq + h) * d + i];
-    }
-    const T* vsrc = row + (size_t)(nq + nkv) * d;
-    T* vdst = vcache + (size_t)sl * nkv * d;
-    for (int idx = threadIdx.x; idx < nkv * d; idx += blockDim.x) vdst[idx] = vsrc[idx];
+    if (dst)  // un-rotated tail of k (rot < d)
+      for (int i = rot + threadIdx.x; i < d; i += blockDim.x) dst[i] = head[i];
+  } else if (sl >= 0) {
+    T* dst = vcache + ((size_t)sl * nkv + (h - nq - nkv)) * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = head[i];
   }
 }
 
@@ -253,15 +244,18 @@ extern "C" int mi_rope_write(void* qkv, const int* pos, const float* inv_freq, c
   if (rot < 0 || rot > d || (rot & 1)) MI_REFUSE("rope: rotary width %d must be even and <= head size %d", rot, d);
   if (rot > 0 && (!pos || !inv_freq)) MI_REFUSE("rope: positions and frequencies are required");
   if ((kcache == nullptr) != (vcache == nullptr)) MI_REFUSE("rope: key and value cache go together");
-  int work = (nq + nkv) * (rot / 2);
-  int threads = 64;
-  while (threads < 256 && threads < work) threads <<= 1;
+  const int heads = nq + nkv + (kcache ? nkv : 0);   // v heads only matter when they are stored
+  if (heads <= 0) return 0;
+  if (heads > 65535) MI_REFUSE("rope: too many heads (%d)", heads);
+  int threads = 32;
+  while (threads < 128 && threads * 2 <= d) threads <<= 1;
+  dim3 grid(M, heads);
   if (dtype == MI_DTYPE_F32)
-    rope_write_kernel<float><<<M, threads, 0, stream>>>((float*)qkv, pos, inv_freq, slot, (float*)kcache,
-                                                        (float*)vcache, nq, nkv, d, rot);
+    rope_write_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, pos, inv_freq, slot, (float*)kcache,
+                                                           (float*)vcache, nq, nkv, d, rot);
   else if (dtype == MI_DTYPE_BF16)
-    rope_write_kernel<bf16><<<M, threads, 0, stream>>>((bf16*)qkv, pos, inv_freq, slot, (bf16*)kcache,
-                                                       (bf16*)vcache, nq, nkv, d, rot);
+    rope_write_kernel<bf16><<<grid, threads, 0, stream>>>((bf16*)qkv, pos, inv_freq, slot, (bf16*)kcache,
+                                                          (bf16*)vcache, nq, nkv, d, rot);
   else
     MI_REFUSE("rope: unknown dtype %d", dtype);
   MI_RETURN_LAUNCH_STATUS();

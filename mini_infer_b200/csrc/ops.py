@@ -93,7 +93,27 @@ def _sig_sampling(lib: ctypes.CDLL) -> None:
                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
 
 
+def _sig_attention_mma(lib: ctypes.CDLL) -> None:
+    lib.mi_attention_decode.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
+        c_void_p]
+    lib.mi_attention_prefill.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+        c_float, c_int, c_void_p]
+    lib.mi_attention_prefill_tile_tokens.argtypes = [c_int]
+    lib.mi_attention_prefill_tile_tokens.restype = c_int
+
+
+def _sig_gemm_skinny(lib: ctypes.CDLL) -> None:
+    lib.mi_gemm_skinny.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                   c_int, c_void_p]
+
+
 _SIGNATURES = {
+    "gemm_skinny": _sig_gemm_skinny,
+    "attention_mma": _sig_attention_mma,
     "elementwise": _sig_elementwise,
     "gemm_f32": _sig_gemm_f32,
     "attention_generic": _sig_attention_generic,
@@ -251,18 +271,119 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
 ATTENTION_TILE_TOKENS = 16
 
 
+def prefill_tile_tokens(group: int) -> int:
+    """Tokens per tile of the tensor-core prefill kernel for ``group`` query heads per
+    key/value head: 128 rows of (token, head in group) per block (attention_mma.cu)."""
+    return 128 // min(group, 128)
+
+
+def attention_tile_sizes(group: int) -> frozenset[int]:
+    """The query tile sizes a step must plan for an attention mixer with this group size."""
+    return frozenset({ATTENTION_TILE_TOKENS, prefill_tile_tokens(group)})
+
+
+_sm_count: dict[int, int] = {}
+
+
+def _sms(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _sm_count:
+        _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_count[idx]
+
+
+def decode_splits(n_requests: int, nq: int, nkv: int, max_kv_len: int, window: int, device) -> int:
+    """How many slices of the keys each (request, key/value head) is cut into so that a
+    decode step fills the GPU (about four blocks per SM), never more than one per 64 keys."""
+    blocks = n_requests * nkv * ((nq // nkv + 15) // 16)
+    span = min(max_kv_len, window + 63) if window else max_kv_len
+    chunks = max(1, -(-span // 64))
+    return max(1, min(chunks, 64, -(-4 * _sms(device) // blocks)))
+
+
 def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq: int, nkv: int,
               head_dim: int, scale: float, window: int = 0) -> None:
     """Attention of this step's queries over one cache layer.
 
     ``cache`` is a ``LayerCache`` (its ``k``/``v`` pages and group index), ``ctx`` the
-    ``StepContext`` (block tables, lengths, query tiles).
+    ``StepContext`` (block tables, lengths, query tiles).  float32 runs the CUDA-core kernel;
+    bfloat16 runs the tensor-core kernels: split-key decode when every request brings one
+    token, the tiled prefill kernel otherwise.
     """
     group = ctx.groups[cache.group]
+    if q.dtype == torch.bfloat16:
+        if ctx.decode_only:
+            attention_decode(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
+                             ctx.q_start, ctx.kv_len, ctx.n_requests, nq, nkv, head_dim, scale, window,
+                             decode_splits(ctx.n_requests, nq, nkv, ctx.max_kv_len, window, q.device))
+        else:
+            tt = prefill_tile_tokens(nq // nkv)
+            tile_req, tile_tok0, n_tiles = ctx.q_tiles(tt)
+            attention_prefill(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
+                              ctx.q_start, ctx.q_len, ctx.kv_len, tile_req, tile_tok0, n_tiles, tt,
+                              nq, nkv, head_dim, scale, window)
+        return
     tile_req, tile_tok0, n_tiles = ctx.q_tiles(ATTENTION_TILE_TOKENS)
     attention_generic(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
                       ctx.q_start, ctx.q_len, ctx.kv_len, tile_req, tile_tok0, n_tiles,
                       nq, nkv, head_dim, scale, window)
+
+
+def _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, ints):
+    for name, t in ints:
+        if t.dtype != torch.int32:
+            raise KernelError(f"attention: {name} must be int32")
+    if kcache.dtype != q.dtype or vcache.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: q, out and caches must share a dtype")
+    if kcache.dim() != 3 or kcache.shape[1:] != (nkv, head_dim) or not kcache.is_contiguous() \
+            or vcache.shape != kcache.shape or not vcache.is_contiguous():
+        raise KernelError("attention: caches must be contiguous [slots, nkv, d]")
+    if out.dim() != 2 or out.shape[1] != nq * head_dim or not out.is_contiguous():
+        raise KernelError("attention: out must be contiguous [tokens, nq * d]")
+    if block_table.dim() != 2 or block_table.stride(1) != 1:
+        raise KernelError("attention: block_table must be [requests, pages] with unit inner stride")
+
+
+def attention_decode(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, kv_len,
+                     n_requests, nq, nkv, head_dim, scale, window=0, n_splits=1) -> None:
+    """bfloat16 decode attention: one query token per request, keys cut into ``n_splits``
+    slices whose partial results are merged through scratch memory (attention_mma.cu)."""
+    _cuda(q, out, kcache, vcache, block_table, q_start, kv_len)
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_decode: bfloat16 only")
+    _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim,
+                          (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len)))
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty((n_requests * nq * n_splits, head_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n_requests * nq * n_splits, 2), dtype=torch.float32, device=q.device)
+    lib = _lib("attention_mma")
+    rc = lib.mi_attention_decode(
+        _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_table),
+        block_table.stride(0), int(page_size), _ptr(q_start), _ptr(kv_len), int(n_requests), nq, nkv,
+        head_dim, float(scale), int(window), int(n_splits), _ptr(part_o), _ptr(part_ml), _stream())
+    _finish(lib, rc, "attention_decode")
+    if n_splits > 1:
+        global launch_count
+        launch_count += 1
+
+
+def attention_prefill(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, q_len, kv_len,
+                      tile_req, tile_tok0, n_tiles, tile_tokens, nq, nkv, head_dim, scale, window=0) -> None:
+    """bfloat16 attention of query portions of any length over the paged cache (attention_mma.cu)."""
+    _cuda(q, out, kcache, vcache, block_table, q_start, q_len, kv_len, tile_req, tile_tok0)
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill: bfloat16 only")
+    _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim,
+                          (("block_table", block_table), ("q_start", q_start), ("q_len", q_len),
+                           ("kv_len", kv_len), ("tile_req", tile_req), ("tile_tok0", tile_tok0)))
+    lib = _lib("attention_mma")
+    rc = lib.mi_attention_prefill(
+        _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_table),
+        block_table.stride(0), int(page_size), _ptr(q_start), _ptr(q_len), _ptr(kv_len), _ptr(tile_req),
+        _ptr(tile_tok0), int(n_tiles), int(tile_tokens), nq, nkv, head_dim, float(scale), int(window),
+        _stream())
+    _finish(lib, rc, "attention_prefill")
 
 
 def attention_generic(
@@ -346,6 +467,34 @@ def sample(
     return out
 
 
+SKINNY_MAX_ROWS = 16
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``x [M <= 16, K] @ w [N, K]^T`` for bfloat16 operands, streaming ``w`` once
+    (gemm_skinny.cu); the result is bfloat16 or float32."""
+    _cuda(x, w)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_skinny: operands must be bfloat16")
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1] or x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError(f"gemm_skinny: shapes {tuple(x.shape)} x {tuple(w.shape)}^T do not match")
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    lib = _lib("gemm_skinny")
+    rc = lib.mi_gemm_skinny(_ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0) if M > 1 else K,
+                            w.stride(0) if N > 1 else K, N, _code(out_dtype), _stream())
+    _finish(lib, rc, "gemm_skinny")
+    return out
+
+
+def _skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    M, K = x.shape
+    return (M <= SKINNY_MAX_ROWS and K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1
+            and (M == 1 or x.stride(0) % 8 == 0) and (w.shape[0] == 1 or w.stride(0) % 8 == 0)
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
 _MM_OUT_DTYPE: bool | None = None
 
 
@@ -353,10 +502,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     """``x [M, K] @ w [N, K]^T``.
 
     float32 operands run the true-fp32 CUDA-core kernel (never a library product, which
-    could pick a reduced-precision mode).  bfloat16 operands use the library product with
-    fp32 accumulation, as the reference does for every linear layer
-    (``distributed/linear.py:167``); ``out_dtype=float32`` keeps the accumulator's
-    precision in the result (used for logits).
+    could pick a reduced-precision mode).  bfloat16 operands with at most 16 rows (decode
+    steps) run the weight-streaming kernel of gemm_skinny.cu; larger ones use the library
+    product with fp32 accumulation, as the reference does for every linear layer
+    (``distributed/linear.py:167``).  ``out_dtype=float32`` keeps the accumulator's precision
+    in the result (used for logits).
     """
     global _MM_OUT_DTYPE, launch_count
     if x.dtype == torch.float32:
@@ -366,6 +516,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
     _cuda(x, w)
+    if out_dtype not in (None, torch.bfloat16, torch.float32):
+        raise KernelError(f"linear: unsupported output dtype {out_dtype}")
+    if _skinny_ok(x, w):
+        return gemm_skinny(x, w, out_dtype or torch.bfloat16)
     launch_count += 1
     if out_dtype in (None, torch.bfloat16):
         return torch.mm(x, w.t())

@@ -47,7 +47,8 @@ def require_cuda(device) -> torch.device:
 
 class ModelRunner:
     def __init__(self, model: DecoderModel, config: Any, *, num_blocks: int = DEFAULT_NUM_BLOCKS,
-                 block_size: int = DEFAULT_BLOCK_SIZE, max_requests: int = 64) -> None:
+                 block_size: int = DEFAULT_BLOCK_SIZE, max_requests: int = 64,
+                 cuda_graph: bool = False) -> None:
         self.model = model
         self.config = config
         self.dtype = model.dtype
@@ -56,7 +57,7 @@ class ModelRunner:
             model.cache_needs(), page_size=block_size, num_pages=num_blocks,
             max_requests=max_requests, dtype=self.dtype, device=self.device,
         )
-        self.stepper = StepRunner(model, self.cache)
+        self.stepper = StepRunner(model, self.cache, cuda_graph=cuda_graph)
         self.vocab_size = model.spec.vocab_size
         self.max_positions = model.spec.max_positions
         self.num_blocks = num_blocks
@@ -65,26 +66,30 @@ class ModelRunner:
     @classmethod
     def from_pretrained(cls, model_dir: str | os.PathLike, *, device="cuda:0", dtype="bfloat16",
                         num_blocks: int = DEFAULT_NUM_BLOCKS, block_size: int = DEFAULT_BLOCK_SIZE,
-                        max_requests: int = 64) -> "ModelRunner":
-        """Load ``config.json`` and the safetensors of a local model folder."""
+                        max_requests: int = 64, cuda_graph: bool = False) -> "ModelRunner":
+        """Load ``config.json`` and the safetensors of a local model folder.  ``cuda_graph``
+        replays decode-only steps as captured CUDA graphs (the reference's option of that name)."""
         device = require_cuda(device)
         tdtype = resolve_dtype(dtype)
         arch, cfg = load_config(model_dir)
         model = DecoderModel(arch.assemble(cfg))
         load_weights(model, model_dir, tdtype, device)
-        return cls(model, cfg, num_blocks=num_blocks, block_size=block_size, max_requests=max_requests)
+        return cls(model, cfg, num_blocks=num_blocks, block_size=block_size, max_requests=max_requests,
+                   cuda_graph=cuda_graph)
 
     @classmethod
     def from_state_dict(cls, raw_config: Mapping[str, Any], state: Mapping[str, torch.Tensor], *,
                         device="cuda:0", dtype="bfloat16", num_blocks: int = DEFAULT_NUM_BLOCKS,
-                        block_size: int = DEFAULT_BLOCK_SIZE, max_requests: int = 64) -> "ModelRunner":
+                        block_size: int = DEFAULT_BLOCK_SIZE, max_requests: int = 64,
+                        cuda_graph: bool = False) -> "ModelRunner":
         """Build from a raw configuration mapping and tensors already in memory."""
         device = require_cuda(device)
         tdtype = resolve_dtype(dtype)
         arch, cfg = load_config(raw_config)
         model = DecoderModel(arch.assemble(cfg))
         bind_state_dict(model, dict(state), tdtype, device)
-        return cls(model, cfg, num_blocks=num_blocks, block_size=block_size, max_requests=max_requests)
+        return cls(model, cfg, num_blocks=num_blocks, block_size=block_size, max_requests=max_requests,
+                   cuda_graph=cuda_graph)
 
     # -- requests -----------------------------------------------------------------------
 

@@ -17,6 +17,7 @@ from typing import Hashable, Sequence
 import torch
 
 from ..cache.manager import AppendPlan, CacheManager
+from ..csrc import ops
 from ..parts.base import GroupView, LayerCache, StepContext
 from ..parts.model import DecoderModel
 
@@ -41,10 +42,32 @@ class StepResult:
     rows: list[tuple[Hashable, int]]  # (request, index within its tokens) of every logits row
 
 
+@dataclass
+class GraphSlot:
+    """A captured decode step: the CUDA graph, its fixed descriptor buffer and its logits."""
+
+    widths: list[int]                 # block-table width (pages) per cache group
+    device_buffer: torch.Tensor       # int32 descriptors at fixed addresses
+    graph: "torch.cuda.CUDAGraph | None" = None
+    logits: torch.Tensor | None = None
+    ctx: StepContext | None = None
+    replays: int = 0
+    launches: int = 0                 # kernels recorded in the graph
+
+
 class StepRunner:
-    def __init__(self, model: DecoderModel, cache: CacheManager) -> None:
+    """``cuda_graph=True`` replays decode-only steps (every request brings one token and
+    wants its logits) as captured CUDA graphs, one per (batch size, block-table width
+    bucket); the reference keeps such graphs per batch bucket
+    (``engine/paged_decode_graph.py:67-225``).  Everything else runs kernel by kernel."""
+
+    GRAPH_WIDTH_BUCKET = 64           # block tables of a captured step grow in steps of 64 pages
+
+    def __init__(self, model: DecoderModel, cache: CacheManager, cuda_graph: bool = False) -> None:
         self.model = model
         self.cache = cache
+        self.cuda_graph = cuda_graph
+        self._graphs: dict[tuple, GraphSlot] = {}
         self.device = model.device
         self.dtype = model.dtype
         self.vocab_size = model.spec.vocab_size
@@ -74,8 +97,12 @@ class StepRunner:
                         f"request {e.rid!r} would pass the model's {self.max_positions} positions"
                     )
 
-    def plan(self, entries: Sequence[StepEntry]) -> tuple[StepContext, list[LayerCache], torch.Tensor | None, list]:
-        """Reserve pages and build the step's descriptors on the device."""
+    def plan(self, entries: Sequence[StepEntry], graphed: bool = False):
+        """Reserve pages and build the step's descriptors on the device.
+
+        With ``graphed`` the descriptors get a layout that depends only on the batch size
+        and the (bucketed) block-table widths, and are copied into that layout's fixed
+        device buffer; the matching ``GraphSlot`` is returned as a fifth value."""
         self._validate(entries)
         plan: AppendPlan = self.cache.plan_append([(e.rid, len(e.tokens)) for e in entries])
         B = len(entries)
@@ -105,6 +132,8 @@ class StepRunner:
         widths: list[int] = []
         for gi in range(len(self.cache.groups)):
             width = max(1, max(len(t) for t in plan.tables[gi]))
+            if graphed:
+                width = -(-width // self.GRAPH_WIDTH_BUCKET) * self.GRAPH_WIDTH_BUCKET
             widths.append(width)
             flat: list[int] = []
             for t in plan.tables[gi]:
@@ -135,7 +164,18 @@ class StepRunner:
             o, n = offsets[name]
             if n:
                 host_np[o:o + n] = lst
-        dev = host.to(self.device, non_blocking=True)
+        slot = None
+        if graphed:
+            key = (B, tuple(widths))
+            slot = self._graphs.get(key)
+            if slot is None:
+                slot = GraphSlot(widths=list(widths),
+                                 device_buffer=torch.empty(host.numel(), dtype=torch.int32, device=self.device))
+                self._graphs[key] = slot
+            dev = slot.device_buffer
+            dev.copy_(host, non_blocking=True)
+        else:
+            dev = host.to(self.device, non_blocking=True)
         self.last_h2d_bytes = host.numel() * 4
 
         def view(name: str) -> torch.Tensor:
@@ -155,7 +195,10 @@ class StepRunner:
             host_q_start=q_start, host_q_len=list(q_len), host_kv_len=kv_len,
             host_state_slot=list(plan.state_slots), groups=groups,
             tiles={n: (view(f"tile_req{n}"), view(f"tile_tok{n}"), tile_counts[n]) for n in self.tile_sizes},
-            decode_only=all(n == 1 for n in q_len), max_kv_len=max(kv_len),
+            decode_only=all(n == 1 for n in q_len),
+            # a captured step must not depend on the lengths of the day: it is planned for
+            # the longest context its block tables can hold
+            max_kv_len=(max(widths) * self.cache.page_size) if graphed else max(kv_len),
         )
         caches: list[LayerCache] = []
         for entry in self.model.schedule:
@@ -165,13 +208,43 @@ class StepRunner:
             lc.state = self.cache.layer_state(entry.cache)
             caches.append(lc)
         want = view("want_rows") if want_rows else None
+        if graphed:
+            return ctx, caches, want, rows, slot
         return ctx, caches, want, rows
 
     # ------------------------------------------------------------------ running
 
+    def _graphable(self, entries: Sequence[StepEntry]) -> bool:
+        return self.cuda_graph and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+
     @torch.inference_mode()
     def step(self, entries: Sequence[StepEntry]) -> StepResult:
+        if self._graphable(entries):
+            return self._graphed_step(entries)
         ctx, caches, want, rows = self.plan(entries)
         logits = self.model.forward(ctx, caches, want, len(rows))
         self.steps_run += 1
         return StepResult(logits=logits, rows=rows)
+
+    def _graphed_step(self, entries: Sequence[StepEntry]) -> StepResult:
+        """Replay (first: capture) the CUDA graph of a decode-only step.  The logits live in
+        the graph's own memory and are overwritten by the next replay of the same graph."""
+        ctx, caches, want, rows, slot = self.plan(entries, graphed=True)
+        if slot.graph is None:
+            # run once kernel by kernel (compiles and configures every kernel), then capture
+            # the same launches; both read the descriptors just copied into the fixed buffer
+            # and write this step's keys and values to the same slots, so repeating is harmless
+            self.model.forward(ctx, caches, want, len(rows))
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count
+            with torch.cuda.graph(graph):
+                slot.logits = self.model.forward(ctx, caches, want, len(rows))
+            slot.launches = ops.launch_count - before
+            ops.launch_count = before
+            slot.graph, slot.ctx = graph, ctx
+        slot.graph.replay()
+        ops.launch_count += slot.launches
+        slot.replays += 1
+        self.steps_run += 1
+        return StepResult(logits=slot.logits, rows=rows)

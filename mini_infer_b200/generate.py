@@ -53,6 +53,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens-per-step", type=int, default=2048)
     ap.add_argument("--decode-headroom-blocks", type=int, default=8)
     ap.add_argument("--eos-token-id", type=int, action="append", default=[])
+    ap.add_argument("--cuda-graph", action="store_true", help="replay decode-only steps as CUDA graphs")
     ap.add_argument("--trace-out", help="write a Chrome trace of the engine steps here")
     args = ap.parse_args(argv)
     if not args.model:
@@ -72,7 +73,7 @@ def main(argv=None) -> int:
 
     runner = ModelRunner.from_pretrained(args.model, device=args.device, dtype=args.dtype,
                                          num_blocks=args.num_blocks, block_size=args.block_size,
-                                         max_requests=args.max_concurrent)
+                                         max_requests=args.max_concurrent, cuda_graph=args.cuda_graph)
     tokenizer = None
     if args.prompt:
         from .engine.tokenizer import Tokenizer

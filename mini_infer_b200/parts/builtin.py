@@ -182,7 +182,7 @@ class GroupedQueryAttention(Mixer):
         return KVNeed(self.nkv, self.d, self.window)
 
     def plan_needs(self):
-        return PlanNeeds(frozenset({ops.ATTENTION_TILE_TOKENS}))
+        return PlanNeeds(ops.attention_tile_sizes(self.nq // self.nkv))
 
     def bind(self, tensors, dtype, device):
         qkv = torch.cat(

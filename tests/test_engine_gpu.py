@@ -144,7 +144,7 @@ def test_attention_part_alone_in_portions(dtype):
     rope.bind({}, dtype, torch.device(DEV))
     need = SimpleNamespace(index=0, kv=mixer.cache_need(), state=None)
     cache = CacheManager([need], page_size=4, num_pages=16, max_requests=1, dtype=dtype, device=DEV)
-    runner = stub_runner(cache, dtype)
+    runner = stub_runner(cache, dtype, tile_sizes=mixer.plan_needs().q_tile_tokens)
     x = (torch.randn(Tn, H, generator=g)).to(torch.bfloat16)
     cache.add_request("r")
     outs, pos = [], 0

@@ -165,6 +165,32 @@ def test_gemm_f32_is_not_reduced_precision():
     assert ops().gemm_f32(a, w).item() == 2.0 ** -20
 
 
+# ----------------------------------------------------------------------------- bf16 product, few rows
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 1000, 64), (3, 50, 176), (8, 4096, 4096), (9, 320, 192), (16, 513, 4104),
+                                   (5, 128256, 256), (8, 16, 8)])
+def test_gemm_skinny(M, N, K, out_dtype):
+    x = rnd(M, K, dtype=torch.bfloat16, seed=20)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=21, scale=0.1)
+    out = ops().gemm_skinny(x.to(DEV), w.to(DEV), out_dtype)
+    want = x.double() @ w.double().T
+    bound = (1e-5 if out_dtype == torch.float32 else 1 / 128) * max(1.0, want.abs().max().item())
+    assert out.dtype == out_dtype
+    assert (out.cpu().double() - want).abs().max().item() <= bound
+
+
+def test_linear_picks_a_kernel_by_shape_and_agrees():
+    w = rnd(300, 264, dtype=torch.bfloat16, seed=22, scale=0.1).to(DEV)
+    x = rnd(40, 264, dtype=torch.bfloat16, seed=23).to(DEV)
+    big = ops().linear(x, w).float()              # library product
+    small = torch.cat([ops().linear(x[i:i + 8].contiguous(), w).float() for i in range(0, 40, 8)])
+    assert (big - small).abs().max().item() <= 1 / 64 * max(1.0, big.abs().max().item())
+    assert ops().linear(x[:4].contiguous(), w, out_dtype=torch.float32).dtype == torch.float32
+    assert ops().linear(x, w, out_dtype=torch.float32).dtype == torch.float32
+
+
 # ----------------------------------------------------------------------------- attention
 
 
@@ -191,7 +217,8 @@ def build_paged(kv_lens, nkv, d, page, dtype, seed, n_extra_pages=3):
     return kc, vc, bt, ks, vs
 
 
-def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, boost=None):
+def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, boost=None, kernel="generic",
+                  n_splits=1):
     o = ops()
     kc, vc, bt, ks, vs = build_paged(kv_lens, nkv, d, page, dtype, seed)
     M = sum(q_lens)
@@ -200,7 +227,7 @@ def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, bo
     if boost is not None:
         boost(q, ks, kc, bt)
     q_start = [sum(q_lens[:i]) for i in range(len(q_lens))]
-    T_ = o.ATTENTION_TILE_TOKENS
+    T_ = o.ATTENTION_TILE_TOKENS if kernel == "generic" else o.prefill_tile_tokens(nq // nkv)
     treq = [i for i, n in enumerate(q_lens) for _ in range(0, n, T_)]
     ttok = [t0 for n in q_lens for t0 in range(0, n, T_)]
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
@@ -209,9 +236,18 @@ def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, bo
     wide[:, : nq * d] = q.view(M, nq * d)
     wide = wide.to(DEV)
     out = torch.full((M, nq * d), float("nan"), dtype=dtype, device=DEV)
-    o.attention_generic(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), page, i32(q_start),
-                        i32(q_lens), i32(kv_lens), i32(treq), i32(ttok), len(treq), nq, nkv, d,
-                        1.0 / math.sqrt(d), window)
+    scale = 1.0 / math.sqrt(d)
+    if kernel == "generic":
+        o.attention_generic(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), page, i32(q_start),
+                            i32(q_lens), i32(kv_lens), i32(treq), i32(ttok), len(treq), nq, nkv, d, scale, window)
+    elif kernel == "prefill":
+        o.attention_prefill(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), page, i32(q_start),
+                            i32(q_lens), i32(kv_lens), i32(treq), i32(ttok), len(treq), T_, nq, nkv, d, scale,
+                            window)
+    else:
+        assert all(n == 1 for n in q_lens)
+        o.attention_decode(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), page, i32(q_start),
+                           i32(kv_lens), len(q_lens), nq, nkv, d, scale, window, n_splits)
     want = torch.empty(M, nq, d, dtype=torch.float64)
     for i, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
         want[q_start[i]:q_start[i] + ql] = P.causal_attention(
@@ -251,6 +287,58 @@ def test_attention_finds_a_far_key_among_hundreds(dtype):
             q[-1, :, 0] = 40.0
         got, want = run_attention([1], [704], nq, nkv, d, page, dtype, seed=5, boost=boost)
         assert (got - want).abs().max().item() <= tol(dtype, fp32=2e-5, bf16=1 / 64)
+
+
+BF16_BOUND = 1 / 64      # probabilities and outputs are rounded to bfloat16 (2^-9 each)
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(6, 2, 48, 8), (4, 4, 16, 16), (32, 8, 128, 16), (3, 1, 256, 4),
+                                            (10, 5, 80, 32), (40, 2, 64, 16), (70, 1, 32, 16)])
+def test_attention_prefill_tensor_cores(nq, nkv, d, page):
+    q_lens = [1, 5, 37, 1, 16, 130]
+    kv_lens = [1, 5, 100, 131, 16, 257]
+    got, want = run_attention(q_lens, kv_lens, nq, nkv, d, page, torch.bfloat16, seed=nq, kernel="prefill")
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max().item() <= BF16_BOUND
+
+
+@pytest.mark.parametrize("window", [1, 7, 20, 64, 100])
+def test_attention_prefill_tensor_cores_window(window):
+    got, want = run_attention([1, 90, 3, 150], [90, 170, 3, 150], 4, 2, 32, 8, torch.bfloat16, window=window,
+                              seed=3, kernel="prefill")
+    assert (got - want).abs().max().item() <= BF16_BOUND
+
+
+@pytest.mark.parametrize("n_splits", [1, 2, 5, 64])
+@pytest.mark.parametrize("nq,nkv,d,page", [(32, 8, 128, 16), (6, 2, 48, 8), (3, 3, 16, 4), (40, 2, 64, 16), (5, 1, 256, 16)])
+def test_attention_decode_split_keys(nq, nkv, d, page, n_splits):
+    kv_lens = [1, 64, 65, 700, 17, 2048 if d <= 128 else 300]
+    got, want = run_attention([1] * len(kv_lens), kv_lens, nq, nkv, d, page, torch.bfloat16, seed=nq + 7,
+                              kernel="decode", n_splits=n_splits)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max().item() <= BF16_BOUND
+
+
+@pytest.mark.parametrize("window", [1, 30, 64, 200])
+def test_attention_decode_window(window):
+    got, want = run_attention([1, 1, 1], [500, 64, 7], 8, 2, 64, 16, torch.bfloat16, window=window, seed=9,
+                              kernel="decode", n_splits=4)
+    assert (got - want).abs().max().item() <= BF16_BOUND
+
+
+@pytest.mark.parametrize("kernel,n_splits", [("prefill", 1), ("decode", 1), ("decode", 7)])
+def test_tensor_core_attention_finds_a_far_key(kernel, n_splits):
+    nq, nkv, d, page = 4, 1, 32, 16
+    for target in (0, 15, 16, 63, 64, 257, 700, 703):
+        def boost(q, ks, kc, bt, target=target):
+            ks[0][target] = 0
+            ks[0][target, 0, 0] = 8.0
+            kc[bt[0, target // page] * page + target % page] = ks[0][target]
+            q[-1] = 0
+            q[-1, :, 0] = 40.0
+        got, want = run_attention([1], [704], nq, nkv, d, page, torch.bfloat16, seed=5, boost=boost,
+                                  kernel=kernel, n_splits=n_splits)
+        assert (got - want).abs().max().item() <= BF16_BOUND
 
 
 def test_attention_refuses_bad_head_size():

@@ -139,3 +139,27 @@ def test_out_of_pages_changes_nothing(model_dirs):
     assert runner.cache.length("a") == 30 and runner.cache.length("b") == 0
     assert runner.cache.num_free_pages() == 1
     runner.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_decode_steps_match_plain(dtype, model_dirs, plain):
+    """With cuda_graph on, single-token steps replay captured CUDA graphs (one per batch
+    size and block-table width); prompt portions and mixed steps still run kernel by kernel."""
+    from mini_infer_b200.engine import ModelRunner
+
+    which = "B"
+    requests = requests_for(which)
+    steps = T.cut_mixed(requests, n_decode=40)
+    ps = PAGE_SIZE[which]
+    runner = ModelRunner.from_pretrained(model_dirs[which], dtype=dtype, block_size=ps,
+                                         num_blocks=T.max_tokens_needed(steps) // ps, max_requests=4,
+                                         cuda_graph=True)
+    got = T.collect(steps, T.replay_in_process(runner, steps), TINY[which]["vocab_size"])
+    assert sum(slot.replays for slot in runner.stepper._graphs.values()) >= 20
+    assert len(runner.stepper._graphs) >= 2          # several batch sizes were captured
+    want = plain[which]
+    scale = max(1.0, max(float(np.abs(want[r]).max()) for r in want))
+    for rid in requests:
+        bad = T.first_bad(got[rid], want[rid], TOL[dtype] * scale)
+        assert bad is None, f"{dtype}: request {rid} first differs at position {bad}"
+    runner.cache.check()
