@@ -246,7 +246,7 @@ def time_e2e(runner, batch: int, context: int, steps: int, warmup: int) -> dict:
                                 max_tokens_per_step=max(context, batch), decode_headroom_blocks=0)
     for _ in range(batch):
         prompt = torch.randint(0, runner.vocab_size, (context,), generator=gen).tolist()
-        sched.submit(Request(prompt, SamplingParams(), max_tokens=steps + warmup + 4))
+        sched.submit(Request(prompt, SamplingParams(), max_tokens=steps + warmup + 2 * batch + 8))
     while sched.has_prefill_work():
         sched.step()
     for _ in range(warmup):
@@ -300,7 +300,7 @@ def main() -> int:
     cfg, layers, batch = LLAMA_8B, args.layers, args.batch
     peaks = load_peaks()
     max_batch = batch if args.skip_points else max(batch, 64)
-    tokens_cap = max_batch * (CONTEXT + args.steps + warmup + 64)
+    tokens_cap = max_batch * (CONTEXT + args.steps + warmup + 2 * batch + 64)
     runner = build_runner(cfg, layers, num_blocks=tokens_cap // PAGE + 8, max_requests=max_batch)
 
     clocks = ClockSampler()

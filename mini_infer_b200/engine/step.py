@@ -68,6 +68,7 @@ class StepRunner:
         self.cache = cache
         self.cuda_graph = cuda_graph
         self._graphs: dict[tuple, GraphSlot] = {}
+        self._layer_caches: list[LayerCache] | None = None
         self.device = model.device
         self.dtype = model.dtype
         self.vocab_size = model.spec.vocab_size
@@ -200,13 +201,16 @@ class StepRunner:
             # the longest context its block tables can hold
             max_kv_len=(max(widths) * self.cache.page_size) if graphed else max(kv_len),
         )
-        caches: list[LayerCache] = []
-        for entry in self.model.schedule:
-            lc = LayerCache(writes=entry.writes_cache)
-            if entry.cache in self.cache.layer_place:
-                lc.group, lc.k, lc.v = self.cache.layer_kv(entry.cache)
-            lc.state = self.cache.layer_state(entry.cache)
-            caches.append(lc)
+        if self._layer_caches is None:     # the views never change: build them once
+            caches: list[LayerCache] = []
+            for entry in self.model.schedule:
+                lc = LayerCache(writes=entry.writes_cache)
+                if entry.cache in self.cache.layer_place:
+                    lc.group, lc.k, lc.v = self.cache.layer_kv(entry.cache)
+                lc.state = self.cache.layer_state(entry.cache)
+                caches.append(lc)
+            self._layer_caches = caches
+        caches = self._layer_caches
         want = view("want_rows") if want_rows else None
         if graphed:
             return ctx, caches, want, rows, slot

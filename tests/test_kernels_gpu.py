@@ -181,11 +181,29 @@ def test_gemm_skinny(M, N, K, out_dtype):
     assert (out.cpu().double() - want).abs().max().item() <= bound
 
 
-def test_linear_picks_a_kernel_by_shape_and_agrees():
+@pytest.mark.parametrize("k_slices", [1, 2, 3, 7])
+def test_gemm_skinny_k_slices_agree(k_slices):
+    """Cutting K across blocks (partial sums in scratch memory, the last block adds them up)
+    gives the same result on every call, whatever the arrival order."""
+    M, N, K = 8, 200, 14336
+    x = rnd(M, K, dtype=torch.bfloat16, seed=24).to(DEV)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=25, scale=0.05).to(DEV)
+    want = x.double().cpu() @ w.double().cpu().T
+    first = ops().gemm_skinny(x, w, torch.float32, k_slices=k_slices)
+    assert (first.cpu().double() - want).abs().max().item() <= 1e-4 * max(1.0, want.abs().max().item())
+    for _ in range(5):
+        assert torch.equal(ops().gemm_skinny(x, w, torch.float32, k_slices=k_slices), first)
+
+
+def test_linear_library_and_streaming_kernels_agree():
     w = rnd(300, 264, dtype=torch.bfloat16, seed=22, scale=0.1).to(DEV)
     x = rnd(40, 264, dtype=torch.bfloat16, seed=23).to(DEV)
     big = ops().linear(x, w).float()              # library product
-    small = torch.cat([ops().linear(x[i:i + 8].contiguous(), w).float() for i in range(0, 40, 8)])
+    ops().USE_SKINNY_GEMM = True
+    try:
+        small = torch.cat([ops().linear(x[i:i + 8].contiguous(), w).float() for i in range(0, 40, 8)])
+    finally:
+        ops().USE_SKINNY_GEMM = False
     assert (big - small).abs().max().item() <= 1 / 64 * max(1.0, big.abs().max().item())
     assert ops().linear(x[:4].contiguous(), w, out_dtype=torch.float32).dtype == torch.float32
     assert ops().linear(x, w, out_dtype=torch.float32).dtype == torch.float32
