@@ -636,3 +636,52 @@ extern "C" int mi_attention_prefill(const void* q, int q_stride, void* out, int 
 #undef MI_PREFILL
   MI_RETURN_LAUNCH_STATUS();
 }
+
+// ------------------------------------------------------------------------------- no allocation
+//
+// The same decode attention with the split-merge scratch in a static device array, for
+// callers that cannot allocate (see attention_noalloc.h).
+
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[MI_ATTENTION_NOALLOC_MAX_FLOATS];
+
+// In host code `g_noalloc_scratch` is only a handle; the address a kernel can use has to be
+// asked for, once per device, with that device current.
+#define MI_NOALLOC_MAX_DEVICES 64
+static float* g_noalloc_device_ptr[MI_NOALLOC_MAX_DEVICES];
+
+extern "C" int mi_attention_decode_noalloc(const void* q, int q_stride, void* out, int out_stride,
+                                           const void* kcache, const void* vcache, const int* block_table,
+                                           int bt_stride, int page_size, const int* q_start, const int* kv_len,
+                                           int B, int nq, int nkv, int d, float scale, int window, int n_splits,
+                                           cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (nq <= 0 || d <= 0 || n_splits < 1) MI_REFUSE("attention (no allocation): bad sizes");
+  const size_t slots = (size_t)B * nq * n_splits;
+  const size_t need = slots * ((size_t)d + 2);
+  if (need > (size_t)MI_ATTENTION_NOALLOC_MAX_FLOATS)
+    MI_REFUSE("attention (no allocation): %zu floats of scratch needed (B=%d, heads=%d, slices=%d, head size=%d), "
+              "the built-in array holds %d",
+              need, B, nq, n_splits, d, MI_ATTENTION_NOALLOC_MAX_FLOATS);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    snprintf(g_mi_error, sizeof(g_mi_error), "CUDA: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  if (dev < 0 || dev >= MI_NOALLOC_MAX_DEVICES) MI_REFUSE("attention (no allocation): device %d is out of range", dev);
+  if (g_noalloc_device_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      snprintf(g_mi_error, sizeof(g_mi_error), "CUDA: cannot resolve the scratch array: %s", cudaGetErrorString(e));
+      return e != cudaSuccess ? (int)e : MI_REFUSED;
+    }
+    g_noalloc_device_ptr[dev] = p;
+  }
+  float* part_o = g_noalloc_device_ptr[dev];
+  float* part_ml = part_o + slots * (size_t)d;
+  return mi_attention_decode(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride, page_size,
+                             q_start, kv_len, B, nq, nkv, d, scale, window, n_splits, part_o, part_ml, stream);
+}

@@ -35,7 +35,7 @@ LIBRARIES: dict[str, tuple[list[str], list[str], list[str]]] = {
     "gemm_f32": (["gemm_f32.cu"], ["common.cuh"], []),
     "attention_generic": (["attention_generic.cu"], ["common.cuh"], []),
     "sampling": (["sampling.cu"], ["common.cuh"], []),
-    "attention_mma": (["attention_mma.cu"], ["common.cuh"], []),
+    "attention_mma": (["attention_mma.cu"], ["common.cuh", "attention_noalloc.h"], []),
     "gemm_skinny": (["gemm_skinny.cu"], ["common.cuh"], []),
 }
 
