@@ -263,16 +263,117 @@ def time_e2e(runner, batch: int, context: int, steps: int, warmup: int) -> dict:
 
 
 def reference_arm(args) -> int:
+    """The unmodified reference (installed under baseline/_ref) on the same metric: its own
+    ``LlamaForCausalLM`` with random bf16 weights at the same sizes, its ``BlockPool`` /
+    ``PagedKVCache``, its ``ModelRunner.forward_step_packed`` with its decode CUDA graph and
+    FlashInfer attention where this process can run them (its published configuration), and
+    its ``sample_tokens``.  Nothing of this repository's engine is on that path."""
     ref = os.path.join(ROOT, "baseline", "_ref")
     line = {"impl": "reference"}
     if not os.path.isdir(os.path.join(ref, "mini_infer")):
-        line["unavailable"] = ("the reference is not installed under baseline/_ref: its build backend "
-                               "(hatchling) is not in the offline wheelhouse")
+        line["unavailable"] = ("the reference is not installed under baseline/_ref (its build backend, "
+                               "hatchling, is not in the offline wheelhouse)")
         print(json.dumps(line))
         return 0
-    line["unavailable"] = "the reference arm is not wired up yet"
+    try:
+        line.update(_reference_measure(args, ref))
+    except Exception as e:  # noqa: BLE001  (any failure of the reference is reported, not raised)
+        line = {"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:300]}".replace("\n", " ")}
     print(json.dumps(line))
     return 0
+
+
+def _reference_measure(args, ref: str) -> dict:
+    os.environ.setdefault("HF_HUB_OFFLINE", "1")
+    os.environ.setdefault("TRANSFORMERS_OFFLINE", "1")
+    sys.path.insert(0, ref)
+    from types import SimpleNamespace
+
+    import torch
+    from mini_infer.cache.block_pool import BlockPool
+    from mini_infer.cache.packed_attention import effective_attention_backend
+    from mini_infer.cache.paged_kv_cache import PagedKVCache
+    from mini_infer.engine.model_runner import ModelRunner
+    from mini_infer.engine.sampler import SamplingParams, sample_tokens
+    from mini_infer.models.llama.llama import LlamaConfig, LlamaForCausalLM
+
+    warmup = max(3, args.warmup)
+    batch, steps, layers = args.batch, args.steps, args.layers
+    raw = dict(LLAMA_8B, num_hidden_layers=layers)
+    cfg = LlamaConfig.from_hf(SimpleNamespace(**raw))
+    torch.manual_seed(0)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device("cuda"):
+            model = LlamaForCausalLM(cfg)
+    finally:
+        torch.set_default_dtype(prev)
+    model = model.to(device="cuda", dtype=torch.bfloat16).eval()
+    with torch.no_grad():      # the engine's own arm uses N(0, 0.02) weights; values do not change the work
+        for prm in model.parameters():
+            if prm.dim() == 2:
+                prm.normal_(0.0, 0.02)
+    backend = "flashinfer" if effective_attention_backend("flashinfer", "cuda", None) == "flashinfer" else "flash_attn"
+    tokens_cap = batch * (CONTEXT + steps + warmup + 64)
+    pool = BlockPool(num_blocks=tokens_cap // PAGE + 8, block_size=PAGE, num_layers=cfg.num_hidden_layers,
+                     num_kv_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim, dtype=torch.bfloat16,
+                     device="cuda", attention_backend=backend)
+    runner = ModelRunner(model=model, tokenizer=None, device="cuda", block_pool=pool)
+    graph = False
+    if backend == "flashinfer":
+        runner.enable_decode_graph()
+        graph = True
+    cache = PagedKVCache(pool)
+    for _ in range(batch):
+        cache.add_request_slot()
+    gen = torch.Generator().manual_seed(3)
+    chunk = 256                                     # the reference's default prompt portion
+    prompts = [torch.randint(0, cfg.vocab_size, (CONTEXT,), generator=gen).tolist() for _ in range(batch)]
+    for s0 in range(0, CONTEXT, chunk):             # every request brings one portion per step
+        ids = [t for p in prompts for t in p[s0:s0 + chunk]]
+        runner.forward_step_packed(cache, ids, [chunk * i for i in range(batch + 1)], cache.seq_lens_list(),
+                                   last_rows_only=True)
+    params = [SamplingParams()] * batch
+    cu = list(range(batch + 1))
+
+    def one(ids):
+        logits = runner.forward_step_packed(cache, ids, cu, cache.seq_lens_list(), last_rows_only=True)
+        return sample_tokens(logits[0].float(), params)
+
+    ids = torch.randint(0, cfg.vocab_size, (batch,), generator=gen).tolist()
+    clocks = ClockSampler()
+    clocks.start()
+    for _ in range(warmup):
+        one(ids)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one(ids)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    # end to end: host ids in, sampled ids read back every step
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ids = one(ids).tolist()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    value = batch * 1000.0 / ms
+    return {
+        "metric": "decode tok/s @ batch 8, 2048-token context (Llama 3.1 8B layer sizes)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(value / BASELINE_DECODE_TOK_S, 3), "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "Llama-3.1-8B sizes, random weights", "layers": layers,
+                   "layers_of_model": LLAMA_8B["num_hidden_layers"], "global_batch": batch, "seq_len": CONTEXT,
+                   "page_size": PAGE, "attention_backend": backend, "cuda_graph": graph,
+                   "parallelism": "single GPU", "l2": "inputs (weights) larger than L2, no flush"},
+        "e2e": {"value": round(batch * steps / dt, 2), "unit": "tokens/s", "ms_per_step": round(1000.0 * dt / steps, 3),
+                "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 8 * batch},
+        "clocks": clocks.stop(),
+    }
 
 
 def main() -> int:

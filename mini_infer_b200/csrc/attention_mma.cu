@@ -5,7 +5,7 @@
 // Two kernels share the machinery:
 //
 //   decode   every request brings one query token.  A block takes one request, one group
-//            of up to 16 query heads that share a key/value head, and one slice of the
+//            of up to 8 query heads that share a key/value head, and one slice of the
 //            keys ("split"); its 4 warps take 16 keys each of every 64-key chunk, keep an
 //            online softmax of their own and are merged at the end.  With more than one
 //            split the block writes an unnormalised partial result (fp32) and its
@@ -111,6 +111,15 @@ __device__ __forceinline__ void load_kv_chunk(bf16* kdst, bf16* vdst, const bf16
 }
 
 // ------------------------------------------------------------------------------- decode
+//
+// Keys sit on the M side of the first product: S[16 keys x 8 heads] = K[16 x d] * Q^T[d x 8],
+// so every MMA row is a real key whatever the group size (query heads would fill only a few
+// of 16 rows).  Q fragments stay in registers for the whole kernel.  The second product is
+// O^T[d x 8 heads] += V^T[d x 16 keys] * P[16 keys x 8 heads]; V^T comes from ldmatrix.trans,
+// and P is moved from the accumulator layout (lane holds keys q, q+8 of heads 2t, 2t+1) to the
+// B-operand layout (lane holds keys 2t, 2t+1, 2t+8, 2t+9 of head q) with four shuffles.
+
+#define DEC_HEADS 8   // query heads of one key/value head handled by a block
 
 template <int DMAX>
 __global__ void __launch_bounds__(NTHREADS)
@@ -122,16 +131,15 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                         float* __restrict__ part_ml) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int sd = d + 8;  // row stride in elements: 16 bytes of padding keep ldmatrix conflict-free
-  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [16][sd]
-  bf16* Ks = Qs + 16 * sd;                               // [2][64][sd]
+  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);          // [2][64][sd]
   bf16* Vs = Ks + 2 * KCHUNK * sd;                       // [2][64][sd]
-  float* merge_o = reinterpret_cast<float*>(Ks);         // [4][16][d] after the main loop
-  __shared__ float merge_m[4][16], merge_l[4][16];
+  float* merge_o = reinterpret_cast<float*>(smem_raw);   // [4][8][d] after the main loop
+  __shared__ float merge_m[4][DEC_HEADS], merge_l[4][DEC_HEADS];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int qd = lane >> 2, t4 = lane & 3;
   const int g = nq / nkv;
-  const int hblocks = (g + 15) >> 4;
+  const int hblocks = (g + DEC_HEADS - 1) / DEC_HEADS;
   const int split = blockIdx.x;
   const int kvh = blockIdx.y / hblocks, hb = blockIdx.y - kvh * hblocks;
   const int b = blockIdx.z;
@@ -142,8 +150,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
   const int per_split = (c_end - c_first + n_splits - 1) / n_splits;
   const int c0 = c_first + split * per_split;
   const int c1 = min(c_end, c0 + per_split);
-  const int heads_here = min(16, g - hb * 16);
-  const int head0 = kvh * g + hb * 16;
+  const int heads_here = min(DEC_HEADS, g - hb * DEC_HEADS);
+  const int head0 = kvh * g + hb * DEC_HEADS;
   const int* table = block_table + (size_t)b * bt_stride;
 
   if (c0 >= c1) {  // nothing for this split (only possible with n_splits > 1)
@@ -155,23 +163,33 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     return;
   }
 
-  const int units = d >> 3;
-  for (int idx = tid; idx < 16 * units; idx += NTHREADS) {
-    const int r = idx / units, u = idx - r * units;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (r < heads_here) v = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (size_t)(head0 + r) * d + u * 8);
-    *reinterpret_cast<uint4*>(Qs + r * sd + u * 8) = v;
-  }
-
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  float o[DMAX / 8][4];
-#pragma unroll
-  for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  const float sc = scale * LOG2E;
-  const int ksteps = d >> 4;
-
   load_kv_chunk<NTHREADS>(Ks, Vs, kcache, vcache, table, page_size, page_shift, c0, lo, kl, nkv, kvh, d, sd);
   cp_async_commit();
+
+  // Q as the B operand: lane (qd, t4) holds head qd, dims ks*16 + 2*t4 + {0,1} and + 8
+  const int ksteps = d >> 4;
+  uint32_t qb[DMAX / 16][2];
+  {
+    const bf16* qrow = q + (size_t)tok * q_stride + (size_t)(head0 + qd) * d;
+#pragma unroll
+    for (int ks = 0; ks < DMAX / 16; ++ks) {
+      qb[ks][0] = qb[ks][1] = 0u;
+      if (ks < ksteps && qd < heads_here) {
+        qb[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
+        qb[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t4);
+      }
+    }
+  }
+
+  // this lane's heads are 2*t4 and 2*t4 + 1
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[DMAX / 16][4];   // O^T: dims dt*16 + qd (+8), heads 2*t4 (+1)
+#pragma unroll
+  for (int i = 0; i < DMAX / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const float sc = scale * LOG2E;
+  // lanes that hold what this lane needs of P: keys 2*t4 and 2*t4 + 1, heads qd (pair qd / 2)
+  const int src0 = (2 * t4) * 4 + (qd >> 1), src1 = (2 * t4 + 1) * 4 + (qd >> 1);
+  const bool odd_head = qd & 1;
 
   for (int c = c0; c < c1; ++c) {
     const int buf = (c - c0) & 1;
@@ -188,57 +206,57 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     const bf16* Vb = Vs + buf * KCHUNK * sd + (warp * 16) * sd;
     const int key0 = c * KCHUNK + warp * 16;
     if (key0 < kl && key0 + 16 > lo) {  // warp-uniform: this warp's 16 keys hold something visible
-      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ks = 0; ks < DMAX / 16; ++ks) {
         if (ks < ksteps) {
-          uint32_t a[4], kb[4];
-          ldmatrix_x4(a, Qs + (lane & 15) * sd + ks * 16 + (lane >> 4) * 8);
-          ldmatrix_x4(kb, Kb + ((lane & 7) + (lane >> 4) * 8) * sd + ks * 16 + ((lane >> 3) & 1) * 8);
-          mma_bf16(s[0], a, kb[0], kb[1]);
-          mma_bf16(s[1], a, kb[2], kb[3]);
+          uint32_t a[4];
+          ldmatrix_x4(a, Kb + (lane & 15) * sd + ks * 16 + (lane >> 4) * 8);
+          mma_bf16(s, a, qb[ks][0], qb[ks][1]);
         }
       }
-      float mx = -INFINITY;  // every row of this block is the same query position: one mask
+      // s[0], s[1]: key qd, heads 2t, 2t+1;  s[2], s[3]: key qd + 8
+      const int j0 = key0 + qd, j1 = j0 + 8;
+      const bool ok0 = j0 < kl && j0 >= lo, ok1 = j1 < kl && j1 >= lo;
+      s[0] = ok0 ? s[0] * sc : -INFINITY;
+      s[1] = ok0 ? s[1] * sc : -INFINITY;
+      s[2] = ok1 ? s[2] * sc : -INFINITY;
+      s[3] = ok1 ? s[3] * sc : -INFINITY;
+      float alpha[2], p[4];
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
+      for (int hh = 0; hh < 2; ++hh) {
+        float mx = fmaxf(s[hh], s[2 + hh]);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        const float m_new = fmaxf(m_run[hh], mx);   // finite: the warp holds at least one visible key
+        alpha[hh] = exp2f(m_run[hh] - m_new);
+        p[hh] = exp2f(s[hh] - m_new);
+        p[2 + hh] = exp2f(s[2 + hh] - m_new);
+        m_run[hh] = m_new;
+        l_run[hh] = l_run[hh] * alpha[hh] + (p[hh] + p[2 + hh]);
+      }
+      if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = key0 + nt * 8 + 2 * t4 + (e & 1);
-          s[nt][e] = (j < kl && j >= lo) ? s[nt][e] * sc : -INFINITY;
-        }
-      uint32_t pa[4];
-#pragma unroll
-      for (int hr = 0; hr < 2; ++hr) {
-        mx = fmaxf(fmaxf(s[0][2 * hr], s[0][2 * hr + 1]), fmaxf(s[1][2 * hr], s[1][2 * hr + 1]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run[hr], mx);
-        float alpha = 1.f, p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
-        if (m_new != -INFINITY) {
-          alpha = exp2f(m_run[hr] - m_new);
-          p0 = exp2f(s[0][2 * hr] - m_new);
-          p1 = exp2f(s[0][2 * hr + 1] - m_new);
-          p2 = exp2f(s[1][2 * hr] - m_new);
-          p3 = exp2f(s[1][2 * hr + 1] - m_new);
-        }
-        m_run[hr] = m_new;
-        l_run[hr] = l_run[hr] * alpha + ((p0 + p1) + (p2 + p3));
-        pa[hr] = pack_bf16(p0, p1);        // a0 / a1: keys 2t, 2t+1 of the first 8
-        pa[2 + hr] = pack_bf16(p2, p3);    // a2 / a3: keys 2t, 2t+1 of the second 8
-#pragma unroll
-        for (int i = 0; i < DMAX / 8; ++i) {
-          o[i][2 * hr] *= alpha;
-          o[i][2 * hr + 1] *= alpha;
+        for (int i = 0; i < DMAX / 16; ++i) {
+          o[i][0] *= alpha[0]; o[i][1] *= alpha[1];
+          o[i][2] *= alpha[0]; o[i][3] *= alpha[1];
         }
       }
+      // P to the B-operand layout
+      const uint32_t p_lo = pack_bf16(p[0], p[1]);   // key qd: heads 2t (low half), 2t+1 (high half)
+      const uint32_t p_hi = pack_bf16(p[2], p[3]);   // key qd + 8
+      const uint32_t x0 = __shfl_sync(0xffffffffu, p_lo, src0), x1 = __shfl_sync(0xffffffffu, p_lo, src1);
+      const uint32_t y0 = __shfl_sync(0xffffffffu, p_hi, src0), y1 = __shfl_sync(0xffffffffu, p_hi, src1);
+      // b0 = (key 2t, key 2t+1) of head qd; b1 = (key 2t+8, key 2t+9)
+      const uint32_t sel = odd_head ? 0x7632u : 0x5410u;
+      const uint32_t pb0 = __byte_perm(x0, x1, sel), pb1 = __byte_perm(y0, y1, sel);
 #pragma unroll
       for (int dt = 0; dt < DMAX / 16; ++dt) {
         if (dt < ksteps) {
-          uint32_t vb[4];
-          ldmatrix_x4_trans(vb, Vb + ((lane & 7) + ((lane >> 3) & 1) * 8) * sd + dt * 16 + (lane >> 4) * 8);
-          mma_bf16(o[2 * dt], pa, vb[0], vb[1]);
-          mma_bf16(o[2 * dt + 1], pa, vb[2], vb[3]);
+          uint32_t va[4];   // V^T: a0 (dim q, keys 2t..), a1 (dim q+8, keys 2t..), a2 / a3 keys +8
+          ldmatrix_x4_trans(va, Vb + ((lane & 7) + (lane >> 4) * 8) * sd + dt * 16 + ((lane >> 3) & 1) * 8);
+          mma_bf16(o[dt], va, pb0, pb1);
         }
       }
     }
@@ -247,25 +265,26 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 
   // merge the four warps (the last __syncthreads above freed the K/V buffers)
 #pragma unroll
-  for (int hr = 0; hr < 2; ++hr) {
-    float l = l_run[hr];
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (t4 == 0) {
-      merge_m[warp][qd + 8 * hr] = m_run[hr];
-      merge_l[warp][qd + 8 * hr] = l;
+  for (int hh = 0; hh < 2; ++hh) {
+    float l = l_run[hh];
+    l += __shfl_xor_sync(0xffffffffu, l, 4);
+    l += __shfl_xor_sync(0xffffffffu, l, 8);
+    l += __shfl_xor_sync(0xffffffffu, l, 16);
+    if (qd == 0) {
+      merge_m[warp][2 * t4 + hh] = m_run[hh];
+      merge_l[warp][2 * t4 + hh] = l;
     }
   }
 #pragma unroll
-  for (int i = 0; i < DMAX / 8; ++i) {
-    if (i * 8 < d) {
+  for (int i = 0; i < DMAX / 16; ++i) {
+    if (i < ksteps) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        merge_o[((size_t)warp * 16 + qd + 8 * (e >> 1)) * d + i * 8 + 2 * t4 + (e & 1)] = o[i][e];
+      for (int e = 0; e < 4; ++e)   // o[i][e]: dim i*16 + qd + 8*(e>>1), head 2*t4 + (e&1)
+        merge_o[((size_t)warp * DEC_HEADS + 2 * t4 + (e & 1)) * d + i * 16 + qd + 8 * (e >> 1)] = o[i][e];
     }
   }
   __syncthreads();
-  const int r = tid >> 3, cgrp = tid & 7;
+  const int r = tid >> 4, cgrp = tid & 15;   // 8 heads x 16 threads
   if (r < heads_here) {
     float m = merge_m[0][r];
 #pragma unroll
@@ -273,26 +292,26 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     float f[4], L = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      f[w] = (m == -INFINITY) ? 0.f : exp2f(merge_m[w][r] - m);
+      f[w] = (merge_m[w][r] == -INFINITY) ? 0.f : exp2f(merge_m[w][r] - m);
       L += merge_l[w][r] * f[w];
     }
     const int head = head0 + r;
     if (n_splits == 1) {
       const float inv = L > 0.f ? 1.f / L : 0.f;
       bf16* orow = out + (size_t)tok * out_stride + (size_t)head * d;
-      for (int k = cgrp; k < d; k += 8) {
+      for (int k = cgrp; k < d; k += 16) {
         float acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) acc += f[w] * merge_o[((size_t)w * 16 + r) * d + k];
+        for (int w = 0; w < 4; ++w) acc += f[w] * merge_o[((size_t)w * DEC_HEADS + r) * d + k];
         orow[k] = __float2bfloat16_rn(acc * inv);
       }
     } else {
       const size_t slot = (size_t)(b * nq + head) * n_splits + split;
       float* po = part_o + slot * d;
-      for (int k = cgrp; k < d; k += 8) {
+      for (int k = cgrp; k < d; k += 16) {
         float acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) acc += f[w] * merge_o[((size_t)w * 16 + r) * d + k];
+        for (int w = 0; w < 4; ++w) acc += f[w] * merge_o[((size_t)w * DEC_HEADS + r) * d + k];
         po[k] = acc;
       }
       if (cgrp == 0) {
@@ -563,9 +582,9 @@ extern "C" int mi_attention_decode(const void* q, int q_stride, void* out, int o
   if (n_splits < 1 || n_splits > 64) MI_REFUSE("attention: n_splits must be in [1, 64], got %d", n_splits);
   const int page_shift = shift_of(page_size);
   if (n_splits > 1 && (!part_o || !part_ml)) MI_REFUSE("attention: split results need scratch memory");
-  const int g = nq / nkv, hblocks = (g + 15) / 16;
+  const int g = nq / nkv, hblocks = (g + DEC_HEADS - 1) / DEC_HEADS;
   if (B > 65535 || nkv * hblocks > 65535) MI_REFUSE("attention: batch or head count too large for one launch");
-  const size_t smem = smem_bytes(16, d);
+  const size_t smem = smem_bytes(0, d);
   dim3 grid(n_splits, nkv * hblocks, B);
 #define MI_DECODE(DMAX)                                                                                 \
   do {                                                                                                  \

@@ -296,7 +296,7 @@ def _sms(device: torch.device) -> int:
 def decode_splits(n_requests: int, nq: int, nkv: int, max_kv_len: int, window: int, device) -> int:
     """How many slices of the keys each (request, key/value head) is cut into so that a
     decode step fills the GPU (about four blocks per SM), never more than one per 64 keys."""
-    blocks = n_requests * nkv * ((nq // nkv + 15) // 16)
+    blocks = n_requests * nkv * ((nq // nkv + 7) // 8)
     span = min(max_kv_len, window + 63) if window else max_kv_len
     chunks = max(1, -(-span // 64))
     return max(1, min(chunks, 64, -(-4 * _sms(device) // blocks)))
