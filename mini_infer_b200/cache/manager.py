@@ -2,7 +2,8 @@
 
 *Groups.*  Cache layers whose mixers keep the same thing (key/value heads, head size,
 window) form a group.  A group owns its pages: a pool of page ids with a LIFO free
-list, one storage tensor ``[layers, 2, pages * page_size, kv_heads, head_dim]`` and one
+list, one storage tensor ``[layers, 2, pages, kv_heads, page_size, head_dim]`` (the keys of a
+page lie together per head, so attention reads long runs) and one
 block table per request.  A page id means the same row range in every layer of its group
 (the reference's pool works that way for its single group, ``cache/block_pool.py:332-351``;
 its free list is LIFO as well, ``:570,735-757``).  Groups with a window give pages back as
@@ -159,7 +160,7 @@ class CacheManager:
         if self.device is not None:
             for g, n in zip(self.groups, pages):
                 self.storage.append(
-                    torch.zeros((len(g.layers), 2, n * page_size, g.kv_heads, g.head_dim),
+                    torch.zeros((len(g.layers), 2, n, g.kv_heads, page_size, g.head_dim),
                                 dtype=dtype, device=self.device)
                 )
             for need in self.needs:
@@ -299,7 +300,8 @@ class CacheManager:
     # ------------------------------------------------------------------ views and checks
 
     def layer_kv(self, cache_layer: int) -> tuple[int, torch.Tensor, torch.Tensor]:
-        """``(group index, keys, values)`` of a cache layer, each ``[slots, kv_heads, head_dim]``."""
+        """``(group index, keys, values)`` of a cache layer, each
+        ``[pages, kv_heads, page_size, head_dim]``."""
         gi, li = self.layer_place[cache_layer]
         st = self.storage[gi]
         return gi, st[li, 0], st[li, 1]

@@ -11,7 +11,8 @@
 // Layouts
 //   q    [tokens, q_stride]   head h at columns [h*d, (h+1)*d)
 //   out  [tokens, out_stride] same head layout
-//   kcache, vcache [slots, nkv, d],  slot = page * page_size + offset
+//   kcache, vcache [pages, nkv, page_size, d]: the page_size keys of a page lie together
+//                  per key/value head
 //   block_table [requests, bt_stride] page ids;  q_start / q_len / kv_len [requests]
 //   tile_req / tile_tok0 [tiles]: request and first token (within the portion) of a tile
 #include "common.cuh"
@@ -36,7 +37,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   float* Qs = Vs + BK * d;                // [BQ][d]
   float* Ks = Qs + BQ * d;                // [BK][d + 1]
   float* Ss = Ks + BK * (d + 1);          // [BQ][BK]
-  int* rowbase = reinterpret_cast<int*>(Ss + BQ * BK);  // [BK]
+  int* rowbase = reinterpret_cast<int*>(Ss + BQ * BK);  // [BK] element offset / d of each key row, -1: none
 
   const int tid = threadIdx.x;
   const int tile = blockIdx.x, h = blockIdx.y;
@@ -70,7 +71,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
       int base = -1;
       if (j >= j_lo && j < j_end) {
         const int page = block_table[(size_t)b * bt_stride + j / page_size];
-        base = page * page_size + j % page_size;
+        base = (page * nkv + kvh) * page_size + j % page_size;
       }
       rowbase[tid] = base;
     }
@@ -81,7 +82,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
       const int base = rowbase[jj];
       float kf[4] = {0.f, 0.f, 0.f, 0.f}, vf[4] = {0.f, 0.f, 0.f, 0.f};
       if (base >= 0) {
-        const size_t off = ((size_t)base * nkv + kvh) * d + k4;
+        const size_t off = (size_t)base * d + k4;
         Vec4<T> kv, vv;
         kv.load(kcache + off);
         vv.load(vcache + off);

@@ -9,13 +9,15 @@
 //            keys ("split"); its 4 warps take 16 keys each of every 64-key chunk, keep an
 //            online softmax of their own and are merged at the end.  With more than one
 //            split the block writes an unnormalised partial result (fp32) and its
-//            (max, sum) to scratch memory, and a second kernel merges the splits.
+//            (max, sum) to scratch memory and counts its arrival; the block that arrives
+//            last merges the splits.
 //   prefill  query portions of any length.  A block takes a tile of tokens of one request
 //            and up to 128 rows (token, head-in-group) that share a key/value head; each
 //            warp owns 16 rows and walks all keys up to the causal limit.
 //
 // A query at absolute position p sees keys j with max(0, p - window + 1) <= j <= p.
-// Layouts are those of attention_generic.cu.
+// Layouts are those of attention_generic.cu (cache pages are [nkv, page_size, d], so the keys of a
+// page lie together per key/value head and a 64-key chunk is read as a few long runs).
 #include "common.cuh"
 
 MI_DEFINE_ERROR_API()
@@ -56,59 +58,84 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Copy the 64 keys and the 64 values of chunk `chunk` of one request into `kdst` / `vdst`
-// ([64][sd] bf16 each).  Keys outside [lo, hi) are zero-filled and their pages never touched.
-// When the thread count is a multiple of the 16-byte units per row (head sizes 16, 32, 64,
-// 128, 256) every thread keeps one unit column and walks rows, so the page lookup is done
-// once per row; other head sizes take the general path.
-template <int THREADS>
-__device__ __forceinline__ void load_kv_chunk(bf16* kdst, bf16* vdst, const bf16* __restrict__ kcache,
-                                              const bf16* __restrict__ vcache, const int* __restrict__ table,
-                                              int page_size, int page_shift, int chunk, int lo, int hi,
-                                              int nkv, int kvh, int d, int sd) {
-  const int units = d >> 3;  // 16-byte units per row
-  const int jbase = chunk * KCHUNK;
-  if (THREADS % units == 0) {
-    const int u = threadIdx.x % units, rstep = THREADS / units;
-    for (int r = threadIdx.x / units; r < KCHUNK; r += rstep) {
-      const int j = jbase + r;
-      bf16* ks = kdst + r * sd + u * 8;
-      bf16* vs = vdst + r * sd + u * 8;
-      if (j >= lo && j < hi) {
-        int page, inpage;
-        if (page_shift >= 0) {
-          page = table[j >> page_shift];
-          inpage = j & (page_size - 1);
-        } else {
-          page = table[j / page_size];
-          inpage = j % page_size;
-        }
-        const size_t off = ((size_t)(page * page_size + inpage) * nkv + kvh) * d + u * 8;
-        cp_async16(ks, kcache + off);
-        cp_async16(vs, vcache + off);
-      } else {
-        *reinterpret_cast<uint4*>(ks) = make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(vs) = make_uint4(0u, 0u, 0u, 0u);
-      }
-    }
-  } else {
-    for (int idx = threadIdx.x; idx < KCHUNK * units; idx += THREADS) {
-      const int r = idx / units, u = idx - r * units;
-      const int j = jbase + r;
-      bf16* ks = kdst + r * sd + u * 8;
-      bf16* vs = vdst + r * sd + u * 8;
-      if (j >= lo && j < hi) {
-        const int page = table[j / page_size];
-        const size_t off = ((size_t)(page * page_size + j % page_size) * nkv + kvh) * d + u * 8;
-        cp_async16(ks, kcache + off);
-        cp_async16(vs, vcache + off);
-      } else {
-        *reinterpret_cast<uint4*>(ks) = make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(vs) = make_uint4(0u, 0u, 0u, 0u);
-      }
+// ---- bulk asynchronous copies (the copy engine writes shared memory and signals an mbarrier)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Wait for a phase of the barrier, but never for ever: after MBAR_SPIN_LIMIT tries the wait
+// gives up and records it in *status; the block then leaves its loop, and blocks that start
+// later return at once (the output is then wrong and the host finds the status word set;
+// nothing hangs).
+#define MBAR_SPIN_LIMIT (1 << 16)
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* status) {
+  for (int it = 0; it < MBAR_SPIN_LIMIT; ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  if (status) atomicExch(status, 1);
+  return false;
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
+
+// Brings 64-key chunks of one request's keys and values into shared memory ([64][sd] bf16
+// each, rows padded for ldmatrix).  One thread per row: threads 0..63 copy the key rows,
+// 64..127 the value rows, each with ONE bulk copy of the whole row (2 * d bytes, contiguous in
+// the cache) that reports to the chunk's mbarrier.  The page id of a thread's row is fetched one
+// chunk ahead.  Rows outside [lo, hi) are zero-filled and their pages never touched.
+struct RowLoader {
+  int pg;
+
+  __device__ __forceinline__ void fetch(const int* __restrict__ table, int page_size, int page_shift, int chunk,
+                                        int lo, int hi) {
+    pg = -1;
+    if (threadIdx.x < 2 * KCHUNK) {
+      const int j = chunk * KCHUNK + (threadIdx.x & (KCHUNK - 1));
+      if (j >= lo && j < hi) pg = table[page_shift >= 0 ? (j >> page_shift) : (j / page_size)];
     }
   }
-}
+
+  // bytes the chunk's copies will deliver (the same for every thread)
+  static __device__ __forceinline__ uint32_t chunk_bytes(int chunk, int lo, int hi, int d) {
+    const int a = max(lo, chunk * KCHUNK), b = min(hi, chunk * KCHUNK + KCHUNK);
+    return b > a ? (uint32_t)(b - a) * (uint32_t)d * 4u : 0u;   // keys and values, 2 bytes each
+  }
+
+  __device__ __forceinline__ void issue(bf16* kdst, bf16* vdst, const bf16* __restrict__ kcache,
+                                        const bf16* __restrict__ vcache, int page_size, int page_shift, int chunk,
+                                        int nkv, int kvh, int d, int sd, uint64_t* bar) const {
+    if (threadIdx.x >= 2 * KCHUNK) return;
+    const int r = threadIdx.x & (KCHUNK - 1);
+    const bool is_v = threadIdx.x >= KCHUNK;
+    bf16* dst = (is_v ? vdst : kdst) + r * sd;
+    if (pg >= 0) {
+      const int j = chunk * KCHUNK + r;
+      const int inpage = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+      const size_t off = (((size_t)pg * nkv + kvh) * page_size + inpage) * d;
+      bulk_copy_g2s(dst, (is_v ? vcache : kcache) + off, (uint32_t)d * 2u, bar);
+    } else {
+      for (int u = 0; u < (d >> 3); ++u) *reinterpret_cast<uint4*>(dst + u * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+};
 
 // ------------------------------------------------------------------------------- decode
 //
@@ -120,6 +147,64 @@ __device__ __forceinline__ void load_kv_chunk(bf16* kdst, bf16* vdst, const bf16
 // B-operand layout (lane holds keys 2t, 2t+1, 2t+8, 2t+9 of head q) with four shuffles.
 
 #define DEC_HEADS 8   // query heads of one key/value head handled by a block
+#define DEC_STAGES 3  // 64-key chunks in the shared-memory ring (two are in flight while one is used)
+
+// After a block has parked its slice's partial result: count arrivals for this (request,
+// head group); the block that arrives last merges all slices in slice order,
+//   out = sum_s f_s O_s / sum_s f_s l_s,  f_s = 2^(m_s - m),
+// writes the output and resets the counter.  Nobody waits for anybody.
+__device__ __forceinline__ void decode_merge_when_last(const float* __restrict__ part_o,
+                                                       const float* __restrict__ part_ml, int* counters,
+                                                       int counter_index, bf16* __restrict__ out,
+                                                       int out_stride, int tok, int b, int nq, int d,
+                                                       int n_splits, int head0, int heads_here) {
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = (atomicAdd(&counters[counter_index], 1) == n_splits - 1) ? 1 : 0;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // (max, sum) of every (head, slice) first, all loads in flight at once
+  __shared__ float sm_m[DEC_HEADS][64], sm_f[DEC_HEADS][64], sm_inv[DEC_HEADS];
+  for (int idx = threadIdx.x; idx < heads_here * n_splits; idx += NTHREADS) {
+    const int r = idx / n_splits, sp = idx - r * n_splits;
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + (size_t)(b * nq + head0 + r) * n_splits + sp);
+    sm_m[r][sp] = ml.x;
+    sm_f[r][sp] = ml.y;
+  }
+  __syncthreads();
+  if (threadIdx.x < heads_here) {
+    const int r = threadIdx.x;
+    float m = -INFINITY;
+    for (int sp = 0; sp < n_splits; ++sp) m = fmaxf(m, sm_m[r][sp]);
+    float L = 0.f;
+    for (int sp = 0; sp < n_splits; ++sp) {
+      const float f = (sm_m[r][sp] == -INFINITY) ? 0.f : exp2f(sm_m[r][sp] - m);
+      L += sm_f[r][sp] * f;
+      sm_f[r][sp] = f;
+    }
+    sm_inv[r] = L > 0.f ? 1.f / L : 0.f;
+  }
+  __syncthreads();
+  const int r = threadIdx.x >> 4, cgrp = threadIdx.x & 15;   // 8 heads x 16 threads
+  if (r < heads_here) {
+    const int head = head0 + r;
+    const float* po = part_o + (size_t)(b * nq + head) * n_splits * d;
+    bf16* orow = out + (size_t)tok * out_stride + (size_t)head * d;
+    for (int k = cgrp; k < d; k += 16) {
+      float acc = 0.f;
+#pragma unroll 8
+      for (int sp = 0; sp < n_splits; ++sp) {
+        const float f = sm_f[r][sp];
+        const float v = __ldcg(po + (size_t)sp * d + k);   // slices that saw nothing hold garbage: f is 0 there
+        acc += f != 0.f ? f * v : 0.f;
+      }
+      orow[k] = __float2bfloat16_rn(acc * sm_inv[r]);
+    }
+  }
+  if (threadIdx.x == 0) counters[counter_index] = 0;   // ready for the next call
+}
 
 template <int DMAX>
 __global__ void __launch_bounds__(NTHREADS)
@@ -128,13 +213,14 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                         const int* __restrict__ block_table, int bt_stride, int page_size, int page_shift,
                         const int* __restrict__ q_start, const int* __restrict__ kv_len, int nq, int nkv,
                         int d, float scale, int window, int n_splits, float* __restrict__ part_o,
-                        float* __restrict__ part_ml) {
+                        float* __restrict__ part_ml, int* __restrict__ counters, int* __restrict__ status) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int sd = d + 8;  // row stride in elements: 16 bytes of padding keep ldmatrix conflict-free
-  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);          // [2][64][sd]
-  bf16* Vs = Ks + 2 * KCHUNK * sd;                       // [2][64][sd]
+  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);          // [DEC_STAGES][64][sd]
+  bf16* Vs = Ks + DEC_STAGES * KCHUNK * sd;              // [DEC_STAGES][64][sd]
   float* merge_o = reinterpret_cast<float*>(smem_raw);   // [4][8][d] after the main loop
   __shared__ float merge_m[4][DEC_HEADS], merge_l[4][DEC_HEADS];
+  __shared__ __align__(8) uint64_t bars[DEC_STAGES];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int qd = lane >> 2, t4 = lane & 3;
@@ -154,17 +240,36 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
   const int head0 = kvh * g + hb * DEC_HEADS;
   const int* table = block_table + (size_t)b * bt_stride;
 
+  if (status && *reinterpret_cast<volatile int*>(status)) return;   // an earlier block gave up waiting
   if (c0 >= c1) {  // nothing for this split (only possible with n_splits > 1)
     for (int r = tid; r < heads_here; r += NTHREADS) {
       float* ml = part_ml + ((size_t)(b * nq + head0 + r) * n_splits + split) * 2;
       ml[0] = -INFINITY;
       ml[1] = 0.f;
     }
+    decode_merge_when_last(part_o, part_ml, counters, b * gridDim.y + blockIdx.y, out, out_stride, tok, b, nq, d,
+                           n_splits, head0, heads_here);
     return;
   }
 
-  load_kv_chunk<NTHREADS>(Ks, Vs, kcache, vcache, table, page_size, page_shift, c0, lo, kl, nkv, kvh, d, sd);
-  cp_async_commit();
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES; ++i) mbar_init(&bars[i], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  RowLoader loader;
+#pragma unroll
+  for (int i = 0; i < DEC_STAGES - 1; ++i) {   // fill the ring but for one stage
+    if (c0 + i < c1) {
+      loader.fetch(table, page_size, page_shift, c0 + i, lo, kl);
+      if (tid == 0) mbar_expect_tx(&bars[i], RowLoader::chunk_bytes(c0 + i, lo, kl, d));
+      loader.issue(Ks + i * KCHUNK * sd, Vs + i * KCHUNK * sd, kcache, vcache, page_size, page_shift, c0 + i, nkv,
+                   kvh, d, sd, &bars[i]);
+    }
+  }
+  if (c0 + DEC_STAGES - 1 < c1) loader.fetch(table, page_size, page_shift, c0 + DEC_STAGES - 1, lo, kl);
+  __syncthreads();   // rows zero-filled above are visible to every warp
 
   // Q as the B operand: lane (qd, t4) holds head qd, dims ks*16 + 2*t4 + {0,1} and + 8
   const int ksteps = d >> 4;
@@ -192,29 +297,46 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
   const bool odd_head = qd & 1;
 
   for (int c = c0; c < c1; ++c) {
-    const int buf = (c - c0) & 1;
-    if (c + 1 < c1) {
-      load_kv_chunk<NTHREADS>(Ks + (buf ^ 1) * KCHUNK * sd, Vs + (buf ^ 1) * KCHUNK * sd, kcache, vcache, table,
-                              page_size, page_shift, c + 1, lo, kl, nkv, kvh, d, sd);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+    const int it = c - c0, buf = it % DEC_STAGES;
+    if (c + DEC_STAGES - 1 < c1) {   // refill the stage that the previous iteration used up
+      const int nb = (it + DEC_STAGES - 1) % DEC_STAGES;
+      if (tid == 0) mbar_expect_tx(&bars[nb], RowLoader::chunk_bytes(c + DEC_STAGES - 1, lo, kl, d));
+      loader.issue(Ks + nb * KCHUNK * sd, Vs + nb * KCHUNK * sd, kcache, vcache, page_size, page_shift,
+                   c + DEC_STAGES - 1, nkv, kvh, d, sd, &bars[nb]);
+      if (c + DEC_STAGES < c1) loader.fetch(table, page_size, page_shift, c + DEC_STAGES, lo, kl);
     }
-    __syncthreads();
+    const bool arrived =
+        __all_sync(0xffffffffu, mbar_wait_bounded(&bars[buf], (it / DEC_STAGES) & 1, status));
     const bf16* Kb = Ks + buf * KCHUNK * sd + (warp * 16) * sd;
     const bf16* Vb = Vs + buf * KCHUNK * sd + (warp * 16) * sd;
     const int key0 = c * KCHUNK + warp * 16;
-    if (key0 < kl && key0 + 16 > lo) {  // warp-uniform: this warp's 16 keys hold something visible
-      float s[4] = {0.f, 0.f, 0.f, 0.f};
+    if (arrived && key0 < kl && key0 + 16 > lo) {  // warp-uniform: this warp's 16 keys hold something visible
+      // All fragment loads of a group of k-steps are issued before the first MMA that needs
+      // them, and two accumulators halve the MMA dependency chain: the warp's critical path is
+      // one load latency plus a few MMAs instead of their sum over all k-steps.
+      constexpr int GROUP = (DMAX / 16) < 8 ? (DMAX / 16) : 8;
+      float s[4] = {0.f, 0.f, 0.f, 0.f}, s_odd[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int ks = 0; ks < DMAX / 16; ++ks) {
-        if (ks < ksteps) {
-          uint32_t a[4];
-          ldmatrix_x4(a, Kb + (lane & 15) * sd + ks * 16 + (lane >> 4) * 8);
-          mma_bf16(s, a, qb[ks][0], qb[ks][1]);
-        }
+      for (int g0 = 0; g0 < DMAX / 16; g0 += GROUP) {
+        uint32_t kf[GROUP][4];
+#pragma unroll
+        for (int i = 0; i < GROUP; ++i)
+          if (g0 + i < ksteps) ldmatrix_x4(kf[i], Kb + (lane & 15) * sd + (g0 + i) * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int i = 0; i < GROUP; ++i)
+          if (g0 + i < ksteps) {
+            if (i & 1) mma_bf16(s_odd, kf[i], qb[g0 + i][0], qb[g0 + i][1]);
+            else mma_bf16(s, kf[i], qb[g0 + i][0], qb[g0 + i][1]);
+          }
       }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[e] += s_odd[e];
+      // the value fragments of the first group do not depend on the softmax: fetch them now
+      uint32_t vf[GROUP][4];
+#pragma unroll
+      for (int i = 0; i < GROUP; ++i)
+        if (i < ksteps)
+          ldmatrix_x4_trans(vf[i], Vb + ((lane & 7) + (lane >> 4) * 8) * sd + i * 16 + ((lane >> 3) & 1) * 8);
       // s[0], s[1]: key qd, heads 2t, 2t+1;  s[2], s[3]: key qd + 8
       const int j0 = key0 + qd, j1 = j0 + 8;
       const bool ok0 = j0 < kl && j0 >= lo, ok1 = j1 < kl && j1 >= lo;
@@ -251,16 +373,23 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
       // b0 = (key 2t, key 2t+1) of head qd; b1 = (key 2t+8, key 2t+9)
       const uint32_t sel = odd_head ? 0x7632u : 0x5410u;
       const uint32_t pb0 = __byte_perm(x0, x1, sel), pb1 = __byte_perm(y0, y1, sel);
+      // V^T fragments: a0 (dim q, keys 2t..), a1 (dim q+8, keys 2t..), a2 / a3 keys +8
 #pragma unroll
-      for (int dt = 0; dt < DMAX / 16; ++dt) {
-        if (dt < ksteps) {
-          uint32_t va[4];   // V^T: a0 (dim q, keys 2t..), a1 (dim q+8, keys 2t..), a2 / a3 keys +8
-          ldmatrix_x4_trans(va, Vb + ((lane & 7) + (lane >> 4) * 8) * sd + dt * 16 + ((lane >> 3) & 1) * 8);
-          mma_bf16(o[dt], va, pb0, pb1);
-        }
+      for (int i = 0; i < GROUP; ++i)
+        if (i < ksteps) mma_bf16(o[i], vf[i], pb0, pb1);
+#pragma unroll
+      for (int g0 = GROUP; g0 < DMAX / 16; g0 += GROUP) {
+#pragma unroll
+        for (int i = 0; i < GROUP; ++i)
+          if (g0 + i < ksteps)
+            ldmatrix_x4_trans(vf[i], Vb + ((lane & 7) + (lane >> 4) * 8) * sd + (g0 + i) * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+        for (int i = 0; i < GROUP; ++i)
+          if (g0 + i < ksteps) mma_bf16(o[g0 + i], vf[i], pb0, pb1);
       }
     }
-    __syncthreads();
+    fence_proxy_async();   // this buffer is next written by the copy engine
+    if (__syncthreads_or(!arrived)) break;   // a wait gave up: stop (status is set)
   }
 
   // merge the four warps (the last __syncthreads above freed the K/V buffers)
@@ -320,44 +449,9 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
       }
     }
   }
-}
-
-// Merge the splits of one (request, head): out = sum_s f_s O_s / sum_s f_s l_s, f_s = 2^(m_s - m).
-// One block per (head, request); n_splits <= 64.
-__global__ void __launch_bounds__(128)
-attention_merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                              bf16* __restrict__ out, int out_stride, const int* __restrict__ q_start, int nq,
-                              int d, int n_splits) {
-  __shared__ float fs[64];
-  __shared__ float inv_l;
-  const int head = blockIdx.x, b = blockIdx.y;
-  const size_t base = (size_t)(b * nq + head) * n_splits;
-  if (threadIdx.x < 32) {
-    const int lane = threadIdx.x;
-    const float m0 = lane < n_splits ? part_ml[(base + lane) * 2] : -INFINITY;
-    const float m1 = lane + 32 < n_splits ? part_ml[(base + lane + 32) * 2] : -INFINITY;
-    const float m = mi_warp_max(fmaxf(m0, m1));
-    const float f0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - m);
-    const float f1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - m);
-    float l = 0.f;
-    if (lane < n_splits) l += f0 * part_ml[(base + lane) * 2 + 1];
-    if (lane + 32 < n_splits) l += f1 * part_ml[(base + lane + 32) * 2 + 1];
-    l = mi_warp_sum(l);
-    fs[lane] = f0;
-    fs[lane + 32] = f1;
-    if (lane == 0) inv_l = l > 0.f ? 1.f / l : 0.f;
-  }
-  __syncthreads();
-  bf16* orow = out + (size_t)q_start[b] * out_stride + (size_t)head * d;
-  for (int k = threadIdx.x; k < d; k += blockDim.x) {
-    float acc = 0.f;
-#pragma unroll 4
-    for (int s = 0; s < n_splits; ++s) {
-      const float f = fs[s];
-      if (f != 0.f) acc += f * part_o[(base + s) * d + k];
-    }
-    orow[k] = __float2bfloat16_rn(acc * inv_l);
-  }
+  if (n_splits > 1)
+    decode_merge_when_last(part_o, part_ml, counters, b * gridDim.y + blockIdx.y, out, out_stride, tok, b, nq, d,
+                           n_splits, head0, heads_here);
 }
 
 // ------------------------------------------------------------------------------- prefill
@@ -373,7 +467,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
                          const int* __restrict__ q_start, const int* __restrict__ q_len,
                          const int* __restrict__ kv_len, const int* __restrict__ tile_req,
                          const int* __restrict__ tile_tok0, int nq, int nkv, int d, float scale, int window,
-                         int gb, int tt) {
+                         int gb, int tt, int* __restrict__ status) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int sd = d + 8;
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);   // [PROWS][sd]
@@ -395,6 +489,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   const int heads_here = min(gb, g - hb * gb);
   const int* table = block_table + (size_t)b * bt_stride;
 
+  if (status && *reinterpret_cast<volatile int*>(status)) return;   // an earlier block gave up waiting
   // row R of the tile: token tok0 + R / gb, head kvh * g + hb * gb + R % gb
   const int units = d >> 3;
   for (int idx = tid; idx < PROWS * units; idx += PTHREADS) {
@@ -432,24 +527,33 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   const int ksteps = d >> 4;
   const int c0 = lo / KCHUNK, c1 = (hi + KCHUNK - 1) / KCHUNK;
 
-  load_kv_chunk<PTHREADS>(Ks, Vs, kcache, vcache, table, page_size, page_shift, c0, lo, hi, nkv, kvh, d, sd);
-  cp_async_commit();
+  __shared__ __align__(8) uint64_t bars[2];
+  if (tid == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  RowLoader loader;
+  loader.fetch(table, page_size, page_shift, c0, lo, hi);
+  if (tid == 0) mbar_expect_tx(&bars[0], RowLoader::chunk_bytes(c0, lo, hi, d));
+  loader.issue(Ks, Vs, kcache, vcache, page_size, page_shift, c0, nkv, kvh, d, sd, &bars[0]);
+  if (c0 + 1 < c1) loader.fetch(table, page_size, page_shift, c0 + 1, lo, hi);
+  __syncthreads();   // the query tile and rows zero-filled above are visible to every warp
 
   for (int c = c0; c < c1; ++c) {
     const int buf = (c - c0) & 1;
     if (c + 1 < c1) {
-      load_kv_chunk<PTHREADS>(Ks + (buf ^ 1) * KCHUNK * sd, Vs + (buf ^ 1) * KCHUNK * sd, kcache, vcache, table,
-                              page_size, page_shift, c + 1, lo, hi, nkv, kvh, d, sd);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+      if (tid == 0) mbar_expect_tx(&bars[buf ^ 1], RowLoader::chunk_bytes(c + 1, lo, hi, d));
+      loader.issue(Ks + (buf ^ 1) * KCHUNK * sd, Vs + (buf ^ 1) * KCHUNK * sd, kcache, vcache, page_size, page_shift,
+                   c + 1, nkv, kvh, d, sd, &bars[buf ^ 1]);
+      if (c + 2 < c1) loader.fetch(table, page_size, page_shift, c + 2, lo, hi);
     }
-    __syncthreads();
+    const bool arrived = __all_sync(0xffffffffu, mbar_wait_bounded(&bars[buf], ((c - c0) >> 1) & 1, status));
     const bf16* Kb = Ks + buf * KCHUNK * sd;
     const bf16* Vb = Vs + buf * KCHUNK * sd;
     const int key0 = c * KCHUNK;
-    if (warp_active && key0 < warp_hi && key0 + KCHUNK > warp_lo) {
+    if (arrived && warp_active && key0 < warp_hi && key0 + KCHUNK > warp_lo) {
       float s[8][4];
 #pragma unroll
       for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -525,7 +629,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
         }
       }
     }
-    __syncthreads();
+    fence_proxy_async();   // this buffer is next written by the copy engine
+    if (__syncthreads_or(!arrived)) break;   // a wait gave up: stop (status is set)
   }
 
 #pragma unroll
@@ -561,6 +666,33 @@ static int check_common(const void* q, int q_stride, const void* out, int out_st
   return 0;
 }
 
+// Set to 1 by a kernel whose bounded wait for a copy gave up (its output is then invalid).
+static __device__ int g_wait_status;
+#define MI_MAX_DEVICES 64
+static int* g_wait_status_ptr[MI_MAX_DEVICES];
+
+static int* wait_status_ptr() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MI_MAX_DEVICES) return nullptr;
+  if (!g_wait_status_ptr[dev]) {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_wait_status) != cudaSuccess) return nullptr;
+    g_wait_status_ptr[dev] = p;
+  }
+  return g_wait_status_ptr[dev];
+}
+
+// 1 if a kernel of this library gave up waiting for a copy since the last reset (synchronises).
+extern "C" int mi_attention_wait_status(int reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_wait_status, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && v) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_wait_status, &zero, sizeof(int));
+  }
+  return v;
+}
+
 static size_t smem_bytes(int q_rows, int d) { return (size_t)(q_rows + 4 * KCHUNK) * (d + 8) * sizeof(bf16); }
 
 static int shift_of(int page_size) {  // log2 for powers of two, else -1
@@ -570,21 +702,28 @@ static int shift_of(int page_size) {  // log2 for powers of two, else -1
   return s;
 }
 
-// Scratch: part_o holds B * nq * n_splits * d floats, part_ml holds B * nq * n_splits * 2 floats
-// (both may be null when n_splits == 1).
+// How many arrival counters a call needs (one per request and head group).
+extern "C" int mi_attention_decode_counters(int B, int nq, int nkv) {
+  const int g = nq / nkv;
+  return B * nkv * ((g + DEC_HEADS - 1) / DEC_HEADS);
+}
+
+// Scratch: part_o holds B * nq * n_splits * d floats, part_ml holds B * nq * n_splits * 2 floats,
+// counters holds mi_attention_decode_counters(B, nq, nkv) ints that are zero on entry (the kernel
+// leaves them zero).  All three may be null when n_splits == 1.
 extern "C" int mi_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
                                    const void* vcache, const int* block_table, int bt_stride, int page_size,
                                    const int* q_start, const int* kv_len, int B, int nq, int nkv, int d,
                                    float scale, int window, int n_splits, float* part_o, float* part_ml,
-                                   cudaStream_t stream) {
+                                   int* counters, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (int rc = check_common(q, q_stride, out, out_stride, kcache, vcache, nq, nkv, d, page_size, window)) return rc;
   if (n_splits < 1 || n_splits > 64) MI_REFUSE("attention: n_splits must be in [1, 64], got %d", n_splits);
   const int page_shift = shift_of(page_size);
-  if (n_splits > 1 && (!part_o || !part_ml)) MI_REFUSE("attention: split results need scratch memory");
+  if (n_splits > 1 && (!part_o || !part_ml || !counters)) MI_REFUSE("attention: split results need scratch memory");
   const int g = nq / nkv, hblocks = (g + DEC_HEADS - 1) / DEC_HEADS;
   if (B > 65535 || nkv * hblocks > 65535) MI_REFUSE("attention: batch or head count too large for one launch");
-  const size_t smem = smem_bytes(0, d);
+  const size_t smem = (size_t)(2 * DEC_STAGES * KCHUNK) * (d + 8) * sizeof(bf16);
   dim3 grid(n_splits, nkv * hblocks, B);
 #define MI_DECODE(DMAX)                                                                                 \
   do {                                                                                                  \
@@ -596,22 +735,13 @@ extern "C" int mi_attention_decode(const void* q, int q_stride, void* out, int o
     kern<<<grid, NTHREADS, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride,            \
                                            (const bf16*)kcache, (const bf16*)vcache, block_table,       \
                                            bt_stride, page_size, page_shift, q_start, kv_len, nq, nkv,  \
-                                           d, scale, window, n_splits, part_o, part_ml);                \
+                                           d, scale, window, n_splits, part_o, part_ml, counters,       \
+                                           wait_status_ptr());                                          \
   } while (0)
   if (d <= 64) MI_DECODE(64);
   else if (d <= 128) MI_DECODE(128);
   else MI_DECODE(256);
 #undef MI_DECODE
-  if (n_splits > 1) {
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) {
-      snprintf(g_mi_error, sizeof(g_mi_error), "CUDA: %s", cudaGetErrorString(e));
-      return (int)e;
-    }
-    dim3 mgrid(nq, B);
-    attention_merge_splits_kernel<<<mgrid, 128, 0, stream>>>(part_o, part_ml, (bf16*)out, out_stride, q_start, nq,
-                                                             d, n_splits);
-  }
   MI_RETURN_LAUNCH_STATUS();
 }
 
@@ -647,7 +777,7 @@ extern "C" int mi_attention_prefill(const void* q, int q_stride, void* out, int 
                                            (const bf16*)kcache, (const bf16*)vcache, block_table,       \
                                            bt_stride, page_size, page_shift, q_start, q_len, kv_len,    \
                                            tile_req, tile_tok0, nq, nkv, d, scale, window, gb,          \
-                                           PROWS / gb);                                                 \
+                                           PROWS / gb, wait_status_ptr());                              \
   } while (0)
   if (d <= 64) MI_PREFILL(64);
   else if (d <= 128) MI_PREFILL(128);
@@ -678,7 +808,8 @@ extern "C" int mi_attention_decode_noalloc(const void* q, int q_stride, void* ou
   if (B <= 0) return 0;
   if (nq <= 0 || d <= 0 || n_splits < 1) MI_REFUSE("attention (no allocation): bad sizes");
   const size_t slots = (size_t)B * nq * n_splits;
-  const size_t need = slots * ((size_t)d + 2);
+  const size_t n_counters = (size_t)mi_attention_decode_counters(B, nq, nkv > 0 ? nkv : 1);
+  const size_t need = slots * ((size_t)d + 2) + n_counters;
   if (need > (size_t)MI_ATTENTION_NOALLOC_MAX_FLOATS)
     MI_REFUSE("attention (no allocation): %zu floats of scratch needed (B=%d, heads=%d, slices=%d, head size=%d), "
               "the built-in array holds %d",
@@ -699,8 +830,19 @@ extern "C" int mi_attention_decode_noalloc(const void* q, int q_stride, void* ou
     }
     g_noalloc_device_ptr[dev] = p;
   }
-  float* part_o = g_noalloc_device_ptr[dev];
+  // the arrival counters come first and must be zero when the kernel starts; the array keeps
+  // whatever the last call left (a call that was cut short could leave a count behind)
+  int* counters = reinterpret_cast<int*>(g_noalloc_device_ptr[dev]);
+  float* part_o = g_noalloc_device_ptr[dev] + n_counters;
   float* part_ml = part_o + slots * (size_t)d;
+  if (n_splits > 1) {
+    e = cudaMemsetAsync(counters, 0, n_counters * sizeof(int), stream);
+    if (e != cudaSuccess) {
+      snprintf(g_mi_error, sizeof(g_mi_error), "CUDA: %s", cudaGetErrorString(e));
+      return (int)e;
+    }
+  }
   return mi_attention_decode(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride, page_size,
-                             q_start, kv_len, B, nq, nkv, d, scale, window, n_splits, part_o, part_ml, stream);
+                             q_start, kv_len, B, nq, nkv, d, scale, window, n_splits, part_o, part_ml, counters,
+                             stream);
 }

@@ -11,14 +11,16 @@
 // The scratch is one file-scope `static __device__` array of
 // MI_ATTENTION_NOALLOC_MAX_FLOATS floats (4 MiB).  Every GPU on which the library is loaded
 // holds that array until the process exits.  A call needs B * nq * n_splits * (d + 2) floats
-// of it and is refused, with a message, when that is more than the array holds.
+// of it plus one arrival counter per (request, group of 8 query heads), and is refused, with a
+// message, when that is more than the array holds.
 //
 // What a caller has to know:
 //   * The first call on a device looks up the array's device address (with that device
 //     current) and remembers it.  Make that first call during set-up, before any stream
 //     capture is begun.
-//   * All calls share the one array and it keeps the previous call's contents.  Nothing in it
-//     has to start at zero: every slot a call reads it has written earlier in the same call.
+//   * All calls share the one array and it keeps the previous call's contents.  Only the
+//     arrival counters have to start at zero, and the entry point clears them on the stream
+//     before it launches; every other slot a call reads it has written earlier in the same call.
 //     Two calls that overlap on the GPU (different streams, or concurrent replays) race on it;
 //     keep calls on one stream or serialise them yourself.
 //   * No cudaMalloc, cudaFree or allocating library routine is called.  Inputs and outputs are

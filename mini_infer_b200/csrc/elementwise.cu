@@ -192,7 +192,8 @@ extern "C" int mi_add_rmsnorm(const void* x, const float* res_in, float* res_out
 //   qkv      [M, (nq + 2 nkv) * d]   q heads, then k heads, then v heads
 //   pos      [M]  absolute positions;  inv_freq [rot/2] fp32
 //   slot     [M]  flat cache slot (page * page_size + offset) of each token, < 0: no write
-//   kcache, vcache  [slots, nkv, d]  (may be null: rotate only)
+//   kcache, vcache  [pages, nkv, page_size, d]  (may be null: rotate only); a slot's row for
+//                   key/value head h lies at ((page * nkv + h) * page_size + offset) * d
 // q is rotated in place.  k is rotated in place too (so that a later reader of the
 // buffer sees what the cache holds) and stored; v is copied.  Angles, sine and cosine
 // are fp32; each output is rounded once.  rot = 0 means no rotation (store only).
@@ -201,7 +202,7 @@ template <typename T>
 __global__ void rope_write_kernel(T* __restrict__ qkv, const int* __restrict__ pos,
                                   const float* __restrict__ inv_freq, const int* __restrict__ slot,
                                   T* __restrict__ kcache, T* __restrict__ vcache, int nq, int nkv,
-                                  int d, int rot) {
+                                  int d, int rot, int page_size) {
   // one block per (token, head); heads are q heads, then k heads, then v heads
   const int t = blockIdx.x, h = blockIdx.y;
   const int width = (nq + 2 * nkv) * d;
@@ -210,7 +211,11 @@ __global__ void rope_write_kernel(T* __restrict__ qkv, const int* __restrict__ p
   const int half = rot >> 1;
   if (h < nq + nkv) {
     const bool is_k = h >= nq;
-    T* dst = (is_k && sl >= 0) ? kcache + ((size_t)sl * nkv + (h - nq)) * d : nullptr;
+    T* dst = nullptr;
+    if (is_k && sl >= 0) {
+      const int page = sl / page_size, off = sl - page * page_size;
+      dst = kcache + (((size_t)page * nkv + (h - nq)) * page_size + off) * d;
+    }
     if (half > 0) {
       const float p = (float)pos[t];
       for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -231,19 +236,21 @@ __global__ void rope_write_kernel(T* __restrict__ qkv, const int* __restrict__ p
     if (dst)  // un-rotated tail of k (rot < d)
       for (int i = rot + threadIdx.x; i < d; i += blockDim.x) dst[i] = head[i];
   } else if (sl >= 0) {
-    T* dst = vcache + ((size_t)sl * nkv + (h - nq - nkv)) * d;
+    const int page = sl / page_size, off = sl - page * page_size;
+    T* dst = vcache + (((size_t)page * nkv + (h - nq - nkv)) * page_size + off) * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = head[i];
   }
 }
 
 extern "C" int mi_rope_write(void* qkv, const int* pos, const float* inv_freq, const int* slot,
                              void* kcache, void* vcache, int M, int nq, int nkv, int d, int rot,
-                             int dtype, cudaStream_t stream) {
+                             int page_size, int dtype, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (nq < 0 || nkv < 0 || d <= 0) MI_REFUSE("rope: bad sizes nq=%d nkv=%d d=%d", nq, nkv, d);
   if (rot < 0 || rot > d || (rot & 1)) MI_REFUSE("rope: rotary width %d must be even and <= head size %d", rot, d);
   if (rot > 0 && (!pos || !inv_freq)) MI_REFUSE("rope: positions and frequencies are required");
   if ((kcache == nullptr) != (vcache == nullptr)) MI_REFUSE("rope: key and value cache go together");
+  if (kcache && page_size <= 0) MI_REFUSE("rope: bad page size %d", page_size);
   const int heads = nq + nkv + (kcache ? nkv : 0);   // v heads only matter when they are stored
   if (heads <= 0) return 0;
   if (heads > 65535) MI_REFUSE("rope: too many heads (%d)", heads);
@@ -252,10 +259,10 @@ extern "C" int mi_rope_write(void* qkv, const int* pos, const float* inv_freq, c
   dim3 grid(M, heads);
   if (dtype == MI_DTYPE_F32)
     rope_write_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, pos, inv_freq, slot, (float*)kcache,
-                                                           (float*)vcache, nq, nkv, d, rot);
+                                                           (float*)vcache, nq, nkv, d, rot, page_size);
   else if (dtype == MI_DTYPE_BF16)
     rope_write_kernel<bf16><<<grid, threads, 0, stream>>>((bf16*)qkv, pos, inv_freq, slot, (bf16*)kcache,
-                                                          (bf16*)vcache, nq, nkv, d, rot);
+                                                          (bf16*)vcache, nq, nkv, d, rot, page_size);
   else
     MI_REFUSE("rope: unknown dtype %d", dtype);
   MI_RETURN_LAUNCH_STATUS();

@@ -71,7 +71,7 @@ def _sig_elementwise(lib: ctypes.CDLL) -> None:
     lib.mi_add_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_int, c_int, c_float, c_int, c_int, c_void_p]
     lib.mi_rope_write.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     lib.mi_silu_mul.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
 
 
@@ -97,7 +97,9 @@ def _sig_attention_mma(lib: ctypes.CDLL) -> None:
     lib.mi_attention_decode.argtypes = [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
-        c_void_p]
+        c_void_p, c_void_p]
+    lib.mi_attention_decode_counters.argtypes = [c_int, c_int, c_int]
+    lib.mi_attention_wait_status.argtypes = [c_int]
     lib.mi_attention_prefill.argtypes = [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -206,7 +208,8 @@ def rope_write(
     vcache: torch.Tensor | None = None,
 ) -> None:
     """Rotate q and k inside ``qkv [M, (nq + 2 nkv) * d]`` (half layout, fp32 angles) and
-    store k and v at ``slots`` of ``kcache`` / ``vcache`` ``[n_slots, nkv, d]``."""
+    store k and v at ``slots`` (page * page_size + offset) of ``kcache`` / ``vcache``
+    ``[pages, nkv, page_size, d]``."""
     _cuda(qkv, positions, inv_freq, slots, kcache, vcache)
     M = qkv.shape[0]
     if qkv.dim() != 2 or qkv.shape[1] != (nq + 2 * nkv) * head_dim or not qkv.is_contiguous():
@@ -220,12 +223,14 @@ def rope_write(
         if slots is None or slots.dtype != torch.int32 or slots.shape != (M,):
             raise KernelError("rope: slots must be int32 [M]")
         for c in (kcache, vcache):
-            if (c is None or c.dtype != qkv.dtype or c.dim() != 3 or c.shape[1:] != (nkv, head_dim)
+            if (c is None or c.dtype != qkv.dtype or c.dim() != 4 or c.shape[1] != nkv or c.shape[3] != head_dim
                     or not c.is_contiguous()):
-                raise KernelError("rope: caches must be contiguous [slots, nkv, d] in qkv's dtype")
+                raise KernelError("rope: caches must be contiguous [pages, nkv, page_size, d] in qkv's dtype")
+    page_size = int(kcache.shape[2]) if kcache is not None else 0
     lib = _lib("elementwise")
     rc = lib.mi_rope_write(_ptr(qkv), _ptr(positions), _ptr(inv_freq), _ptr(slots), _ptr(kcache),
-                           _ptr(vcache), M, nq, nkv, head_dim, rotary_dim, _code(qkv.dtype), _stream())
+                           _ptr(vcache), M, nq, nkv, head_dim, rotary_dim, page_size, _code(qkv.dtype),
+                           _stream())
     _finish(lib, rc, "rope")
 
 
@@ -295,11 +300,12 @@ def _sms(device: torch.device) -> int:
 
 def decode_splits(n_requests: int, nq: int, nkv: int, max_kv_len: int, window: int, device) -> int:
     """How many slices of the keys each (request, key/value head) is cut into so that a
-    decode step fills the GPU (about four blocks per SM), never more than one per 64 keys."""
+    decode step fills the GPU in one wave (three blocks fit an SM), never more than one per
+    64 keys."""
     blocks = n_requests * nkv * ((nq // nkv + 7) // 8)
     span = min(max_kv_len, window + 63) if window else max_kv_len
     chunks = max(1, -(-span // 64))
-    return max(1, min(chunks, 64, -(-4 * _sms(device) // blocks)))
+    return max(1, min(chunks, 64, 3 * _sms(device) // blocks))
 
 
 def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq: int, nkv: int,
@@ -330,19 +336,32 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq:
                       nq, nkv, head_dim, scale, window)
 
 
-def _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, ints):
+def _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, page_size, ints):
     for name, t in ints:
         if t.dtype != torch.int32:
             raise KernelError(f"attention: {name} must be int32")
     if kcache.dtype != q.dtype or vcache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, out and caches must share a dtype")
-    if kcache.dim() != 3 or kcache.shape[1:] != (nkv, head_dim) or not kcache.is_contiguous() \
+    if kcache.dim() != 4 or kcache.shape[1:] != (nkv, page_size, head_dim) or not kcache.is_contiguous() \
             or vcache.shape != kcache.shape or not vcache.is_contiguous():
-        raise KernelError("attention: caches must be contiguous [slots, nkv, d]")
+        raise KernelError("attention: caches must be contiguous [pages, nkv, page_size, d]")
     if out.dim() != 2 or out.shape[1] != nq * head_dim or not out.is_contiguous():
         raise KernelError("attention: out must be contiguous [tokens, nq * d]")
     if block_table.dim() != 2 or block_table.stride(1) != 1:
         raise KernelError("attention: block_table must be [requests, pages] with unit inner stride")
+
+
+# Arrival counters of the split-key decode kernel, per device: zero between calls (the kernel
+# resets them).  Never freed once handed out: a captured CUDA graph may hold the address.
+_decode_counter_bufs: dict[int, list[torch.Tensor]] = {}
+
+
+def _decode_counters(device: torch.device, n: int) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    stack = _decode_counter_bufs.setdefault(idx, [])
+    if not stack or stack[-1].numel() < n:
+        stack.append(torch.zeros(max(n, 16384), dtype=torch.int32, device=device))
+    return stack[-1]
 
 
 def attention_decode(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, kv_len,
@@ -352,21 +371,26 @@ def attention_decode(q, q_stride, out, kcache, vcache, block_table, page_size, q
     _cuda(q, out, kcache, vcache, block_table, q_start, kv_len)
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_decode: bfloat16 only")
-    _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim,
+    _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, page_size,
                           (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len)))
-    part_o = part_ml = None
+    part_o = part_ml = counters = None
+    lib = _lib("attention_mma")
     if n_splits > 1:
         part_o = torch.empty((n_requests * nq * n_splits, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n_requests * nq * n_splits, 2), dtype=torch.float32, device=q.device)
-    lib = _lib("attention_mma")
+        counters = _decode_counters(q.device, lib.mi_attention_decode_counters(int(n_requests), nq, nkv))
     rc = lib.mi_attention_decode(
         _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_table),
         block_table.stride(0), int(page_size), _ptr(q_start), _ptr(kv_len), int(n_requests), nq, nkv,
-        head_dim, float(scale), int(window), int(n_splits), _ptr(part_o), _ptr(part_ml), _stream())
+        head_dim, float(scale), int(window), int(n_splits), _ptr(part_o), _ptr(part_ml), _ptr(counters),
+        _stream())
     _finish(lib, rc, "attention_decode")
-    if n_splits > 1:
-        global launch_count
-        launch_count += 1
+
+
+def attention_wait_status(reset: bool = True) -> int:
+    """1 if a tensor-core attention kernel gave up waiting for a copy since the last reset
+    (its output was then invalid); synchronises the device."""
+    return int(_lib("attention_mma").mi_attention_wait_status(1 if reset else 0))
 
 
 def attention_prefill(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, q_len, kv_len,
@@ -375,7 +399,7 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_table, page_size, 
     _cuda(q, out, kcache, vcache, block_table, q_start, q_len, kv_len, tile_req, tile_tok0)
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill: bfloat16 only")
-    _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim,
+    _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, page_size,
                           (("block_table", block_table), ("q_start", q_start), ("q_len", q_len),
                            ("kv_len", kv_len), ("tile_req", tile_req), ("tile_tok0", tile_tok0)))
     lib = _lib("attention_mma")
@@ -419,9 +443,9 @@ def attention_generic(
             raise KernelError(f"attention: {name} must be int32")
     if kcache.dtype != q.dtype or vcache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, out and caches must share a dtype")
-    if kcache.dim() != 3 or kcache.shape[1:] != (nkv, head_dim) or not kcache.is_contiguous() \
+    if kcache.dim() != 4 or kcache.shape[1:] != (nkv, page_size, head_dim) or not kcache.is_contiguous() \
             or vcache.shape != kcache.shape or not vcache.is_contiguous():
-        raise KernelError("attention: caches must be contiguous [slots, nkv, d]")
+        raise KernelError("attention: caches must be contiguous [pages, nkv, page_size, d]")
     if out.dim() != 2 or out.shape[1] != nq * head_dim or not out.is_contiguous():
         raise KernelError("attention: out must be contiguous [tokens, nq * d]")
     if block_table.dim() != 2 or block_table.stride(1) != 1:

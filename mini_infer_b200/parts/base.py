@@ -92,7 +92,7 @@ class LayerCache:
     """What one schedule entry's mixer gets from the cache manager."""
 
     group: int | None = None           # index into StepContext.groups
-    k: torch.Tensor | None = None      # [slots, kv_heads, head_dim]
+    k: torch.Tensor | None = None      # [pages, kv_heads, page_size, head_dim]
     v: torch.Tensor | None = None
     state: torch.Tensor | None = None  # [request slots, *StateNeed.shape]
     writes: bool = True

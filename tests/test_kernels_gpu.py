@@ -97,7 +97,8 @@ def test_rope_write(dtype, nq, nkv, d, rot):
     slots = torch.tensor([5, 6, 7, 39, 0, 17, 18, 19, 20, 33, 2], dtype=torch.int32)
     inv = P.rope_inv_freq(rot, 500000.0, None) if rot == d else (
         1.0 / (500000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / d)))
-    kc = torch.zeros(n_slots, nkv, d, dtype=dtype, device=DEV)
+    page = 8                                   # 40 slots = 5 pages of 8; a page is [nkv, page, d]
+    kc = torch.zeros(n_slots // page, nkv, page, d, dtype=dtype, device=DEV)
     vc = torch.zeros_like(kc)
     buf = qkv.to(DEV).clone()
     ops().rope_write(buf, nq, nkv, d, positions=pos.to(DEV), inv_freq=inv.to(DEV), rotary_dim=rot,
@@ -110,11 +111,13 @@ def test_rope_write(dtype, nq, nkv, d, rot):
     bound = tol(dtype, fp32=3e-5) * 4.0     # sine/cosine of angles up to 1.3e5 rad in fp32
     assert (got - want).abs().max().item() <= bound
     # the cache holds exactly what the buffer holds, at the given slots, and nothing else
+    by_slot = lambda c: c.permute(0, 2, 1, 3).reshape(n_slots, nkv, d)      # [slot, head, d]
+    ks, vs = by_slot(kc), by_slot(vc)
     for t in range(M):
-        assert torch.equal(kc[slots[t]].cpu(), buf[t].view(nq + 2 * nkv, d)[nq:nq + nkv].cpu())
-        assert torch.equal(vc[slots[t]].cpu(), qkv[t].view(nq + 2 * nkv, d)[nq + nkv:])
+        assert torch.equal(ks[slots[t]].cpu(), buf[t].view(nq + 2 * nkv, d)[nq:nq + nkv].cpu())
+        assert torch.equal(vs[slots[t]].cpu(), qkv[t].view(nq + 2 * nkv, d)[nq + nkv:])
     untouched = sorted(set(range(n_slots)) - set(slots.tolist()))
-    assert kc[untouched].abs().sum().item() == 0 and vc[untouched].abs().sum().item() == 0
+    assert ks[untouched].abs().sum().item() == 0 and vs[untouched].abs().sum().item() == 0
 
 
 def test_rope_write_refuses_bad_rotary_width():
@@ -213,7 +216,8 @@ def test_linear_library_and_streaming_kernels_agree():
 
 
 def build_paged(kv_lens, nkv, d, page, dtype, seed, n_extra_pages=3):
-    """Random keys/values of several requests scattered over shuffled pages."""
+    """Random keys/values of several requests scattered over shuffled pages, addressed by
+    slot ([pages * page, nkv, d]); ``as_pages`` gives the layout the kernels read."""
     g = torch.Generator().manual_seed(seed)
     n_pages = sum(-(-L // page) for L in kv_lens) + n_extra_pages
     perm = torch.randperm(n_pages, generator=g).tolist()
@@ -233,6 +237,12 @@ def build_paged(kv_lens, nkv, d, page, dtype, seed, n_extra_pages=3):
     width = max(len(t) for t in tables)
     bt = torch.tensor([t + [-1] * (width - len(t)) for t in tables], dtype=torch.int32)
     return kc, vc, bt, ks, vs
+
+
+def as_pages(c, page):
+    """[pages * page, nkv, d] by slot -> [pages, nkv, page, d], the cache layout."""
+    n, nkv, d = c.shape
+    return c.view(n // page, page, nkv, d).permute(0, 2, 1, 3).contiguous()
 
 
 def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, boost=None, kernel="generic",
@@ -255,6 +265,7 @@ def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, bo
     wide = wide.to(DEV)
     out = torch.full((M, nq * d), float("nan"), dtype=dtype, device=DEV)
     scale = 1.0 / math.sqrt(d)
+    kc, vc = as_pages(kc, page), as_pages(vc, page)
     if kernel == "generic":
         o.attention_generic(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), page, i32(q_start),
                             i32(q_lens), i32(kv_lens), i32(treq), i32(ttok), len(treq), nq, nkv, d, scale, window)
@@ -266,6 +277,8 @@ def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, bo
         assert all(n == 1 for n in q_lens)
         o.attention_decode(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), page, i32(q_start),
                            i32(kv_lens), len(q_lens), nq, nkv, d, scale, window, n_splits)
+    if kernel != "generic":
+        assert o.attention_wait_status() == 0, "a kernel gave up waiting for its copies"
     want = torch.empty(M, nq, d, dtype=torch.float64)
     for i, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
         want[q_start[i]:q_start[i] + ql] = P.causal_attention(

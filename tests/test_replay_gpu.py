@@ -68,6 +68,9 @@ def test_replay_matches_plain(which, dtype, cutting, model_dirs, plain):
     runner.cache.check()
     assert runner.cache.num_requests == 0
     assert runner.cache.num_free_pages() == runner.cache.pools[0].num_pages
+    if dtype == "bfloat16":
+        from mini_infer_b200.csrc import ops
+        assert ops.attention_wait_status() == 0
     want = plain[which]
     scale = max(1.0, max(float(np.abs(want[r]).max()) for r in want))
     for rid in requests:

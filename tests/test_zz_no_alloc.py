@@ -25,8 +25,8 @@ def paged_case(kv_lens, nq, nkv, d, page, seed):
     g = torch.Generator().manual_seed(seed)
     n_pages = sum(-(-L // page) for L in kv_lens) + 2
     perm = torch.randperm(n_pages, generator=g).tolist()
-    kc = torch.randn(n_pages * page, nkv, d, generator=g).to(torch.bfloat16)
-    vc = torch.randn(n_pages * page, nkv, d, generator=g).to(torch.bfloat16)
+    kc = torch.randn(n_pages, nkv, page, d, generator=g).to(torch.bfloat16)      # a page is [nkv, page, d]
+    vc = torch.randn(n_pages, nkv, page, d, generator=g).to(torch.bfloat16)
     tables = [[perm.pop() for _ in range(-(-L // page))] for L in kv_lens]
     width = max(len(t) for t in tables)
     bt = torch.tensor([t + [-1] * (width - len(t)) for t in tables], dtype=torch.int32)
