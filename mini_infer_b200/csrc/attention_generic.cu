@@ -12,7 +12,8 @@
 //   q    [tokens, q_stride]   head h at columns [h*d, (h+1)*d)
 //   out  [tokens, out_stride] same head layout
 //   kcache, vcache [pages, nkv, page_size, d]: the page_size keys of a page lie together
-//                  per key/value head
+//                  per key/value head; the 16-byte chunks of a row are permuted by the key's
+//                  in-page offset (mi_swizzled in common.cuh)
 //   block_table [requests, bt_stride] page ids;  q_start / q_len / kv_len [requests]
 //   tile_req / tile_tok0 [tiles]: request and first token (within the portion) of a tile
 #include "common.cuh"
@@ -38,6 +39,9 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   float* Ks = Qs + BQ * d;                // [BK][d + 1]
   float* Ss = Ks + BK * (d + 1);          // [BQ][BK]
   int* rowbase = reinterpret_cast<int*>(Ss + BQ * BK);  // [BK] element offset / d of each key row, -1: none
+  int* rowswz = rowbase + BK;                            // [BK] chunk permutation of each key row
+  constexpr int EPC = 16 / (int)sizeof(T);
+  const int swz_mask = mi_swizzle_mask(d, (int)sizeof(T));
 
   const int tid = threadIdx.x;
   const int tile = blockIdx.x, h = blockIdx.y;
@@ -74,6 +78,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         base = (page * nkv + kvh) * page_size + j % page_size;
       }
       rowbase[tid] = base;
+      rowswz[tid] = (j % page_size) & swz_mask;
     }
     __syncthreads();
     const int d4 = d >> 2;
@@ -82,7 +87,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
       const int base = rowbase[jj];
       float kf[4] = {0.f, 0.f, 0.f, 0.f}, vf[4] = {0.f, 0.f, 0.f, 0.f};
       if (base >= 0) {
-        const size_t off = (size_t)base * d + k4;
+        const size_t off = (size_t)base * d + ((((k4 / EPC) ^ rowswz[jj]) * EPC) + (k4 % EPC));
         Vec4<T> kv, vv;
         kv.load(kcache + off);
         vv.load(vcache + off);
@@ -158,7 +163,7 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
                   const int* tile_tok0, int n_tiles, int nq, int nkv, int d, float scale, int window,
                   cudaStream_t stream) {
   const size_t smem = ((size_t)BK * d + (size_t)BQ * d + (size_t)BK * (d + 1) + BQ * BK) * sizeof(float) +
-                      BK * sizeof(int);
+                      2 * BK * sizeof(int);
   auto kern = attention_generic_kernel<T, DMAX>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

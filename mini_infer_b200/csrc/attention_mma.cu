@@ -96,46 +96,79 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
 
-// Brings 64-key chunks of one request's keys and values into shared memory ([64][sd] bf16
-// each, rows padded for ldmatrix).  One thread per row: threads 0..63 copy the key rows,
-// 64..127 the value rows, each with ONE bulk copy of the whole row (2 * d bytes, contiguous in
-// the cache) that reports to the chunk's mbarrier.  The page id of a thread's row is fetched one
-// chunk ahead.  Rows outside [lo, hi) are zero-filled and their pages never touched.
-struct RowLoader {
+__device__ __forceinline__ int inpage_of(int j, int page_size, int page_shift) {
+  return page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+}
+
+// Brings 64-key chunks of one request's keys and values into shared memory, [64][d] bf16 each,
+// rows unpadded.  The cache stores every row with its 16-byte chunks permuted by the in-page
+// offset (common.cuh), so a linear copy lands in a layout that ldmatrix reads without bank
+// conflicts; the readers below apply the same permutation.
+//
+// With a power-of-two page size the keys of a page are one contiguous run per head, and a chunk
+// is 64 / min(page, 64) pieces: one thread per piece and tensor issues ONE bulk copy (4 KB for
+// 16-key pages of 128-wide heads) that reports to the chunk's mbarrier.  Other page sizes copy
+// row by row.  The page id a thread needs is fetched one chunk ahead.  Pieces (rows) that lie
+// wholly outside [lo, hi) are not copied; what they leave in shared memory is masked by the
+// caller (scores) or zeroed (values, zero_masked_values).
+struct PageLoader {
   int pg;
+
+  static __device__ __forceinline__ int piece_rows(int page_size, int page_shift) {
+    return page_shift >= 0 ? min(page_size, KCHUNK) : 1;
+  }
 
   __device__ __forceinline__ void fetch(const int* __restrict__ table, int page_size, int page_shift, int chunk,
                                         int lo, int hi) {
     pg = -1;
-    if (threadIdx.x < 2 * KCHUNK) {
-      const int j = chunk * KCHUNK + (threadIdx.x & (KCHUNK - 1));
-      if (j >= lo && j < hi) pg = table[page_shift >= 0 ? (j >> page_shift) : (j / page_size)];
+    const int rows = piece_rows(page_size, page_shift), n = KCHUNK / rows;
+    if (threadIdx.x < 2 * n) {
+      const int j0 = chunk * KCHUNK + (threadIdx.x % n) * rows;
+      if (j0 < hi && j0 + rows > lo) pg = table[page_shift >= 0 ? (j0 >> page_shift) : (j0 / page_size)];
     }
   }
 
   // bytes the chunk's copies will deliver (the same for every thread)
-  static __device__ __forceinline__ uint32_t chunk_bytes(int chunk, int lo, int hi, int d) {
-    const int a = max(lo, chunk * KCHUNK), b = min(hi, chunk * KCHUNK + KCHUNK);
-    return b > a ? (uint32_t)(b - a) * (uint32_t)d * 4u : 0u;   // keys and values, 2 bytes each
+  static __device__ __forceinline__ uint32_t chunk_bytes(int chunk, int lo, int hi, int d, int page_size,
+                                                         int page_shift) {
+    const int rows = piece_rows(page_size, page_shift), n = KCHUNK / rows, cb = chunk * KCHUNK;
+    const int first = lo > cb ? (lo - cb) / rows : 0;
+    const int last = min(n - 1, (hi - 1 - cb) / rows);
+    const int cnt = (hi > cb && last >= first) ? last - first + 1 : 0;
+    return (uint32_t)cnt * (uint32_t)rows * (uint32_t)d * 4u;   // keys and values, 2 bytes each
   }
 
   __device__ __forceinline__ void issue(bf16* kdst, bf16* vdst, const bf16* __restrict__ kcache,
                                         const bf16* __restrict__ vcache, int page_size, int page_shift, int chunk,
-                                        int nkv, int kvh, int d, int sd, uint64_t* bar) const {
-    if (threadIdx.x >= 2 * KCHUNK) return;
-    const int r = threadIdx.x & (KCHUNK - 1);
-    const bool is_v = threadIdx.x >= KCHUNK;
-    bf16* dst = (is_v ? vdst : kdst) + r * sd;
-    if (pg >= 0) {
-      const int j = chunk * KCHUNK + r;
-      const int inpage = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
-      const size_t off = (((size_t)pg * nkv + kvh) * page_size + inpage) * d;
-      bulk_copy_g2s(dst, (is_v ? vcache : kcache) + off, (uint32_t)d * 2u, bar);
-    } else {
-      for (int u = 0; u < (d >> 3); ++u) *reinterpret_cast<uint4*>(dst + u * 8) = make_uint4(0u, 0u, 0u, 0u);
-    }
+                                        int nkv, int kvh, int d, uint64_t* bar) const {
+    const int rows = piece_rows(page_size, page_shift), n = KCHUNK / rows;
+    if (threadIdx.x >= 2 * n || pg < 0) return;
+    const int piece = threadIdx.x % n;
+    const bool is_v = threadIdx.x >= n;
+    const int j0 = chunk * KCHUNK + piece * rows;
+    const size_t off = (((size_t)pg * nkv + kvh) * page_size + inpage_of(j0, page_size, page_shift)) * d;
+    bulk_copy_g2s((is_v ? vdst : kdst) + (size_t)piece * rows * d, (is_v ? vcache : kcache) + off,
+                  (uint32_t)rows * (uint32_t)d * 2u, bar);
   }
 };
+
+// Rows of the value tile whose keys are outside [lo, hi) may hold anything (never-written cache
+// slots, or shared memory nobody wrote); their probabilities are exactly 0, but 0 * NaN is NaN,
+// so they are cleared.  Only a request's first and last chunks have such rows.  Every thread of
+// the block must call this (it ends with a barrier when the chunk has masked rows).
+template <int THREADS>
+__device__ __forceinline__ void zero_masked_values(bf16* vtile, int chunk, int lo, int hi, int d) {
+  const int cb = chunk * KCHUNK;
+  if (cb >= lo && cb + KCHUNK <= hi) return;   // block-uniform
+  const int units = d >> 3;
+  for (int idx = threadIdx.x; idx < KCHUNK * units; idx += THREADS) {
+    const int r = idx / units, u = idx - r * units;
+    const int j = cb + r;
+    if (j < lo || j >= hi) *reinterpret_cast<uint4*>(vtile + r * d + u * 8) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  fence_proxy_async();   // these writes come before the copy engine's next writes to the tile
+  __syncthreads();
+}
 
 // ------------------------------------------------------------------------------- decode
 //
@@ -215,9 +248,9 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                         int d, float scale, int window, int n_splits, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int* __restrict__ counters, int* __restrict__ status) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int sd = d + 8;  // row stride in elements: 16 bytes of padding keep ldmatrix conflict-free
-  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);          // [DEC_STAGES][64][sd]
-  bf16* Vs = Ks + DEC_STAGES * KCHUNK * sd;              // [DEC_STAGES][64][sd]
+  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);          // [DEC_STAGES][64][d]
+  bf16* Vs = Ks + DEC_STAGES * KCHUNK * d;               // [DEC_STAGES][64][d]
+  const int swz_mask = mi_swizzle_mask(d, 2);
   float* merge_o = reinterpret_cast<float*>(smem_raw);   // [4][8][d] after the main loop
   __shared__ float merge_m[4][DEC_HEADS], merge_l[4][DEC_HEADS];
   __shared__ __align__(8) uint64_t bars[DEC_STAGES];
@@ -258,18 +291,17 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     fence_mbar_init();
   }
   __syncthreads();
-  RowLoader loader;
+  PageLoader loader;
 #pragma unroll
   for (int i = 0; i < DEC_STAGES - 1; ++i) {   // fill the ring but for one stage
     if (c0 + i < c1) {
       loader.fetch(table, page_size, page_shift, c0 + i, lo, kl);
-      if (tid == 0) mbar_expect_tx(&bars[i], RowLoader::chunk_bytes(c0 + i, lo, kl, d));
-      loader.issue(Ks + i * KCHUNK * sd, Vs + i * KCHUNK * sd, kcache, vcache, page_size, page_shift, c0 + i, nkv,
-                   kvh, d, sd, &bars[i]);
+      if (tid == 0) mbar_expect_tx(&bars[i], PageLoader::chunk_bytes(c0 + i, lo, kl, d, page_size, page_shift));
+      loader.issue(Ks + i * KCHUNK * d, Vs + i * KCHUNK * d, kcache, vcache, page_size, page_shift, c0 + i, nkv,
+                   kvh, d, &bars[i]);
     }
   }
   if (c0 + DEC_STAGES - 1 < c1) loader.fetch(table, page_size, page_shift, c0 + DEC_STAGES - 1, lo, kl);
-  __syncthreads();   // rows zero-filled above are visible to every warp
 
   // Q as the B operand: lane (qd, t4) holds head qd, dims ks*16 + 2*t4 + {0,1} and + 8
   const int ksteps = d >> 4;
@@ -300,16 +332,22 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     const int it = c - c0, buf = it % DEC_STAGES;
     if (c + DEC_STAGES - 1 < c1) {   // refill the stage that the previous iteration used up
       const int nb = (it + DEC_STAGES - 1) % DEC_STAGES;
-      if (tid == 0) mbar_expect_tx(&bars[nb], RowLoader::chunk_bytes(c + DEC_STAGES - 1, lo, kl, d));
-      loader.issue(Ks + nb * KCHUNK * sd, Vs + nb * KCHUNK * sd, kcache, vcache, page_size, page_shift,
-                   c + DEC_STAGES - 1, nkv, kvh, d, sd, &bars[nb]);
+      if (tid == 0)
+        mbar_expect_tx(&bars[nb], PageLoader::chunk_bytes(c + DEC_STAGES - 1, lo, kl, d, page_size, page_shift));
+      loader.issue(Ks + nb * KCHUNK * d, Vs + nb * KCHUNK * d, kcache, vcache, page_size, page_shift,
+                   c + DEC_STAGES - 1, nkv, kvh, d, &bars[nb]);
       if (c + DEC_STAGES < c1) loader.fetch(table, page_size, page_shift, c + DEC_STAGES, lo, kl);
     }
     const bool arrived =
         __all_sync(0xffffffffu, mbar_wait_bounded(&bars[buf], (it / DEC_STAGES) & 1, status));
-    const bf16* Kb = Ks + buf * KCHUNK * sd + (warp * 16) * sd;
-    const bf16* Vb = Vs + buf * KCHUNK * sd + (warp * 16) * sd;
+    zero_masked_values<NTHREADS>(Vs + buf * KCHUNK * d, c, lo, kl, d);
     const int key0 = c * KCHUNK + warp * 16;
+    // this lane's ldmatrix rows (keys) in the warp's 16-key slice, with their chunk permutation
+    const int kr = lane & 15, vr = (lane & 7) + (lane >> 4) * 8;
+    const int ksw = inpage_of(key0 + kr, page_size, page_shift) & swz_mask;
+    const int vsw = inpage_of(key0 + vr, page_size, page_shift) & swz_mask;
+    const bf16* Kb = Ks + buf * KCHUNK * d + (warp * 16 + kr) * d;
+    const bf16* Vb = Vs + buf * KCHUNK * d + (warp * 16 + vr) * d;
     if (arrived && key0 < kl && key0 + 16 > lo) {  // warp-uniform: this warp's 16 keys hold something visible
       // All fragment loads of a group of k-steps are issued before the first MMA that needs
       // them, and two accumulators halve the MMA dependency chain: the warp's critical path is
@@ -321,7 +359,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
         uint32_t kf[GROUP][4];
 #pragma unroll
         for (int i = 0; i < GROUP; ++i)
-          if (g0 + i < ksteps) ldmatrix_x4(kf[i], Kb + (lane & 15) * sd + (g0 + i) * 16 + (lane >> 4) * 8);
+          if (g0 + i < ksteps) ldmatrix_x4(kf[i], Kb + ((((g0 + i) * 2 + (lane >> 4)) ^ ksw) << 3));
 #pragma unroll
         for (int i = 0; i < GROUP; ++i)
           if (g0 + i < ksteps) {
@@ -336,7 +374,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 #pragma unroll
       for (int i = 0; i < GROUP; ++i)
         if (i < ksteps)
-          ldmatrix_x4_trans(vf[i], Vb + ((lane & 7) + (lane >> 4) * 8) * sd + i * 16 + ((lane >> 3) & 1) * 8);
+          ldmatrix_x4_trans(vf[i], Vb + (((i * 2 + ((lane >> 3) & 1)) ^ vsw) << 3));
       // s[0], s[1]: key qd, heads 2t, 2t+1;  s[2], s[3]: key qd + 8
       const int j0 = key0 + qd, j1 = j0 + 8;
       const bool ok0 = j0 < kl && j0 >= lo, ok1 = j1 < kl && j1 >= lo;
@@ -382,13 +420,12 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 #pragma unroll
         for (int i = 0; i < GROUP; ++i)
           if (g0 + i < ksteps)
-            ldmatrix_x4_trans(vf[i], Vb + ((lane & 7) + (lane >> 4) * 8) * sd + (g0 + i) * 16 + ((lane >> 3) & 1) * 8);
+            ldmatrix_x4_trans(vf[i], Vb + ((((g0 + i) * 2 + ((lane >> 3) & 1)) ^ vsw) << 3));
 #pragma unroll
         for (int i = 0; i < GROUP; ++i)
           if (g0 + i < ksteps) mma_bf16(o[g0 + i], vf[i], pb0, pb1);
       }
     }
-    fence_proxy_async();   // this buffer is next written by the copy engine
     if (__syncthreads_or(!arrived)) break;   // a wait gave up: stop (status is set)
   }
 
@@ -470,9 +507,10 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
                          int gb, int tt, int* __restrict__ status) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int sd = d + 8;
-  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);   // [PROWS][sd]
-  bf16* Ks = Qs + PROWS * sd;                        // [2][64][sd]
-  bf16* Vs = Ks + 2 * KCHUNK * sd;                // [2][64][sd]
+  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);   // [2][64][d], rows unpadded (chunks permuted)
+  bf16* Vs = Ks + 2 * KCHUNK * d;                 // [2][64][d]
+  bf16* Qs = Vs + 2 * KCHUNK * d;                 // [PROWS][sd], rows padded
+  const int swz_mask = mi_swizzle_mask(d, 2);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int qd = lane >> 2, t4 = lane & 3;
@@ -534,25 +572,35 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     fence_mbar_init();
   }
   __syncthreads();
-  RowLoader loader;
+  PageLoader loader;
   loader.fetch(table, page_size, page_shift, c0, lo, hi);
-  if (tid == 0) mbar_expect_tx(&bars[0], RowLoader::chunk_bytes(c0, lo, hi, d));
-  loader.issue(Ks, Vs, kcache, vcache, page_size, page_shift, c0, nkv, kvh, d, sd, &bars[0]);
+  if (tid == 0) mbar_expect_tx(&bars[0], PageLoader::chunk_bytes(c0, lo, hi, d, page_size, page_shift));
+  loader.issue(Ks, Vs, kcache, vcache, page_size, page_shift, c0, nkv, kvh, d, &bars[0]);
   if (c0 + 1 < c1) loader.fetch(table, page_size, page_shift, c0 + 1, lo, hi);
-  __syncthreads();   // the query tile and rows zero-filled above are visible to every warp
+  __syncthreads();   // the query tile is visible to every warp
 
   for (int c = c0; c < c1; ++c) {
     const int buf = (c - c0) & 1;
     if (c + 1 < c1) {
-      if (tid == 0) mbar_expect_tx(&bars[buf ^ 1], RowLoader::chunk_bytes(c + 1, lo, hi, d));
-      loader.issue(Ks + (buf ^ 1) * KCHUNK * sd, Vs + (buf ^ 1) * KCHUNK * sd, kcache, vcache, page_size, page_shift,
-                   c + 1, nkv, kvh, d, sd, &bars[buf ^ 1]);
+      if (tid == 0)
+        mbar_expect_tx(&bars[buf ^ 1], PageLoader::chunk_bytes(c + 1, lo, hi, d, page_size, page_shift));
+      loader.issue(Ks + (buf ^ 1) * KCHUNK * d, Vs + (buf ^ 1) * KCHUNK * d, kcache, vcache, page_size, page_shift,
+                   c + 1, nkv, kvh, d, &bars[buf ^ 1]);
       if (c + 2 < c1) loader.fetch(table, page_size, page_shift, c + 2, lo, hi);
     }
     const bool arrived = __all_sync(0xffffffffu, mbar_wait_bounded(&bars[buf], ((c - c0) >> 1) & 1, status));
-    const bf16* Kb = Ks + buf * KCHUNK * sd;
-    const bf16* Vb = Vs + buf * KCHUNK * sd;
+    zero_masked_values<PTHREADS>(Vs + buf * KCHUNK * d, c, lo, hi, d);
+    const bf16* Kb = Ks + buf * KCHUNK * d;
+    const bf16* Vb = Vs + buf * KCHUNK * d;
     const int key0 = c * KCHUNK;
+    // this lane's ldmatrix rows within each group of 16 keys, with their chunk permutations
+    const int kr = (lane & 7) + (lane >> 4) * 8, vr = (lane & 7) + ((lane >> 3) & 1) * 8;
+    int ksw[4], vsw[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      ksw[i] = inpage_of(key0 + i * 16 + kr, page_size, page_shift) & swz_mask;
+      vsw[i] = inpage_of(key0 + i * 16 + vr, page_size, page_shift) & swz_mask;
+    }
     if (arrived && warp_active && key0 < warp_hi && key0 + KCHUNK > warp_lo) {
       float s[8][4];
 #pragma unroll
@@ -565,7 +613,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 #pragma unroll
           for (int kp = 0; kp < 4; ++kp) {
             uint32_t kb[4];
-            ldmatrix_x4(kb, Kb + (kp * 16 + (lane & 7) + (lane >> 4) * 8) * sd + ks * 16 + ((lane >> 3) & 1) * 8);
+            ldmatrix_x4(kb, Kb + (kp * 16 + kr) * d + (((ks * 2 + ((lane >> 3) & 1)) ^ ksw[kp]) << 3));
             mma_bf16(s[2 * kp], a, kb[0], kb[1]);
             mma_bf16(s[2 * kp + 1], a, kb[2], kb[3]);
           }
@@ -622,14 +670,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             uint32_t vb[4];
-            ldmatrix_x4_trans(vb, Vb + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * sd + dt * 16 + (lane >> 4) * 8);
+            ldmatrix_x4_trans(vb, Vb + (kk * 16 + vr) * d + (((dt * 2 + (lane >> 4)) ^ vsw[kk]) << 3));
             mma_bf16(o[2 * dt], pa[kk], vb[0], vb[1]);
             mma_bf16(o[2 * dt + 1], pa[kk], vb[2], vb[3]);
           }
         }
       }
     }
-    fence_proxy_async();   // this buffer is next written by the copy engine
     if (__syncthreads_or(!arrived)) break;   // a wait gave up: stop (status is set)
   }
 
@@ -693,7 +740,9 @@ extern "C" int mi_attention_wait_status(int reset) {
   return v;
 }
 
-static size_t smem_bytes(int q_rows, int d) { return (size_t)(q_rows + 4 * KCHUNK) * (d + 8) * sizeof(bf16); }
+static size_t smem_bytes(int q_rows, int d) {   // padded query rows, two unpadded key and value tiles
+  return ((size_t)q_rows * (d + 8) + (size_t)4 * KCHUNK * d) * sizeof(bf16);
+}
 
 static int shift_of(int page_size) {  // log2 for powers of two, else -1
   if (page_size & (page_size - 1)) return -1;
@@ -723,12 +772,12 @@ extern "C" int mi_attention_decode(const void* q, int q_stride, void* out, int o
   if (n_splits > 1 && (!part_o || !part_ml || !counters)) MI_REFUSE("attention: split results need scratch memory");
   const int g = nq / nkv, hblocks = (g + DEC_HEADS - 1) / DEC_HEADS;
   if (B > 65535 || nkv * hblocks > 65535) MI_REFUSE("attention: batch or head count too large for one launch");
-  const size_t smem = (size_t)(2 * DEC_STAGES * KCHUNK) * (d + 8) * sizeof(bf16);
+  const size_t smem = (size_t)(2 * DEC_STAGES * KCHUNK) * d * sizeof(bf16);
   dim3 grid(n_splits, nkv * hblocks, B);
 #define MI_DECODE(DMAX)                                                                                 \
   do {                                                                                                  \
     auto kern = attention_decode_kernel<DMAX>;                                                          \
-    if (smem > 48 * 1024) {                                                                             \
+    if (smem > 40 * 1024) { /* the kernel also has a few KB of static shared memory */                  \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return (int)e;                                                              \
     }                                                                                                   \
@@ -769,7 +818,7 @@ extern "C" int mi_attention_prefill(const void* q, int q_stride, void* out, int 
 #define MI_PREFILL(DMAX)                                                                                \
   do {                                                                                                  \
     auto kern = attention_prefill_kernel<DMAX>;                                                         \
-    if (smem > 48 * 1024) {                                                                             \
+    if (smem > 40 * 1024) {                                                                             \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return (int)e;                                                              \
     }                                                                                                   \

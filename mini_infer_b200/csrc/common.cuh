@@ -105,4 +105,19 @@ __device__ __forceinline__ float mi_block_sum(float v, float* scratch) {
   return t;
 }
 
+// Cache rows are stored with their 16-byte chunks permuted: chunk c of the row of the token at
+// in-page offset t sits at chunk position c ^ (t & mask).  A linear copy of a page into shared
+// memory then lands in a layout whose 8-row ldmatrix reads touch all banks.  mask depends on
+// the row size only: chunks per row n = d * elem_size / 16; mask = min(n, 8) - 1 when n is a
+// power of two, else 0 (no permutation).
+__host__ __device__ inline int mi_swizzle_mask(int d, int elem_size) {
+  const int n = d * elem_size / 16;
+  if (n < 2 || (n & (n - 1))) return 0;
+  return (n < 8 ? n : 8) - 1;
+}
+// Physical element index within a row of logical element k (epc = elements per 16-byte chunk).
+__device__ __forceinline__ int mi_swizzled(int k, int t, int mask, int epc) {
+  return (((k / epc) ^ (t & mask)) * epc) + (k % epc);
+}
+
 static inline bool mi_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

@@ -193,7 +193,8 @@ extern "C" int mi_add_rmsnorm(const void* x, const float* res_in, float* res_out
 //   pos      [M]  absolute positions;  inv_freq [rot/2] fp32
 //   slot     [M]  flat cache slot (page * page_size + offset) of each token, < 0: no write
 //   kcache, vcache  [pages, nkv, page_size, d]  (may be null: rotate only); a slot's row for
-//                   key/value head h lies at ((page * nkv + h) * page_size + offset) * d
+//                   key/value head h lies at ((page * nkv + h) * page_size + offset) * d, with its
+//                   16-byte chunks permuted by the in-page offset (mi_swizzled in common.cuh)
 // q is rotated in place.  k is rotated in place too (so that a later reader of the
 // buffer sees what the cache holds) and stored; v is copied.  Angles, sine and cosine
 // are fp32; each output is rounded once.  rot = 0 means no rotation (store only).
@@ -209,13 +210,13 @@ __global__ void rope_write_kernel(T* __restrict__ qkv, const int* __restrict__ p
   T* head = qkv + (size_t)t * width + (size_t)h * d;
   const int sl = (slot && kcache) ? slot[t] : -1;
   const int half = rot >> 1;
+  constexpr int EPC = 16 / (int)sizeof(T);
+  const int mask = mi_swizzle_mask(d, (int)sizeof(T));
+  const int page = sl >= 0 ? sl / page_size : 0, off = sl >= 0 ? sl - page * page_size : 0;
   if (h < nq + nkv) {
     const bool is_k = h >= nq;
     T* dst = nullptr;
-    if (is_k && sl >= 0) {
-      const int page = sl / page_size, off = sl - page * page_size;
-      dst = kcache + (((size_t)page * nkv + (h - nq)) * page_size + off) * d;
-    }
+    if (is_k && sl >= 0) dst = kcache + (((size_t)page * nkv + (h - nq)) * page_size + off) * d;
     if (half > 0) {
       const float p = (float)pos[t];
       for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -228,17 +229,16 @@ __global__ void rope_write_kernel(T* __restrict__ qkv, const int* __restrict__ p
         head[i] = y1;
         head[i + half] = y2;
         if (dst) {
-          dst[i] = y1;
-          dst[i + half] = y2;
+          dst[mi_swizzled(i, off, mask, EPC)] = y1;
+          dst[mi_swizzled(i + half, off, mask, EPC)] = y2;
         }
       }
     }
     if (dst)  // un-rotated tail of k (rot < d)
-      for (int i = rot + threadIdx.x; i < d; i += blockDim.x) dst[i] = head[i];
+      for (int i = rot + threadIdx.x; i < d; i += blockDim.x) dst[mi_swizzled(i, off, mask, EPC)] = head[i];
   } else if (sl >= 0) {
-    const int page = sl / page_size, off = sl - page * page_size;
     T* dst = vcache + (((size_t)page * nkv + (h - nq - nkv)) * page_size + off) * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = head[i];
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[mi_swizzled(i, off, mask, EPC)] = head[i];
   }
 }
 

@@ -273,6 +273,43 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
     return out
 
 
+def cache_swizzle_mask(head_dim: int, dtype: torch.dtype) -> int:
+    """The chunk permutation mask of cache rows (``mi_swizzle_mask`` in common.cuh)."""
+    n = head_dim * torch.empty((), dtype=dtype).element_size() // 16
+    if n < 2 or n & (n - 1):
+        return 0
+    return min(n, 8) - 1
+
+
+def _chunk_permutation(page_size: int, head_dim: int, dtype: torch.dtype) -> torch.Tensor:
+    """``perm[t, k]``: where element ``k`` of the row at in-page offset ``t`` is stored."""
+    epc = 16 // torch.empty((), dtype=dtype).element_size()
+    mask = cache_swizzle_mask(head_dim, dtype)
+    t = torch.arange(page_size).view(-1, 1)
+    k = torch.arange(head_dim).view(1, -1)
+    return ((k // epc) ^ (t & mask)) * epc + k % epc
+
+
+def pack_cache_pages(by_slot: torch.Tensor, page_size: int) -> torch.Tensor:
+    """``[pages * page_size, kv_heads, d]`` (one row per slot) -> the cache layout
+    ``[pages, kv_heads, page_size, d]`` with each row's 16-byte chunks permuted by its in-page
+    offset.  For tests and tools; the engine writes the cache with the rope/store kernel."""
+    n, nkv, d = by_slot.shape
+    pages = by_slot.view(n // page_size, page_size, nkv, d).permute(0, 2, 1, 3).contiguous()
+    perm = _chunk_permutation(page_size, d, by_slot.dtype).to(by_slot.device)
+    out = torch.empty_like(pages)
+    out.scatter_(3, perm.view(1, 1, page_size, d).expand_as(pages), pages)
+    return out
+
+
+def unpack_cache_pages(pages: torch.Tensor) -> torch.Tensor:
+    """The inverse of ``pack_cache_pages``: ``[pages * page_size, kv_heads, d]`` by slot."""
+    n_pages, nkv, page_size, d = pages.shape
+    perm = _chunk_permutation(page_size, d, pages.dtype).to(pages.device)
+    plain = torch.gather(pages, 3, perm.view(1, 1, page_size, d).expand_as(pages))
+    return plain.permute(0, 2, 1, 3).reshape(n_pages * page_size, nkv, d)
+
+
 # Query tokens per tile of the CUDA-core attention kernel (BQ in attention_generic.cu).
 ATTENTION_TILE_TOKENS = 16
 

@@ -111,8 +111,7 @@ def test_rope_write(dtype, nq, nkv, d, rot):
     bound = tol(dtype, fp32=3e-5) * 4.0     # sine/cosine of angles up to 1.3e5 rad in fp32
     assert (got - want).abs().max().item() <= bound
     # the cache holds exactly what the buffer holds, at the given slots, and nothing else
-    by_slot = lambda c: c.permute(0, 2, 1, 3).reshape(n_slots, nkv, d)      # [slot, head, d]
-    ks, vs = by_slot(kc), by_slot(vc)
+    ks, vs = ops().unpack_cache_pages(kc), ops().unpack_cache_pages(vc)      # [slot, head, d]
     for t in range(M):
         assert torch.equal(ks[slots[t]].cpu(), buf[t].view(nq + 2 * nkv, d)[nq:nq + nkv].cpu())
         assert torch.equal(vs[slots[t]].cpu(), qkv[t].view(nq + 2 * nkv, d)[nq + nkv:])
@@ -240,9 +239,8 @@ def build_paged(kv_lens, nkv, d, page, dtype, seed, n_extra_pages=3):
 
 
 def as_pages(c, page):
-    """[pages * page, nkv, d] by slot -> [pages, nkv, page, d], the cache layout."""
-    n, nkv, d = c.shape
-    return c.view(n // page, page, nkv, d).permute(0, 2, 1, 3).contiguous()
+    """[pages * page, nkv, d] by slot -> the cache layout (pages per head, rows chunk-permuted)."""
+    return ops().pack_cache_pages(c, page)
 
 
 def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, boost=None, kernel="generic",
