@@ -113,6 +113,7 @@ __device__ __forceinline__ int inpage_of(int j, int page_size, int page_shift) {
 // caller (scores) or zeroed (values, zero_masked_values).
 struct PageLoader {
   int pg;
+  int t = threadIdx.x;   // which copy this thread issues; a producer warp sets its lane
 
   static __device__ __forceinline__ int piece_rows(int page_size, int page_shift) {
     return page_shift >= 0 ? min(page_size, KCHUNK) : 1;
@@ -122,8 +123,8 @@ struct PageLoader {
                                         int lo, int hi) {
     pg = -1;
     const int rows = piece_rows(page_size, page_shift), n = KCHUNK / rows;
-    if (threadIdx.x < 2 * n) {
-      const int j0 = chunk * KCHUNK + (threadIdx.x % n) * rows;
+    if (t < 2 * n) {
+      const int j0 = chunk * KCHUNK + (t % n) * rows;
       if (j0 < hi && j0 + rows > lo) pg = table[page_shift >= 0 ? (j0 >> page_shift) : (j0 / page_size)];
     }
   }
@@ -142,9 +143,9 @@ struct PageLoader {
                                         const bf16* __restrict__ vcache, int page_size, int page_shift, int chunk,
                                         int nkv, int kvh, int d, uint64_t* bar) const {
     const int rows = piece_rows(page_size, page_shift), n = KCHUNK / rows;
-    if (threadIdx.x >= 2 * n || pg < 0) return;
-    const int piece = threadIdx.x % n;
-    const bool is_v = threadIdx.x >= n;
+    if (t >= 2 * n || pg < 0) return;
+    const int piece = t % n;
+    const bool is_v = t >= n;
     const int j0 = chunk * KCHUNK + piece * rows;
     const size_t off = (((size_t)pg * nkv + kvh) * page_size + inpage_of(j0, page_size, page_shift)) * d;
     bulk_copy_g2s((is_v ? vdst : kdst) + (size_t)piece * rows * d, (is_v ? vcache : kcache) + off,
@@ -156,10 +157,18 @@ struct PageLoader {
 // slots, or shared memory nobody wrote); their probabilities are exactly 0, but 0 * NaN is NaN,
 // so they are cleared.  Only a request's first and last chunks have such rows.  Every thread of
 // the block must call this (it ends with a barrier when the chunk has masked rows).
-template <int THREADS>
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// barrier among the first `count` threads of the block (count a multiple of 32), id 1
+__device__ __forceinline__ void consumer_barrier(int count) {
+  asm volatile("bar.sync 1, %0;\n" ::"r"(count) : "memory");
+}
+
+template <int THREADS, bool NAMED = false>
 __device__ __forceinline__ void zero_masked_values(bf16* vtile, int chunk, int lo, int hi, int d) {
   const int cb = chunk * KCHUNK;
-  if (cb >= lo && cb + KCHUNK <= hi) return;   // block-uniform
+  if (cb >= lo && cb + KCHUNK <= hi) return;   // uniform over the calling threads
   const int units = d >> 3;
   for (int idx = threadIdx.x; idx < KCHUNK * units; idx += THREADS) {
     const int r = idx / units, u = idx - r * units;
@@ -167,7 +176,8 @@ __device__ __forceinline__ void zero_masked_values(bf16* vtile, int chunk, int l
     if (j < lo || j >= hi) *reinterpret_cast<uint4*>(vtile + r * d + u * 8) = make_uint4(0u, 0u, 0u, 0u);
   }
   fence_proxy_async();   // these writes come before the copy engine's next writes to the tile
-  __syncthreads();
+  if (NAMED) consumer_barrier(THREADS);
+  else __syncthreads();
 }
 
 // ------------------------------------------------------------------------------- decode
@@ -181,6 +191,7 @@ __device__ __forceinline__ void zero_masked_values(bf16* vtile, int chunk, int l
 
 #define DEC_HEADS 8   // query heads of one key/value head handled by a block
 #define DEC_STAGES 3  // 64-key chunks in the shared-memory ring (two are in flight while one is used)
+#define DEC_THREADS (NTHREADS + 32)   // four consumer warps and one producer warp
 
 // After a block has parked its slice's partial result: count arrivals for this (request,
 // head group); the block that arrives last merges all slices in slice order,
@@ -200,7 +211,7 @@ __device__ __forceinline__ void decode_merge_when_last(const float* __restrict__
   __threadfence();
   // (max, sum) of every (head, slice) first, all loads in flight at once
   __shared__ float sm_m[DEC_HEADS][64], sm_f[DEC_HEADS][64], sm_inv[DEC_HEADS];
-  for (int idx = threadIdx.x; idx < heads_here * n_splits; idx += NTHREADS) {
+  for (int idx = threadIdx.x; idx < heads_here * n_splits; idx += blockDim.x) {
     const int r = idx / n_splits, sp = idx - r * n_splits;
     const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + (size_t)(b * nq + head0 + r) * n_splits + sp);
     sm_m[r][sp] = ml.x;
@@ -240,7 +251,7 @@ __device__ __forceinline__ void decode_merge_when_last(const float* __restrict__
 }
 
 template <int DMAX>
-__global__ void __launch_bounds__(NTHREADS)
+__global__ void __launch_bounds__(DEC_THREADS)
 attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                         const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                         const int* __restrict__ block_table, int bt_stride, int page_size, int page_shift,
@@ -253,7 +264,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
   const int swz_mask = mi_swizzle_mask(d, 2);
   float* merge_o = reinterpret_cast<float*>(smem_raw);   // [4][8][d] after the main loop
   __shared__ float merge_m[4][DEC_HEADS], merge_l[4][DEC_HEADS];
-  __shared__ __align__(8) uint64_t bars[DEC_STAGES];
+  __shared__ __align__(8) uint64_t bars[DEC_STAGES];    // "full": a chunk has landed in its stage
+  __shared__ __align__(8) uint64_t empty[DEC_STAGES];   // "empty": all four consumer warps are done with it
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int qd = lane >> 2, t4 = lane & 3;
@@ -275,7 +287,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 
   if (status && *reinterpret_cast<volatile int*>(status)) return;   // an earlier block gave up waiting
   if (c0 >= c1) {  // nothing for this split (only possible with n_splits > 1)
-    for (int r = tid; r < heads_here; r += NTHREADS) {
+    for (int r = tid; r < heads_here; r += DEC_THREADS) {
       float* ml = part_ml + ((size_t)(b * nq + head0 + r) * n_splits + split) * 2;
       ml[0] = -INFINITY;
       ml[1] = 0.f;
@@ -287,22 +299,36 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 
   if (tid == 0) {
 #pragma unroll
-    for (int i = 0; i < DEC_STAGES; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < DEC_STAGES; ++i) {
+      mbar_init(&bars[i], 1);
+      mbar_init(&empty[i], 4);
+    }
     fence_mbar_init();
   }
   __syncthreads();
-  PageLoader loader;
-#pragma unroll
-  for (int i = 0; i < DEC_STAGES - 1; ++i) {   // fill the ring but for one stage
-    if (c0 + i < c1) {
-      loader.fetch(table, page_size, page_shift, c0 + i, lo, kl);
-      if (tid == 0) mbar_expect_tx(&bars[i], PageLoader::chunk_bytes(c0 + i, lo, kl, d, page_size, page_shift));
-      loader.issue(Ks + i * KCHUNK * d, Vs + i * KCHUNK * d, kcache, vcache, page_size, page_shift, c0 + i, nkv,
-                   kvh, d, &bars[i]);
+
+  if (warp == 4) {
+    // The producer warp: keeps the ring full.  Issuing a copy costs a warp hundreds of cycles;
+    // here that is nobody's critical path.
+    PageLoader loader;
+    loader.t = lane;
+    const int pieces = 2 * (KCHUNK / PageLoader::piece_rows(page_size, page_shift));   // copies per chunk
+    bool ok = true;
+    for (int c = c0; c < c1 && ok; ++c) {
+      const int it = c - c0, st = it % DEC_STAGES;
+      if (it >= DEC_STAGES)
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty[st], ((it / DEC_STAGES) - 1) & 1, status));
+      if (!ok) break;
+      if (lane == 0) mbar_expect_tx(&bars[st], PageLoader::chunk_bytes(c, lo, kl, d, page_size, page_shift));
+      __syncwarp();
+      for (int t0 = 0; t0 < pieces; t0 += 32) {   // more than 32 copies only with odd page sizes
+        loader.t = t0 + lane;
+        loader.fetch(table, page_size, page_shift, c, lo, kl);
+        loader.issue(Ks + st * KCHUNK * d, Vs + st * KCHUNK * d, kcache, vcache, page_size, page_shift, c, nkv, kvh,
+                     d, &bars[st]);
+      }
     }
   }
-  if (c0 + DEC_STAGES - 1 < c1) loader.fetch(table, page_size, page_shift, c0 + DEC_STAGES - 1, lo, kl);
-
   // Q as the B operand: lane (qd, t4) holds head qd, dims ks*16 + 2*t4 + {0,1} and + 8
   const int ksteps = d >> 4;
   uint32_t qb[DMAX / 16][2];
@@ -328,19 +354,11 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
   const int src0 = (2 * t4) * 4 + (qd >> 1), src1 = (2 * t4 + 1) * 4 + (qd >> 1);
   const bool odd_head = qd & 1;
 
-  for (int c = c0; c < c1; ++c) {
+  for (int c = c0; c < c1 && warp < 4; ++c) {
     const int it = c - c0, buf = it % DEC_STAGES;
-    if (c + DEC_STAGES - 1 < c1) {   // refill the stage that the previous iteration used up
-      const int nb = (it + DEC_STAGES - 1) % DEC_STAGES;
-      if (tid == 0)
-        mbar_expect_tx(&bars[nb], PageLoader::chunk_bytes(c + DEC_STAGES - 1, lo, kl, d, page_size, page_shift));
-      loader.issue(Ks + nb * KCHUNK * d, Vs + nb * KCHUNK * d, kcache, vcache, page_size, page_shift,
-                   c + DEC_STAGES - 1, nkv, kvh, d, &bars[nb]);
-      if (c + DEC_STAGES < c1) loader.fetch(table, page_size, page_shift, c + DEC_STAGES, lo, kl);
-    }
     const bool arrived =
         __all_sync(0xffffffffu, mbar_wait_bounded(&bars[buf], (it / DEC_STAGES) & 1, status));
-    zero_masked_values<NTHREADS>(Vs + buf * KCHUNK * d, c, lo, kl, d);
+    zero_masked_values<NTHREADS, true>(Vs + buf * KCHUNK * d, c, lo, kl, d);
     const int key0 = c * KCHUNK + warp * 16;
     // this lane's ldmatrix rows (keys) in the warp's 16-key slice, with their chunk permutation
     const int kr = lane & 15, vr = (lane & 7) + (lane >> 4) * 8;
@@ -426,31 +444,34 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
           if (g0 + i < ksteps) mma_bf16(o[g0 + i], vf[i], pb0, pb1);
       }
     }
-    if (__syncthreads_or(!arrived)) break;   // a wait gave up: stop (status is set)
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[buf]);   // this warp is done with the stage
+    if (!arrived) break;                       // a wait gave up: stop (status is set)
   }
+  __syncthreads();   // every warp has left its loop: the ring can be reused
 
-  // merge the four warps (the last __syncthreads above freed the K/V buffers)
+  // merge the four consumer warps
 #pragma unroll
   for (int hh = 0; hh < 2; ++hh) {
     float l = l_run[hh];
     l += __shfl_xor_sync(0xffffffffu, l, 4);
     l += __shfl_xor_sync(0xffffffffu, l, 8);
     l += __shfl_xor_sync(0xffffffffu, l, 16);
-    if (qd == 0) {
+    if (qd == 0 && warp < 4) {
       merge_m[warp][2 * t4 + hh] = m_run[hh];
       merge_l[warp][2 * t4 + hh] = l;
     }
   }
 #pragma unroll
   for (int i = 0; i < DMAX / 16; ++i) {
-    if (i < ksteps) {
+    if (i < ksteps && warp < 4) {
 #pragma unroll
       for (int e = 0; e < 4; ++e)   // o[i][e]: dim i*16 + qd + 8*(e>>1), head 2*t4 + (e&1)
         merge_o[((size_t)warp * DEC_HEADS + 2 * t4 + (e & 1)) * d + i * 16 + qd + 8 * (e >> 1)] = o[i][e];
     }
   }
   __syncthreads();
-  const int r = tid >> 4, cgrp = tid & 15;   // 8 heads x 16 threads
+  const int r = tid >> 4, cgrp = tid & 15;   // 8 heads x 16 threads (the producer warp's r is out of range)
   if (r < heads_here) {
     float m = merge_m[0][r];
 #pragma unroll
@@ -781,7 +802,7 @@ extern "C" int mi_attention_decode(const void* q, int q_stride, void* out, int o
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return (int)e;                                                              \
     }                                                                                                   \
-    kern<<<grid, NTHREADS, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride,            \
+    kern<<<grid, DEC_THREADS, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride,         \
                                            (const bf16*)kcache, (const bf16*)vcache, block_table,       \
                                            bt_stride, page_size, page_shift, q_start, kv_len, nq, nkv,  \
                                            d, scale, window, n_splits, part_o, part_ml, counters,       \

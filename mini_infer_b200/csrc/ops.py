@@ -336,13 +336,13 @@ def _sms(device: torch.device) -> int:
 
 
 def decode_splits(n_requests: int, nq: int, nkv: int, max_kv_len: int, window: int, device) -> int:
-    """How many slices of the keys each (request, key/value head) is cut into so that a
-    decode step fills the GPU in one wave (three blocks fit an SM), never more than one per
-    64 keys."""
+    """How many slices of the keys each (request, key/value head) is cut into: enough blocks
+    for about two per SM, but at least four 64-key chunks per slice (a slice costs a fixed
+    prologue and a merge, measured at roughly ten chunks' worth of time)."""
     blocks = n_requests * nkv * ((nq // nkv + 7) // 8)
     span = min(max_kv_len, window + 63) if window else max_kv_len
     chunks = max(1, -(-span // 64))
-    return max(1, min(chunks, 64, 3 * _sms(device) // blocks))
+    return max(1, min(2 * _sms(device) // blocks, chunks // 4, 64))
 
 
 def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq: int, nkv: int,
