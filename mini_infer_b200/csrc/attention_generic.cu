@@ -33,6 +33,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ kv_len, const int* __restrict__ tile_req,
                          const int* __restrict__ tile_tok0, int nq, int nkv, int d, float scale,
                          int window) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
   extern __shared__ __align__(16) float smem[];
   float* Vs = smem;                       // [BK][d]
   float* Qs = Vs + BK * d;                // [BQ][d]
@@ -170,7 +171,7 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(n_tiles, nq);
-  kern<<<grid, NTHREADS, smem, stream>>>((const T*)q, q_stride, (T*)out, out_stride, (const T*)kcache,
+  MI_LAUNCH((kern), grid, NTHREADS, smem, stream, (const T*)q, q_stride, (T*)out, out_stride, (const T*)kcache,
                                          (const T*)vcache, block_table, bt_stride, page_size, q_start,
                                          q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, scale, window);
   return 0;

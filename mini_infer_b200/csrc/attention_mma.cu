@@ -197,6 +197,7 @@ __device__ __forceinline__ void zero_masked_values(bf16* vtile, int chunk, int l
 // head group); the block that arrives last merges all slices in slice order,
 //   out = sum_s f_s O_s / sum_s f_s l_s,  f_s = 2^(m_s - m),
 // writes the output and resets the counter.  Nobody waits for anybody.
+template <int DMAX>
 __device__ __forceinline__ void decode_merge_when_last(const float* __restrict__ part_o,
                                                        const float* __restrict__ part_ml, int* counters,
                                                        int counter_index, bf16* __restrict__ out,
@@ -209,42 +210,85 @@ __device__ __forceinline__ void decode_merge_when_last(const float* __restrict__
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  // (max, sum) of every (head, slice) first, all loads in flight at once
-  __shared__ float sm_m[DEC_HEADS][64], sm_f[DEC_HEADS][64], sm_inv[DEC_HEADS];
-  for (int idx = threadIdx.x; idx < heads_here * n_splits; idx += blockDim.x) {
-    const int r = idx / n_splits, sp = idx - r * n_splits;
-    const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + (size_t)(b * nq + head0 + r) * n_splits + sp);
-    sm_m[r][sp] = ml.x;
-    sm_f[r][sp] = ml.y;
-  }
-  __syncthreads();
-  if (threadIdx.x < heads_here) {
-    const int r = threadIdx.x;
-    float m = -INFINITY;
-    for (int sp = 0; sp < n_splits; ++sp) m = fmaxf(m, sm_m[r][sp]);
-    float L = 0.f;
-    for (int sp = 0; sp < n_splits; ++sp) {
-      const float f = (sm_m[r][sp] == -INFINITY) ? 0.f : exp2f(sm_m[r][sp] - m);
-      L += sm_f[r][sp] * f;
-      sm_f[r][sp] = f;
-    }
-    sm_inv[r] = L > 0.f ? 1.f / L : 0.f;
-  }
-  __syncthreads();
   const int r = threadIdx.x >> 4, cgrp = threadIdx.x & 15;   // 8 heads x 16 threads
-  if (r < heads_here) {
-    const int head = head0 + r;
-    const float* po = part_o + (size_t)(b * nq + head) * n_splits * d;
-    bf16* orow = out + (size_t)tok * out_stride + (size_t)head * d;
-    for (int k = cgrp; k < d; k += 16) {
-      float acc = 0.f;
-#pragma unroll 8
-      for (int sp = 0; sp < n_splits; ++sp) {
-        const float f = sm_f[r][sp];
-        const float v = __ldcg(po + (size_t)sp * d + k);   // slices that saw nothing hold garbage: f is 0 there
-        acc += f != 0.f ? f * v : 0.f;
+  if (n_splits <= 8) {
+    // Few slices: every load this thread needs ((max, sum) of its head's slices and its eight
+    // output columns of every slice) is issued before the first one is used, so the merge
+    // costs one round trip to L2 instead of one per step.
+    if (r < heads_here) {
+      const int head = head0 + r;
+      const float2* ml = reinterpret_cast<const float2*>(part_ml) + (size_t)(b * nq + head) * n_splits;
+      const float* po = part_o + (size_t)(b * nq + head) * n_splits * d;
+      float2 mls[8];
+      float v[8][DMAX / 16];
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) {
+        mls[sp] = sp < n_splits ? __ldcg(ml + sp) : make_float2(-INFINITY, 0.f);
+#pragma unroll
+        for (int i = 0; i < DMAX / 16; ++i)
+          v[sp][i] = (sp < n_splits && cgrp + 16 * i < d) ? __ldcg(po + (size_t)sp * d + cgrp + 16 * i) : 0.f;
       }
-      orow[k] = __float2bfloat16_rn(acc * sm_inv[r]);
+      float m = -INFINITY;
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) m = fmaxf(m, mls[sp].x);
+      float L = 0.f, acc[DMAX / 16];
+#pragma unroll
+      for (int i = 0; i < DMAX / 16; ++i) acc[i] = 0.f;
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) {
+        const float f = (mls[sp].x == -INFINITY) ? 0.f : exp2f(mls[sp].x - m);
+        L += mls[sp].y * f;
+#pragma unroll
+        for (int i = 0; i < DMAX / 16; ++i) acc[i] += f != 0.f ? f * v[sp][i] : 0.f;   // unused slices hold garbage
+      }
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      bf16* orow = out + (size_t)tok * out_stride + (size_t)head * d;
+#pragma unroll
+      for (int i = 0; i < DMAX / 16; ++i)
+        if (cgrp + 16 * i < d) orow[cgrp + 16 * i] = __float2bfloat16_rn(acc[i] * inv);
+    }
+  } else {
+    // (max, sum) of every (head, slice) first, all loads in flight at once
+    __shared__ float sm_m[DEC_HEADS][64], sm_f[DEC_HEADS][64], sm_inv[DEC_HEADS];
+    for (int idx = threadIdx.x; idx < heads_here * n_splits; idx += blockDim.x) {
+      const int rr = idx / n_splits, sp = idx - rr * n_splits;
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml) + (size_t)(b * nq + head0 + rr) * n_splits + sp);
+      sm_m[rr][sp] = ml.x;
+      sm_f[rr][sp] = ml.y;
+    }
+    __syncthreads();
+    if (threadIdx.x < heads_here) {
+      const int rr = threadIdx.x;
+      float m = -INFINITY;
+      for (int sp = 0; sp < n_splits; ++sp) m = fmaxf(m, sm_m[rr][sp]);
+      float L = 0.f;
+      for (int sp = 0; sp < n_splits; ++sp) {
+        const float f = (sm_m[rr][sp] == -INFINITY) ? 0.f : exp2f(sm_m[rr][sp] - m);
+        L += sm_f[rr][sp] * f;
+        sm_f[rr][sp] = f;
+      }
+      sm_inv[rr] = L > 0.f ? 1.f / L : 0.f;
+    }
+    __syncthreads();
+    if (r < heads_here) {
+      const int head = head0 + r;
+      const float* po = part_o + (size_t)(b * nq + head) * n_splits * d;
+      bf16* orow = out + (size_t)tok * out_stride + (size_t)head * d;
+      float acc[DMAX / 16];
+#pragma unroll
+      for (int i = 0; i < DMAX / 16; ++i) acc[i] = 0.f;
+      for (int sp = 0; sp < n_splits; ++sp) {   // the columns of a slice are loaded together
+        const float f = sm_f[r][sp];
+        float v[DMAX / 16];
+#pragma unroll
+        for (int i = 0; i < DMAX / 16; ++i)
+          v[i] = (cgrp + 16 * i < d) ? __ldcg(po + (size_t)sp * d + cgrp + 16 * i) : 0.f;
+#pragma unroll
+        for (int i = 0; i < DMAX / 16; ++i) acc[i] += f != 0.f ? f * v[i] : 0.f;   // unused slices hold garbage
+      }
+#pragma unroll
+      for (int i = 0; i < DMAX / 16; ++i)
+        if (cgrp + 16 * i < d) orow[cgrp + 16 * i] = __float2bfloat16_rn(acc[i] * sm_inv[r]);
     }
   }
   if (threadIdx.x == 0) counters[counter_index] = 0;   // ready for the next call
@@ -258,6 +302,11 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                         const int* __restrict__ q_start, const int* __restrict__ kv_len, int nq, int nkv,
                         int d, float scale, int window, int n_splits, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int* __restrict__ counters, int* __restrict__ status) {
+  // The next kernel's blocks may be scheduled.  This kernel reads the batch description and
+  // the keys and values of earlier positions before it waits for the kernels ahead of it: the
+  // description was uploaded before the step's first kernel, and the step's own kernels write
+  // only the newest position of each request (kv_len - 1) and the queries.
+  mi_pdl_launch_dependents();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Ks = reinterpret_cast<bf16*>(smem_raw);          // [DEC_STAGES][64][d]
   bf16* Vs = Ks + DEC_STAGES * KCHUNK * d;               // [DEC_STAGES][64][d]
@@ -287,12 +336,13 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 
   if (status && *reinterpret_cast<volatile int*>(status)) return;   // an earlier block gave up waiting
   if (c0 >= c1) {  // nothing for this split (only possible with n_splits > 1)
+    mi_pdl_wait();
     for (int r = tid; r < heads_here; r += DEC_THREADS) {
       float* ml = part_ml + ((size_t)(b * nq + head0 + r) * n_splits + split) * 2;
       ml[0] = -INFINITY;
       ml[1] = 0.f;
     }
-    decode_merge_when_last(part_o, part_ml, counters, b * gridDim.y + blockIdx.y, out, out_stride, tok, b, nq, d,
+    decode_merge_when_last<DMAX>(part_o, part_ml, counters, b * gridDim.y + blockIdx.y, out, out_stride, tok, b, nq, d,
                            n_splits, head0, heads_here);
     return;
   }
@@ -319,6 +369,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
       if (it >= DEC_STAGES)
         ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty[st], ((it / DEC_STAGES) - 1) & 1, status));
       if (!ok) break;
+      if ((c + 1) * KCHUNK >= kl) mi_pdl_wait();   // the chunk with the newest position: written by this step
       if (lane == 0) mbar_expect_tx(&bars[st], PageLoader::chunk_bytes(c, lo, kl, d, page_size, page_shift));
       __syncwarp();
       for (int t0 = 0; t0 < pieces; t0 += 32) {   // more than 32 copies only with odd page sizes
@@ -329,6 +380,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
       }
     }
   }
+  if (warp < 4) mi_pdl_wait();   // the queries come from the kernel before this one
   // Q as the B operand: lane (qd, t4) holds head qd, dims ks*16 + 2*t4 + {0,1} and + 8
   const int ksteps = d >> 4;
   uint32_t qb[DMAX / 16][2];
@@ -508,7 +560,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
     }
   }
   if (n_splits > 1)
-    decode_merge_when_last(part_o, part_ml, counters, b * gridDim.y + blockIdx.y, out, out_stride, tok, b, nq, d,
+    decode_merge_when_last<DMAX>(part_o, part_ml, counters, b * gridDim.y + blockIdx.y, out, out_stride, tok, b, nq, d,
                            n_splits, head0, heads_here);
 }
 
@@ -526,6 +578,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
                          const int* __restrict__ kv_len, const int* __restrict__ tile_req,
                          const int* __restrict__ tile_tok0, int nq, int nkv, int d, float scale, int window,
                          int gb, int tt, int* __restrict__ status) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int sd = d + 8;
   bf16* Ks = reinterpret_cast<bf16*>(smem_raw);   // [2][64][d], rows unpadded (chunks permuted)
@@ -802,7 +855,7 @@ extern "C" int mi_attention_decode(const void* q, int q_stride, void* out, int o
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return (int)e;                                                              \
     }                                                                                                   \
-    kern<<<grid, DEC_THREADS, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride,         \
+    MI_LAUNCH((kern), grid, DEC_THREADS, smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,         \
                                            (const bf16*)kcache, (const bf16*)vcache, block_table,       \
                                            bt_stride, page_size, page_shift, q_start, kv_len, nq, nkv,  \
                                            d, scale, window, n_splits, part_o, part_ml, counters,       \
@@ -843,7 +896,7 @@ extern "C" int mi_attention_prefill(const void* q, int q_stride, void* out, int 
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return (int)e;                                                              \
     }                                                                                                   \
-    kern<<<grid, PTHREADS, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride,            \
+    MI_LAUNCH((kern), grid, PTHREADS, smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,            \
                                            (const bf16*)kcache, (const bf16*)vcache, block_table,       \
                                            bt_stride, page_size, page_shift, q_start, q_len, kv_len,    \
                                            tile_req, tile_tok0, nq, nkv, d, scale, window, gb,          \

@@ -40,6 +40,58 @@
 
 typedef __nv_bfloat16 bf16;
 
+// ---- programmatic dependent launch
+//
+// Every kernel of the engine is launched with programmatic stream serialization (MI_LAUNCH):
+// its blocks may be scheduled while the kernel before it in the stream still runs, which hides
+// the launch latency and lets a kernel do work that does not depend on its predecessors (set
+// up barriers, stream weights into shared memory) ahead of time.  The contract: a kernel calls
+// mi_pdl_wait() before it reads or writes anything that an earlier kernel may write or read;
+// before that it touches only immutable data (weights) and its own shared or tensor memory.
+// mi_pdl_launch_dependents() lets the next kernel's blocks be scheduled; it is called first
+// thing, so the look-ahead is limited only by what fits on the SMs.  Kernels launched by
+// other libraries take part as ordinary stream work: they start after everything before them
+// has finished, and a kernel after them waits for all of them.
+__device__ __forceinline__ void mi_pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+__device__ __forceinline__ void mi_pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+// for kernels with nothing to do before their inputs are ready
+__device__ __forceinline__ void mi_pdl_enter() {
+  mi_pdl_launch_dependents();
+  mi_pdl_wait();
+}
+
+#ifdef __CUDACC__
+#include <stdlib.h>
+// MINI_INFER_PDL=0 in the environment launches kernels the ordinary way (for comparisons).
+static inline bool mi_pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("MINI_INFER_PDL");
+    enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  return enabled != 0;
+}
+template <typename... KArgs, typename... Args>
+static inline cudaError_t mi_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = mi_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Args&&>(args)...);
+}
+#define MI_LAUNCH(kernel, grid, block, smem, stream, ...) \
+  mi_launch(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
+#endif
+
 __device__ __forceinline__ float mi_to_float(float x) { return x; }
 __device__ __forceinline__ float mi_to_float(bf16 x) { return __bfloat162float(x); }
 

@@ -15,6 +15,7 @@ MI_DEFINE_ERROR_API()
 template <typename T, int VEC>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  T* __restrict__ out, int H, int V) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
   const int t = blockIdx.x;
   const int id = ids[t];
   T* dst = out + (size_t)t * H;
@@ -42,12 +43,12 @@ extern "C" int mi_embedding(const void* table, const int* ids, void* out, int M,
   const bool vec = (H % 4 == 0) && mi_aligned(table, 16) && mi_aligned(out, 16) && ((H * es) % 16 == 0 || es == 4);
   int threads = H / 4 >= 256 ? 256 : (H / 4 >= 128 ? 128 : 64);
   if (dtype == MI_DTYPE_F32) {
-    if (vec) embedding_kernel<float, 4><<<M, threads, 0, stream>>>((const float*)table, ids, (float*)out, H, V);
-    else embedding_kernel<float, 1><<<M, threads, 0, stream>>>((const float*)table, ids, (float*)out, H, V);
+    if (vec) MI_LAUNCH((embedding_kernel<float, 4>), M, threads, 0, stream, (const float*)table, ids, (float*)out, H, V);
+    else MI_LAUNCH((embedding_kernel<float, 1>), M, threads, 0, stream, (const float*)table, ids, (float*)out, H, V);
   } else if (dtype == MI_DTYPE_BF16) {
     const bool vecb = vec && (H % 8 == 0);
-    if (vecb) embedding_kernel<bf16, 4><<<M, threads, 0, stream>>>((const bf16*)table, ids, (bf16*)out, H, V);
-    else embedding_kernel<bf16, 1><<<M, threads, 0, stream>>>((const bf16*)table, ids, (bf16*)out, H, V);
+    if (vecb) MI_LAUNCH((embedding_kernel<bf16, 4>), M, threads, 0, stream, (const bf16*)table, ids, (bf16*)out, H, V);
+    else MI_LAUNCH((embedding_kernel<bf16, 1>), M, threads, 0, stream, (const bf16*)table, ids, (bf16*)out, H, V);
   } else {
     MI_REFUSE("embedding: unknown dtype %d", dtype);
   }
@@ -67,6 +68,7 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, const float* __restr
                                    float* __restrict__ res_out, const WT* __restrict__ w,
                                    T* __restrict__ out, const int* __restrict__ rows, int H,
                                    float eps, int cache_row) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
   extern __shared__ float smem[];
   float* red = smem;         // 32 floats
   float* rbuf = smem + 32;   // H floats when cache_row
@@ -161,7 +163,7 @@ static int launch_add_rmsnorm(const void* x, const float* res_in, float* res_out
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  kern<<<M, threads, smem, stream>>>((const T*)x, res_in, res_out, (const WT*)w, (T*)out, rows, H, eps,
+  MI_LAUNCH((kern), M, threads, smem, stream, (const T*)x, res_in, res_out, (const WT*)w, (T*)out, rows, H, eps,
                                      cache_row);
   return 0;
 }
@@ -204,6 +206,7 @@ __global__ void rope_write_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   const float* __restrict__ inv_freq, const int* __restrict__ slot,
                                   T* __restrict__ kcache, T* __restrict__ vcache, int nq, int nkv,
                                   int d, int rot, int page_size) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
   // one block per (token, head); heads are q heads, then k heads, then v heads
   const int t = blockIdx.x, h = blockIdx.y;
   const int width = (nq + 2 * nkv) * d;
@@ -258,10 +261,10 @@ extern "C" int mi_rope_write(void* qkv, const int* pos, const float* inv_freq, c
   while (threads < 128 && threads * 2 <= d) threads <<= 1;
   dim3 grid(M, heads);
   if (dtype == MI_DTYPE_F32)
-    rope_write_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, pos, inv_freq, slot, (float*)kcache,
+    MI_LAUNCH((rope_write_kernel<float>), grid, threads, 0, stream, (float*)qkv, pos, inv_freq, slot, (float*)kcache,
                                                            (float*)vcache, nq, nkv, d, rot, page_size);
   else if (dtype == MI_DTYPE_BF16)
-    rope_write_kernel<bf16><<<grid, threads, 0, stream>>>((bf16*)qkv, pos, inv_freq, slot, (bf16*)kcache,
+    MI_LAUNCH((rope_write_kernel<bf16>), grid, threads, 0, stream, (bf16*)qkv, pos, inv_freq, slot, (bf16*)kcache,
                                                           (bf16*)vcache, nq, nkv, d, rot, page_size);
   else
     MI_REFUSE("rope: unknown dtype %d", dtype);
@@ -273,6 +276,7 @@ extern "C" int mi_rope_write(void* qkv, const int* pos, const float* inv_freq, c
 // ---------------------------------------------------------------------------
 template <typename T, int VEC>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
   const int m = blockIdx.x;
   const T* g = gu + (size_t)m * 2 * I;
   const T* u = g + I;
@@ -304,13 +308,13 @@ extern "C" int mi_silu_mul(const void* gu, void* out, int M, int I, int dtype, c
   const int threads = 256;
   if (vec) {
     dim3 grid(M, (I / 4 + threads - 1) / threads);
-    if (dtype == MI_DTYPE_F32) silu_mul_kernel<float, 4><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, I);
-    else if (dtype == MI_DTYPE_BF16) silu_mul_kernel<bf16, 4><<<grid, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I);
+    if (dtype == MI_DTYPE_F32) MI_LAUNCH((silu_mul_kernel<float, 4>), grid, threads, 0, stream, (const float*)gu, (float*)out, I);
+    else if (dtype == MI_DTYPE_BF16) MI_LAUNCH((silu_mul_kernel<bf16, 4>), grid, threads, 0, stream, (const bf16*)gu, (bf16*)out, I);
     else MI_REFUSE("silu_mul: unknown dtype %d", dtype);
   } else {
     dim3 grid(M, (I + threads - 1) / threads);
-    if (dtype == MI_DTYPE_F32) silu_mul_kernel<float, 1><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, I);
-    else if (dtype == MI_DTYPE_BF16) silu_mul_kernel<bf16, 1><<<grid, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I);
+    if (dtype == MI_DTYPE_F32) MI_LAUNCH((silu_mul_kernel<float, 1>), grid, threads, 0, stream, (const float*)gu, (float*)out, I);
+    else if (dtype == MI_DTYPE_BF16) MI_LAUNCH((silu_mul_kernel<bf16, 1>), grid, threads, 0, stream, (const bf16*)gu, (bf16*)out, I);
     else MI_REFUSE("silu_mul: unknown dtype %d", dtype);
   }
   MI_RETURN_LAUNCH_STATUS();

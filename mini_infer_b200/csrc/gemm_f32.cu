@@ -11,6 +11,7 @@ template <int BM, int BN, int BK, int TM, int TN, bool VEC>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C,
                 int M, int N, int K, int lda, int ldw, int ldc) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
   constexpr int THREADS = (BM / TM) * (BN / TN);
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
@@ -82,9 +83,9 @@ static void launch(const float* A, const float* W, float* C, int M, int N, int K
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   constexpr int THREADS = (BM / TM) * (BN / TN);
   if (vec)
-    gemm_f32_kernel<BM, BN, BK, TM, TN, true><<<grid, THREADS, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+    MI_LAUNCH((gemm_f32_kernel<BM, BN, BK, TM, TN, true>), grid, THREADS, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
   else
-    gemm_f32_kernel<BM, BN, BK, TM, TN, false><<<grid, THREADS, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+    MI_LAUNCH((gemm_f32_kernel<BM, BN, BK, TM, TN, false>), grid, THREADS, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
 }
 
 // Zero-padded K tails add exact zeros at the end of the sum, so they do not change it.

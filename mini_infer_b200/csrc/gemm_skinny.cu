@@ -53,6 +53,7 @@ __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out,
                    float* __restrict__ partial, int* __restrict__ counters, int M, int N, int K, int ldx,
                    int ldw, int ldo, int ksplit, int blocks_per_split) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
   constexpr int G = SK_UNITS / (2 * RT);   // k blocks per stage
   constexpr int ROWS = RT * 16;
   constexpr int MT = NT * 8;
@@ -242,7 +243,7 @@ extern "C" int mi_gemm_skinny(const void* x, const void* W, void* out, int M, in
     auto kern = gemm_skinny_kernel<4, NT, T>;                                                             \
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
     if (e != cudaSuccess) return (int)e;                                                                  \
-    kern<<<grid, SK_THREADS, smem, stream>>>(xp, wp, (T*)out, partial, counters, M, N, K, ldx, ldw, ldo,  \
+    MI_LAUNCH((kern), grid, SK_THREADS, smem, stream, xp, wp, (T*)out, partial, counters, M, N, K, ldx, ldw, ldo,  \
                                              k_slices, per_split);                                        \
   } while (0)
   if (out_dtype == MI_DTYPE_BF16) {

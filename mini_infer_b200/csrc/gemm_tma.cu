@@ -1,0 +1,500 @@
+// y[M, N] = x[M, K] * W[N, K]^T for few rows of x (decode): a weight-streaming product on
+// the fifth-generation tensor cores.
+//
+// With a handful of tokens the product is bound by reading W once, so the kernel is built
+// around that stream.  The operands are swapped: 128 rows of W are the M side of the MMA and
+// the tokens are its N side (16 to 128, zero-filled by the copy engine beyond M), so no tensor
+// core row is wasted on padding.  One persistent block per SM:
+//
+//   warp 0   one thread issues TMA tile loads (W: 128 rows x 64 k, x: tokens x 64 k, both with
+//            the 128-byte swizzle) into a ring of shared-memory stages; each load reports its
+//            bytes to the stage's "full" mbarrier
+//   warp 1   one thread issues tcgen05.mma (M 128, N tokens, K 16; four per stage) with the
+//            accumulator in tensor memory; tcgen05.commit frees the stage ("empty") and, at the
+//            end of a tile's k range, hands the accumulator to the epilogue
+//   warps 2-5  read the accumulator (tcgen05.ld, one TMEM lane = one row of W per thread),
+//            convert and store y, coalesced along N
+//
+// Work is cut stream-K fashion: the (tile, k chunk) units are numbered tile-major and every
+// block takes an equal contiguous range, so all SMs stream the same number of bytes whatever
+// N and K are.  A block whose range covers only part of a tile's k parks an fp32 partial
+// tile; the block that arrives last at a tile (a counter per tile) adds the partials in block
+// order and stores the result, so the sum's order is fixed and nobody waits for anybody.
+//
+// Every mbarrier wait is bounded: a wait that gives up sets a status word, the block leaves
+// its loops, frees its tensor memory and returns (the output is then wrong and the host finds
+// the status set).
+#include "common.cuh"
+
+#include <cuda.h>
+
+MI_DEFINE_ERROR_API()
+
+#define TILE_ROWS 128   // rows of W per tile: the MMA's M
+#define TILE_K 64       // k elements per stage: 128 bytes of bf16, one swizzle row
+#define UMMA_K 16
+#define GT_THREADS 192
+#define MAX_TOKENS 128
+#define SMEM_BUDGET (200 * 1024)   // ring of stages; about 100 KB per SM must be in flight to keep memory busy
+#define BOXES_PER_STAGE 2          // k boxes per stage: one box per stage leaves the issuing threads behind
+#define MAX_STAGES 12
+#define SPIN_LIMIT (1 << 22)
+
+static __device__ int g_gemm_tma_status;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* give_up) {
+  for (int it = 0; it < SPIN_LIMIT; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 1023) == 1023 && *give_up) return false;   // another role of this block gave up
+  }
+  atomicExch(&g_gemm_tma_status, 1);
+  *give_up = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::
+          "r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n" ::
+          "r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the
+// 128-byte swizzle in groups of 8 rows (1024 bytes apart).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);   // start address
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride between 8-row groups
+  d |= (uint64_t)1 << 46;                        // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                        // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M x N as given.
+__device__ __forceinline__ uint32_t umma_idesc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// The units [u0, u1) of block c out of G, and the block that holds unit u.
+__device__ __forceinline__ long long first_unit(long long total, int c, int G) { return total * c / G; }
+__device__ __forceinline__ int block_of_unit(long long total, long long u, int G) {
+  return (int)(((u + 1) * G - 1) / total);
+}
+
+// A block's range of units cut into segments, one per tile it touches.  In natural order the
+// first and the last segment may cover only part of their tile's k range.  They are processed
+// first and the whole tiles after them: the exchange of partial tiles then runs beside the
+// block's remaining stream instead of at the kernel's end.
+struct Segments {
+  int nseg, tile_begin, kc_begin, first_len, last_len, kchunks;
+  __device__ Segments(long long u0, long long u1, int kchunks_) : kchunks(kchunks_) {
+    const int n_units = (int)(u1 - u0);
+    tile_begin = (int)(u0 / kchunks);
+    kc_begin = (int)(u0 - (long long)tile_begin * kchunks);
+    first_len = min(kchunks - kc_begin, n_units);
+    const int rest = n_units - first_len;
+    nseg = 1 + (rest + kchunks - 1) / kchunks;
+    last_len = nseg > 1 ? rest - (nseg - 2) * kchunks : first_len;
+  }
+  // the i-th segment to process: its natural index, tile, first k chunk and length
+  __device__ __forceinline__ void get(int i, int& natural, int& tile, int& kc0, int& len) const {
+    natural = i;
+    if (nseg >= 3) natural = i == 0 ? 0 : (i == 1 ? nseg - 1 : i - 1);
+    tile = tile_begin + natural;
+    kc0 = natural == 0 ? kc_begin : 0;
+    len = natural == 0 ? first_len : (natural == nseg - 1 ? last_len : kchunks);
+  }
+};
+
+template <typename OutT>
+__global__ void __launch_bounds__(GT_THREADS, 1)
+gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                OutT* __restrict__ y, int ldy, int M, int N, int K, int n_tok, int stages, int kb, int chunked,
+                float* __restrict__ partials, int* __restrict__ counters) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // stage s: kb W boxes [128][64] bf16 (16 KB each), then kb x boxes [n_tok][64] bf16
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t w_bytes = TILE_ROWS * TILE_K * 2, x_bytes = (uint32_t)n_tok * TILE_K * 2;
+  const uint32_t stage_bytes = (w_bytes + x_bytes) * kb;
+  __shared__ __align__(8) uint64_t full[MAX_STAGES], empty[MAX_STAGES], acc_full, acc_empty;
+  __shared__ uint32_t tmem_base_holder;
+  __shared__ int give_up, is_last, epilogue_stop;
+
+  // The kernel that follows in the stream may start its blocks now; it waits for this grid's
+  // results itself before it touches them.
+  mi_pdl_launch_dependents();
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kchunks = (K + TILE_K * kb - 1) / (TILE_K * kb);   // a unit of work: kb boxes along k
+  const int n_tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
+  const long long total = (long long)n_tiles * kchunks;
+  const int G = gridDim.x;
+  const Segments segs(first_unit(total, blockIdx.x, G), first_unit(total, blockIdx.x + 1, G), kchunks);
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < (uint32_t)n_tok) tmem_cols <<= 1;
+  volatile int* gu = &give_up;
+
+  if (warp == 0) {
+    // The producer starts at once: it sets up the barriers, tells the other warps (without
+    // waiting for them) and streams W.  Weights do not depend on the kernel before this one,
+    // so the ring is filled with them before the wait for that kernel; x follows after it.
+    if (lane == 0) {
+      for (int i = 0; i < stages; ++i) {
+        mbar_init(&full[i], 1);
+        mbar_init(&empty[i], 1);
+      }
+      mbar_init(&acc_full, 1);
+      mbar_init(&acc_empty, 4);
+      give_up = 0;
+      epilogue_stop = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+      asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+      asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
+    }
+    __syncwarp();
+    asm volatile("bar.arrive 2, 192;\n" ::: "memory");
+    if (lane == 0) {
+      // the x boxes of unit kc (kb boxes along k), to the x part of a stage
+      auto load_x = [&](unsigned char* xdst, int kc, uint64_t* bar) {
+        if (chunked) {
+          tma_load_3d(xdst, &map_x, 0, 0, kc * kb, bar);
+        } else {
+          for (int b = 0; b < kb; ++b) tma_load_2d(xdst + b * x_bytes, &map_x, (kc * kb + b) * TILE_K, 0, bar);
+        }
+      };
+      int st = 0, round = 0, issued = 0;
+      bool waited = false, ok = true;
+      for (int i = 0; i < segs.nseg && ok; ++i) {
+        int natural, tile, kc0, len;
+        segs.get(i, natural, tile, kc0, len);
+        for (int kc = kc0; kc < kc0 + len; ++kc) {
+          if (!waited && issued == stages) {
+            // the ring is full of weights: now the kernel before this one must be done
+            mi_pdl_wait();
+            waited = true;
+            int st2 = 0, i2 = 0, kc2 = 0, nat2, tile2, kc02, len2 = 0;
+            for (int n = 0; n < issued; ++n) {   // x for the stages already under way
+              while (kc2 == len2) { segs.get(i2++, nat2, tile2, kc02, len2); kc2 = 0; }
+              unsigned char* dst2 = smem + (size_t)st2 * stage_bytes + kb * w_bytes;
+              load_x(dst2, kc02 + kc2, &full[st2]);
+              ++kc2;
+              ++st2;
+            }
+          }
+          if (round > 0 && !mbar_wait(&empty[st], (round - 1) & 1, gu)) { ok = false; break; }
+          unsigned char* dst = smem + (size_t)st * stage_bytes;
+          mbar_expect_tx(&full[st], stage_bytes);
+          if (chunked) {
+            tma_load_3d(dst, &map_w, 0, tile * TILE_ROWS, kc * kb, &full[st]);
+          } else {
+            for (int b = 0; b < kb; ++b)
+              tma_load_2d(dst + b * w_bytes, &map_w, (kc * kb + b) * TILE_K, tile * TILE_ROWS, &full[st]);
+          }
+          if (waited) load_x(dst + kb * w_bytes, kc, &full[st]);
+          ++issued;
+          if (++st == stages) { st = 0; ++round; }
+        }
+      }
+      if (!waited && ok) {   // fewer units than stages: everything is under way, x still to come
+        mi_pdl_wait();
+        int st2 = 0, i2 = 0, kc2 = 0, nat2, tile2, kc02, len2 = 0;
+        for (int n = 0; n < issued; ++n) {
+          while (kc2 == len2) { segs.get(i2++, nat2, tile2, kc02, len2); kc2 = 0; }
+          unsigned char* dst2 = smem + (size_t)st2 * stage_bytes + kb * w_bytes;
+          load_x(dst2, kc02 + kc2, &full[st2]);
+          ++kc2;
+          ++st2;
+        }
+      }
+    }
+  } else {
+    if (warp == 1) {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_holder)),
+                   "r"(tmem_cols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    asm volatile("bar.sync 2, 192;\n" ::: "memory");   // barriers initialised (warp 0 arrived), TMEM allocated
+    tc_fence_after();
+  }
+  const uint32_t tmem_acc = warp == 0 ? 0u : tmem_base_holder;
+
+  if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(TILE_ROWS, n_tok);
+      int st = 0, round = 0;
+      bool ok = true;
+      for (int i = 0; i < segs.nseg && ok; ++i) {
+        int natural, tile, kc0, len;
+        segs.get(i, natural, tile, kc0, len);
+        if (i > 0) {   // the epilogue must have drained the previous accumulator
+          if (!mbar_wait(&acc_empty, (i - 1) & 1, gu)) break;
+          tc_fence_after();
+        }
+        for (int kc = 0; kc < len; ++kc) {
+          if (!mbar_wait(&full[st], round & 1, gu)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a0 = smem_u32(smem + (size_t)st * stage_bytes), b0 = a0 + kb * w_bytes;
+          for (int b = 0; b < kb; ++b) {
+            const uint64_t da = umma_desc_sw128(a0 + b * w_bytes), db = umma_desc_sw128(b0 + b * x_bytes);
+#pragma unroll
+            for (int k = 0; k < TILE_K / UMMA_K; ++k)   // 32 bytes further along k: 2 in the address field
+              umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kc == 0 && b == 0 && k == 0) ? 0u : 1u);
+          }
+          umma_commit(&empty[st]);           // the stage is free once these MMAs have read it
+          if (++st == stages) { st = 0; ++round; }
+        }
+        if (ok) umma_commit(&acc_full);      // the accumulator of this segment is complete
+      }
+    }
+  } else if (warp >= 2) {
+    // epilogue: TMEM lane quarter (warp & 3), one row of W per thread
+    const int quarter = warp & 3, row = quarter * 32 + lane;
+    const int etid = (warp - 2) * 32 + lane;   // 0..127 among the epilogue threads
+    for (int i = 0; i < segs.nseg; ++i) {
+      int natural, tile, kc0, len;
+      segs.get(i, natural, tile, kc0, len);
+      const bool whole = (len == kchunks);
+      const int n = tile * TILE_ROWS + row;
+      // the four warps leave together or not at all (they meet at named barriers below)
+      if (!mbar_wait(&acc_full, i & 1, gu)) epilogue_stop = 1;
+      asm volatile("bar.sync 1, 128;\n" ::: "memory");
+      if (epilogue_stop) break;
+      tc_fence_after();
+      // partial tiles of this block: slot 0 for its first segment (natural order), 1 for its last
+      const int slot = blockIdx.x * 2 + (natural == 0 ? 0 : 1);
+      float* part = partials + (size_t)slot * n_tok * TILE_ROWS;
+      for (int c0 = 0; c0 < n_tok; c0 += 16) {
+        float v[16];
+        tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+        if (whole) {
+          if (n < N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c0 + j < M) y[(size_t)(c0 + j) * ldy + n] = mi_from_float<OutT>(v[j]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c0 + j < M) part[(size_t)(c0 + j) * TILE_ROWS + row] = v[j];
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty);
+      if (!whole) {
+        // count this block in; the last one to arrive adds the partial tiles in block order
+        __threadfence();
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        const long long t0 = (long long)tile * kchunks;
+        const int c_first = block_of_unit(total, t0, G), c_last = block_of_unit(total, t0 + kchunks - 1, G);
+        if (etid == 0) is_last = (atomicAdd(&counters[tile], 1) == c_last - c_first) ? 1 : 0;
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        if (is_last) {
+          __threadfence();
+          // Every block after the tile's first one begins inside the tile, so the tile is its
+          // first segment (slot 0); the first block's is slot 0 only if it begins with the tile.
+          const int first_slot = c_first * 2 + (first_unit(total, c_first, G) == t0 ? 0 : 1);
+          if (n < N) {
+            // sixteen tokens and four blocks' partial tiles at a time: 64 independent loads are in
+            // flight per thread; the additions still run in block order
+            for (int j0 = 0; j0 < M; j0 += 16) {
+              float acc[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+              for (int cb = c_first; cb <= c_last; cb += 4) {
+                float v[4][16];
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                  const int c = cb + cc;
+                  const int s = c == c_first ? first_slot : c * 2;
+                  const float* p = partials + ((size_t)s * n_tok + j0) * TILE_ROWS + row;
+#pragma unroll
+                  for (int j = 0; j < 16; ++j)   // only rows below M were written
+                    v[cc][j] = (c <= c_last && j0 + j < M) ? __ldcg(p + (size_t)j * TILE_ROWS) : 0.f;
+                }
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) acc[j] += v[cc][j];
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (j0 + j < M) y[(size_t)(j0 + j) * ldy + n] = mi_from_float<OutT>(acc[j]);
+            }
+          }
+          if (etid == 0) counters[tile] = 0;   // ready for the next call
+        }
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");   // is_last is read before it is written again
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base_holder), "r"(tmem_cols) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------- host
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// A [rows, cols] bf16 matrix with `ld` elements between rows, read in boxes of box_rows x 64
+// with the 128-byte swizzle; out-of-range elements read as zero.
+// The same matrix seen as [cols / 64 chunks][rows][64] (cols a multiple of 64): one copy then
+// brings `chunks` consecutive boxes, laid out one after the other.
+static bool make_map_chunked(CUtensorMap* map, const void* base, int rows, int cols, long long ld, int box_rows,
+                             int chunks) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {TILE_K, (cuuint64_t)rows, (cuuint64_t)(cols / TILE_K)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, TILE_K * 2};
+  cuuint32_t box[3] = {TILE_K, (cuuint32_t)box_rows, (cuuint32_t)chunks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {TILE_K, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+extern "C" int mi_gemm_tma_status(int reset) {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_gemm_tma_status, sizeof(int));
+  if (reset && v) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_gemm_tma_status, &z, sizeof(int));
+  }
+  return v;
+}
+
+// floats of `partials` and ints of `counters` a call with these sizes needs
+extern "C" int mi_gemm_tma_workspace(int M, int N, int blocks, long long* partial_floats, int* counter_ints) {
+  const int n_tok = ((M < 1 ? 1 : M) + 15) / 16 * 16;
+  *partial_floats = (long long)blocks * 2 * n_tok * TILE_ROWS;
+  *counter_ints = (N + TILE_ROWS - 1) / TILE_ROWS;
+  return 0;
+}
+
+// x [M, K] bf16 (row stride ldx), w [N, K] bf16 contiguous, y [M, N] (row stride ldy) bf16 or
+// fp32.  `blocks` is the number of persistent blocks (the number of SMs); `partials` and
+// `counters` (zero before the first call; the kernel leaves them zero) as mi_gemm_tma_workspace
+// says.
+extern "C" int mi_gemm_tma(const void* x, long long ldx, const void* w, void* y, long long ldy, int M, int N, int K,
+                           int out_dtype, int blocks, float* partials, int* counters, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > MAX_TOKENS) MI_REFUSE("gemm_tma: %d rows of x; this kernel takes at most %d", M, MAX_TOKENS);
+  if (K <= 0 || K % 8 != 0 || ldx % 8 != 0)
+    MI_REFUSE("gemm_tma: K (%d) and the row stride of x (%lld) must be multiples of 8 (16-byte rows)", K, ldx);
+  if (!mi_aligned(x, 16) || !mi_aligned(w, 16)) MI_REFUSE("gemm_tma: operands must be 16-byte aligned");
+  if (blocks <= 0) MI_REFUSE("gemm_tma: bad block count %d", blocks);
+  if (out_dtype != MI_DTYPE_BF16 && out_dtype != MI_DTYPE_F32) MI_REFUSE("gemm_tma: unknown output dtype %d", out_dtype);
+  const int n_tok = (M + 15) / 16 * 16;
+  const int kb = BOXES_PER_STAGE;
+  const int budget = SMEM_BUDGET;
+  const long long total = (long long)((N + TILE_ROWS - 1) / TILE_ROWS) * ((K + TILE_K * kb - 1) / (TILE_K * kb));
+  const int grid = (int)(total < blocks ? total : blocks);
+  const int stage_bytes = (TILE_ROWS * TILE_K * 2 + n_tok * TILE_K * 2) * kb;
+  int stages = budget / stage_bytes;
+  if (stages < 2) stages = 2;
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  const size_t smem = (size_t)stages * stage_bytes + 1024;
+  CUtensorMap map_w, map_x;
+  const int chunked = (K % TILE_K == 0 && kb > 1) ? 1 : 0;   // else the k tail needs the 2-D view's zero fill
+  const bool maps_ok = chunked ? (make_map_chunked(&map_w, w, N, K, K, TILE_ROWS, kb) &&
+                                  make_map_chunked(&map_x, x, M, K, ldx, n_tok, kb))
+                               : (make_map(&map_w, w, N, K, K, TILE_ROWS) && make_map(&map_x, x, M, K, ldx, n_tok));
+  if (!maps_ok)
+    MI_REFUSE("gemm_tma: the driver refused a tensor map (N %d, K %d, M %d)", N, K, M);
+  cudaError_t e;
+  if (out_dtype == MI_DTYPE_BF16) {
+    auto kern = gemm_tma_kernel<bf16>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    MI_LAUNCH((kern), grid, GT_THREADS, smem, stream, map_w, map_x, (bf16*)y, (int)ldy, M, N, K, n_tok, stages, kb, chunked, partials, counters);
+  } else {
+    auto kern = gemm_tma_kernel<float>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    MI_LAUNCH((kern), grid, GT_THREADS, smem, stream, map_w, map_x, (float*)y, (int)ldy, M, N, K, n_tok, stages, kb, chunked, partials, counters);
+  }
+  MI_RETURN_LAUNCH_STATUS();
+}

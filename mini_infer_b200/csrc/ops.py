@@ -11,6 +11,7 @@ path: a tensor that is not on a CUDA device is an error.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -114,7 +115,16 @@ def _sig_gemm_skinny(lib: ctypes.CDLL) -> None:
     lib.mi_gemm_skinny_plan.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)]
 
 
+def _sig_gemm_tma(lib: ctypes.CDLL) -> None:
+    lib.mi_gemm_tma.argtypes = [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int,
+                                c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
+    lib.mi_gemm_tma_workspace.argtypes = [c_int, c_int, c_int, ctypes.POINTER(ctypes.c_longlong),
+                                          ctypes.POINTER(c_int)]
+    lib.mi_gemm_tma_status.argtypes = [c_int]
+
+
 _SIGNATURES = {
+    "gemm_tma": _sig_gemm_tma,
     "gemm_skinny": _sig_gemm_skinny,
     "attention_mma": _sig_attention_mma,
     "elementwise": _sig_elementwise,
@@ -584,6 +594,65 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch
     return out
 
 
+TMA_GEMM_MAX_ROWS = 128            # what gemm_tma.cu takes
+# ``linear`` routes inputs of up to this many rows to gemm_tma; measured on a B200 inside a
+# captured decode step (Llama 3.1 8B sizes) it is ahead of the library product up to 8 rows
+# (3.91 vs 4.15 ms per step at batch 8) and behind it from 16 rows on (4.39 vs 4.26 ms).
+TMA_GEMM_DISPATCH_ROWS = 8
+USE_TMA_GEMM = os.environ.get("MINI_INFER_TMA_GEMM", "1") != "0"
+_tma_ws: dict[int, list[tuple[torch.Tensor, torch.Tensor]]] = {}
+
+
+def _tma_workspace(device: torch.device, floats: int, counters: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Partial tiles and per-tile arrival counters (zero between calls) of the streaming
+    product, per device; never freed once handed out (a captured graph may hold the address)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    stack = _tma_ws.setdefault(idx, [])
+    if not stack or stack[-1][0].numel() < floats or stack[-1][1].numel() < counters:
+        stack.append((
+            torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device),
+            torch.zeros(max(counters, 4096), dtype=torch.int32, device=device),
+        ))
+    return stack[-1]
+
+
+def gemm_tma_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``gemm_tma`` takes these operands (few rows, 16-byte aligned rows)."""
+    return (x.dim() == 2 and w.dim() == 2 and 0 < x.shape[0] <= TMA_GEMM_MAX_ROWS and x.shape[1] % 8 == 0
+            and x.stride(1) == 1 and w.is_contiguous() and (x.shape[0] == 1 or x.stride(0) % 8 == 0)
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tma(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``x [M <= 128, K] @ w [N, K]^T`` for bfloat16 operands on the tcgen05 tensor cores,
+    streaming ``w`` once through TMA (gemm_tma.cu); the result is bfloat16 or float32."""
+    global launch_count
+    _cuda(x, w)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tma: operands must be bfloat16")
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1] or x.stride(1) != 1 or not w.is_contiguous():
+        raise KernelError(f"gemm_tma: shapes {tuple(x.shape)} x {tuple(w.shape)}^T do not match")
+    M, K = x.shape
+    N = w.shape[0]
+    lib = _lib("gemm_tma")
+    blocks = _sms(x.device)
+    floats, counters = ctypes.c_longlong(0), c_int(0)
+    lib.mi_gemm_tma_workspace(M, N, blocks, ctypes.byref(floats), ctypes.byref(counters))
+    partial, count = _tma_workspace(x.device, int(floats.value), int(counters.value))
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    launch_count += 1
+    rc = lib.mi_gemm_tma(_ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), N, M, N, K, _code(out_dtype),
+                         blocks, _ptr(partial), _ptr(count), _stream())
+    _finish(lib, rc, "gemm_tma")
+    return out
+
+
+def gemm_tma_status(reset: bool = True) -> int:
+    """Non-zero when a block of the streaming product gave up a bounded wait since the last
+    reset (its output is then wrong).  Synchronises the device."""
+    return int(_lib("gemm_tma").mi_gemm_tma_status(1 if reset else 0))
+
+
 def _skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     M, K = x.shape
     return (M <= SKINNY_MAX_ROWS and K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1
@@ -598,11 +667,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     """``x [M, K] @ w [N, K]^T``.
 
     float32 operands run the true-fp32 CUDA-core kernel (never a library product, which
-    could pick a reduced-precision mode).  bfloat16 operands use the library product with
-    fp32 accumulation, as the reference does for every linear layer
-    (``distributed/linear.py:167``); measured on a B200 it streams weights at 4.5 to 6.7 TB/s
-    for decode-sized inputs, ahead of the hand-written kernel of gemm_skinny.cu, which stays
-    available as ``gemm_skinny`` (set ``USE_SKINNY_GEMM`` to route small inputs to it).
+    could pick a reduced-precision mode).  bfloat16 operands with few rows (decode) run the
+    weight-streaming tcgen05 kernel of gemm_tma.cu, which starts streaming weights while the
+    kernel before it still runs; other bfloat16 operands use the library product with fp32
+    accumulation, as the reference does for every linear layer (``distributed/linear.py:167``).
+    The CUDA-core kernel of gemm_skinny.cu stays available as ``gemm_skinny``.
     ``out_dtype=float32`` keeps the accumulator's precision in the result (used for logits).
     """
     global _MM_OUT_DTYPE, launch_count
@@ -615,6 +684,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     _cuda(x, w)
     if out_dtype not in (None, torch.bfloat16, torch.float32):
         raise KernelError(f"linear: unsupported output dtype {out_dtype}")
+    if USE_TMA_GEMM and x.shape[0] <= TMA_GEMM_DISPATCH_ROWS and gemm_tma_ok(x, w):
+        return gemm_tma(x, w, out_dtype or torch.bfloat16)
     if USE_SKINNY_GEMM and _skinny_ok(x, w):
         return gemm_skinny(x, w, out_dtype or torch.bfloat16)
     launch_count += 1

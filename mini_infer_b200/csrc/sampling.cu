@@ -83,6 +83,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const uint32_t* __restrict__ seed_lo, const uint32_t* __restrict__ seed_hi,
               const uint32_t* __restrict__ draw_index, int* __restrict__ out) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
   __shared__ ArgBest best_scratch[32];
   __shared__ unsigned int hist_cnt[256];
   __shared__ unsigned long long hist_mass[256];
@@ -237,7 +238,7 @@ extern "C" int mi_sample(const float* logits, int ld, int B, int V, const float*
   if (V <= 0 || ld < V) MI_REFUSE("sample: bad vocabulary %d (row stride %d)", V, ld);
   if (temperature && (!seed_lo || !seed_hi || !draw_index))
     MI_REFUSE("sample: seeds and draw indices are required with a temperature");
-  sample_kernel<<<B, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, seed_lo,
+  MI_LAUNCH((sample_kernel), B, SAMPLE_THREADS, 0, stream, logits, ld, V, temperature, top_k, top_p, seed_lo,
                                                   seed_hi, draw_index, out);
   MI_RETURN_LAUNCH_STATUS();
 }

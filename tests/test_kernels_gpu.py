@@ -197,6 +197,48 @@ def test_gemm_skinny_k_slices_agree(k_slices):
         assert torch.equal(ops().gemm_skinny(x, w, torch.float32, k_slices=k_slices), first)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 1000, 64), (3, 50, 176), (8, 4096, 4096), (9, 320, 192), (16, 513, 4104),
+                                   (5, 128256, 256), (8, 16, 8), (17, 6144, 1024), (64, 264, 14336),
+                                   (128, 520, 1032)])
+def test_gemm_tma(M, N, K, out_dtype):
+    """The tcgen05 weight-streaming product against a float64 product, at sizes that are no
+    multiples of its tiles (128 rows of W, 64 of k, 16 tokens) and that cut tiles' k ranges
+    across blocks."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=30)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=31, scale=0.1)
+    out = ops().gemm_tma(x.to(DEV), w.to(DEV), out_dtype)
+    want = x.double() @ w.double().T
+    bound = (1e-5 if out_dtype == torch.float32 else 1 / 128) * max(1.0, want.abs().max().item())
+    assert out.dtype == out_dtype
+    assert (out.cpu().double() - want).abs().max().item() <= bound
+    assert ops().gemm_tma_status() == 0
+
+
+def test_gemm_tma_is_deterministic_and_independent_of_other_rows():
+    """Partial tiles are added in block order whatever the arrival order, and a row of x gives
+    the same result alone as among other rows."""
+    N, K = 4096, 14336
+    x = rnd(8, K, dtype=torch.bfloat16, seed=32).to(DEV)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=33, scale=0.05).to(DEV)
+    first = ops().gemm_tma(x, w, torch.float32)
+    for _ in range(5):
+        assert torch.equal(ops().gemm_tma(x, w, torch.float32), first)
+    alone = ops().gemm_tma(x[3:4].contiguous(), w, torch.float32)
+    assert torch.equal(alone[0], first[3])
+    assert ops().gemm_tma_status() == 0
+
+
+def test_gemm_tma_refuses_what_it_cannot_take():
+    w = rnd(64, 36, dtype=torch.bfloat16, seed=34).to(DEV)
+    with pytest.raises(ops().KernelError, match="multiples of 8"):
+        ops().gemm_tma(rnd(2, 36, dtype=torch.bfloat16, seed=35).to(DEV), w)
+    w = rnd(64, 64, dtype=torch.bfloat16, seed=36).to(DEV)
+    with pytest.raises(ops().KernelError, match="at most"):
+        ops().gemm_tma(rnd(129, 64, dtype=torch.bfloat16, seed=37).to(DEV), w)
+    assert not ops().gemm_tma_ok(rnd(2, 36, dtype=torch.bfloat16, seed=35).to(DEV), rnd(64, 36, dtype=torch.bfloat16).to(DEV))
+
+
 def test_linear_library_and_streaming_kernels_agree():
     w = rnd(300, 264, dtype=torch.bfloat16, seed=22, scale=0.1).to(DEV)
     x = rnd(40, 264, dtype=torch.bfloat16, seed=23).to(DEV)
