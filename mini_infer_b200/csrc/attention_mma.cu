@@ -570,7 +570,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 #define PROWS 128   // rows (token, head in group) per block: 8 warps of 16
 
 template <int DMAX>
-__global__ void __launch_bounds__(PTHREADS)
+__global__ void __launch_bounds__(PTHREADS, DMAX <= 128 ? 2 : 1)
 attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                          const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                          const int* __restrict__ block_table, int bt_stride, int page_size, int page_shift,
@@ -590,7 +590,10 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   const int qd = lane >> 2, t4 = lane & 3;
   const int g = nq / nkv;
   const int hblocks = (g + gb - 1) / gb;
-  const int tile = blockIdx.x;
+  // Blocks start in the order of their index.  Tiles are listed in token order and, with a
+  // causal mask, the later a tile the more keys it walks: take them last first, so that the
+  // long ones do not end up alone in the last wave.
+  const int tile = gridDim.x - 1 - blockIdx.x;
   const int kvh = blockIdx.y / hblocks, hb = blockIdx.y - kvh * hblocks;
   const int b = tile_req[tile], tok0 = tile_tok0[tile];
   const int ql = q_len[b], kl = kv_len[b], qs = q_start[b];

@@ -245,6 +245,93 @@ __global__ void rope_write_kernel(T* __restrict__ qkv, const int* __restrict__ p
   }
 }
 
+// The same work in 16-byte chunks: a block takes one token and ROPE_HEADS consecutive heads;
+// sine and cosine of the token's angles are computed once per block into shared memory, then
+// every thread rotates one pair of chunks (elements [j, j + E) of both halves) or copies one
+// chunk of an un-rotated tail or of v.  Needs rot / 2 to be a multiple of the chunk's E
+// elements; other sizes take the element-wise kernel above.
+#define ROPE_HEADS 8
+template <typename T>
+struct Chunk16 {
+  static constexpr int E = 16 / (int)sizeof(T);
+  uint4 raw;
+  __device__ __forceinline__ void load(const T* p) { raw = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void store(T* p) const { *reinterpret_cast<uint4*>(p) = raw; }
+  __device__ __forceinline__ void get(float (&f)[E]) const {
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < E; ++i) f[i] = mi_to_float(e[i]);
+  }
+  __device__ __forceinline__ void set(const float (&f)[E]) {
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < E; ++i) e[i] = mi_from_float<T>(f[i]);
+  }
+};
+
+template <typename T>
+__global__ void rope_write_chunks_kernel(T* __restrict__ qkv, const int* __restrict__ pos,
+                                         const float* __restrict__ inv_freq, const int* __restrict__ slot,
+                                         T* __restrict__ kcache, T* __restrict__ vcache, int nq, int nkv,
+                                         int d, int rot, int page_size, int heads) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
+  extern __shared__ float rope_sc[];   // [half] sines, [half] cosines
+  constexpr int E = Chunk16<T>::E;
+  const int t = blockIdx.x, h0 = blockIdx.y * ROPE_HEADS;
+  const int half = rot >> 1;
+  if (half > 0 && h0 < nq + nkv) {
+    const float p = (float)pos[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(p * inv_freq[i], &rope_sc[i], &rope_sc[half + i]);
+  }
+  __syncthreads();
+  const int width = (nq + 2 * nkv) * d;
+  const int sl = (slot && kcache) ? slot[t] : -1;
+  const int page = sl >= 0 ? sl / page_size : 0, off = sl >= 0 ? sl - page * page_size : 0;
+  const int swz = off & mi_swizzle_mask(d, (int)sizeof(T));
+  const int cpr = d / E;                     // chunks per head row; also the items per head
+  const int n_rot = half / E, n_tail = (d - rot) / E;
+  const int n_heads = min(ROPE_HEADS, heads - h0);
+  for (int item = threadIdx.x; item < n_heads * cpr; item += blockDim.x) {
+    const int h = h0 + item / cpr, j = item % cpr;
+    T* head = qkv + (size_t)t * width + (size_t)h * d;
+    if (h < nq + nkv) {
+      T* dst = (h >= nq && sl >= 0) ? kcache + (((size_t)page * nkv + (h - nq)) * page_size + off) * d : nullptr;
+      if (j < n_rot) {
+        Chunk16<T> a, b;
+        a.load(head + j * E);
+        b.load(head + half + j * E);
+        float x1[E], x2[E], y1[E], y2[E];
+        a.get(x1);
+        b.get(x2);
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+          const float s = rope_sc[j * E + i], c = rope_sc[half + j * E + i];
+          y1[i] = x1[i] * c - x2[i] * s;
+          y2[i] = x2[i] * c + x1[i] * s;
+        }
+        a.set(y1);
+        b.set(y2);
+        a.store(head + j * E);
+        b.store(head + half + j * E);
+        if (dst) {
+          a.store(dst + ((j ^ swz) * E));
+          b.store(dst + (((n_rot + j) ^ swz) * E));
+        }
+      } else if (j < n_rot + n_tail && dst) {   // un-rotated tail of k
+        const int c = 2 * n_rot + (j - n_rot);
+        Chunk16<T> a;
+        a.load(head + c * E);
+        a.store(dst + ((c ^ swz) * E));
+      }
+    } else if (sl >= 0) {
+      T* dst = vcache + (((size_t)page * nkv + (h - nq - nkv)) * page_size + off) * d;
+      Chunk16<T> a;
+      a.load(head + j * E);
+      a.store(dst + ((j ^ swz) * E));
+    }
+  }
+}
+
 extern "C" int mi_rope_write(void* qkv, const int* pos, const float* inv_freq, const int* slot,
                              void* kcache, void* vcache, int M, int nq, int nkv, int d, int rot,
                              int page_size, int dtype, cudaStream_t stream) {
@@ -257,6 +344,19 @@ extern "C" int mi_rope_write(void* qkv, const int* pos, const float* inv_freq, c
   const int heads = nq + nkv + (kcache ? nkv : 0);   // v heads only matter when they are stored
   if (heads <= 0) return 0;
   if (heads > 65535) MI_REFUSE("rope: too many heads (%d)", heads);
+  const int es = dtype == MI_DTYPE_F32 ? 4 : 2, epc = 16 / es;
+  if ((dtype == MI_DTYPE_F32 || dtype == MI_DTYPE_BF16) && (rot / 2) % epc == 0 && d % epc == 0 &&
+      mi_aligned(qkv, 16) && (!kcache || (mi_aligned(kcache, 16) && mi_aligned(vcache, 16)))) {
+    dim3 cgrid(M, (heads + ROPE_HEADS - 1) / ROPE_HEADS);
+    const size_t smem = (size_t)rot * sizeof(float);
+    if (dtype == MI_DTYPE_F32)
+      MI_LAUNCH((rope_write_chunks_kernel<float>), cgrid, 128, smem, stream, (float*)qkv, pos, inv_freq, slot,
+                (float*)kcache, (float*)vcache, nq, nkv, d, rot, page_size, heads);
+    else
+      MI_LAUNCH((rope_write_chunks_kernel<bf16>), cgrid, 128, smem, stream, (bf16*)qkv, pos, inv_freq, slot,
+                (bf16*)kcache, (bf16*)vcache, nq, nkv, d, rot, page_size, heads);
+    MI_RETURN_LAUNCH_STATUS();
+  }
   int threads = 32;
   while (threads < 128 && threads * 2 <= d) threads <<= 1;
   dim3 grid(M, heads);
