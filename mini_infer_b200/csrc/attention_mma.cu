@@ -47,6 +47,17 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(s));
 }
+// the same with a shared-memory address already in hand (32-bit arithmetic in the caller)
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t s) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t s) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -566,11 +577,30 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 
 // ------------------------------------------------------------------------------- prefill
 
-#define PTHREADS 256
-#define PROWS 128   // rows (token, head in group) per block: 8 warps of 16
+// 2^x as one instruction of the special-function unit (2 ulp, results below 2^-126 are 0):
+// the prefill kernel computes one per score, and exp2f's range fix-ups double its cost.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+#define PROWS 128   // rows (token, head in group) per block
+
+// Each warp owns MT groups of 16 rows.  With MT = 2 a key or value fragment fetched from
+// shared memory feeds two MMAs instead of one (four warps, 128 threads, up to 255 registers,
+// two blocks per SM); head sizes above 128 keep MT = 1 (eight warps), where the output
+// accumulators of two row groups would not fit the register file.
+template <int DMAX>
+struct PrefillShape {
+  static constexpr int MT = DMAX <= 128 ? 2 : 1;
+  static constexpr int WARPS = PROWS / (16 * MT);
+  static constexpr int THREADS = WARPS * 32;
+  static constexpr int BLOCKS_PER_SM = DMAX <= 128 ? 2 : 1;
+};
 
 template <int DMAX>
-__global__ void __launch_bounds__(PTHREADS, DMAX <= 128 ? 2 : 1)
+__global__ void __launch_bounds__(PrefillShape<DMAX>::THREADS, PrefillShape<DMAX>::BLOCKS_PER_SM)
 attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                          const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                          const int* __restrict__ block_table, int bt_stride, int page_size, int page_shift,
@@ -578,6 +608,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
                          const int* __restrict__ kv_len, const int* __restrict__ tile_req,
                          const int* __restrict__ tile_tok0, int nq, int nkv, int d, float scale, int window,
                          int gb, int tt, int* __restrict__ status) {
+  constexpr int MT = PrefillShape<DMAX>::MT;
+  constexpr int THREADS = PrefillShape<DMAX>::THREADS;
   mi_pdl_enter();   // inputs come from the kernels before this one
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int sd = d + 8;
@@ -607,7 +639,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   if (status && *reinterpret_cast<volatile int*>(status)) return;   // an earlier block gave up waiting
   // row R of the tile: token tok0 + R / gb, head kvh * g + hb * gb + R % gb
   const int units = d >> 3;
-  for (int idx = tid; idx < PROWS * units; idx += PTHREADS) {
+  for (int idx = tid; idx < PROWS * units; idx += THREADS) {
     const int R = idx / units, u = idx - R * units;
     const int tk = R / gb, mem = R - tk * gb;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -617,30 +649,39 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     *reinterpret_cast<uint4*>(Qs + R * sd + u * 8) = v;
   }
 
-  // this lane's two rows
-  int prow[2], lorow[2];
-  bool rvalid[2];
+  // this lane's rows: two per group of 16
+  const int row0 = warp * 16 * MT;   // the warp's first row
+  int prow[MT][2], lorow[MT][2];
+  bool rvalid[MT][2];
 #pragma unroll
-  for (int hr = 0; hr < 2; ++hr) {
-    const int R = warp * 16 + qd + 8 * hr;
-    const int tk = R / gb, mem = R - tk * gb;
-    rvalid[hr] = tk < ntok && mem < heads_here;
-    prow[hr] = p_first + tk;
-    lorow[hr] = window > 0 ? max(0, prow[hr] - window + 1) : 0;
-  }
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      const int R = row0 + mt * 16 + qd + 8 * hr;
+      const int tk = R / gb, mem = R - tk * gb;
+      rvalid[mt][hr] = tk < ntok && mem < heads_here;
+      prow[mt][hr] = p_first + tk;
+      lorow[mt][hr] = window > 0 ? max(0, prow[mt][hr] - window + 1) : 0;
+    }
   // the warp's rows span tokens [wt0, wt1]
-  const int wt0 = (warp * 16) / gb, wt1 = min(ntok - 1, (warp * 16 + 15) / gb);
+  const int wt0 = row0 / gb, wt1 = min(ntok - 1, (row0 + 16 * MT - 1) / gb);
   const bool warp_active = wt0 < ntok;
   const int warp_hi = p_first + wt1 + 1;                                   // one past its last visible key
   const int warp_lo = window > 0 ? max(0, p_first + wt0 - window + 1) : 0;  // its first visible key
 
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  float o[DMAX / 8][4];
+  float m_run[MT][2], l_run[MT][2];
+  float o[MT][DMAX / 8][4];
 #pragma unroll
-  for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  for (int mt = 0; mt < MT; ++mt) {
+    m_run[mt][0] = m_run[mt][1] = -INFINITY;
+    l_run[mt][0] = l_run[mt][1] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; ++i) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.f;
+  }
   const float sc = scale * LOG2E;
   const int ksteps = d >> 4;
   const int c0 = lo / KCHUNK, c1 = (hi + KCHUNK - 1) / KCHUNK;
+  const uint32_t q_addr = smem_u32(Qs) + (uint32_t)((row0 + (lane & 15)) * sd + (lane >> 4) * 8) * 2u;
 
   __shared__ __align__(8) uint64_t bars[2];
   if (tid == 0) {
@@ -666,80 +707,124 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
       if (c + 2 < c1) loader.fetch(table, page_size, page_shift, c + 2, lo, hi);
     }
     const bool arrived = __all_sync(0xffffffffu, mbar_wait_bounded(&bars[buf], ((c - c0) >> 1) & 1, status));
-    zero_masked_values<PTHREADS>(Vs + buf * KCHUNK * d, c, lo, hi, d);
+    zero_masked_values<THREADS>(Vs + buf * KCHUNK * d, c, lo, hi, d);
     const bf16* Kb = Ks + buf * KCHUNK * d;
     const bf16* Vb = Vs + buf * KCHUNK * d;
     const int key0 = c * KCHUNK;
     // this lane's ldmatrix rows within each group of 16 keys, with their chunk permutations
     const int kr = (lane & 7) + (lane >> 4) * 8, vr = (lane & 7) + ((lane >> 3) & 1) * 8;
-    int ksw[4], vsw[4];
+    // Shared-memory addresses of the fragments: chunk (2 * step + b) ^ sw of row r lies at
+    //   base(r) + (((b ^ sw) & 1) << 4)  +  ((step * 32) ^ ((sw & ~1) << 4))
+    // so the inner loops add one constant xor-ed with a per-row pattern.
+    uint32_t kaddr[4], kxor[4], vaddr[4], vxor[4];
+    {
+      const uint32_t kbuf = smem_u32(Kb), vbuf = smem_u32(Vb);
+      const int kbit = (lane >> 3) & 1, vbit = lane >> 4;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      ksw[i] = inpage_of(key0 + i * 16 + kr, page_size, page_shift) & swz_mask;
-      vsw[i] = inpage_of(key0 + i * 16 + vr, page_size, page_shift) & swz_mask;
+      for (int i = 0; i < 4; ++i) {
+        const int ksw = inpage_of(key0 + i * 16 + kr, page_size, page_shift) & swz_mask;
+        const int vsw = inpage_of(key0 + i * 16 + vr, page_size, page_shift) & swz_mask;
+        kaddr[i] = kbuf + (uint32_t)((i * 16 + kr) * d) * 2u + (uint32_t)(((kbit ^ ksw) & 1) << 4);
+        kxor[i] = (uint32_t)((ksw & ~1) << 4);
+        vaddr[i] = vbuf + (uint32_t)((i * 16 + vr) * d) * 2u + (uint32_t)(((vbit ^ vsw) & 1) << 4);
+        vxor[i] = (uint32_t)((vsw & ~1) << 4);
+      }
     }
     if (arrived && warp_active && key0 < warp_hi && key0 + KCHUNK > warp_lo) {
-      float s[8][4];
+      float s[MT][8][4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[mt][i][0] = s[mt][i][1] = s[mt][i][2] = s[mt][i][3] = 0.f;
 #pragma unroll
       for (int ks = 0; ks < DMAX / 16; ++ks) {
         if (ks < ksteps) {
-          uint32_t a[4];
-          ldmatrix_x4(a, Qs + (warp * 16 + (lane & 15)) * sd + ks * 16 + (lane >> 4) * 8);
+          uint32_t a[MT][4];
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            ldsm_x4(a[mt], q_addr + (uint32_t)(mt * 16 * sd * 2 + ks * 32));
 #pragma unroll
           for (int kp = 0; kp < 4; ++kp) {
             uint32_t kb[4];
-            ldmatrix_x4(kb, Kb + (kp * 16 + kr) * d + (((ks * 2 + ((lane >> 3) & 1)) ^ ksw[kp]) << 3));
-            mma_bf16(s[2 * kp], a, kb[0], kb[1]);
-            mma_bf16(s[2 * kp + 1], a, kb[2], kb[3]);
+            ldsm_x4(kb, kaddr[kp] + ((uint32_t)(ks * 32) ^ kxor[kp]));
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              mma_bf16(s[mt][2 * kp], a[mt], kb[0], kb[1]);
+              mma_bf16(s[mt][2 * kp + 1], a[mt], kb[2], kb[3]);
+            }
           }
         }
       }
+      uint32_t pa[MT][4][4];
+      // A chunk that every row of the warp sees whole (all of them, in a long prompt, but the
+      // few on the diagonal and at a window's edge) needs no mask.  Scores stay unscaled; the
+      // scale is folded into the exponent's multiply-add: p = 2^(s * sc - m), m = sc * max(s).
+      const bool interior = key0 + KCHUNK - 1 <= p_first + wt0 &&
+                            key0 >= (window > 0 ? max(0, p_first + wt1 - window + 1) : 0);
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
+      for (int mt = 0; mt < MT; ++mt) {
+        if (!interior) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int hr = e >> 1;
-          const int j = key0 + nt * 8 + 2 * t4 + (e & 1);
-          s[nt][e] = (rvalid[hr] && j <= prow[hr] && j >= lorow[hr]) ? s[nt][e] * sc : -INFINITY;
+          for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int hr = e >> 1;
+              const int j = key0 + nt * 8 + 2 * t4 + (e & 1);
+              if (!(rvalid[mt][hr] && j <= prow[mt][hr] && j >= lorow[mt][hr])) s[mt][nt][e] = -INFINITY;
+            }
         }
-      uint32_t pa[4][4];
+        // both rows of the lane side by side and sums in four strands: short dependency chains
+        float mx[2], alpha[2] = {1.f, 1.f};
 #pragma unroll
-      for (int hr = 0; hr < 2; ++hr) {
-        float mx = -INFINITY;
+        for (int hr = 0; hr < 2; ++hr) {
+          float m4[4];
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) mx = fmaxf(mx, fmaxf(s[nt][2 * hr], s[nt][2 * hr + 1]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run[hr], mx);
-        float alpha = 1.f, sum = 0.f;
-        if (m_new != -INFINITY) {
-          alpha = exp2f(m_run[hr] - m_new);
+          for (int i = 0; i < 4; ++i)
+            m4[i] = fmaxf(fmaxf(s[mt][2 * i][2 * hr], s[mt][2 * i][2 * hr + 1]),
+                          fmaxf(s[mt][2 * i + 1][2 * hr], s[mt][2 * i + 1][2 * hr + 1]));
+          mx[hr] = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        }
 #pragma unroll
-          for (int nt = 0; nt < 8; ++nt) {
-            s[nt][2 * hr] = exp2f(s[nt][2 * hr] - m_new);
-            s[nt][2 * hr + 1] = exp2f(s[nt][2 * hr + 1] - m_new);
-            sum += s[nt][2 * hr] + s[nt][2 * hr + 1];
+        for (int hr = 0; hr < 2; ++hr) {
+          mx[hr] = fmaxf(mx[hr], __shfl_xor_sync(0xffffffffu, mx[hr], 1));
+          mx[hr] = fmaxf(mx[hr], __shfl_xor_sync(0xffffffffu, mx[hr], 2));
+        }
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr) {
+          const float m_new = fmaxf(m_run[mt][hr], mx[hr] * sc);   // sc > 0
+          float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+          if (m_new != -INFINITY) {
+            alpha[hr] = fast_exp2(m_run[mt][hr] - m_new);
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+              s[mt][nt][2 * hr] = fast_exp2(fmaf(s[mt][nt][2 * hr], sc, -m_new));
+              s[mt][nt][2 * hr + 1] = fast_exp2(fmaf(s[mt][nt][2 * hr + 1], sc, -m_new));
+              sum4[nt & 3] += s[mt][nt][2 * hr] + s[mt][nt][2 * hr + 1];
+            }
+          } else {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) s[mt][nt][2 * hr] = s[mt][nt][2 * hr + 1] = 0.f;
           }
-        } else {
-#pragma unroll
-          for (int nt = 0; nt < 8; ++nt) s[nt][2 * hr] = s[nt][2 * hr + 1] = 0.f;
+          m_run[mt][hr] = m_new;
+          l_run[mt][hr] = l_run[mt][hr] * alpha[hr] + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         }
-        m_run[hr] = m_new;
-        l_run[hr] = l_run[hr] * alpha + sum;
+        // the accumulators are rescaled only when some row's maximum moved (exact: alpha is 1 otherwise)
+        if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-        for (int i = 0; i < DMAX / 8; ++i) {
-          o[i][2 * hr] *= alpha;
-          o[i][2 * hr + 1] *= alpha;
+          for (int i = 0; i < DMAX / 8; ++i) {
+            o[mt][i][0] *= alpha[0];
+            o[mt][i][1] *= alpha[0];
+            o[mt][i][2] *= alpha[1];
+            o[mt][i][3] *= alpha[1];
+          }
         }
-      }
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        pa[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-        pa[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-        pa[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-        pa[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+        for (int kk = 0; kk < 4; ++kk) {
+          pa[mt][kk][0] = pack_bf16(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+          pa[mt][kk][1] = pack_bf16(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+          pa[mt][kk][2] = pack_bf16(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+          pa[mt][kk][3] = pack_bf16(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+        }
       }
 #pragma unroll
       for (int dt = 0; dt < DMAX / 16; ++dt) {
@@ -747,9 +832,12 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             uint32_t vb[4];
-            ldmatrix_x4_trans(vb, Vb + (kk * 16 + vr) * d + (((dt * 2 + (lane >> 4)) ^ vsw[kk]) << 3));
-            mma_bf16(o[2 * dt], pa[kk], vb[0], vb[1]);
-            mma_bf16(o[2 * dt + 1], pa[kk], vb[2], vb[3]);
+            ldsm_x4_trans(vb, vaddr[kk] + ((uint32_t)(dt * 32) ^ vxor[kk]));
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              mma_bf16(o[mt][2 * dt], pa[mt][kk], vb[0], vb[1]);
+              mma_bf16(o[mt][2 * dt + 1], pa[mt][kk], vb[2], vb[3]);
+            }
           }
         }
       }
@@ -758,23 +846,25 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   }
 
 #pragma unroll
-  for (int hr = 0; hr < 2; ++hr) {
-    float l = l_run[hr];
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (!rvalid[hr] || !(l > 0.f)) continue;
-    const float inv = 1.f / l;
-    const int R = warp * 16 + qd + 8 * hr;
-    const int tk = R / gb, mem = R - tk * gb;
-    bf16* orow = out + (size_t)(qs + tok0 + tk) * out_stride + (size_t)(kvh * g + hb * gb + mem) * d;
+  for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int i = 0; i < DMAX / 8; ++i) {
-      if (i * 8 < d) {
-        const uint32_t v = pack_bf16(o[i][2 * hr] * inv, o[i][2 * hr + 1] * inv);
-        *reinterpret_cast<uint32_t*>(orow + i * 8 + 2 * t4) = v;
+    for (int hr = 0; hr < 2; ++hr) {
+      float l = l_run[mt][hr];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      if (!rvalid[mt][hr] || !(l > 0.f)) continue;
+      const float inv = 1.f / l;
+      const int R = row0 + mt * 16 + qd + 8 * hr;
+      const int tk = R / gb, mem = R - tk * gb;
+      bf16* orow = out + (size_t)(qs + tok0 + tk) * out_stride + (size_t)(kvh * g + hb * gb + mem) * d;
+#pragma unroll
+      for (int i = 0; i < DMAX / 8; ++i) {
+        if (i * 8 < d) {
+          const uint32_t v = pack_bf16(o[mt][i][2 * hr] * inv, o[mt][i][2 * hr + 1] * inv);
+          *reinterpret_cast<uint32_t*>(orow + i * 8 + 2 * t4) = v;
+        }
       }
     }
-  }
 }
 
 // ------------------------------------------------------------------------------- host side
@@ -884,6 +974,7 @@ extern "C" int mi_attention_prefill(const void* q, int q_stride, void* out, int 
                                     int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (int rc = check_common(q, q_stride, out, out_stride, kcache, vcache, nq, nkv, d, page_size, window)) return rc;
+  if (!(scale > 0.f)) MI_REFUSE("attention: the score scale must be positive (the row maximum is taken before scaling)");
   const int g = nq / nkv;
   const int gb = g < PROWS ? g : PROWS;
   if (tile_tokens != PROWS / gb) MI_REFUSE("attention: tiles of %d tokens, the kernel wants %d", tile_tokens, PROWS / gb);
@@ -899,7 +990,7 @@ extern "C" int mi_attention_prefill(const void* q, int q_stride, void* out, int 
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return (int)e;                                                              \
     }                                                                                                   \
-    MI_LAUNCH((kern), grid, PTHREADS, smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,            \
+    MI_LAUNCH((kern), grid, PrefillShape<DMAX>::THREADS, smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, \
                                            (const bf16*)kcache, (const bf16*)vcache, block_table,       \
                                            bt_stride, page_size, page_shift, q_start, q_len, kv_len,    \
                                            tile_req, tile_tok0, nq, nkv, d, scale, window, gb,          \
