@@ -271,8 +271,9 @@ def reference_arm(args) -> int:
     ref = os.path.join(ROOT, "baseline", "_ref")
     line = {"impl": "reference"}
     if not os.path.isdir(os.path.join(ref, "mini_infer")):
-        line["unavailable"] = ("the reference is not installed under baseline/_ref (its build backend, "
-                               "hatchling, is not in the offline wheelhouse)")
+        line["unavailable"] = ("the reference is not installed under baseline/_ref (the stated pip command fails "
+                               "offline: its build backend, hatchling, is not in the wheelhouse; it installs from "
+                               "a copy whose build-system table names setuptools, sources unchanged)")
         print(json.dumps(line))
         return 0
     try:
