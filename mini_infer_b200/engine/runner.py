@@ -99,5 +99,8 @@ class ModelRunner:
     def free_request(self, rid) -> None:
         self.cache.free_request(rid)
 
-    def step(self, entries: Sequence[StepEntry]) -> StepResult:
-        return self.stepper.step(entries)
+    # a scheduler may feed the sampler's device output to the next step (see StepRunner.step)
+    device_token_feedback = True
+
+    def step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> StepResult:
+        return self.stepper.step(entries, device_tokens)

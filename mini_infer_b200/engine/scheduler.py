@@ -101,6 +101,7 @@ class RunningRequest:
         self.done = threading.Event()
         self.on_token: Callable[[int], None] | None = None
         self.cancel_requested = False
+        self.in_flight_after_done = False       # finished while a step launched ahead still writes its pages
 
     def result(self, detokenize=None) -> GenerationResult:
         text = detokenize(self.generated) if detokenize else ""
@@ -130,6 +131,18 @@ class RequestHandle:
         return self._rr.done.is_set()
 
 
+@dataclasses.dataclass
+class _InFlightStep:
+    """A decode step that has been launched and not yet read back."""
+
+    entries: list
+    owners: list                      # RunningRequest of each entry
+    sampled: object                   # the sampler's output on the device, one id per entry
+    host: object                      # the same ids on their way to (pinned) host memory
+    ready: object                     # event recorded after that copy (None: the copy was synchronous)
+    t0: float
+
+
 class ContinuousScheduler:
     def __init__(
         self,
@@ -143,6 +156,7 @@ class ContinuousScheduler:
         sampler=None,
         tokenizer=None,
         trace_out: str | None = None,
+        lookahead: bool | None = None,
     ) -> None:
         if max_concurrent <= 0 or chunk_size <= 0 or max_tokens_per_step <= 0:
             raise ValueError("max_concurrent, chunk_size and max_tokens_per_step must be positive")
@@ -175,6 +189,16 @@ class ContinuousScheduler:
         self.tokens_generated = 0
         self.preemptions = 0
         self.last_step_entries: list[StepEntry] = []
+        # Decode look-ahead: while every live request is decoding and nobody waits, the next
+        # step is launched from the sampler's device output before the host reads it, so the
+        # GPU never idles behind the host's bookkeeping.  A request that turns out to have
+        # finished (a stop token) has then one token computed in vain; its pages are given
+        # back when that step has been read.  Needs a runner that takes device tokens.
+        if lookahead is None:
+            lookahead = bool(getattr(runner, "device_token_feedback", False))
+        self.lookahead = lookahead
+        self._inflight: _InFlightStep | None = None
+        self.wasted_tokens = 0
 
     # ------------------------------------------------------------------ public
 
@@ -242,6 +266,7 @@ class ContinuousScheduler:
         if self._thread is not None:
             self._thread.join()
             self._thread = None
+        self._drain()
         with self._lock:
             for rr in list(self._live):
                 self._release(rr)
@@ -269,7 +294,13 @@ class ContinuousScheduler:
     # ------------------------------------------------------------------ one engine step
 
     def step(self) -> bool:
-        """Admit, plan, run one batch, sample, finish.  False when there is nothing to do."""
+        """Admit, plan, run one batch, sample, finish.  False when there is nothing to do.
+        One call hands out one batch's tokens, whether or not a step was launched ahead."""
+        if self._inflight is not None:
+            cur, self._inflight = self._inflight, None
+            self._inflight = self._launch_ahead(cur)
+            self._collect(cur)
+            return True
         with self._lock:
             for rr in [r for r in self._live if r.cancel_requested]:
                 self._retire(rr, "cancelled")
@@ -280,6 +311,11 @@ class ContinuousScheduler:
             entries, owners = self._plan()
         if not entries:
             return False
+        if self.lookahead and self._pure_decode(entries, owners):
+            cur = self._launch(entries, owners, None)
+            self._inflight = self._launch_ahead(cur)
+            self._collect(cur)
+            return True
         t0 = time.time()
         result = self.runner.step(entries)
         self.last_step_entries = entries
@@ -315,6 +351,112 @@ class ContinuousScheduler:
                              "total_q": sum(len(e.tokens) for e in entries)},
                 })
         return True
+
+    # ------------------------------------------------------------------ decode look-ahead
+
+    def _pure_decode(self, entries, owners) -> bool:
+        with self._lock:
+            return (not self._waiting and len(owners) == len(self._live)
+                    and all(rr.state is RequestState.DECODING and len(e.tokens) == 1
+                            for rr, e in zip(owners, entries)))
+
+    def _launch(self, entries, owners, device_tokens) -> _InFlightStep:
+        """Put a decode step and its sampling on the stream; start the copy of the sampled ids
+        to the host; do not wait for any of it."""
+        import torch
+
+        t0 = time.time()
+        if device_tokens is None:
+            result = self.runner.step(entries)
+        else:
+            result = self.runner.step(entries, device_tokens=device_tokens)
+        self.last_step_entries = entries
+        self.steps += 1
+        # the draw index counts the tokens a request has been given, the one in flight included
+        ahead = 0 if device_tokens is None else 1
+        sampled = self.sampler.sample(
+            result.logits,
+            [rr.request.sampling_params for rr in owners],
+            [rr.seed for rr in owners],
+            [len(rr.generated) + ahead for rr in owners],
+        )
+        ready = None
+        if isinstance(sampled, torch.Tensor) and sampled.is_cuda:
+            host = torch.empty(sampled.shape, dtype=sampled.dtype, pin_memory=True)
+            host.copy_(sampled, non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream(sampled.device))
+        else:
+            host = sampled
+        with self._lock:
+            for rr in owners:
+                rr.next_token = None
+        return _InFlightStep(entries=entries, owners=owners, sampled=sampled, host=host, ready=ready, t0=t0)
+
+    def _launch_ahead(self, cur: _InFlightStep) -> _InFlightStep | None:
+        """The step after ``cur`` for the requests that are known to go on (none has reached
+        its length), fed from ``cur``'s sampled ids on the device; None when the batch is
+        about to change (someone waits, prefills or wants out) or pages are short: the
+        ordinary path then decides with everything read back."""
+        import torch
+
+        if not self.lookahead or not isinstance(cur.sampled, torch.Tensor):
+            return None
+        with self._lock:
+            if self._waiting or any(rr.cancel_requested or rr.state is not RequestState.DECODING
+                                    for rr in self._live):
+                return None
+            keep: list[int] = []
+            for i, rr in enumerate(cur.owners):
+                if rr.in_flight_after_done or rr.state is not RequestState.DECODING:
+                    continue
+                if len(rr.generated) + 1 >= rr.request.max_tokens:
+                    continue                     # cur's token is its last
+                if self.max_positions is not None and self.cache.length(rr.rid) + 1 > self.max_positions:
+                    continue
+                keep.append(i)
+            if not keep or not self.cache.can_append([(cur.owners[i].rid, 1) for i in keep]):
+                return None
+            owners = [cur.owners[i] for i in keep]
+        if len(keep) == len(cur.owners):
+            tokens = cur.sampled
+        else:
+            index = torch.tensor(keep, dtype=torch.int64)
+            if cur.sampled.is_cuda:
+                index = index.pin_memory().to(cur.sampled.device, non_blocking=True)
+            tokens = cur.sampled.index_select(0, index)
+        entries = [StepEntry(rr.rid, [0], [0]) for rr in owners]
+        return self._launch(entries, owners, tokens.to(torch.int32))
+
+    def _collect(self, cur: _InFlightStep) -> None:
+        """Read a launched step's tokens and hand them to their requests."""
+        if cur.ready is not None:
+            cur.ready.synchronize()
+        ids = [int(t) for t in (cur.host.tolist() if hasattr(cur.host, "tolist") else cur.host)]
+        nxt = self._inflight
+        ahead = set(id(rr) for rr in nxt.owners) if nxt is not None else set()
+        with self._lock:
+            for rr, tok in zip(cur.owners, ids):
+                if rr.in_flight_after_done:
+                    # the step that was launched before its end was known: nothing to keep,
+                    # and nothing writes its pages any more
+                    rr.in_flight_after_done = False
+                    self.wasted_tokens += 1
+                    self._release(rr)
+                    continue
+                self._consume(rr, tok, still_in_flight=id(rr) in ahead)
+            if self.trace_out is not None:
+                self._trace.append({
+                    "name": "step", "ph": "X", "pid": 0, "tid": 0, "ts": cur.t0 * 1e6,
+                    "dur": (time.time() - cur.t0) * 1e6,
+                    "args": {"B": len(cur.entries), "phase": "decode", "total_q": len(cur.entries)},
+                })
+
+    def _drain(self) -> None:
+        """Read back whatever was launched ahead (used before the engine stops)."""
+        while self._inflight is not None:
+            cur, self._inflight = self._inflight, None
+            self._collect(cur)
 
     # ------------------------------------------------------------------ internals (lock held)
 
@@ -422,24 +564,29 @@ class ContinuousScheduler:
         if rr.rid in self.cache:
             self.cache.free_request(rr.rid)
 
-    def _consume(self, rr: RunningRequest, token: int) -> None:
-        """A sampled token: emit it, or finish the request (reference ``:847-860``)."""
+    def _consume(self, rr: RunningRequest, token: int, still_in_flight: bool = False) -> None:
+        """A sampled token: emit it, or finish the request (reference ``:847-860``).  With
+        ``still_in_flight`` a step launched ahead holds the request: if it ends here, its
+        pages stay until that step has been read."""
         if token in self.eos_token_ids:
-            self._retire(rr, "stop")
+            self._retire(rr, "stop", still_in_flight)
             return
         rr.generated.append(token)
         rr.next_token = token
         self.tokens_generated += 1
         if rr.on_token is not None:
             rr.on_token(token)
-        held = self.cache.length(rr.rid)
+        held = self.cache.length(rr.rid) - (1 if still_in_flight else 0)   # without the token launched ahead
         if len(rr.generated) >= rr.request.max_tokens:
-            self._retire(rr, "length")
+            self._retire(rr, "length", still_in_flight)
         elif self.max_positions is not None and held + 1 > self.max_positions:
-            self._retire(rr, "length")
+            self._retire(rr, "length", still_in_flight)
 
-    def _retire(self, rr: RunningRequest, reason: str) -> None:
-        self._release(rr)
+    def _retire(self, rr: RunningRequest, reason: str, still_in_flight: bool = False) -> None:
+        if still_in_flight:
+            rr.in_flight_after_done = True
+        else:
+            self._release(rr)
         if rr in self._live:
             self._live.remove(rr)
         self._finish(rr, reason)
@@ -458,7 +605,8 @@ class ContinuousScheduler:
             rr.cancel_requested = True
             if self._thread is None:
                 if rr in self._live:
-                    self._retire(rr, "cancelled")
+                    held_ahead = self._inflight is not None and any(o is rr for o in self._inflight.owners)
+                    self._retire(rr, "cancelled", still_in_flight=held_ahead)
                 else:
                     try:
                         self._waiting.remove(rr)

@@ -222,18 +222,33 @@ class StepRunner:
         return self.cuda_graph and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
 
     @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry]) -> StepResult:
+    def step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> StepResult:
+        """Run one batch.  ``device_tokens`` (int32 on the device, one per entry) replaces the
+        entries' token ids for a step whose every entry brings exactly one token: the ids are
+        then taken from that tensor on the device, in stream order, and the ids in ``entries``
+        are placeholders.  A scheduler uses it to launch the next decode step from the
+        sampler's output before the host has seen it."""
+        if device_tokens is not None:
+            if any(len(e.tokens) != 1 for e in entries):
+                raise StepError("device_tokens needs entries of exactly one token each")
+            if (device_tokens.dtype != torch.int32 or device_tokens.shape != (len(entries),)
+                    or device_tokens.device != self.device):
+                raise StepError("device_tokens must be an int32 vector on the model's device, one per entry")
         if self._graphable(entries):
-            return self._graphed_step(entries)
+            return self._graphed_step(entries, device_tokens)
         ctx, caches, want, rows = self.plan(entries)
+        if device_tokens is not None:
+            ctx.token_ids.copy_(device_tokens)
         logits = self.model.forward(ctx, caches, want, len(rows))
         self.steps_run += 1
         return StepResult(logits=logits, rows=rows)
 
-    def _graphed_step(self, entries: Sequence[StepEntry]) -> StepResult:
+    def _graphed_step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> StepResult:
         """Replay (first: capture) the CUDA graph of a decode-only step.  The logits live in
         the graph's own memory and are overwritten by the next replay of the same graph."""
         ctx, caches, want, rows, slot = self.plan(entries, graphed=True)
+        if device_tokens is not None:
+            ctx.token_ids.copy_(device_tokens)   # into the graph's fixed descriptor buffer
         if slot.graph is None:
             # run once kernel by kernel (compiles and configures every kernel), then capture
             # the same launches; both read the descriptors just copied into the fixed buffer

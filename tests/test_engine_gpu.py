@@ -95,6 +95,39 @@ def test_sampling_is_seeded_and_independent_of_batching(model_dirs):
         assert score[tok] >= score.max() - 1e-3
 
 
+@pytest.mark.parametrize("cuda_graph", [False, True])
+def test_decode_lookahead_gives_the_same_tokens(model_dirs, cuda_graph):
+    """Launching the next decode step from the sampler's device output, before the host has
+    read it, changes nothing but the time: same tokens with and without, with a stop token
+    that ends one request early (its step ahead is thrown away and its pages come back)."""
+    from mini_infer_b200.engine import ContinuousScheduler, ModelRunner, Request
+    from mini_infer_b200.sampling import SamplingParams
+
+    which = "A"
+    prompts = [prompt_ids(which, n, salt=70 + i) for i, n in enumerate([9, 33, 50])]
+    params = [SamplingParams(), SamplingParams(temperature=0.7, seed=11), SamplingParams(temperature=1.1, top_k=20, seed=12)]
+    runner = ModelRunner.from_pretrained(model_dirs[which], dtype="bfloat16", block_size=16, num_blocks=40,
+                                         max_requests=3, cuda_graph=cuda_graph)
+    free = runner.cache.num_free_pages()
+
+    def run(lookahead, eos=()):
+        sched = ContinuousScheduler(runner, lookahead=lookahead, eos_token_ids=eos, chunk_size=64,
+                                    max_tokens_per_step=128)
+        res = sched.generate([Request(p, sp, 20) for p, sp in zip(prompts, params)])
+        assert runner.cache.num_free_pages() == free and runner.cache.num_requests == 0
+        return [r.tokens for r in res], [r.finish_reason for r in res], sched
+
+    plain_tokens, _, _ = run(False)
+    ahead_tokens, _, sched = run(True)
+    assert ahead_tokens == plain_tokens
+    assert sched.wasted_tokens == 0
+    stop = plain_tokens[1][7]          # make the eighth token of the second request a stop token
+    plain_tokens, plain_why, _ = run(False, eos=[stop])
+    ahead_tokens, ahead_why, sched = run(True, eos=[stop])
+    assert ahead_tokens == plain_tokens and ahead_why == plain_why
+    assert "stop" in ahead_why and sched.wasted_tokens >= 1
+
+
 def test_preemption_by_recompute_gives_the_same_tokens(model_dirs):
     from mini_infer_b200.engine import ContinuousScheduler, ModelRunner, Request
     from mini_infer_b200.sampling import SamplingParams

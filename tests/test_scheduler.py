@@ -232,3 +232,90 @@ def test_trace_out(tmp_path):
     assert len(events) == len(runner.log)
     assert {e["args"]["phase"] for e in events} <= {"prefill", "decode", "mixed"}
     assert events[0]["args"]["total_q"] == 8 and events[0]["args"]["B"] == 1
+
+
+# ----------------------------------------------------------------------------- decode look-ahead
+
+
+class FeedbackRunner(FakeRunner):
+    """A runner that takes the next tokens from a tensor (the sampler's output), as the real
+    one does on the device."""
+
+    device_token_feedback = True
+
+    def step(self, entries, device_tokens=None):
+        if device_tokens is not None:
+            assert all(len(e.tokens) == 1 for e in entries)
+            entries = [SimpleNamespace(rid=e.rid, tokens=[int(t)], want=e.want)
+                       for e, t in zip(entries, device_tokens.tolist())]
+        return super().step(entries)
+
+
+class TensorSampler(FakeSampler):
+    def sample(self, logits, params, seeds, draw_index):
+        import torch
+
+        return torch.tensor(super().sample(logits, params, seeds, draw_index), dtype=torch.int32)
+
+
+def make_lookahead(num_pages=64, eos_at=None, **kw):
+    runner = FeedbackRunner(num_pages, page_size=4, max_requests=8)
+    sched = ContinuousScheduler(runner, sampler=TensorSampler(eos_at), **kw)
+    assert sched.lookahead
+    return runner, sched
+
+
+def test_lookahead_gives_the_same_tokens_and_frees_everything():
+    requests = [Request(prompt(n), SamplingParams(), m) for n, m in ((5, 9), (17, 4), (30, 12))]
+    _, plain = make(max_tokens_per_step=64, chunk_size=64)
+    want = [r.tokens for r in plain.generate(requests)]
+    runner, sched = make_lookahead(max_tokens_per_step=64, chunk_size=64)
+    got = sched.generate(requests)
+    assert [r.tokens for r in got] == want
+    assert all(r.finish_reason == "length" for r in got)
+    assert sched.wasted_tokens == 0, "a length is known before the step is launched"
+    assert runner.cache.num_requests == 0 and runner.cache.num_free_pages() == 64
+    for rid, (n, _) in enumerate(((5, 9), (17, 4), (30, 12))):
+        assert runner.fed[rid] == prompt(n) + got[rid].tokens[:-1]
+    # while all three decode, two steps are in flight per call: fewer calls than steps is not
+    # observable here, but every decode step after the first was fed from the sampler's tensor
+    assert sched.steps == plain.steps
+
+
+def test_lookahead_stop_token_costs_one_token_and_its_pages_come_back():
+    eos = {1: 3}          # request 1 samples the end id as its fourth token
+    requests = [Request(prompt(6), SamplingParams(), 10), Request(prompt(9), SamplingParams(), 10)]
+    _, plain = make(max_tokens_per_step=64, chunk_size=64, eos_token_ids=[0], sampler=FakeSampler(eos))
+    want = plain.generate(requests)
+    runner, sched = make_lookahead(eos_at=eos, max_tokens_per_step=64, chunk_size=64, eos_token_ids=[0])
+    got = sched.generate(requests)
+    assert [r.tokens for r in got] == [r.tokens for r in want]
+    assert [r.finish_reason for r in got] == ["length", "stop"]
+    assert sched.wasted_tokens == 1
+    assert runner.cache.num_requests == 0 and runner.cache.num_free_pages() == 64
+
+
+def test_lookahead_drains_when_a_request_arrives():
+    runner, sched = make_lookahead(max_tokens_per_step=64, chunk_size=64)
+    first = sched.submit(Request(prompt(7), SamplingParams(), 12))
+    for _ in range(4):
+        sched.step()
+    assert sched._inflight is not None, "a lone decoding request runs one step ahead"
+    second = sched.submit(Request(prompt(11, base=300), SamplingParams(), 5))
+    sched.run_until_done()
+    assert first.wait().tokens == expected_tokens(0, 7, 12)
+    assert second.wait().tokens == expected_tokens(1, 11, 5)
+    assert runner.cache.num_requests == 0 and runner.cache.num_free_pages() == 64
+
+
+def test_lookahead_cancel_while_a_step_is_ahead():
+    runner, sched = make_lookahead(max_tokens_per_step=64, chunk_size=64)
+    h = sched.submit(Request(prompt(7), SamplingParams(), 50))
+    other = sched.submit(Request(prompt(3, base=500), SamplingParams(), 8))
+    for _ in range(3):
+        sched.step()
+    h.cancel()
+    sched.run_until_done()
+    assert h.wait().finish_reason == "cancelled"
+    assert other.wait().tokens == expected_tokens(1, 3, 8)
+    assert runner.cache.num_requests == 0 and runner.cache.num_free_pages() == 64
