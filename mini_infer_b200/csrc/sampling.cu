@@ -78,11 +78,95 @@ __device__ __forceinline__ ArgBest block_best(ArgBest x, ArgBest* scratch) {
   return r;
 }
 
+// Calls f(i, logit_i) for the elements [begin, end) of a row that this thread owns.  With
+// `vec` (row start 16-byte aligned, begin a multiple of 4) elements are fetched four at a time,
+// two such loads in flight per thread: a pass over a row is bound by the latency of its loads,
+// not by their bytes.  Which thread sees which element does not matter to any caller (all
+// reductions here are order-independent).
+template <typename F>
+__device__ __forceinline__ void scan_row(const float* __restrict__ lg, int begin, int end, bool vec, int tid,
+                                         int nthreads, F f) {
+  if (vec) {
+    const int n4 = (end - begin) >> 2;
+    const float4* p = reinterpret_cast<const float4*>(lg + begin);
+    for (int j = tid; j < n4; j += 2 * nthreads) {
+      const int j2 = j + nthreads;
+      const float4 a = p[j];
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j2 < n4) b = p[j2];
+      const int ia = begin + 4 * j, ib = begin + 4 * j2;
+      f(ia, a.x); f(ia + 1, a.y); f(ia + 2, a.z); f(ia + 3, a.w);
+      if (j2 < n4) { f(ib, b.x); f(ib + 1, b.y); f(ib + 2, b.z); f(ib + 3, b.w); }
+    }
+    for (int i = begin + (n4 << 2) + tid; i < end; i += nthreads) f(i, lg[i]);
+  } else {
+    for (int i = begin + tid; i < end; i += nthreads) f(i, lg[i]);
+  }
+}
+
+// Greedy choice with a row cut across ARGMAX_SPLITS blocks: each block finds the best of its
+// slice, parks it, and the block that arrives last at the row picks the best of the slices
+// (lowest index among equals, as everywhere) and resets the row's counter.  The scratch is a
+// file-scope array: calls on different streams of one device must not overlap.
+#define ARGMAX_SPLITS 16
+#define ARGMAX_MAX_ROWS 4096
+static __device__ ArgBest g_argmax_part[ARGMAX_MAX_ROWS * ARGMAX_SPLITS];
+static __device__ int g_argmax_count[ARGMAX_MAX_ROWS];
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_split_kernel(const float* __restrict__ logits, int ld, int V, int vec, int* __restrict__ out) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
+  __shared__ ArgBest best_scratch[32];
+  __shared__ int is_last;
+  const int row = blockIdx.y, part = blockIdx.x, tid = threadIdx.x;
+  const float* lg = logits + (size_t)row * ld;
+  const int per = ((V + ARGMAX_SPLITS - 1) / ARGMAX_SPLITS + 3) & ~3;   // slices begin at multiples of 4
+  const int begin = min(V, part * per), end = min(V, begin + per);
+  ArgBest b;
+  b.v = 0.f;
+  b.i = -1;
+  scan_row(lg, begin, end, vec != 0, tid, SAMPLE_THREADS, [&](int i, float x) {
+    ArgBest c;
+    c.v = x;
+    c.i = i;
+    if (x == x) b = better(b, c);  // NaN never wins
+  });
+  b = block_best(b, best_scratch);
+  if (tid == 0) {
+    g_argmax_part[row * ARGMAX_SPLITS + part] = b;
+    __threadfence();
+    is_last = atomicAdd(&g_argmax_count[row], 1) == ARGMAX_SPLITS - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  if (tid < 32) {
+    __threadfence();
+    ArgBest r;
+    r.v = 0.f;
+    r.i = -1;
+    if (tid < ARGMAX_SPLITS) {
+      r.v = __ldcg(&g_argmax_part[row * ARGMAX_SPLITS + tid].v);
+      r.i = __ldcg(&g_argmax_part[row * ARGMAX_SPLITS + tid].i);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ArgBest y;
+      y.v = __shfl_xor_sync(0xffffffffu, r.v, o);
+      y.i = __shfl_xor_sync(0xffffffffu, r.i, o);
+      r = better(r, y);
+    }
+    if (tid == 0) {
+      out[row] = r.i;
+      g_argmax_count[row] = 0;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const uint32_t* __restrict__ seed_lo, const uint32_t* __restrict__ seed_hi,
-              const uint32_t* __restrict__ draw_index, int* __restrict__ out) {
+              const uint32_t* __restrict__ draw_index, int vec, int* __restrict__ out) {
   mi_pdl_enter();   // inputs come from the kernels before this one
   __shared__ ArgBest best_scratch[32];
   __shared__ unsigned int hist_cnt[256];
@@ -100,12 +184,12 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     ArgBest b;
     b.v = 0.f;
     b.i = -1;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+    scan_row(lg, 0, V, vec != 0, tid, SAMPLE_THREADS, [&](int i, float x) {
       ArgBest c;
-      c.v = lg[i];
+      c.v = x;
       c.i = i;
-      if (c.v == c.v) b = better(b, c);  // NaN never wins
-    }
+      if (x == x) b = better(b, c);  // NaN never wins
+    });
     b = block_best(b, best_scratch);
     if (tid == 0) out[row] = b.i;
     return;
@@ -122,10 +206,10 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
       const int shift = 24 - 8 * pass;
       for (int b = tid; b < 256; b += SAMPLE_THREADS) hist_cnt[b] = 0u;
       __syncthreads();
-      for (int i = tid; i < V; i += SAMPLE_THREADS) {
-        const uint32_t key = order_key(lg[i] / T);
+      scan_row(lg, 0, V, vec != 0, tid, SAMPLE_THREADS, [&](int i, float x) {
+        const uint32_t key = order_key(x / T);
         if ((key & mask) == prefix) atomicAdd(&hist_cnt[(key >> shift) & 255u], 1u);
-      }
+      });
       __syncthreads();
       if (tid == 0) {
         unsigned int rem = sh_krem, cum = 0u;
@@ -150,7 +234,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
   if (p < 1.f) {
     // largest s for a stable exponent
     float mx = -INFINITY;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) mx = fmaxf(mx, lg[i] / T);
+    scan_row(lg, 0, V, vec != 0, tid, SAMPLE_THREADS, [&](int i, float x) { mx = fmaxf(mx, x / T); });
     mx = mi_warp_max(mx);
     __shared__ float sh_max[32];
     __syncthreads();
@@ -168,10 +252,10 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     __syncthreads();
     // total mass of the kept set
     unsigned long long part = 0ull;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
-      const float s = lg[i] / T;
+    scan_row(lg, 0, V, vec != 0, tid, SAMPLE_THREADS, [&](int i, float x) {
+      const float s = x / T;
       if (order_key(s) >= kmin) part += __float2ull_rd(expf(s - mx) * 1099511627776.f);
-    }
+    });
     atomicAdd(&sh_total, part);
     __syncthreads();
     const unsigned long long target = (unsigned long long)((double)p * (double)sh_total);
@@ -179,12 +263,12 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
       const int shift = 24 - 8 * pass;
       for (int b = tid; b < 256; b += SAMPLE_THREADS) hist_mass[b] = 0ull;
       __syncthreads();
-      for (int i = tid; i < V; i += SAMPLE_THREADS) {
-        const float s = lg[i] / T;
+      scan_row(lg, 0, V, vec != 0, tid, SAMPLE_THREADS, [&](int i, float x) {
+        const float s = x / T;
         const uint32_t key = order_key(s);
         if (key >= kmin && (key & mask) == prefix)
           atomicAdd(&hist_mass[(key >> shift) & 255u], __float2ull_rd(expf(s - mx) * 1099511627776.f));
-      }
+      });
       __syncthreads();
       if (tid == 0) {
         unsigned long long above = sh_above;
@@ -215,15 +299,15 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
   ArgBest b;
   b.v = 0.f;
   b.i = -1;
-  for (int i = tid; i < V; i += SAMPLE_THREADS) {
-    const float s = lg[i] / T;
+  scan_row(lg, 0, V, vec != 0, tid, SAMPLE_THREADS, [&](int i, float x) {
+    const float s = x / T;
     if (s == s && order_key(s) >= kmin) {
       ArgBest c;
       c.v = s + gumbel_noise((uint32_t)i, draw, k0, k1);
       c.i = i;
       b = better(b, c);
     }
-  }
+  });
   b = block_best(b, best_scratch);
   if (tid == 0) out[row] = b.i;
 }
@@ -238,7 +322,12 @@ extern "C" int mi_sample(const float* logits, int ld, int B, int V, const float*
   if (V <= 0 || ld < V) MI_REFUSE("sample: bad vocabulary %d (row stride %d)", V, ld);
   if (temperature && (!seed_lo || !seed_hi || !draw_index))
     MI_REFUSE("sample: seeds and draw indices are required with a temperature");
+  const int vec = (mi_aligned(logits, 16) && ld % 4 == 0) ? 1 : 0;
+  if (!temperature && B <= ARGMAX_MAX_ROWS && V >= 4096) {   // all greedy: rows cut across blocks
+    MI_LAUNCH((argmax_split_kernel), dim3(ARGMAX_SPLITS, B), SAMPLE_THREADS, 0, stream, logits, ld, V, vec, out);
+    MI_RETURN_LAUNCH_STATUS();
+  }
   MI_LAUNCH((sample_kernel), B, SAMPLE_THREADS, 0, stream, logits, ld, V, temperature, top_k, top_p, seed_lo,
-                                                  seed_hi, draw_index, out);
+                                                  seed_hi, draw_index, vec, out);
   MI_RETURN_LAUNCH_STATUS();
 }

@@ -445,6 +445,25 @@ def test_sample_greedy_is_argmax_with_lowest_index():
     assert got == want
 
 
+@pytest.mark.parametrize("V", [4096, 50001, 128256])
+def test_sample_greedy_with_rows_cut_across_blocks(V):
+    """Large vocabularies are scanned by several blocks per row; equal maxima in different
+    slices still give the lowest index, and a vocabulary that is no multiple of the slices,
+    or of four, loses no element."""
+    logits = rnd(5, V, seed=15)
+    logits[1, 3] = logits[1, V - 1] = 60.0          # a tie between the first and the last slice
+    logits[2, V - 1] = 70.0                         # the very last element wins
+    logits[3, V // 2 + 1] = logits[3, V // 2 + 2] = 65.0
+    want = logits.argmax(dim=-1).tolist()
+    want[1], want[3] = 3, V // 2 + 1
+    for _ in range(3):                              # the arrival counters reset themselves
+        assert sample_rows(logits) == want
+    # a view whose rows are not 16-byte aligned takes the element-wise scan
+    wide = torch.zeros(5, V + 3)
+    wide[:, 1:V + 1] = logits
+    assert sample_rows(wide.to(DEV)[:, 1:V + 1]) == want
+
+
 def test_sample_matches_reference_draws():
     V = 1000
     logits = rnd(8, V, seed=14, scale=2.0)
