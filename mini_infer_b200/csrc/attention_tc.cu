@@ -1,0 +1,547 @@
+// Prefill attention over the paged cache on the fifth-generation tensor cores.
+//
+// One block takes a tile of 128 rows (tokens x the query heads that share one key/value head)
+// and walks the request's keys in chunks of 64:
+//
+//   warp 4   one thread issues TMA copies of key and value pages into a two-stage ring.  The
+//            cache stores every row with its 16-byte chunks permuted by the key's in-page
+//            offset, which is exactly the 128-byte-swizzle pattern of the tensor cores' shared
+//            memory operands, so un-swizzled box copies of [page_size keys x 64 dims] land in
+//            the canonical layout: K as a K-major operand, V as an MN-major one.
+//   warp 5   one thread issues tcgen05.mma: S = Q K^T (128 x 64, fp32 in tensor memory, two
+//            buffers so that the next chunk's scores are computed while this one's softmax
+//            runs) and O += P V (128 x d, fp32 in tensor memory).
+//   warps 0-3  softmax, one row per thread: read the row of S from tensor memory, mask what
+//            the row must not see, keep the running maximum and sum in registers (fp32, log2
+//            domain), rescale O in tensor memory when the maximum moved, write P (bf16) into
+//            shared memory as the K-major A operand of the second product.
+//
+// Takes head sizes 64 and 128, power-of-two page sizes from 8 to 64, any group size that
+// divides 128; the mma.sync kernel of attention_mma.cu takes everything else.
+// Every mbarrier wait is bounded: a wait that gives up sets a status word, the block leaves
+// its loops, frees its tensor memory and returns.
+#include "common.cuh"
+
+#include <cuda.h>
+
+MI_DEFINE_ERROR_API()
+
+#define ROWS 128
+#define KC 64            // keys per chunk
+#define TC_THREADS 192
+#define SPIN_LIMIT (1 << 22)
+#define LOG2E 1.4426950408889634f
+#define RESCALE_LOG2 8.0f   // how far (in powers of two) a score may exceed the running reference before O is rescaled
+
+static __device__ int g_tc_status;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* give_up) {
+  for (int it = 0; it < SPIN_LIMIT; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 1023) == 1023 && *give_up) return false;   // another role of this block gave up
+  }
+  atomicExch(&g_tc_status, 1);
+  *give_up = 1;
+  return false;
+}
+// the same for a whole warp: every lane waits, and they leave together
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* give_up) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, give_up));
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::
+          "r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+// Shared-memory operand descriptors, 128-byte swizzle, 8-row groups 1024 bytes apart.
+// K-major: rows are 128 bytes of k.  MN-major: rows are 128 bytes (64 elements) of m/n, one row
+// per k; `lbo` is the distance to the next 64 elements of m/n.
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t addr, uint32_t lbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// bf16 x bf16 -> fp32; b_mn: the B operand is MN-major
+__device__ __forceinline__ uint32_t idesc_bf16(int m, int n, int b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+// 32 consecutive columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// the same without waiting: the registers are valid after tmem_ld_wait()
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+      "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+      "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+      "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+      "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+      "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+      "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+      "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+      "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// barriers of the block, in one array
+#define NSTAGE 4   // chunks of keys and values in flight: a chunk's copies start three chunks ahead
+enum {
+  B_KFULL = 0, B_VFULL = NSTAGE, B_KEMPTY = 2 * NSTAGE, B_VEMPTY = 3 * NSTAGE, B_SFULL = 4 * NSTAGE,
+  B_SEMPTY = 4 * NSTAGE + 2, B_PFULL = 4 * NSTAGE + 4, B_PVDONE = 4 * NSTAGE + 5, B_COUNT = 4 * NSTAGE + 6
+};
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+                            const int* __restrict__ block_table, int bt_stride, int page_size, int page_shift,
+                            const int* __restrict__ q_start, const int* __restrict__ q_len,
+                            const int* __restrict__ kv_len, const int* __restrict__ tile_req,
+                            const int* __restrict__ tile_tok0, int nq, int nkv, int d, float scale, int window,
+                            int gb, int tt) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int halves = d >> 6;                       // 64-element (128-byte) column blocks of a row
+  const uint32_t tile_bytes = KC * 128 * halves;   // one K or V chunk: [half][64 keys][128 B]
+  unsigned char* Qs = smem;                        // [half][128 rows][128 B]
+  unsigned char* Ps = Qs + ROWS * 128 * halves;    // [128 rows][128 B]
+  unsigned char* Ks = Ps + ROWS * 128;             // [NSTAGE][tile]
+  unsigned char* Vs = Ks + NSTAGE * tile_bytes;    // [NSTAGE][tile]
+  __shared__ __align__(8) uint64_t bars[B_COUNT];
+  __shared__ uint32_t tmem_base_holder;
+  __shared__ int give_up;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = nq / nkv;
+  const int hblocks = (g + gb - 1) / gb;
+  const int tile = gridDim.x - 1 - blockIdx.x;     // longest tiles first (causal)
+  const int kvh = blockIdx.y / hblocks, hb = blockIdx.y - kvh * hblocks;
+  const int b = tile_req[tile], tok0 = tile_tok0[tile];
+  const int ql = q_len[b], kl = kv_len[b], qs = q_start[b];
+  const int ntok = min(tt, ql - tok0);
+  const int p_first = kl - ql + tok0;
+  const int hi = p_first + ntok;                   // one past the last key any row of the tile sees
+  const int lo = window > 0 ? max(0, p_first - window + 1) : 0;
+  const int heads_here = min(gb, g - hb * gb);
+  const int c0 = lo / KC, c1 = (hi + KC - 1) / KC;
+  const int n_chunks = c1 - c0;
+  volatile int* gu = &give_up;
+
+  if (tid == 0) {
+    for (int i = 0; i < B_COUNT; ++i)   // the softmax warps arrive one thread each
+      mbar_init(&bars[i], (i == B_SEMPTY || i == B_SEMPTY + 1 || i == B_PFULL) ? 4 : 1);
+    give_up = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_holder)),
+                 "r"(256)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  // the query tile, row R = (token tok0 + R / gb, head kvh * g + hb * gb + R % gb), into the
+  // swizzled K-major layout; rows that do not exist are zero
+  {
+    const int units = d >> 3;   // 16-byte chunks per row
+    for (int idx = tid; idx < ROWS * units; idx += TC_THREADS) {
+      const int R = idx / units, u = idx - R * units;
+      const int tk = R / gb, mem = R - tk * gb;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (tk < ntok && mem < heads_here)
+        v = *reinterpret_cast<const uint4*>(q + (size_t)(qs + tok0 + tk) * q_stride +
+                                            (size_t)(kvh * g + hb * gb + mem) * d + u * 8);
+      const int half = u >> 3, c = u & 7;
+      *reinterpret_cast<uint4*>(Qs + half * (ROWS * 128) + R * 128 + ((c ^ (R & 7)) << 4)) = v;
+    }
+    fence_async_smem();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_holder;
+  const uint32_t tmem_s0 = tmem, tmem_o = tmem + 128;   // S buffers at columns 0 and 64, O at 128
+
+  if (warp == 4) {
+    // The copy warp: lane p owns page p of the chunk (its id is fetched one chunk ahead, all
+    // lanes at once) and issues that page's boxes, so a chunk costs one round trip to the block
+    // table, not one per page.
+    const int* table = block_table + (size_t)b * bt_stride;
+    const int ppc = KC >> page_shift;   // pages per chunk
+    auto page_of = [&](int it) -> int {
+      const int key = (c0 + it) * KC + (lane << page_shift);
+      return (it < n_chunks && lane < ppc && key < hi) ? table[key >> page_shift] : -1;
+    };
+    int page = page_of(0);
+    for (int it = 0; it < n_chunks; ++it) {
+      const int st = it % NSTAGE, round = it / NSTAGE;
+      const int next_page = page_of(it + 1);
+      if (round > 0) {
+        if (!warp_wait(&bars[B_KEMPTY + st], (round - 1) & 1, gu)) break;
+        if (!warp_wait(&bars[B_VEMPTY + st], (round - 1) & 1, gu)) break;
+      }
+      // pages of the chunk that hold a key below hi (the others are never touched: their
+      // scores are masked and their value rows are cleared by the softmax warps)
+      const int key0 = (c0 + it) * KC;
+      const int n_pages = min(ppc, (hi - key0 + page_size - 1) >> page_shift);
+      if (lane == 0) {
+        const uint32_t bytes = (uint32_t)n_pages * page_size * 128u * halves;
+        mbar_expect_tx(&bars[B_KFULL + st], bytes);
+        mbar_expect_tx(&bars[B_VFULL + st], bytes);
+      }
+      __syncwarp();
+      if (lane < n_pages) {
+        const int row = (page * nkv + kvh) * page_size;
+        for (int h = 0; h < halves; ++h)
+          tma_load_2d(Ks + st * tile_bytes + h * (KC * 128) + lane * page_size * 128, &map_k, h * 64, row,
+                      &bars[B_KFULL + st]);
+        for (int h = 0; h < halves; ++h)
+          tma_load_2d(Vs + st * tile_bytes + h * (KC * 128) + lane * page_size * 128, &map_v, h * 64, row,
+                      &bars[B_VFULL + st]);
+      }
+      page = next_page;
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t idesc_qk = idesc_bf16(ROWS, KC, 0), idesc_pv = idesc_bf16(ROWS, d, 1);
+      const uint32_t q_addr = smem_u32(Qs), p_addr = smem_u32(Ps);
+      auto issue_qk = [&](int it) -> bool {   // S[it & 1] = Q K^T of chunk it
+        const int st = it % NSTAGE, round = it / NSTAGE, sb = it & 1, sround = it >> 1;
+        if (sround > 0 && !mbar_wait(&bars[B_SEMPTY + sb], (sround - 1) & 1, gu)) return false;
+        if (!mbar_wait(&bars[B_KFULL + st], round & 1, gu)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(Ks + st * tile_bytes);
+        uint32_t acc = 0;
+        for (int h = 0; h < halves; ++h)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {   // 16 of the 64 dims of a half per MMA: 32 bytes along the row
+            umma(tmem_s0 + sb * KC, desc_sw128(q_addr + h * (ROWS * 128) + k * 32, 0),
+                 desc_sw128(k_addr + h * (KC * 128) + k * 32, 0), idesc_qk, acc);
+            acc = 1;
+          }
+        umma_commit(&bars[B_KEMPTY + st]);
+        umma_commit(&bars[B_SFULL + sb]);
+        return true;
+      };
+      bool ok = n_chunks > 0 && issue_qk(0);
+      for (int it = 0; it < n_chunks && ok; ++it) {
+        if (it + 1 < n_chunks) ok = issue_qk(it + 1);   // the next scores, beside this chunk's softmax
+        if (!ok) break;
+        const int st = it % NSTAGE, round = it / NSTAGE;
+        if (!mbar_wait(&bars[B_VFULL + st], round & 1, gu)) break;
+        if (!mbar_wait(&bars[B_PFULL], it & 1, gu)) break;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(Vs + st * tile_bytes);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
+          umma(tmem_o, desc_sw128(p_addr + k * 32, 0), desc_sw128(v_addr + k * 2048, KC * 128), idesc_pv,
+               (it > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&bars[B_VEMPTY + st]);
+        umma_commit(&bars[B_PVDONE]);
+      }
+    }
+  } else {
+    // softmax: thread = row (TMEM lane)
+    const int R = tid;
+    const int tk = R / gb, mem = R - tk * gb;
+    const bool rvalid = tk < ntok && mem < heads_here;
+    const int prow = p_first + tk;
+    const int lorow = window > 0 ? max(0, prow - window + 1) : 0;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const float sc = scale * LOG2E;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int it = 0; it < n_chunks; ++it) {
+      const int c = c0 + it, sb = it & 1, sround = it >> 1, st = it % NSTAGE, round = it / NSTAGE;
+      const int key0 = c * KC;
+      if (!warp_wait(&bars[B_SFULL + sb], sround & 1, gu)) { ok = false; break; }
+      tc_fence_after();
+      float s[64];
+      {
+        uint32_t ra[32], rb[32];
+        tmem_ld32_issue(tmem_s0 + lane_addr + sb * KC, ra);
+        tmem_ld32_issue(tmem_s0 + lane_addr + sb * KC + 32, rb);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          s[i] = __uint_as_float(ra[i]);
+          s[32 + i] = __uint_as_float(rb[i]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[B_SEMPTY + sb]);   // the scores are in registers
+      const bool interior = key0 + KC - 1 <= p_first && key0 >= (window > 0 ? max(0, hi - window) : 0) && key0 >= lo;
+      if (!interior || !rvalid) {
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          if (!(rvalid && key0 + j <= prow && key0 + j >= lorow)) s[j] = -INFINITY;
+      }
+      float mx8[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        mx8[i] = fmaxf(fmaxf(fmaxf(s[8 * i], s[8 * i + 1]), fmaxf(s[8 * i + 2], s[8 * i + 3])),
+                       fmaxf(fmaxf(s[8 * i + 4], s[8 * i + 5]), fmaxf(s[8 * i + 6], s[8 * i + 7])));
+      }
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * sc;   // sc > 0
+      // The exponents are taken relative to m_run, which follows the true running maximum
+      // lazily: it moves (and O and l are rescaled) only when some row of the warp found a
+      // score more than 2^RESCALE_LOG2 above it.  Probabilities may then exceed 1 by that
+      // factor, which fp32 sums and bf16 products hold without loss; the result is the same
+      // quotient, and rescaling O in tensor memory becomes rare instead of the rule.
+      const bool moved = __any_sync(0xffffffffu, mx > m_run + RESCALE_LOG2);
+      const float m_new = moved ? fmaxf(m_run, mx) : m_run;
+      float alpha = 1.f, sum = 0.f;
+      if (m_new != -INFINITY) {
+        alpha = fast_exp2(m_run - m_new);
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          s[j] = fast_exp2(fmaf(s[j], sc, -m_new));
+          sum4[j & 3] += s[j];
+        }
+        sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) s[j] = 0.f;
+      }
+      m_run = m_new;
+      l_run = l_run * alpha + sum;
+      // P's buffer and O are free once the previous chunk's second product has finished
+      if (it > 0 && !warp_wait(&bars[B_PVDONE], (it - 1) & 1, gu)) { ok = false; break; }
+      tc_fence_after();
+      if (it > 0 && moved) {
+        for (int c32 = 0; c32 < d; c32 += 32) {
+          float t[32];
+          tmem_ld32(tmem_o + lane_addr + c32, t);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) t[i] *= alpha;
+          tmem_st32(tmem_o + lane_addr + c32, t);
+        }
+        tmem_st_wait();
+      }
+      // P as bf16 into the swizzled K-major tile: row R, 16-byte chunk cc holds keys 8cc .. 8cc+7
+      {
+        unsigned char* prow_ptr = Ps + R * 128;
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          uint4 v;
+          v.x = pack_bf16(s[8 * cc], s[8 * cc + 1]);
+          v.y = pack_bf16(s[8 * cc + 2], s[8 * cc + 3]);
+          v.z = pack_bf16(s[8 * cc + 4], s[8 * cc + 5]);
+          v.w = pack_bf16(s[8 * cc + 6], s[8 * cc + 7]);
+          *reinterpret_cast<uint4*>(prow_ptr + ((cc ^ (R & 7)) << 4)) = v;
+        }
+      }
+      // value rows of keys nobody may see can hold anything (pages never written, stale rows):
+      // clear them, 0 * NaN is NaN.  Only a request's first and last chunks have such rows.
+      if (key0 < lo || key0 + KC > hi) {
+        if (!warp_wait(&bars[B_VFULL + st], round & 1, gu)) { ok = false; break; }
+        unsigned char* vt = Vs + st * tile_bytes;
+        for (int idx = tid; idx < KC * halves * 8; idx += 128) {
+          const int j = idx / (halves * 8), rest = idx - j * (halves * 8);
+          if (key0 + j < lo || key0 + j >= hi)
+            *reinterpret_cast<uint4*>(vt + (rest >> 3) * (KC * 128) + j * 128 + ((rest & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[B_PFULL]);
+    }
+    // the output: O / l
+    if (ok && n_chunks > 0 && warp_wait(&bars[B_PVDONE], (n_chunks - 1) & 1, gu)) {
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      bf16* orow = out + (size_t)(qs + tok0 + tk) * out_stride + (size_t)(kvh * g + hb * gb + mem) * d;
+      for (int c32 = 0; c32 < d; c32 += 32) {
+        float t[32];
+        tmem_ld32(tmem_o + lane_addr + c32, t);   // every thread of the warp takes part in the load
+        if (rvalid && l_run > 0.f) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack_bf16(t[i] * inv, t[i + 1] * inv);
+            v.y = pack_bf16(t[i + 2] * inv, t[i + 3] * inv);
+            v.z = pack_bf16(t[i + 4] * inv, t[i + 5] * inv);
+            v.w = pack_bf16(t[i + 6] * inv, t[i + 7] * inv);
+            *reinterpret_cast<uint4*>(orow + c32 + i) = v;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base_holder), "r"(256) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------- host
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// A cache [rows, d] bf16 read in boxes of page_size rows x 64 elements, bytes copied as they are
+// (the rows are already stored in the swizzled order).
+static bool make_cache_map(CUtensorMap* map, const void* base, long long rows, int d, int page_size) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)d * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+extern "C" int mi_attention_tc_status(int reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && v) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+  }
+  return v;
+}
+
+// 1 if the kernel takes these sizes (the caller uses the mma.sync kernel otherwise)
+extern "C" int mi_attention_prefill_tc_supported(int nq, int nkv, int d, int page_size) {
+  if (d != 64 && d != 128) return 0;
+  if (page_size < 8 || page_size > KC || (page_size & (page_size - 1))) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv) return 0;
+  const int g = nq / nkv, gb = g < ROWS ? g : ROWS;
+  return ROWS % gb == 0 ? 1 : 0;
+}
+
+// Same arguments as mi_attention_prefill (attention_mma.cu) plus the number of pages of the
+// cache; tiles are ROWS / min(g, ROWS) tokens.
+extern "C" int mi_attention_prefill_tc(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
+                                       const void* vcache, long long n_pages, const int* block_table, int bt_stride,
+                                       int page_size, const int* q_start, const int* q_len, const int* kv_len,
+                                       const int* tile_req, const int* tile_tok0, int n_tiles, int tile_tokens,
+                                       int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (!mi_attention_prefill_tc_supported(nq, nkv, d, page_size))
+    MI_REFUSE("attention_tc: sizes not taken (heads %d/%d, head size %d, pages of %d)", nq, nkv, d, page_size);
+  if (!(scale > 0.f)) MI_REFUSE("attention_tc: the score scale must be positive");
+  if (window < 0) MI_REFUSE("attention_tc: bad window %d", window);
+  if (!mi_aligned(q, 16) || q_stride % 8 != 0) MI_REFUSE("attention_tc: queries must be 16-byte aligned rows");
+  if (!mi_aligned(out, 16) || out_stride % 8 != 0) MI_REFUSE("attention_tc: output rows must be 16-byte aligned");
+  if (!mi_aligned(kcache, 128) || !mi_aligned(vcache, 128)) MI_REFUSE("attention_tc: the cache must be 128-byte aligned");
+  const int g = nq / nkv, gb = g < ROWS ? g : ROWS;
+  if (tile_tokens != ROWS / gb) MI_REFUSE("attention_tc: tiles of %d tokens, the kernel wants %d", tile_tokens, ROWS / gb);
+  const int hblocks = (g + gb - 1) / gb;
+  if (nkv * hblocks > 65535) MI_REFUSE("attention_tc: too many heads for one launch");
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  CUtensorMap map_k, map_v;
+  const long long rows = n_pages * nkv * page_size;
+  if (!make_cache_map(&map_k, kcache, rows, d, page_size) || !make_cache_map(&map_v, vcache, rows, d, page_size))
+    MI_REFUSE("attention_tc: the driver refused a tensor map");
+  const int halves = d / 64;
+  const size_t smem = (size_t)ROWS * 128 * halves + ROWS * 128 + 2 * NSTAGE * (size_t)KC * 128 * halves + 1024;
+  auto kern = attention_prefill_tc_kernel;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid(n_tiles, nkv * hblocks);
+  MI_LAUNCH((kern), grid, TC_THREADS, smem, stream, map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride,
+            block_table, bt_stride, page_size, page_shift, q_start, q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, scale,
+            window, gb, ROWS / gb);
+  MI_RETURN_LAUNCH_STATUS();
+}

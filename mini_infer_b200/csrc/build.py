@@ -38,6 +38,7 @@ LIBRARIES: dict[str, tuple[list[str], list[str], list[str]]] = {
     "attention_mma": (["attention_mma.cu"], ["common.cuh", "attention_noalloc.h"], []),
     "gemm_skinny": (["gemm_skinny.cu"], ["common.cuh"], []),
     "gemm_tma": (["gemm_tma.cu"], ["common.cuh"], []),
+    "attention_tc": (["attention_tc.cu"], ["common.cuh"], []),
 }
 
 

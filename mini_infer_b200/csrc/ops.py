@@ -123,7 +123,17 @@ def _sig_gemm_tma(lib: ctypes.CDLL) -> None:
     lib.mi_gemm_tma_status.argtypes = [c_int]
 
 
+def _sig_attention_tc(lib: ctypes.CDLL) -> None:
+    lib.mi_attention_prefill_tc.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+        c_void_p]
+    lib.mi_attention_prefill_tc_supported.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mi_attention_tc_status.argtypes = [c_int]
+
+
 _SIGNATURES = {
+    "attention_tc": _sig_attention_tc,
     "gemm_tma": _sig_gemm_tma,
     "gemm_skinny": _sig_gemm_skinny,
     "attention_mma": _sig_attention_mma,
@@ -362,7 +372,8 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq:
     ``cache`` is a ``LayerCache`` (its ``k``/``v`` pages and group index), ``ctx`` the
     ``StepContext`` (block tables, lengths, query tiles).  float32 runs the CUDA-core kernel;
     bfloat16 runs the tensor-core kernels: split-key decode when every request brings one
-    token, the tiled prefill kernel otherwise.
+    token, otherwise the tcgen05 prefill kernel where it takes the sizes and the mma.sync
+    prefill kernel elsewhere.
     """
     group = ctx.groups[cache.group]
     if q.dtype == torch.bfloat16:
@@ -373,9 +384,11 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq:
         else:
             tt = prefill_tile_tokens(nq // nkv)
             tile_req, tile_tok0, n_tiles = ctx.q_tiles(tt)
-            attention_prefill(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
-                              ctx.q_start, ctx.q_len, ctx.kv_len, tile_req, tile_tok0, n_tiles, tt,
-                              nq, nkv, head_dim, scale, window)
+            tc = USE_TC_PREFILL and prefill_tc_supported(nq, nkv, head_dim, group.page_size)
+            (attention_prefill_tc if tc else attention_prefill)(
+                q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
+                ctx.q_start, ctx.q_len, ctx.kv_len, tile_req, tile_tok0, n_tiles, tt,
+                nq, nkv, head_dim, scale, window)
         return
     tile_req, tile_tok0, n_tiles = ctx.q_tiles(ATTENTION_TILE_TOKENS)
     attention_generic(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
@@ -456,6 +469,39 @@ def attention_prefill(q, q_stride, out, kcache, vcache, block_table, page_size, 
         _ptr(tile_tok0), int(n_tiles), int(tile_tokens), nq, nkv, head_dim, float(scale), int(window),
         _stream())
     _finish(lib, rc, "attention_prefill")
+
+
+USE_TC_PREFILL = os.environ.get("MINI_INFER_TC_PREFILL", "1") != "0"
+
+
+def prefill_tc_supported(nq: int, nkv: int, head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 prefill kernel (attention_tc.cu) takes these sizes."""
+    return bool(_lib("attention_tc").mi_attention_prefill_tc_supported(nq, nkv, head_dim, page_size))
+
+
+def attention_prefill_tc(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, q_len, kv_len,
+                         tile_req, tile_tok0, n_tiles, tile_tokens, nq, nkv, head_dim, scale, window=0) -> None:
+    """bfloat16 attention of query portions over the paged cache on tcgen05 (attention_tc.cu);
+    same arguments as ``attention_prefill``."""
+    _cuda(q, out, kcache, vcache, block_table, q_start, q_len, kv_len, tile_req, tile_tok0)
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill_tc: bfloat16 only")
+    _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, page_size,
+                          (("block_table", block_table), ("q_start", q_start), ("q_len", q_len),
+                           ("kv_len", kv_len), ("tile_req", tile_req), ("tile_tok0", tile_tok0)))
+    lib = _lib("attention_tc")
+    rc = lib.mi_attention_prefill_tc(
+        _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), int(kcache.shape[0]),
+        _ptr(block_table), block_table.stride(0), int(page_size), _ptr(q_start), _ptr(q_len), _ptr(kv_len),
+        _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), int(tile_tokens), nq, nkv, head_dim, float(scale),
+        int(window), _stream())
+    _finish(lib, rc, "attention_prefill_tc")
+
+
+def attention_tc_status(reset: bool = True) -> int:
+    """Non-zero when a block of the tcgen05 prefill kernel gave up a bounded wait since the
+    last reset (its output is then wrong).  Synchronises the device."""
+    return int(_lib("attention_tc").mi_attention_tc_status(1 if reset else 0))
 
 
 def attention_generic(

@@ -1,7 +1,7 @@
 """Time one kernel of the engine alone, at sizes given on the command line.
 
     python -m mini_infer_b200.microbench attention_decode --batch 8 --context 2048
-    python -m mini_infer_b200.microbench attention_prefill --tokens 2048
+    python -m mini_infer_b200.microbench attention_prefill --tokens 2048 [--impl mma]
     python -m mini_infer_b200.microbench gemm_tma --rows 8 --n 28672 --k 4096
     python -m mini_infer_b200.microbench add_rmsnorm --rows 8 --width 4096
     python -m mini_infer_b200.microbench rope_write --rows 2048
@@ -83,9 +83,11 @@ def attention_prefill(args, ops, device, flush) -> tuple[float, str]:
     tile_req = torch.zeros(n_tiles, device=device, dtype=torch.int32)
     tile_tok0 = (torch.arange(n_tiles, device=device, dtype=torch.int32) * tile).contiguous()
 
+    kernel = ops.attention_prefill_tc if args.impl == "tc" else ops.attention_prefill
+
     def run():
-        ops.attention_prefill(qkv, qkv.stride(0), out, kcache, vcache, table, args.page, q_start, q_len, kv_len,
-                              tile_req, tile_tok0, n_tiles, tile, nq, nkv, d, 1.0 / math.sqrt(d), 0)
+        kernel(qkv, qkv.stride(0), out, kcache, vcache, table, args.page, q_start, q_len, kv_len,
+               tile_req, tile_tok0, n_tiles, tile, nq, nkv, d, 1.0 / math.sqrt(d), 0)
 
     us = _time(run, args.iters, args.warmup, flush)
     flops = 4.0 * nq * d * T * (T + 1) / 2     # causal: QK^T and PV over the visible half
@@ -189,6 +191,8 @@ def main(argv=None) -> int:
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--top-k", type=int, default=0)
     ap.add_argument("--top-p", type=float, default=1.0)
+    ap.add_argument("--impl", choices=["tc", "mma"], default="tc",
+                    help="attention_prefill: the tcgen05 kernel or the mma.sync kernel")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)

@@ -309,10 +309,12 @@ def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, bo
     if kernel == "generic":
         o.attention_generic(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), page, i32(q_start),
                             i32(q_lens), i32(kv_lens), i32(treq), i32(ttok), len(treq), nq, nkv, d, scale, window)
-    elif kernel == "prefill":
-        o.attention_prefill(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), page, i32(q_start),
-                            i32(q_lens), i32(kv_lens), i32(treq), i32(ttok), len(treq), T_, nq, nkv, d, scale,
-                            window)
+    elif kernel in ("prefill", "prefill_tc"):
+        fn = o.attention_prefill if kernel == "prefill" else o.attention_prefill_tc
+        fn(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), page, i32(q_start),
+           i32(q_lens), i32(kv_lens), i32(treq), i32(ttok), len(treq), T_, nq, nkv, d, scale, window)
+        if kernel == "prefill_tc":
+            assert o.attention_tc_status() == 0, "a block of the tcgen05 kernel gave up a wait"
     else:
         assert all(n == 1 for n in q_lens)
         o.attention_decode(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), page, i32(q_start),
@@ -378,6 +380,49 @@ def test_attention_prefill_tensor_cores_window(window):
     got, want = run_attention([1, 90, 3, 150], [90, 170, 3, 150], 4, 2, 32, 8, torch.bfloat16, window=window,
                               seed=3, kernel="prefill")
     assert (got - want).abs().max().item() <= BF16_BOUND
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(32, 8, 128, 16), (8, 1, 128, 8), (4, 4, 64, 16), (16, 2, 64, 64),
+                                            (2, 1, 128, 32), (64, 1, 64, 16)])
+def test_attention_prefill_tcgen05(nq, nkv, d, page):
+    """The tcgen05 prefill kernel at the sizes it takes: both head sizes, every page size, group
+    sizes from 1 (128 tokens per tile) to 64 (2 tokens per tile); requests of one token, of
+    lengths that end inside a page and inside a 64-key chunk, and portions that start deep in
+    the cache.  Never-written cache slots hold NaN (build_paged), so a masked value row that is
+    not cleared would show."""
+    assert ops().prefill_tc_supported(nq, nkv, d, page)
+    q_lens = [1, 5, 37, 1, 16, 130, 64]
+    kv_lens = [1, 5, 100, 131, 16, 257, 320]
+    got, want = run_attention(q_lens, kv_lens, nq, nkv, d, page, torch.bfloat16, seed=nq, kernel="prefill_tc")
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max().item() <= BF16_BOUND
+
+
+@pytest.mark.parametrize("window", [1, 7, 20, 64, 100])
+def test_attention_prefill_tcgen05_window(window):
+    got, want = run_attention([1, 90, 3, 150], [90, 170, 3, 150], 4, 2, 64, 8, torch.bfloat16, window=window,
+                              seed=3, kernel="prefill_tc")
+    assert (got - want).abs().max().item() <= BF16_BOUND
+
+
+def test_attention_prefill_tcgen05_far_key_and_big_scores():
+    """One key far back matches the last query strongly (its score is hundreds of units above
+    the rest, far beyond the lazy-rescale threshold), in the first chunk, at a chunk's edge and
+    in the last chunk; and the sizes the kernel does not take are refused."""
+    nq, nkv, d, page = 2, 1, 64, 16
+    for target in (0, 63, 64, 257, 700, 703):
+        def boost(q, ks, kc, bt, target=target):
+            ks[0][target] = 0
+            ks[0][target, 0, 0] = 8.0
+            kc[bt[0, target // page] * page + target % page] = ks[0][target]
+            q[-1] = 0
+            q[-1, :, 0] = 40.0
+        got, want = run_attention([70], [704], nq, nkv, d, page, torch.bfloat16, seed=5, boost=boost,
+                                  kernel="prefill_tc")
+        assert (got - want).abs().max().item() <= BF16_BOUND
+    assert not ops().prefill_tc_supported(6, 2, 48, 8)
+    assert not ops().prefill_tc_supported(4, 4, 64, 4)
+    assert not ops().prefill_tc_supported(3, 1, 128, 16)
 
 
 @pytest.mark.parametrize("n_splits", [1, 2, 5, 64])
