@@ -3,15 +3,15 @@
 // One block takes a tile of 128 rows (tokens x the query heads that share one key/value head)
 // and walks the request's keys in chunks of 64:
 //
-//   warp 4   one thread issues TMA copies of key and value pages into a two-stage ring.  The
+//   warps 8, 10  issue TMA copies of key and value pages into a two-stage ring.  The
 //            cache stores every row with its 16-byte chunks permuted by the key's in-page
 //            offset, which is exactly the 128-byte-swizzle pattern of the tensor cores' shared
 //            memory operands, so un-swizzled box copies of [page_size keys x 64 dims] land in
 //            the canonical layout: K as a K-major operand, V as an MN-major one.
-//   warp 5   one thread issues tcgen05.mma: S = Q K^T (128 x 64, fp32 in tensor memory, two
+//   warps 9, 11  one thread each issues tcgen05.mma: S = Q K^T (128 x 64, fp32 in tensor memory, two
 //            buffers so that the next chunk's scores are computed while this one's softmax
 //            runs) and O += P V (128 x d, fp32 in tensor memory).
-//   warps 0-3  softmax, one row per thread: read the row of S from tensor memory, mask what
+//   warps 0-7  softmax, two threads per row (32 of a chunk's 64 keys each): read S from tensor memory, mask what
 //            the row must not see, keep the running maximum and sum in registers (fp32, log2
 //            domain), rescale O in tensor memory when the maximum moved, write P (bf16) into
 //            shared memory as the K-major A operand of the second product.
@@ -28,7 +28,7 @@ MI_DEFINE_ERROR_API()
 
 #define ROWS 128
 #define KC 64            // keys per chunk
-#define TC_THREADS 192
+#define TC_THREADS 384   // eight softmax warps, key copies, first product, value copies, second product
 #define SPIN_LIMIT (1 << 22)
 #define LOG2E 1.4426950408889634f
 #define RESCALE_LOG2 8.0f   // how far (in powers of two) a score may exceed the running reference before O is rescaled
@@ -166,7 +166,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 #define NSTAGE 4   // chunks of keys and values in flight: a chunk's copies start three chunks ahead
 enum {
   B_KFULL = 0, B_VFULL = NSTAGE, B_KEMPTY = 2 * NSTAGE, B_VEMPTY = 3 * NSTAGE, B_SFULL = 4 * NSTAGE,
-  B_SEMPTY = 4 * NSTAGE + 2, B_PFULL = 4 * NSTAGE + 4, B_PVDONE = 4 * NSTAGE + 5, B_COUNT = 4 * NSTAGE + 6
+  B_SEMPTY = 4 * NSTAGE + 2, B_PFULL = 4 * NSTAGE + 4, B_PVDONE = 4 * NSTAGE + 6, B_PAIR = 4 * NSTAGE + 8,
+  B_COUNT = 4 * NSTAGE + 12
 };
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -183,12 +184,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int halves = d >> 6;                       // 64-element (128-byte) column blocks of a row
   const uint32_t tile_bytes = KC * 128 * halves;   // one K or V chunk: [half][64 keys][128 B]
   unsigned char* Qs = smem;                        // [half][128 rows][128 B]
-  unsigned char* Ps = Qs + ROWS * 128 * halves;    // [128 rows][128 B]
-  unsigned char* Ks = Ps + ROWS * 128;             // [NSTAGE][tile]
+  unsigned char* Ps = Qs + ROWS * 128 * halves;    // [2][128 rows][128 B]
+  unsigned char* Ks = Ps + 2 * ROWS * 128;         // [NSTAGE][tile]
   unsigned char* Vs = Ks + NSTAGE * tile_bytes;    // [NSTAGE][tile]
   __shared__ __align__(8) uint64_t bars[B_COUNT];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int give_up;
+  __shared__ float xch_max[2][2][ROWS], xch_sum[2][ROWS];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = nq / nkv;
@@ -208,11 +210,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   if (tid == 0) {
     for (int i = 0; i < B_COUNT; ++i)   // the softmax warps arrive one thread each
-      mbar_init(&bars[i], (i == B_SEMPTY || i == B_SEMPTY + 1 || i == B_PFULL) ? 4 : 1);
+      mbar_init(&bars[i], i >= B_PAIR ? 64 : ((i >= B_SEMPTY && i < B_PVDONE) ? 8 : 1));
     give_up = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_holder)),
                  "r"(256)
                  : "memory");
@@ -240,12 +242,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const uint32_t tmem = tmem_base_holder;
   const uint32_t tmem_s0 = tmem, tmem_o = tmem + 128;   // S buffers at columns 0 and 64, O at 128
 
-  if (warp == 4) {
-    // The copy warp: lane p owns page p of the chunk (its id is fetched one chunk ahead, all
-    // lanes at once) and issues that page's boxes, so a chunk costs one round trip to the block
-    // table, not one per page.
+  if (warp == 8 || warp == 10) {
+    // The copy warps, one for keys and one for values: lane p owns page p of the chunk (its id
+    // is fetched one chunk ahead, all lanes at once) and issues that page's boxes, so a chunk
+    // costs one round trip to the block table, not one per page.  A key stage is free as soon
+    // as its scores are computed, a value stage only after the second product: the two rings
+    // run independently, each as far ahead as its own stages allow.
+    const bool is_v = warp == 10;
     const int* table = block_table + (size_t)b * bt_stride;
     const int ppc = KC >> page_shift;   // pages per chunk
+    const CUtensorMap* map = is_v ? &map_v : &map_k;
+    unsigned char* ring = is_v ? Vs : Ks;
+    const int full0 = is_v ? B_VFULL : B_KFULL, empty0 = is_v ? B_VEMPTY : B_KEMPTY;
     auto page_of = [&](int it) -> int {
       const int key = (c0 + it) * KC + (lane << page_shift);
       return (it < n_chunks && lane < ppc && key < hi) ? table[key >> page_shift] : -1;
@@ -254,115 +262,102 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     for (int it = 0; it < n_chunks; ++it) {
       const int st = it % NSTAGE, round = it / NSTAGE;
       const int next_page = page_of(it + 1);
-      if (round > 0) {
-        if (!warp_wait(&bars[B_KEMPTY + st], (round - 1) & 1, gu)) break;
-        if (!warp_wait(&bars[B_VEMPTY + st], (round - 1) & 1, gu)) break;
-      }
+      if (round > 0 && !warp_wait(&bars[empty0 + st], (round - 1) & 1, gu)) break;
       // pages of the chunk that hold a key below hi (the others are never touched: their
       // scores are masked and their value rows are cleared by the softmax warps)
       const int key0 = (c0 + it) * KC;
       const int n_pages = min(ppc, (hi - key0 + page_size - 1) >> page_shift);
-      if (lane == 0) {
-        const uint32_t bytes = (uint32_t)n_pages * page_size * 128u * halves;
-        mbar_expect_tx(&bars[B_KFULL + st], bytes);
-        mbar_expect_tx(&bars[B_VFULL + st], bytes);
-      }
+      if (lane == 0) mbar_expect_tx(&bars[full0 + st], (uint32_t)n_pages * page_size * 128u * halves);
       __syncwarp();
       if (lane < n_pages) {
         const int row = (page * nkv + kvh) * page_size;
         for (int h = 0; h < halves; ++h)
-          tma_load_2d(Ks + st * tile_bytes + h * (KC * 128) + lane * page_size * 128, &map_k, h * 64, row,
-                      &bars[B_KFULL + st]);
-        for (int h = 0; h < halves; ++h)
-          tma_load_2d(Vs + st * tile_bytes + h * (KC * 128) + lane * page_size * 128, &map_v, h * 64, row,
-                      &bars[B_VFULL + st]);
+          tma_load_2d(ring + st * tile_bytes + h * (KC * 128) + lane * page_size * 128, map, h * 64, row,
+                      &bars[full0 + st]);
       }
       page = next_page;
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
+    // The first product's issuer: S[it & 1] = Q K^T, one chunk ahead of the softmax.  Operand
+    // descriptors are built once; a stage, a half or a k step only adds to the address field.
     if (lane == 0) {
-      const uint32_t idesc_qk = idesc_bf16(ROWS, KC, 0), idesc_pv = idesc_bf16(ROWS, d, 1);
-      const uint32_t q_addr = smem_u32(Qs), p_addr = smem_u32(Ps);
-      auto issue_qk = [&](int it) -> bool {   // S[it & 1] = Q K^T of chunk it
+      const uint32_t idesc_qk = idesc_bf16(ROWS, KC, 0);
+      const uint64_t q_desc = desc_sw128(smem_u32(Qs), 0), k_desc = desc_sw128(smem_u32(Ks), 0);
+      for (int it = 0; it < n_chunks; ++it) {
         const int st = it % NSTAGE, round = it / NSTAGE, sb = it & 1, sround = it >> 1;
-        if (sround > 0 && !mbar_wait(&bars[B_SEMPTY + sb], (sround - 1) & 1, gu)) return false;
-        if (!mbar_wait(&bars[B_KFULL + st], round & 1, gu)) return false;
+        if (sround > 0 && !mbar_wait(&bars[B_SEMPTY + sb], (sround - 1) & 1, gu)) break;
+        if (!mbar_wait(&bars[B_KFULL + st], round & 1, gu)) break;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(Ks + st * tile_bytes);
-        uint32_t acc = 0;
+        const uint64_t kd = k_desc + ((st * tile_bytes) >> 4);
         for (int h = 0; h < halves; ++h)
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {   // 16 of the 64 dims of a half per MMA: 32 bytes along the row
-            umma(tmem_s0 + sb * KC, desc_sw128(q_addr + h * (ROWS * 128) + k * 32, 0),
-                 desc_sw128(k_addr + h * (KC * 128) + k * 32, 0), idesc_qk, acc);
-            acc = 1;
-          }
+          for (int k = 0; k < 4; ++k)   // 16 of the 64 dims of a half per MMA: 32 bytes along the row
+            umma(tmem_s0 + sb * KC, q_desc + ((h * (ROWS * 128) + k * 32) >> 4), kd + ((h * (KC * 128) + k * 32) >> 4),
+                 idesc_qk, (h | k) ? 1u : 0u);
         umma_commit(&bars[B_KEMPTY + st]);
         umma_commit(&bars[B_SFULL + sb]);
-        return true;
-      };
-      bool ok = n_chunks > 0 && issue_qk(0);
-      for (int it = 0; it < n_chunks && ok; ++it) {
-        if (it + 1 < n_chunks) ok = issue_qk(it + 1);   // the next scores, beside this chunk's softmax
-        if (!ok) break;
+      }
+    }
+  } else if (warp == 11) {
+    // The second product's issuer: O += P V as soon as a chunk's probabilities are published.
+    if (lane == 0) {
+      const uint32_t idesc_pv = idesc_bf16(ROWS, d, 1);
+      const uint64_t p_desc = desc_sw128(smem_u32(Ps), 0), v_desc = desc_sw128(smem_u32(Vs), KC * 128);
+      for (int it = 0; it < n_chunks; ++it) {
         const int st = it % NSTAGE, round = it / NSTAGE;
         if (!mbar_wait(&bars[B_VFULL + st], round & 1, gu)) break;
-        if (!mbar_wait(&bars[B_PFULL], it & 1, gu)) break;
+        if (!mbar_wait(&bars[B_PFULL + (it & 1)], (it >> 1) & 1, gu)) break;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(Vs + st * tile_bytes);
+        const uint64_t pd = p_desc + (((it & 1) * (ROWS * 128)) >> 4), vd = v_desc + ((st * tile_bytes) >> 4);
 #pragma unroll
         for (int k = 0; k < 4; ++k)   // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
-          umma(tmem_o, desc_sw128(p_addr + k * 32, 0), desc_sw128(v_addr + k * 2048, KC * 128), idesc_pv,
-               (it > 0 || k > 0) ? 1u : 0u);
+          umma(tmem_o, pd + ((k * 32) >> 4), vd + ((k * 2048) >> 4), idesc_pv, (it > 0 || k > 0) ? 1u : 0u);
         umma_commit(&bars[B_VEMPTY + st]);
-        umma_commit(&bars[B_PVDONE]);
+        umma_commit(&bars[B_PVDONE + (it & 1)]);
       }
     }
   } else {
-    // softmax: thread = row (TMEM lane)
-    const int R = tid;
+    // softmax: two threads per row (TMEM lane), each with half of a chunk's 64 keys.  Warps w
+    // and w + 4 share TMEM lanes 32 (w & 3) .. + 31; they exchange their halves' maxima (and at
+    // the end their sums) through shared memory and meet at a named barrier of their own.
+    const int R = tid & (ROWS - 1), part = tid >> 7;
+    uint64_t* pair_bar = &bars[B_PAIR + (warp & 3)];   // the two warps' meeting point (64 arrivals a phase)
     const int tk = R / gb, mem = R - tk * gb;
     const bool rvalid = tk < ntok && mem < heads_here;
     const int prow = p_first + tk;
     const int lorow = window > 0 ? max(0, prow - window + 1) : 0;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const float sc = scale * LOG2E;
+    const int ocols = d >> 1;   // output columns of this thread
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int it = 0; it < n_chunks; ++it) {
       const int c = c0 + it, sb = it & 1, sround = it >> 1, st = it % NSTAGE, round = it / NSTAGE;
-      const int key0 = c * KC;
+      const int key0 = c * KC, kbase = key0 + part * 32;
       if (!warp_wait(&bars[B_SFULL + sb], sround & 1, gu)) { ok = false; break; }
       tc_fence_after();
-      float s[64];
-      {
-        uint32_t ra[32], rb[32];
-        tmem_ld32_issue(tmem_s0 + lane_addr + sb * KC, ra);
-        tmem_ld32_issue(tmem_s0 + lane_addr + sb * KC + 32, rb);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          s[i] = __uint_as_float(ra[i]);
-          s[32 + i] = __uint_as_float(rb[i]);
-        }
-      }
+      float s[32];
+      tmem_ld32(tmem_s0 + lane_addr + sb * KC + part * 32, s);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[B_SEMPTY + sb]);   // the scores are in registers
       const bool interior = key0 + KC - 1 <= p_first && key0 >= (window > 0 ? max(0, hi - window) : 0) && key0 >= lo;
       if (!interior || !rvalid) {
 #pragma unroll
-        for (int j = 0; j < 64; ++j)
-          if (!(rvalid && key0 + j <= prow && key0 + j >= lorow)) s[j] = -INFINITY;
+        for (int j = 0; j < 32; ++j)
+          if (!(rvalid && kbase + j <= prow && kbase + j >= lorow)) s[j] = -INFINITY;
       }
-      float mx8[8];
+      float mx4[4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        mx8[i] = fmaxf(fmaxf(fmaxf(s[8 * i], s[8 * i + 1]), fmaxf(s[8 * i + 2], s[8 * i + 3])),
+      for (int i = 0; i < 4; ++i) {
+        mx4[i] = fmaxf(fmaxf(fmaxf(s[8 * i], s[8 * i + 1]), fmaxf(s[8 * i + 2], s[8 * i + 3])),
                        fmaxf(fmaxf(s[8 * i + 4], s[8 * i + 5]), fmaxf(s[8 * i + 6], s[8 * i + 7])));
       }
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * sc;   // sc > 0
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;   // sc > 0
+      xch_max[it & 1][part][R] = mx;
+      mbar_arrive(pair_bar);
+      if (!warp_wait(pair_bar, it & 1, gu)) { ok = false; break; }
+      mx = fmaxf(mx, xch_max[it & 1][part ^ 1][R]);
       // The exponents are taken relative to m_run, which follows the true running maximum
       // lazily: it moves (and O and l are rescaled) only when some row of the warp found a
       // score more than 2^RESCALE_LOG2 above it.  Probabilities may then exceed 1 by that
@@ -375,40 +370,43 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         alpha = fast_exp2(m_run - m_new);
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
+        for (int j = 0; j < 32; ++j) {
           s[j] = fast_exp2(fmaf(s[j], sc, -m_new));
           sum4[j & 3] += s[j];
         }
         sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       } else {
 #pragma unroll
-        for (int j = 0; j < 64; ++j) s[j] = 0.f;
+        for (int j = 0; j < 32; ++j) s[j] = 0.f;
       }
       m_run = m_new;
       l_run = l_run * alpha + sum;
-      // P's buffer and O are free once the previous chunk's second product has finished
-      if (it > 0 && !warp_wait(&bars[B_PVDONE], (it - 1) & 1, gu)) { ok = false; break; }
-      tc_fence_after();
+      // P has two buffers: this one is free once the second product of two chunks ago is done.
+      // O may be touched only after the previous chunk's second product (rare: see above).
+      if (it > 1 && !warp_wait(&bars[B_PVDONE + (it & 1)], ((it >> 1) - 1) & 1, gu)) { ok = false; break; }
       if (it > 0 && moved) {
-        for (int c32 = 0; c32 < d; c32 += 32) {
+        if (!warp_wait(&bars[B_PVDONE + ((it - 1) & 1)], ((it - 1) >> 1) & 1, gu)) { ok = false; break; }
+        tc_fence_after();
+        for (int c32 = 0; c32 < ocols; c32 += 32) {
           float t[32];
-          tmem_ld32(tmem_o + lane_addr + c32, t);
+          tmem_ld32(tmem_o + lane_addr + part * ocols + c32, t);
 #pragma unroll
           for (int i = 0; i < 32; ++i) t[i] *= alpha;
-          tmem_st32(tmem_o + lane_addr + c32, t);
+          tmem_st32(tmem_o + lane_addr + part * ocols + c32, t);
         }
         tmem_st_wait();
       }
       // P as bf16 into the swizzled K-major tile: row R, 16-byte chunk cc holds keys 8cc .. 8cc+7
       {
-        unsigned char* prow_ptr = Ps + R * 128;
+        unsigned char* prow_ptr = Ps + (it & 1) * (ROWS * 128) + R * 128;
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
+        for (int i = 0; i < 4; ++i) {
+          const int cc = part * 4 + i;
           uint4 v;
-          v.x = pack_bf16(s[8 * cc], s[8 * cc + 1]);
-          v.y = pack_bf16(s[8 * cc + 2], s[8 * cc + 3]);
-          v.z = pack_bf16(s[8 * cc + 4], s[8 * cc + 5]);
-          v.w = pack_bf16(s[8 * cc + 6], s[8 * cc + 7]);
+          v.x = pack_bf16(s[8 * i], s[8 * i + 1]);
+          v.y = pack_bf16(s[8 * i + 2], s[8 * i + 3]);
+          v.z = pack_bf16(s[8 * i + 4], s[8 * i + 5]);
+          v.w = pack_bf16(s[8 * i + 6], s[8 * i + 7]);
           *reinterpret_cast<uint4*>(prow_ptr + ((cc ^ (R & 7)) << 4)) = v;
         }
       }
@@ -417,7 +415,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       if (key0 < lo || key0 + KC > hi) {
         if (!warp_wait(&bars[B_VFULL + st], round & 1, gu)) { ok = false; break; }
         unsigned char* vt = Vs + st * tile_bytes;
-        for (int idx = tid; idx < KC * halves * 8; idx += 128) {
+        for (int idx = tid; idx < KC * halves * 8; idx += 2 * ROWS) {
           const int j = idx / (halves * 8), rest = idx - j * (halves * 8);
           if (key0 + j < lo || key0 + j >= hi)
             *reinterpret_cast<uint4*>(vt + (rest >> 3) * (KC * 128) + j * 128 + ((rest & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
@@ -426,17 +424,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[B_PFULL]);
+      if (lane == 0) mbar_arrive(&bars[B_PFULL + (it & 1)]);
     }
-    // the output: O / l
-    if (ok && n_chunks > 0 && warp_wait(&bars[B_PVDONE], (n_chunks - 1) & 1, gu)) {
+    // the output: O / l, each thread its half of the columns
+    xch_sum[part][R] = l_run;
+    mbar_arrive(pair_bar);
+    ok = ok && warp_wait(pair_bar, n_chunks & 1, gu);
+    const float l_all = l_run + xch_sum[part ^ 1][R];
+    if (ok && n_chunks > 0 && warp_wait(&bars[B_PVDONE + ((n_chunks - 1) & 1)], ((n_chunks - 1) >> 1) & 1, gu)) {
       tc_fence_after();
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      bf16* orow = out + (size_t)(qs + tok0 + tk) * out_stride + (size_t)(kvh * g + hb * gb + mem) * d;
-      for (int c32 = 0; c32 < d; c32 += 32) {
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      bf16* orow = out + (size_t)(qs + tok0 + tk) * out_stride + (size_t)(kvh * g + hb * gb + mem) * d + part * ocols;
+      for (int c32 = 0; c32 < ocols; c32 += 32) {
         float t[32];
-        tmem_ld32(tmem_o + lane_addr + c32, t);   // every thread of the warp takes part in the load
-        if (rvalid && l_run > 0.f) {
+        tmem_ld32(tmem_o + lane_addr + part * ocols + c32, t);   // every thread of the warp takes part in the load
+        if (rvalid && l_all > 0.f) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 v;
@@ -452,7 +454,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base_holder), "r"(256) : "memory");
   }
@@ -535,7 +537,7 @@ extern "C" int mi_attention_prefill_tc(const void* q, int q_stride, void* out, i
   if (!make_cache_map(&map_k, kcache, rows, d, page_size) || !make_cache_map(&map_v, vcache, rows, d, page_size))
     MI_REFUSE("attention_tc: the driver refused a tensor map");
   const int halves = d / 64;
-  const size_t smem = (size_t)ROWS * 128 * halves + ROWS * 128 + 2 * NSTAGE * (size_t)KC * 128 * halves + 1024;
+  const size_t smem = (size_t)ROWS * 128 * halves + 2 * ROWS * 128 + 2 * NSTAGE * (size_t)KC * 128 * halves + 1024;
   auto kern = attention_prefill_tc_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
