@@ -31,11 +31,12 @@ def pytest_collection_modifyitems(config, items):
 
 @pytest.fixture(scope="session")
 def model_dirs(tmp_path_factory):
-    """Model folders of the two tiny configurations, made once per session in a temporary place."""
+    """Model folders of the tiny configurations, made once per session in a temporary place."""
     from tiny_configs import make_model_dir
 
     root = str(tmp_path_factory.mktemp("models"))
     return {
         "A": make_model_dir("A", root),
         "B": make_model_dir("B", root),
+        "C": make_model_dir("C", root),
     }

@@ -19,6 +19,7 @@ TOL = {"float32": 1e-4, "bfloat16": 3e-2}
 LENGTHS = {
     "A": [17, 33, 64, 5, 70, 90],        # prompts 1/17/48 plus 16 decoded, and three more
     "B": [25, 31, 87, 154, 224, 3],      # prompts 1/7/63/130/200 plus 24 decoded, and one more
+    "C": [40, 130, 65, 7, 200, 96],      # ends inside a page, inside a 64-key chunk, on a chunk's edge
 }
 
 
@@ -29,7 +30,7 @@ def requests_for(which):
 @pytest.fixture(scope="module")
 def plain(model_dirs):
     out = {}
-    for which in ("A", "B"):
+    for which in ("A", "B", "C"):
         state = load_state(model_dirs[which])
         out[which] = T.plain_logits(state, TINY[which], requests_for(which))
     return out
@@ -56,7 +57,7 @@ CUTTINGS = {
 
 @pytest.mark.parametrize("cutting", list(CUTTINGS))
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("which", ["A", "B", "C"])
 def test_replay_matches_plain(which, dtype, cutting, model_dirs, plain):
     requests = requests_for(which)
     steps = CUTTINGS[cutting](requests)
@@ -71,6 +72,11 @@ def test_replay_matches_plain(which, dtype, cutting, model_dirs, plain):
     if dtype == "bfloat16":
         from mini_infer_b200.csrc import ops
         assert ops.attention_wait_status() == 0
+        if which == "C":     # the sizes of C are the ones the tcgen05 kernels take
+            cfg = TINY[which]
+            assert ops.prefill_tc_supported(cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                                            cfg["head_dim"], PAGE_SIZE[which])
+            assert ops.attention_tc_status() == 0 and ops.gemm_tma_status() == 0
     want = plain[which]
     scale = max(1.0, max(float(np.abs(want[r]).max()) for r in want))
     for rid in requests:
@@ -144,13 +150,14 @@ def test_out_of_pages_changes_nothing(model_dirs):
     runner.cache.check()
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_captured_decode_steps_match_plain(dtype, model_dirs, plain):
+@pytest.mark.parametrize("which,dtype", [("B", "float32"), ("B", "bfloat16"), ("C", "bfloat16")])
+def test_captured_decode_steps_match_plain(which, dtype, model_dirs, plain):
     """With cuda_graph on, single-token steps replay captured CUDA graphs (one per batch
-    size and block-table width); prompt portions and mixed steps still run kernel by kernel."""
+    size and block-table width); prompt portions and mixed steps still run kernel by kernel.
+    Inside a captured step the kernels overlap through programmatic dependent launch (with
+    configuration C: the tcgen05 product and decode attention that work ahead of their inputs)."""
     from mini_infer_b200.engine import ModelRunner
 
-    which = "B"
     requests = requests_for(which)
     steps = T.cut_mixed(requests, n_decode=40)
     ps = PAGE_SIZE[which]

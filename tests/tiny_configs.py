@@ -51,9 +51,29 @@ TINY_B = {
     "tie_word_embeddings": True,
 }
 
-TINY = {"A": TINY_A, "B": TINY_B}
-PAGE_SIZE = {"A": 16, "B": 8}
-SEED = {"A": 11, "B": 23}
+# A third one whose sizes put the Blackwell-specific kernels on the engine's path: head size
+# 64 with a group of 4 and pages of 16 (the tcgen05 prefill kernel), widths that are multiples
+# of 8 (the TMA / tcgen05 product for decode-sized inputs).
+TINY_C = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "vocab_size": 640,
+    "hidden_size": 256,
+    "intermediate_size": 384,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 8,
+    "num_key_value_heads": 2,
+    "head_dim": 64,
+    "rms_norm_eps": 1e-5,
+    "rope_theta": 100000.0,
+    "rope_scaling": None,
+    "max_position_embeddings": 2048,
+    "tie_word_embeddings": False,
+}
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 16}
+SEED = {"A": 11, "B": 23, "C": 37}
 
 # Attention that is almost uniform hides position and cache faults; q and k projections
 # drawn this wide make single keys stand out (the reference's own rope test widens them
@@ -65,7 +85,7 @@ def peaked(which: str) -> dict:
     return {"q_proj": s, "k_proj": s}
 
 
-PEAKED = {"A": peaked("A"), "B": peaked("B")}
+PEAKED = {w: peaked(w) for w in TINY}
 
 
 def make_model_dir(which: str, root: str | None = None, peaked: bool = True) -> str:
