@@ -400,6 +400,56 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
   }
 }
 
+// The same with gate and up interleaved: out[m, i] = silu(gu[m, 2 i]) * gu[m, 2 i + 1] (the
+// layout of a merged gate/up projection whose rows alternate, so that a matrix product's
+// epilogue finds both halves of a pair side by side).
+template <typename T, int VEC>
+__global__ void silu_mul_pairs_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
+  const int m = blockIdx.x;
+  const T* in = gu + (size_t)m * 2 * I;
+  T* o = out + (size_t)m * I;
+  const int i0 = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+  if (i0 >= I) return;
+  if (VEC == 4) {
+    Vec4<T> a, b, ov;
+    a.load(in + 2 * i0);
+    b.load(in + 2 * i0 + 4);
+    float af[4], bf[4], of[4];
+    a.get(af);
+    b.get(bf);
+    of[0] = (af[0] / (1.f + expf(-af[0]))) * af[1];
+    of[1] = (af[2] / (1.f + expf(-af[2]))) * af[3];
+    of[2] = (bf[0] / (1.f + expf(-bf[0]))) * bf[1];
+    of[3] = (bf[2] / (1.f + expf(-bf[2]))) * bf[3];
+    ov.set(of);
+    ov.store(o + i0);
+  } else {
+    const float gf = mi_to_float(in[2 * i0]), uf = mi_to_float(in[2 * i0 + 1]);
+    o[i0] = mi_from_float<T>((gf / (1.f + expf(-gf))) * uf);
+  }
+}
+
+extern "C" int mi_silu_mul_pairs(const void* gu, void* out, int M, int I, int dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (I <= 0) MI_REFUSE("silu_mul: bad width %d", I);
+  const size_t es = dtype == MI_DTYPE_F32 ? 4 : 2;
+  const bool vec = (I % 4 == 0) && mi_aligned(gu, 16) && mi_aligned(out, 16);
+  const int threads = 256;
+  if (dtype != MI_DTYPE_F32 && dtype != MI_DTYPE_BF16) MI_REFUSE("silu_mul: unknown dtype %d", dtype);
+  (void)es;
+  if (vec) {
+    dim3 grid(M, (I / 4 + threads - 1) / threads);
+    if (dtype == MI_DTYPE_F32) MI_LAUNCH((silu_mul_pairs_kernel<float, 4>), grid, threads, 0, stream, (const float*)gu, (float*)out, I);
+    else MI_LAUNCH((silu_mul_pairs_kernel<bf16, 4>), grid, threads, 0, stream, (const bf16*)gu, (bf16*)out, I);
+  } else {
+    dim3 grid(M, (I + threads - 1) / threads);
+    if (dtype == MI_DTYPE_F32) MI_LAUNCH((silu_mul_pairs_kernel<float, 1>), grid, threads, 0, stream, (const float*)gu, (float*)out, I);
+    else MI_LAUNCH((silu_mul_pairs_kernel<bf16, 1>), grid, threads, 0, stream, (const bf16*)gu, (bf16*)out, I);
+  }
+  MI_RETURN_LAUNCH_STATUS();
+}
+
 extern "C" int mi_silu_mul(const void* gu, void* out, int M, int I, int dtype, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (I <= 0) MI_REFUSE("silu_mul: bad width %d", I);

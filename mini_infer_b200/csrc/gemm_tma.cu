@@ -160,7 +160,7 @@ struct Segments {
 template <typename OutT>
 __global__ void __launch_bounds__(GT_THREADS, 1)
 gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                OutT* __restrict__ y, int ldy, int M, int N, int K, int n_tok, int stages, int kb, int chunked,
+                OutT* __restrict__ y, int ldy, int M, int N, int K, int n_tok, int stages, int kb, int chunked, int swiglu,
                 float* __restrict__ partials, int* __restrict__ counters) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // stage s: kb W boxes [128][64] bf16 (16 KB each), then kb x boxes [n_tok][64] bf16
@@ -320,7 +320,15 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         float v[16];
         tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
         if (whole) {
-          if (n < N) {
+          if (swiglu) {
+            // rows alternate gate, up: the even lane of a pair has the gate, its neighbour the up
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
+              if (!(row & 1) && n < N && c0 + j < M)
+                y[(size_t)(c0 + j) * ldy + (n >> 1)] = mi_from_float<OutT>((v[j] / (1.f + expf(-v[j]))) * other);
+            }
+          } else if (n < N) {
 #pragma unroll
             for (int j = 0; j < 16; ++j)
               if (c0 + j < M) y[(size_t)(c0 + j) * ldy + n] = mi_from_float<OutT>(v[j]);
@@ -347,7 +355,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           // Every block after the tile's first one begins inside the tile, so the tile is its
           // first segment (slot 0); the first block's is slot 0 only if it begins with the tile.
           const int first_slot = c_first * 2 + (first_unit(total, c_first, G) == t0 ? 0 : 1);
-          if (n < N) {
+          {
             // sixteen tokens and four blocks' partial tiles at a time: 64 independent loads are in
             // flight per thread; the additions still run in block order
             for (int j0 = 0; j0 < M; j0 += 16) {
@@ -363,16 +371,26 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                   const float* p = partials + ((size_t)s * n_tok + j0) * TILE_ROWS + row;
 #pragma unroll
                   for (int j = 0; j < 16; ++j)   // only rows below M were written
-                    v[cc][j] = (c <= c_last && j0 + j < M) ? __ldcg(p + (size_t)j * TILE_ROWS) : 0.f;
+                    v[cc][j] = (c <= c_last && j0 + j < M && n < N) ? __ldcg(p + (size_t)j * TILE_ROWS) : 0.f;
                 }
 #pragma unroll
                 for (int cc = 0; cc < 4; ++cc)
 #pragma unroll
                   for (int j = 0; j < 16; ++j) acc[j] += v[cc][j];
               }
+              if (swiglu) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (j0 + j < M) y[(size_t)(j0 + j) * ldy + n] = mi_from_float<OutT>(acc[j]);
+                for (int j = 0; j < 16; ++j) {
+                  const float other = __shfl_xor_sync(0xffffffffu, acc[j], 1);
+                  if (!(row & 1) && n < N && j0 + j < M)
+                    y[(size_t)(j0 + j) * ldy + (n >> 1)] =
+                        mi_from_float<OutT>((acc[j] / (1.f + expf(-acc[j]))) * other);
+                }
+              } else if (n < N) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  if (j0 + j < M) y[(size_t)(j0 + j) * ldy + n] = mi_from_float<OutT>(acc[j]);
+              }
             }
           }
           if (etid == 0) counters[tile] = 0;   // ready for the next call
@@ -455,11 +473,13 @@ extern "C" int mi_gemm_tma_workspace(int M, int N, int blocks, long long* partia
 }
 
 // x [M, K] bf16 (row stride ldx), w [N, K] bf16 contiguous, y [M, N] (row stride ldy) bf16 or
-// fp32.  `blocks` is the number of persistent blocks (the number of SMs); `partials` and
+// fp32.  With `swiglu` the rows of w alternate gate, up and y is [M, N / 2]:
+// y[m, i] = silu(x w[2i]) * (x w[2i+1]), computed on the fp32 accumulators.  `blocks` is the number of persistent blocks (the number of SMs); `partials` and
 // `counters` (zero before the first call; the kernel leaves them zero) as mi_gemm_tma_workspace
 // says.
 extern "C" int mi_gemm_tma(const void* x, long long ldx, const void* w, void* y, long long ldy, int M, int N, int K,
-                           int out_dtype, int blocks, float* partials, int* counters, cudaStream_t stream) {
+                           int out_dtype, int swiglu, int blocks, float* partials, int* counters, cudaStream_t stream) {
+  if (swiglu && (N % 2)) MI_REFUSE("gemm_tma: the gate/up epilogue needs an even number of rows of W, got %d", N);
   if (M <= 0 || N <= 0) return 0;
   if (M > MAX_TOKENS) MI_REFUSE("gemm_tma: %d rows of x; this kernel takes at most %d", M, MAX_TOKENS);
   if (K <= 0 || K % 8 != 0 || ldx % 8 != 0)
@@ -489,12 +509,12 @@ extern "C" int mi_gemm_tma(const void* x, long long ldx, const void* w, void* y,
     auto kern = gemm_tma_kernel<bf16>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    MI_LAUNCH((kern), grid, GT_THREADS, smem, stream, map_w, map_x, (bf16*)y, (int)ldy, M, N, K, n_tok, stages, kb, chunked, partials, counters);
+    MI_LAUNCH((kern), grid, GT_THREADS, smem, stream, map_w, map_x, (bf16*)y, (int)ldy, M, N, K, n_tok, stages, kb, chunked, swiglu ? 1 : 0, partials, counters);
   } else {
     auto kern = gemm_tma_kernel<float>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    MI_LAUNCH((kern), grid, GT_THREADS, smem, stream, map_w, map_x, (float*)y, (int)ldy, M, N, K, n_tok, stages, kb, chunked, partials, counters);
+    MI_LAUNCH((kern), grid, GT_THREADS, smem, stream, map_w, map_x, (float*)y, (int)ldy, M, N, K, n_tok, stages, kb, chunked, swiglu ? 1 : 0, partials, counters);
   }
   MI_RETURN_LAUNCH_STATUS();
 }

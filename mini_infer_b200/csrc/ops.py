@@ -74,6 +74,7 @@ def _sig_elementwise(lib: ctypes.CDLL) -> None:
     lib.mi_rope_write.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     lib.mi_silu_mul.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.mi_silu_mul_pairs.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
 
 
 def _sig_gemm_f32(lib: ctypes.CDLL) -> None:
@@ -117,7 +118,7 @@ def _sig_gemm_skinny(lib: ctypes.CDLL) -> None:
 
 def _sig_gemm_tma(lib: ctypes.CDLL) -> None:
     lib.mi_gemm_tma.argtypes = [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int,
-                                c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
+                                c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
     lib.mi_gemm_tma_workspace.argtypes = [c_int, c_int, c_int, ctypes.POINTER(ctypes.c_longlong),
                                           ctypes.POINTER(c_int)]
     lib.mi_gemm_tma_status.argtypes = [c_int]
@@ -254,8 +255,10 @@ def rope_write(
     _finish(lib, rc, "rope")
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``silu(gate_up[:, :I]) * gate_up[:, I:]`` with fp32 arithmetic."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, pairs: bool = False) -> torch.Tensor:
+    """``silu(gate) * up`` with fp32 arithmetic, for ``gate_up [M, 2 I]`` laid out as halves
+    (``gate = gate_up[:, :I]``, ``up = gate_up[:, I:]``) or, with ``pairs``, interleaved
+    (``gate = gate_up[:, 0::2]``, ``up = gate_up[:, 1::2]``)."""
     _cuda(gate_up, out)
     if gate_up.dim() != 2 or gate_up.shape[1] % 2 or not gate_up.is_contiguous():
         raise KernelError("silu_mul: input must be contiguous [M, 2 I]")
@@ -266,7 +269,8 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Te
     elif out.shape != (M, I) or out.dtype != gate_up.dtype or not out.is_contiguous():
         raise KernelError("silu_mul: bad output tensor")
     lib = _lib("elementwise")
-    rc = lib.mi_silu_mul(_ptr(gate_up), _ptr(out), M, I, _code(gate_up.dtype), _stream())
+    fn = lib.mi_silu_mul_pairs if pairs else lib.mi_silu_mul
+    rc = fn(_ptr(gate_up), _ptr(out), M, I, _code(gate_up.dtype), _stream())
     _finish(lib, rc, "silu_mul")
     return out
 
@@ -669,9 +673,12 @@ def gemm_tma_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_tma(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+def gemm_tma(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+             swiglu: bool = False) -> torch.Tensor:
     """``x [M <= 128, K] @ w [N, K]^T`` for bfloat16 operands on the tcgen05 tensor cores,
-    streaming ``w`` once through TMA (gemm_tma.cu); the result is bfloat16 or float32."""
+    streaming ``w`` once through TMA (gemm_tma.cu); the result is bfloat16 or float32.  With
+    ``swiglu`` the rows of ``w`` alternate gate, up and the result is ``[M, N / 2]``:
+    ``silu(gate) * up`` computed on the fp32 accumulators in the product's epilogue."""
     global launch_count
     _cuda(x, w)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -685,10 +692,13 @@ def gemm_tma(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bf
     floats, counters = ctypes.c_longlong(0), c_int(0)
     lib.mi_gemm_tma_workspace(M, N, blocks, ctypes.byref(floats), ctypes.byref(counters))
     partial, count = _tma_workspace(x.device, int(floats.value), int(counters.value))
-    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if swiglu and N % 2:
+        raise KernelError("gemm_tma: the gate/up epilogue needs an even number of rows")
+    n_out = N // 2 if swiglu else N
+    out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     launch_count += 1
-    rc = lib.mi_gemm_tma(_ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), N, M, N, K, _code(out_dtype),
-                         blocks, _ptr(partial), _ptr(count), _stream())
+    rc = lib.mi_gemm_tma(_ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), n_out, M, N, K,
+                         _code(out_dtype), 1 if swiglu else 0, blocks, _ptr(partial), _ptr(count), _stream())
     _finish(lib, rc, "gemm_tma")
     return out
 
@@ -704,6 +714,17 @@ def _skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (M <= SKINNY_MAX_ROWS and K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1
             and (M == 1 or x.stride(0) % 8 == 0) and (w.shape[0] == 1 or w.stride(0) % 8 == 0)
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor) -> torch.Tensor:
+    """``silu(x Wg^T) * (x Wu^T)`` for a merged projection whose rows alternate gate, up
+    (``w_pairs [2 I, K]``).  Decode-sized bfloat16 inputs run the product and the activation
+    as one kernel (gemm_tma with its gate/up epilogue); everything else runs ``linear`` and
+    the SiLU-multiply kernel on the interleaved result."""
+    if (x.dtype == torch.bfloat16 and USE_TMA_GEMM and x.shape[0] <= TMA_GEMM_DISPATCH_ROWS
+            and w_pairs.dtype == torch.bfloat16 and gemm_tma_ok(x, w_pairs)):
+        return gemm_tma(x, w_pairs, torch.bfloat16, swiglu=True)
+    return silu_mul(linear(x, w_pairs), pairs=True)
 
 
 _MM_OUT_DTYPE: bool | None = None

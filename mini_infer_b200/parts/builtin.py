@@ -210,8 +210,10 @@ class GroupedQueryAttention(Mixer):
 
 class SwiGLU(FeedForward):
     """``down(silu(gate(x)) * up(x))``, no biases (reference ``models/blocks/swiglu.py:35-46``,
-    ``models/blocks/activations.py:36-45``).  gate and up are one merged product; SiLU and
-    the product are fp32 per element.
+    ``models/blocks/activations.py:36-45``).  gate and up are one merged product whose rows
+    alternate (gate 0, up 0, gate 1, up 1, ...), so that the activation can run in the
+    product's epilogue, where both halves of a pair sit side by side; SiLU and the product
+    are fp32 per element.
 
     params: ``hidden_size``, ``intermediate_size``.
     tensors: ``gate_proj.weight``, ``up_proj.weight``, ``down_proj.weight``.
@@ -226,15 +228,13 @@ class SwiGLU(FeedForward):
         }
 
     def bind(self, tensors, dtype, device):
-        gate_up = torch.cat(
-            [_as_compute(tensors["gate_proj.weight"], dtype), _as_compute(tensors["up_proj.weight"], dtype)],
-            dim=0,
-        ).contiguous()
+        gate, up = _as_compute(tensors["gate_proj.weight"], dtype), _as_compute(tensors["up_proj.weight"], dtype)
+        gate_up = torch.stack([gate, up], dim=1).reshape(2 * gate.shape[0], gate.shape[1]).contiguous()
         self.gate_up_proj = Linear(gate_up)
         self.down_proj = Linear(_as_compute(tensors["down_proj.weight"], dtype).contiguous())
 
     def forward(self, x, ctx):
-        return self.down_proj(ops.silu_mul(self.gate_up_proj(x)))
+        return self.down_proj(ops.linear_swiglu(x, self.gate_up_proj.weight))
 
 
 # ----------------------------------------------------------------------------- embedding / head

