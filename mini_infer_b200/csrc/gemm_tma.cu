@@ -36,6 +36,7 @@ MI_DEFINE_ERROR_API()
 #define GT_THREADS 192
 #define MAX_TOKENS 128
 #define SMEM_BUDGET (200 * 1024)   // ring of stages; about 100 KB per SM must be in flight to keep memory busy
+#define ALIGNED_GRID_MIN_PCT 85     // use a block count that divides into the tiles if it keeps this share of the SMs
 #define BOXES_PER_STAGE 2          // k boxes per stage: one box per stage leaves the issuing threads behind
 #define MAX_STAGES 12
 #define SPIN_LIMIT (1 << 22)
@@ -491,7 +492,17 @@ extern "C" int mi_gemm_tma(const void* x, long long ldx, const void* w, void* y,
   const int kb = BOXES_PER_STAGE;
   const int budget = SMEM_BUDGET;
   const long long total = (long long)((N + TILE_ROWS - 1) / TILE_ROWS) * ((K + TILE_K * kb - 1) / (TILE_K * kb));
-  const int grid = (int)(total < blocks ? total : blocks);
+  int grid = (int)(total < blocks ? total : blocks);
+  {
+    // With fewer tiles than blocks, a block count that is a multiple of the tile count gives every
+    // block one stretch of one tile (one partial tile to exchange instead of two for the blocks
+    // that would straddle a tile boundary), at the price of leaving a few SMs idle.
+    const int n_tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
+    if (n_tiles < blocks && total >= blocks) {
+      const int aligned = n_tiles * (blocks / n_tiles);
+      if (aligned * 100 >= blocks * ALIGNED_GRID_MIN_PCT) grid = aligned;
+    }
+  }
   const int stage_bytes = (TILE_ROWS * TILE_K * 2 + n_tok * TILE_K * 2) * kb;
   int stages = budget / stage_bytes;
   if (stages < 2) stages = 2;
