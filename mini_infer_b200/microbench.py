@@ -8,10 +8,12 @@
     python -m mini_infer_b200.microbench silu_mul --rows 2048 --width 14336
     python -m mini_infer_b200.microbench sample --rows 8 --vocab 128256
 
-Each iteration is timed with CUDA events on the launching stream after a buffer larger than
-the L2 cache has been overwritten, so every run starts cold; the line printed gives the
-median time and the bytes (or flops) the kernel has to move divided by it.  The same command
-under ``ncu -k regex:<kernel>`` profiles exactly these launches.
+Before each iteration a buffer larger than the L2 cache is overwritten, so every run starts
+cold.  The time is the device-side duration of the kernels the call launches (``--timer
+events`` takes CUDA events around the call instead, which adds the host's launch work); the
+line printed gives the median and the bytes (or flops) the kernel has to move divided by
+it.  The same command with ``--timer events`` under ``ncu -k regex:<kernel>`` profiles
+exactly these launches.
 """
 
 from __future__ import annotations
@@ -28,18 +30,42 @@ def _flush_buffer(device) -> torch.Tensor:
     return torch.empty(256 << 20, dtype=torch.uint8, device=device)
 
 
+TIMER = "device"
+
+
 def _time(fn, iters: int, warmup: int, flush: torch.Tensor) -> float:
-    """Median microseconds of ``fn()``, L2 flushed before each call."""
-    times = []
-    for i in range(warmup + iters):
+    """Median microseconds of ``fn()``, L2 flushed before each call.
+
+    ``TIMER == "device"``: the sum of the device-side durations of the kernels ``fn`` launches
+    (from the profiler's activity records), which leaves out the host's launch work; that
+    matters for kernels of a few microseconds.  ``"events"``: CUDA events around the call."""
+    if TIMER == "events":
+        times = []
+        for i in range(warmup + iters):
+            flush.zero_()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            if i >= warmup:
+                times.append(start.elapsed_time(end) * 1e3)
+        return statistics.median(times)
+    from torch.profiler import ProfilerActivity, profile
+
+    for _ in range(warmup):
         flush.zero_()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
         fn()
-        end.record()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush.zero_()
         torch.cuda.synchronize()
-        if i >= warmup:
-            times.append(start.elapsed_time(end) * 1e3)
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            fn()
+            torch.cuda.synchronize()
+        times.append(sum(ev.device_time for ev in prof.events()
+                         if ev.device_type == torch.autograd.DeviceType.CUDA))
     return statistics.median(times)
 
 
@@ -193,6 +219,8 @@ def main(argv=None) -> int:
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--impl", choices=["tc", "mma"], default="tc",
                     help="attention_prefill: the tcgen05 kernel or the mma.sync kernel")
+    ap.add_argument("--timer", choices=["device", "events"], default="device",
+                    help="device: kernel durations from the profiler's records; events: CUDA events around the call")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)
@@ -201,11 +229,13 @@ def main(argv=None) -> int:
         return 2
     from .csrc import ops
 
+    global TIMER
+    TIMER = args.timer
     device = torch.device("cuda:0")
     torch.manual_seed(0)
     flush = _flush_buffer(device)
     us, note = KERNELS[args.kernel](args, ops, device, flush)
-    print(f"{args.kernel}: {us:.1f} us median of {args.iters} cold runs; {note}")
+    print(f"{args.kernel}: {us:.1f} us median of {args.iters} cold runs ({args.timer} timer); {note}")
     return 0
 
 

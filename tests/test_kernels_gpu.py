@@ -457,6 +457,20 @@ def test_attention_prefill_tcgen05_far_key_and_big_scores():
     assert not ops().prefill_tc_supported(3, 1, 128, 16)
 
 
+def test_attention_long_contexts():
+    """Tens of thousands of keys: decode over 20,000 cached tokens with few and many key
+    slices, and a 4,100-token portion through both prefill kernels (65 chunks per tile, many
+    rounds of every ring of stages and of every barrier phase)."""
+    got, want = run_attention([1, 1], [20000, 8191], 4, 2, 64, 16, torch.bfloat16, seed=21, kernel="decode", n_splits=3)
+    assert (got - want).abs().max().item() <= BF16_BOUND
+    got, want = run_attention([1, 1], [20000, 8191], 4, 2, 64, 16, torch.bfloat16, seed=21, kernel="decode", n_splits=64)
+    assert (got - want).abs().max().item() <= BF16_BOUND
+    for kernel in ("prefill", "prefill_tc"):
+        got, want = run_attention([4100], [4100], 2, 1, 64, 16, torch.bfloat16, seed=22, kernel=kernel)
+        assert torch.isfinite(got).all()
+        assert (got - want).abs().max().item() <= BF16_BOUND
+
+
 @pytest.mark.parametrize("n_splits", [1, 2, 5, 64])
 @pytest.mark.parametrize("nq,nkv,d,page", [(32, 8, 128, 16), (6, 2, 48, 8), (3, 3, 16, 4), (40, 2, 64, 16), (5, 1, 256, 16)])
 def test_attention_decode_split_keys(nq, nkv, d, page, n_splits):
