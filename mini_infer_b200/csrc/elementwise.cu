@@ -245,7 +245,7 @@ __global__ void rope_write_kernel(T* __restrict__ qkv, const int* __restrict__ p
   }
 }
 
-// The same work in 16-byte chunks: a block takes one token and ROPE_HEADS consecutive heads;
+// The same work in 16-byte chunks: a block takes one token and some consecutive heads;
 // sine and cosine of the token's angles are computed once per block into shared memory, then
 // every thread rotates one pair of chunks (elements [j, j + E) of both halves) or copies one
 // chunk of an un-rotated tail or of v.  Needs rot / 2 to be a multiple of the chunk's E
@@ -273,11 +273,11 @@ template <typename T>
 __global__ void rope_write_chunks_kernel(T* __restrict__ qkv, const int* __restrict__ pos,
                                          const float* __restrict__ inv_freq, const int* __restrict__ slot,
                                          T* __restrict__ kcache, T* __restrict__ vcache, int nq, int nkv,
-                                         int d, int rot, int page_size, int heads) {
+                                         int d, int rot, int page_size, int heads, int heads_per_block) {
   mi_pdl_enter();   // inputs come from the kernels before this one
   extern __shared__ float rope_sc[];   // [half] sines, [half] cosines
   constexpr int E = Chunk16<T>::E;
-  const int t = blockIdx.x, h0 = blockIdx.y * ROPE_HEADS;
+  const int t = blockIdx.x, h0 = blockIdx.y * heads_per_block;
   const int half = rot >> 1;
   if (half > 0 && h0 < nq + nkv) {
     const float p = (float)pos[t];
@@ -290,7 +290,7 @@ __global__ void rope_write_chunks_kernel(T* __restrict__ qkv, const int* __restr
   const int swz = off & mi_swizzle_mask(d, (int)sizeof(T));
   const int cpr = d / E;                     // chunks per head row; also the items per head
   const int n_rot = half / E, n_tail = (d - rot) / E;
-  const int n_heads = min(ROPE_HEADS, heads - h0);
+  const int n_heads = min(heads_per_block, heads - h0);
   for (int item = threadIdx.x; item < n_heads * cpr; item += blockDim.x) {
     const int h = h0 + item / cpr, j = item % cpr;
     T* head = qkv + (size_t)t * width + (size_t)h * d;
@@ -347,14 +347,19 @@ extern "C" int mi_rope_write(void* qkv, const int* pos, const float* inv_freq, c
   const int es = dtype == MI_DTYPE_F32 ? 4 : 2, epc = 16 / es;
   if ((dtype == MI_DTYPE_F32 || dtype == MI_DTYPE_BF16) && (rot / 2) % epc == 0 && d % epc == 0 &&
       mi_aligned(qkv, 16) && (!kcache || (mi_aligned(kcache, 16) && mi_aligned(vcache, 16)))) {
-    dim3 cgrid(M, (heads + ROPE_HEADS - 1) / ROPE_HEADS);
+    // Few tokens (decode): many small blocks, the kernel is bound by latency.  Many tokens
+    // (prefill): one block per token, so the angles are computed once and every thread has
+    // several independent chunks in flight.
+    const int hpb = M < 256 ? ROPE_HEADS : heads;
+    const int threads = M < 256 ? 128 : 256;
+    dim3 cgrid(M, (heads + hpb - 1) / hpb);
     const size_t smem = (size_t)rot * sizeof(float);
     if (dtype == MI_DTYPE_F32)
-      MI_LAUNCH((rope_write_chunks_kernel<float>), cgrid, 128, smem, stream, (float*)qkv, pos, inv_freq, slot,
-                (float*)kcache, (float*)vcache, nq, nkv, d, rot, page_size, heads);
+      MI_LAUNCH((rope_write_chunks_kernel<float>), cgrid, threads, smem, stream, (float*)qkv, pos, inv_freq, slot,
+                (float*)kcache, (float*)vcache, nq, nkv, d, rot, page_size, heads, hpb);
     else
-      MI_LAUNCH((rope_write_chunks_kernel<bf16>), cgrid, 128, smem, stream, (bf16*)qkv, pos, inv_freq, slot,
-                (bf16*)kcache, (bf16*)vcache, nq, nkv, d, rot, page_size, heads);
+      MI_LAUNCH((rope_write_chunks_kernel<bf16>), cgrid, threads, smem, stream, (bf16*)qkv, pos, inv_freq, slot,
+                (bf16*)kcache, (bf16*)vcache, nq, nkv, d, rot, page_size, heads, hpb);
     MI_RETURN_LAUNCH_STATUS();
   }
   int threads = 32;
@@ -430,6 +435,27 @@ __global__ void silu_mul_pairs_kernel(const T* __restrict__ gu, T* __restrict__ 
   }
 }
 
+// bfloat16, eight outputs per thread: two 16-byte loads, one 16-byte store
+__global__ void silu_mul_pairs8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I) {
+  mi_pdl_enter();   // inputs come from the kernels before this one
+  const int m = blockIdx.x;
+  const int i0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i0 >= I) return;
+  const uint4* in = reinterpret_cast<const uint4*>(gu + (size_t)m * 2 * I + 2 * i0);
+  const uint4 a = in[0], b = in[1];
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};   // each word: (gate, up) of one output
+  uint32_t r[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[2 * j]));
+    const float2 p1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[2 * j + 1]));
+    const __nv_bfloat162 o = __floats2bfloat162_rn((p0.x / (1.f + expf(-p0.x))) * p0.y,
+                                                   (p1.x / (1.f + expf(-p1.x))) * p1.y);
+    r[j] = *reinterpret_cast<const uint32_t*>(&o);
+  }
+  *reinterpret_cast<uint4*>(out + (size_t)m * I + i0) = make_uint4(r[0], r[1], r[2], r[3]);
+}
+
 extern "C" int mi_silu_mul_pairs(const void* gu, void* out, int M, int I, int dtype, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (I <= 0) MI_REFUSE("silu_mul: bad width %d", I);
@@ -438,6 +464,11 @@ extern "C" int mi_silu_mul_pairs(const void* gu, void* out, int M, int I, int dt
   const int threads = 256;
   if (dtype != MI_DTYPE_F32 && dtype != MI_DTYPE_BF16) MI_REFUSE("silu_mul: unknown dtype %d", dtype);
   (void)es;
+  if (vec && dtype == MI_DTYPE_BF16 && I % 8 == 0) {
+    dim3 grid(M, (I / 8 + threads - 1) / threads);
+    MI_LAUNCH((silu_mul_pairs8_kernel), grid, threads, 0, stream, (const bf16*)gu, (bf16*)out, I);
+    MI_RETURN_LAUNCH_STATUS();
+  }
   if (vec) {
     dim3 grid(M, (I / 4 + threads - 1) / threads);
     if (dtype == MI_DTYPE_F32) MI_LAUNCH((silu_mul_pairs_kernel<float, 4>), grid, threads, 0, stream, (const float*)gu, (float*)out, I);
