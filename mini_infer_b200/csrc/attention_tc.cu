@@ -1,7 +1,7 @@
 // Prefill attention over the paged cache on the fifth-generation tensor cores.
 //
-// One block takes a tile of 128 rows (tokens x the query heads that share one key/value head)
-// and walks the request's keys in chunks of 64:
+// One block takes two tiles of 128 rows (tokens x the query heads that share one key/value
+// head) and walks the request's keys in chunks of 64, each chunk loaded once for both tiles:
 //
 //   warps 8, 10  issue TMA copies of key and value pages into a two-stage ring.  The
 //            cache stores every row with its 16-byte chunks permuted by the key's in-page
@@ -11,7 +11,7 @@
 //   warps 9, 11  one thread each issues tcgen05.mma: S = Q K^T (128 x 64, fp32 in tensor memory, two
 //            buffers so that the next chunk's scores are computed while this one's softmax
 //            runs) and O += P V (128 x d, fp32 in tensor memory).
-//   warps 0-7  softmax, two threads per row (32 of a chunk's 64 keys each): read S from tensor memory, mask what
+//   warps 0-7  softmax, four warps per tile, one row per thread: read the row of S from tensor memory, mask what
 //            the row must not see, keep the running maximum and sum in registers (fp32, log2
 //            domain), rescale O in tensor memory when the maximum moved, write P (bf16) into
 //            shared memory as the K-major A operand of the second product.
@@ -163,10 +163,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // barriers of the block, in one array
-#define NSTAGE 4   // chunks of keys and values in flight: a chunk's copies start three chunks ahead
+#define NSTAGE 3   // chunks of keys and values in flight
+#define NTILE 2    // query tiles of 128 rows per block
 enum {
-  B_KFULL = 0, B_VFULL = NSTAGE, B_KEMPTY = 2 * NSTAGE, B_VEMPTY = 3 * NSTAGE, B_SFULL = 4 * NSTAGE,
-  B_SEMPTY = 4 * NSTAGE + 2, B_PFULL = 4 * NSTAGE + 4, B_PVDONE = 4 * NSTAGE + 6, B_PAIR = 4 * NSTAGE + 8,
+  B_KFULL = 0, B_VFULL = NSTAGE, B_KEMPTY = 2 * NSTAGE, B_VEMPTY = 3 * NSTAGE,
+  B_SFULL = 4 * NSTAGE,               // [tile][2 buffers]
+  B_SEMPTY = 4 * NSTAGE + 4,          // [tile][2 buffers], the four softmax warps of the tile arrive
+  B_PFULL = 4 * NSTAGE + 8,           // [tile], the four softmax warps arrive
+  B_PVDONE = 4 * NSTAGE + 10,         // [tile]
   B_COUNT = 4 * NSTAGE + 12
 };
 
@@ -183,14 +187,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int halves = d >> 6;                       // 64-element (128-byte) column blocks of a row
   const uint32_t tile_bytes = KC * 128 * halves;   // one K or V chunk: [half][64 keys][128 B]
-  unsigned char* Qs = smem;                        // [half][128 rows][128 B]
-  unsigned char* Ps = Qs + ROWS * 128 * halves;    // [2][128 rows][128 B]
-  unsigned char* Ks = Ps + 2 * ROWS * 128;         // [NSTAGE][tile]
+  const uint32_t q_bytes = ROWS * 128 * halves;    // one query tile: [half][128 rows][128 B]
+  unsigned char* Qs = smem;                        // [NTILE][q tile]
+  unsigned char* Ps = Qs + NTILE * q_bytes;        // [NTILE][128 rows][128 B]
+  unsigned char* Ks = Ps + NTILE * ROWS * 128;     // [NSTAGE][tile]
   unsigned char* Vs = Ks + NSTAGE * tile_bytes;    // [NSTAGE][tile]
   __shared__ __align__(8) uint64_t bars[B_COUNT];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int give_up;
-  __shared__ float xch_max[2][2][ROWS], xch_sum[2][ROWS];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = nq / nkv;
@@ -201,7 +205,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int ql = q_len[b], kl = kv_len[b], qs = q_start[b];
   const int ntok = min(tt, ql - tok0);
   const int p_first = kl - ql + tok0;
-  const int hi = p_first + ntok;                   // one past the last key any row of the tile sees
+  const int hi = p_first + ntok;                   // one past the last key any row of the block sees
   const int lo = window > 0 ? max(0, p_first - window + 1) : 0;
   const int heads_here = min(gb, g - hb * gb);
   const int c0 = lo / KC, c1 = (hi + KC - 1) / KC;
@@ -210,29 +214,30 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   if (tid == 0) {
     for (int i = 0; i < B_COUNT; ++i)   // the softmax warps arrive one thread each
-      mbar_init(&bars[i], i >= B_PAIR ? 64 : ((i >= B_SEMPTY && i < B_PVDONE) ? 8 : 1));
+      mbar_init(&bars[i], (i >= B_SEMPTY && i < B_PVDONE) ? 4 : 1);
     give_up = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_holder)),
-                 "r"(256)
+                 "r"(512)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
-  // the query tile, row R = (token tok0 + R / gb, head kvh * g + hb * gb + R % gb), into the
-  // swizzled K-major layout; rows that do not exist are zero
+  // the query tiles, row R of the block = (token tok0 + R / gb, head kvh * g + hb * gb + R % gb),
+  // rows 0..127 in tile 0 and 128..255 in tile 1, into the swizzled K-major layout; rows that
+  // do not exist are zero
   {
     const int units = d >> 3;   // 16-byte chunks per row
-    for (int idx = tid; idx < ROWS * units; idx += TC_THREADS) {
+    for (int idx = tid; idx < NTILE * ROWS * units; idx += TC_THREADS) {
       const int R = idx / units, u = idx - R * units;
       const int tk = R / gb, mem = R - tk * gb;
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (tk < ntok && mem < heads_here)
         v = *reinterpret_cast<const uint4*>(q + (size_t)(qs + tok0 + tk) * q_stride +
                                             (size_t)(kvh * g + hb * gb + mem) * d + u * 8);
-      const int half = u >> 3, c = u & 7;
-      *reinterpret_cast<uint4*>(Qs + half * (ROWS * 128) + R * 128 + ((c ^ (R & 7)) << 4)) = v;
+      const int t = R / ROWS, r = R - t * ROWS, half = u >> 3, c = u & 7;
+      *reinterpret_cast<uint4*>(Qs + t * q_bytes + half * (ROWS * 128) + r * 128 + ((c ^ (r & 7)) << 4)) = v;
     }
     fence_async_smem();
   }
@@ -240,7 +245,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_holder;
-  const uint32_t tmem_s0 = tmem, tmem_o = tmem + 128;   // S buffers at columns 0 and 64, O at 128
+  // tensor memory: S of tile t, buffer sb at columns (2 t + sb) * 64; O of tile t at 256 + 128 t
 
   if (warp == 8 || warp == 10) {
     // The copy warps, one for keys and one for values: lane p owns page p of the chunk (its id
@@ -278,86 +283,104 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       page = next_page;
     }
   } else if (warp == 9) {
-    // The first product's issuer: S[it & 1] = Q K^T, one chunk ahead of the softmax.  Operand
-    // descriptors are built once; a stage, a half or a k step only adds to the address field.
+    // The first product's issuer: S[t][it & 1] = Q_t K^T for both tiles, ahead of the softmax.
+    // Operand descriptors are built once; a tile, a stage, a half or a k step only adds to the
+    // address field.
     if (lane == 0) {
       const uint32_t idesc_qk = idesc_bf16(ROWS, KC, 0);
       const uint64_t q_desc = desc_sw128(smem_u32(Qs), 0), k_desc = desc_sw128(smem_u32(Ks), 0);
-      for (int it = 0; it < n_chunks; ++it) {
+      bool ok = true;
+      for (int it = 0; it < n_chunks && ok; ++it) {
         const int st = it % NSTAGE, round = it / NSTAGE, sb = it & 1, sround = it >> 1;
-        if (sround > 0 && !mbar_wait(&bars[B_SEMPTY + sb], (sround - 1) & 1, gu)) break;
         if (!mbar_wait(&bars[B_KFULL + st], round & 1, gu)) break;
-        tc_fence_after();
         const uint64_t kd = k_desc + ((st * tile_bytes) >> 4);
-        for (int h = 0; h < halves; ++h)
+        for (int t = 0; t < NTILE; ++t) {
+          if (sround > 0 && !mbar_wait(&bars[B_SEMPTY + 2 * t + sb], (sround - 1) & 1, gu)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t qd = q_desc + ((t * q_bytes) >> 4);
+          for (int h = 0; h < halves; ++h)
 #pragma unroll
-          for (int k = 0; k < 4; ++k)   // 16 of the 64 dims of a half per MMA: 32 bytes along the row
-            umma(tmem_s0 + sb * KC, q_desc + ((h * (ROWS * 128) + k * 32) >> 4), kd + ((h * (KC * 128) + k * 32) >> 4),
-                 idesc_qk, (h | k) ? 1u : 0u);
-        umma_commit(&bars[B_KEMPTY + st]);
-        umma_commit(&bars[B_SFULL + sb]);
+            for (int k = 0; k < 4; ++k)   // 16 of the 64 dims of a half per MMA: 32 bytes along the row
+              umma(tmem + (2 * t + sb) * KC, qd + ((h * (ROWS * 128) + k * 32) >> 4),
+                   kd + ((h * (KC * 128) + k * 32) >> 4), idesc_qk, (h | k) ? 1u : 0u);
+          umma_commit(&bars[B_SFULL + 2 * t + sb]);
+        }
+        if (ok) umma_commit(&bars[B_KEMPTY + st]);
       }
     }
   } else if (warp == 11) {
-    // The second product's issuer: O += P V as soon as a chunk's probabilities are published.
+    // The second product's issuer: O_t += P_t V as soon as a tile's probabilities are published.
     if (lane == 0) {
       const uint32_t idesc_pv = idesc_bf16(ROWS, d, 1);
       const uint64_t p_desc = desc_sw128(smem_u32(Ps), 0), v_desc = desc_sw128(smem_u32(Vs), KC * 128);
-      for (int it = 0; it < n_chunks; ++it) {
+      bool ok = true;
+      for (int it = 0; it < n_chunks && ok; ++it) {
         const int st = it % NSTAGE, round = it / NSTAGE;
         if (!mbar_wait(&bars[B_VFULL + st], round & 1, gu)) break;
-        if (!mbar_wait(&bars[B_PFULL + (it & 1)], (it >> 1) & 1, gu)) break;
-        tc_fence_after();
-        const uint64_t pd = p_desc + (((it & 1) * (ROWS * 128)) >> 4), vd = v_desc + ((st * tile_bytes) >> 4);
+        const uint64_t vd = v_desc + ((st * tile_bytes) >> 4);
+        for (int t = 0; t < NTILE; ++t) {
+          if (!mbar_wait(&bars[B_PFULL + t], it & 1, gu)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t pd = p_desc + ((t * (ROWS * 128)) >> 4);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)   // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
-          umma(tmem_o, pd + ((k * 32) >> 4), vd + ((k * 2048) >> 4), idesc_pv, (it > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&bars[B_VEMPTY + st]);
-        umma_commit(&bars[B_PVDONE + (it & 1)]);
+          for (int k = 0; k < 4; ++k)   // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
+            umma(tmem + 256 + t * 128, pd + ((k * 32) >> 4), vd + ((k * 2048) >> 4), idesc_pv, (it > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&bars[B_PVDONE + t]);
+        }
+        if (ok) umma_commit(&bars[B_VEMPTY + st]);
       }
     }
   } else {
-    // softmax: two threads per row (TMEM lane), each with half of a chunk's 64 keys.  Warps w
-    // and w + 4 share TMEM lanes 32 (w & 3) .. + 31; they exchange their halves' maxima (and at
-    // the end their sums) through shared memory and meet at a named barrier of their own.
-    const int R = tid & (ROWS - 1), part = tid >> 7;
-    uint64_t* pair_bar = &bars[B_PAIR + (warp & 3)];   // the two warps' meeting point (64 arrivals a phase)
+    // softmax: warps 0-3 own tile 0, warps 4-7 tile 1; one thread per row (TMEM lane).  The two
+    // groups run out of step with each other, so one computes exponentials while the other
+    // waits for its scores or publishes its probabilities.
+    const int t = warp >> 2, r = tid & (ROWS - 1), R = t * ROWS + r;
     const int tk = R / gb, mem = R - tk * gb;
     const bool rvalid = tk < ntok && mem < heads_here;
     const int prow = p_first + tk;
     const int lorow = window > 0 ? max(0, prow - window + 1) : 0;
+    // the tile's own range of tokens: chunks past its last row's position are skipped wholesale
+    const int t_first = p_first + (t * ROWS) / gb, t_last = min(hi - 1, p_first + (t * ROWS + ROWS - 1) / gb);
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tmem_o = tmem + 256 + t * 128;
+    unsigned char* Pt = Ps + t * (ROWS * 128);
     const float sc = scale * LOG2E;
-    const int ocols = d >> 1;   // output columns of this thread
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int it = 0; it < n_chunks; ++it) {
       const int c = c0 + it, sb = it & 1, sround = it >> 1, st = it % NSTAGE, round = it / NSTAGE;
-      const int key0 = c * KC, kbase = key0 + part * 32;
-      if (!warp_wait(&bars[B_SFULL + sb], sround & 1, gu)) { ok = false; break; }
+      const int key0 = c * KC;
+      if (!warp_wait(&bars[B_SFULL + 2 * t + sb], sround & 1, gu)) { ok = false; break; }
       tc_fence_after();
-      float s[32];
-      tmem_ld32(tmem_s0 + lane_addr + sb * KC + part * 32, s);
+      float s[64];
+      {
+        uint32_t ra[32], rb[32];
+        tmem_ld32_issue(tmem + lane_addr + (2 * t + sb) * KC, ra);
+        tmem_ld32_issue(tmem + lane_addr + (2 * t + sb) * KC + 32, rb);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          s[i] = __uint_as_float(ra[i]);
+          s[32 + i] = __uint_as_float(rb[i]);
+        }
+      }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[B_SEMPTY + sb]);   // the scores are in registers
-      const bool interior = key0 + KC - 1 <= p_first && key0 >= (window > 0 ? max(0, hi - window) : 0) && key0 >= lo;
+      if (lane == 0) mbar_arrive(&bars[B_SEMPTY + 2 * t + sb]);   // the scores are in registers
+      const bool interior = key0 + KC - 1 <= t_first && key0 >= (window > 0 ? max(0, t_last - window + 1) : 0) && key0 >= lo;
       if (!interior || !rvalid) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (!(rvalid && kbase + j <= prow && kbase + j >= lorow)) s[j] = -INFINITY;
+        for (int j = 0; j < 64; ++j)
+          if (!(rvalid && key0 + j <= prow && key0 + j >= lorow)) s[j] = -INFINITY;
       }
-      float mx4[4];
+      float mx8[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        mx4[i] = fmaxf(fmaxf(fmaxf(s[8 * i], s[8 * i + 1]), fmaxf(s[8 * i + 2], s[8 * i + 3])),
+      for (int i = 0; i < 8; ++i) {
+        mx8[i] = fmaxf(fmaxf(fmaxf(s[8 * i], s[8 * i + 1]), fmaxf(s[8 * i + 2], s[8 * i + 3])),
                        fmaxf(fmaxf(s[8 * i + 4], s[8 * i + 5]), fmaxf(s[8 * i + 6], s[8 * i + 7])));
       }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;   // sc > 0
-      xch_max[it & 1][part][R] = mx;
-      mbar_arrive(pair_bar);
-      if (!warp_wait(pair_bar, it & 1, gu)) { ok = false; break; }
-      mx = fmaxf(mx, xch_max[it & 1][part ^ 1][R]);
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * sc;   // sc > 0
       // The exponents are taken relative to m_run, which follows the true running maximum
       // lazily: it moves (and O and l are rescaled) only when some row of the warp found a
       // score more than 2^RESCALE_LOG2 above it.  Probabilities may then exceed 1 by that
@@ -370,52 +393,50 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         alpha = fast_exp2(m_run - m_new);
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < 64; ++j) {
           s[j] = fast_exp2(fmaf(s[j], sc, -m_new));
           sum4[j & 3] += s[j];
         }
         sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) s[j] = 0.f;
+        for (int j = 0; j < 64; ++j) s[j] = 0.f;
       }
       m_run = m_new;
       l_run = l_run * alpha + sum;
-      // P has two buffers: this one is free once the second product of two chunks ago is done.
-      // O may be touched only after the previous chunk's second product (rare: see above).
-      if (it > 1 && !warp_wait(&bars[B_PVDONE + (it & 1)], ((it >> 1) - 1) & 1, gu)) { ok = false; break; }
+      // the tile's P buffer and its O are free once its previous second product has finished
+      if (it > 0 && !warp_wait(&bars[B_PVDONE + t], (it - 1) & 1, gu)) { ok = false; break; }
+      tc_fence_after();
       if (it > 0 && moved) {
-        if (!warp_wait(&bars[B_PVDONE + ((it - 1) & 1)], ((it - 1) >> 1) & 1, gu)) { ok = false; break; }
-        tc_fence_after();
-        for (int c32 = 0; c32 < ocols; c32 += 32) {
-          float t[32];
-          tmem_ld32(tmem_o + lane_addr + part * ocols + c32, t);
+        for (int c32 = 0; c32 < d; c32 += 32) {
+          float o32[32];
+          tmem_ld32(tmem_o + lane_addr + c32, o32);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) t[i] *= alpha;
-          tmem_st32(tmem_o + lane_addr + part * ocols + c32, t);
+          for (int i = 0; i < 32; ++i) o32[i] *= alpha;
+          tmem_st32(tmem_o + lane_addr + c32, o32);
         }
         tmem_st_wait();
       }
-      // P as bf16 into the swizzled K-major tile: row R, 16-byte chunk cc holds keys 8cc .. 8cc+7
+      // P as bf16 into the swizzled K-major tile: row r, 16-byte chunk cc holds keys 8cc .. 8cc+7
       {
-        unsigned char* prow_ptr = Ps + (it & 1) * (ROWS * 128) + R * 128;
+        unsigned char* prow_ptr = Pt + r * 128;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int cc = part * 4 + i;
+        for (int cc = 0; cc < 8; ++cc) {
           uint4 v;
-          v.x = pack_bf16(s[8 * i], s[8 * i + 1]);
-          v.y = pack_bf16(s[8 * i + 2], s[8 * i + 3]);
-          v.z = pack_bf16(s[8 * i + 4], s[8 * i + 5]);
-          v.w = pack_bf16(s[8 * i + 6], s[8 * i + 7]);
-          *reinterpret_cast<uint4*>(prow_ptr + ((cc ^ (R & 7)) << 4)) = v;
+          v.x = pack_bf16(s[8 * cc], s[8 * cc + 1]);
+          v.y = pack_bf16(s[8 * cc + 2], s[8 * cc + 3]);
+          v.z = pack_bf16(s[8 * cc + 4], s[8 * cc + 5]);
+          v.w = pack_bf16(s[8 * cc + 6], s[8 * cc + 7]);
+          *reinterpret_cast<uint4*>(prow_ptr + ((cc ^ (r & 7)) << 4)) = v;
         }
       }
       // value rows of keys nobody may see can hold anything (pages never written, stale rows):
-      // clear them, 0 * NaN is NaN.  Only a request's first and last chunks have such rows.
-      if (key0 < lo || key0 + KC > hi) {
+      // clear them, 0 * NaN is NaN.  Only a request's first and last chunks have such rows; tile
+      // 0 does it (its second product is always issued before tile 1's).
+      if (t == 0 && (key0 < lo || key0 + KC > hi)) {
         if (!warp_wait(&bars[B_VFULL + st], round & 1, gu)) { ok = false; break; }
         unsigned char* vt = Vs + st * tile_bytes;
-        for (int idx = tid; idx < KC * halves * 8; idx += 2 * ROWS) {
+        for (int idx = r; idx < KC * halves * 8; idx += ROWS) {
           const int j = idx / (halves * 8), rest = idx - j * (halves * 8);
           if (key0 + j < lo || key0 + j >= hi)
             *reinterpret_cast<uint4*>(vt + (rest >> 3) * (KC * 128) + j * 128 + ((rest & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
@@ -424,28 +445,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[B_PFULL + (it & 1)]);
+      if (lane == 0) mbar_arrive(&bars[B_PFULL + t]);
     }
-    // the output: O / l, each thread its half of the columns
-    xch_sum[part][R] = l_run;
-    mbar_arrive(pair_bar);
-    ok = ok && warp_wait(pair_bar, n_chunks & 1, gu);
-    const float l_all = l_run + xch_sum[part ^ 1][R];
-    if (ok && n_chunks > 0 && warp_wait(&bars[B_PVDONE + ((n_chunks - 1) & 1)], ((n_chunks - 1) >> 1) & 1, gu)) {
+    // the output: O / l
+    if (ok && n_chunks > 0 && warp_wait(&bars[B_PVDONE + t], (n_chunks - 1) & 1, gu)) {
       tc_fence_after();
-      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-      bf16* orow = out + (size_t)(qs + tok0 + tk) * out_stride + (size_t)(kvh * g + hb * gb + mem) * d + part * ocols;
-      for (int c32 = 0; c32 < ocols; c32 += 32) {
-        float t[32];
-        tmem_ld32(tmem_o + lane_addr + part * ocols + c32, t);   // every thread of the warp takes part in the load
-        if (rvalid && l_all > 0.f) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      bf16* orow = out + (size_t)(qs + tok0 + tk) * out_stride + (size_t)(kvh * g + hb * gb + mem) * d;
+      for (int c32 = 0; c32 < d; c32 += 32) {
+        float o32[32];
+        tmem_ld32(tmem_o + lane_addr + c32, o32);   // every thread of the warp takes part in the load
+        if (rvalid && l_run > 0.f) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 v;
-            v.x = pack_bf16(t[i] * inv, t[i + 1] * inv);
-            v.y = pack_bf16(t[i + 2] * inv, t[i + 3] * inv);
-            v.z = pack_bf16(t[i + 4] * inv, t[i + 5] * inv);
-            v.w = pack_bf16(t[i + 6] * inv, t[i + 7] * inv);
+            v.x = pack_bf16(o32[i] * inv, o32[i + 1] * inv);
+            v.y = pack_bf16(o32[i + 2] * inv, o32[i + 3] * inv);
+            v.z = pack_bf16(o32[i + 4] * inv, o32[i + 5] * inv);
+            v.w = pack_bf16(o32[i + 6] * inv, o32[i + 7] * inv);
             *reinterpret_cast<uint4*>(orow + c32 + i) = v;
           }
         }
@@ -456,7 +473,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __syncthreads();
   if (warp == 9) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base_holder), "r"(256) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base_holder), "r"(512) : "memory");
   }
 }
 
@@ -511,8 +528,15 @@ extern "C" int mi_attention_prefill_tc_supported(int nq, int nkv, int d, int pag
   return ROWS % gb == 0 ? 1 : 0;
 }
 
+// Tokens per tile the kernel wants for a group of g query heads per key/value head (a block
+// takes NTILE * ROWS rows).
+extern "C" int mi_attention_prefill_tc_tile_tokens(int g) {
+  const int gb = g < ROWS ? g : ROWS;
+  return NTILE * ROWS / gb;
+}
+
 // Same arguments as mi_attention_prefill (attention_mma.cu) plus the number of pages of the
-// cache; tiles are ROWS / min(g, ROWS) tokens.
+// cache; tiles are mi_attention_prefill_tc_tile_tokens(g) tokens.
 extern "C" int mi_attention_prefill_tc(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
                                        const void* vcache, long long n_pages, const int* block_table, int bt_stride,
                                        int page_size, const int* q_start, const int* q_len, const int* kv_len,
@@ -527,7 +551,8 @@ extern "C" int mi_attention_prefill_tc(const void* q, int q_stride, void* out, i
   if (!mi_aligned(out, 16) || out_stride % 8 != 0) MI_REFUSE("attention_tc: output rows must be 16-byte aligned");
   if (!mi_aligned(kcache, 128) || !mi_aligned(vcache, 128)) MI_REFUSE("attention_tc: the cache must be 128-byte aligned");
   const int g = nq / nkv, gb = g < ROWS ? g : ROWS;
-  if (tile_tokens != ROWS / gb) MI_REFUSE("attention_tc: tiles of %d tokens, the kernel wants %d", tile_tokens, ROWS / gb);
+  if (tile_tokens != NTILE * ROWS / gb)
+    MI_REFUSE("attention_tc: tiles of %d tokens, the kernel wants %d", tile_tokens, NTILE * ROWS / gb);
   const int hblocks = (g + gb - 1) / gb;
   if (nkv * hblocks > 65535) MI_REFUSE("attention_tc: too many heads for one launch");
   int page_shift = 0;
@@ -537,13 +562,13 @@ extern "C" int mi_attention_prefill_tc(const void* q, int q_stride, void* out, i
   if (!make_cache_map(&map_k, kcache, rows, d, page_size) || !make_cache_map(&map_v, vcache, rows, d, page_size))
     MI_REFUSE("attention_tc: the driver refused a tensor map");
   const int halves = d / 64;
-  const size_t smem = (size_t)ROWS * 128 * halves + 2 * ROWS * 128 + 2 * NSTAGE * (size_t)KC * 128 * halves + 1024;
+  const size_t smem = (size_t)NTILE * ROWS * 128 * halves + NTILE * ROWS * 128 + 2 * NSTAGE * (size_t)KC * 128 * halves + 1024;
   auto kern = attention_prefill_tc_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(n_tiles, nkv * hblocks);
   MI_LAUNCH((kern), grid, TC_THREADS, smem, stream, map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride,
             block_table, bt_stride, page_size, page_shift, q_start, q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, scale,
-            window, gb, ROWS / gb);
+            window, gb, NTILE * ROWS / gb);
   MI_RETURN_LAUNCH_STATUS();
 }

@@ -344,9 +344,15 @@ def prefill_tile_tokens(group: int) -> int:
     return 128 // min(group, 128)
 
 
+def prefill_tc_tile_tokens(group: int) -> int:
+    """Tokens per tile of the tcgen05 prefill kernel: two tiles of 128 rows of (token, head
+    in group) per block (attention_tc.cu)."""
+    return 256 // min(group, 128)
+
+
 def attention_tile_sizes(group: int) -> frozenset[int]:
     """The query tile sizes a step must plan for an attention mixer with this group size."""
-    return frozenset({ATTENTION_TILE_TOKENS, prefill_tile_tokens(group)})
+    return frozenset({ATTENTION_TILE_TOKENS, prefill_tile_tokens(group), prefill_tc_tile_tokens(group)})
 
 
 _sm_count: dict[int, int] = {}
@@ -386,9 +392,9 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq:
                              ctx.q_start, ctx.kv_len, ctx.n_requests, nq, nkv, head_dim, scale, window,
                              decode_splits(ctx.n_requests, nq, nkv, ctx.max_kv_len, window, q.device))
         else:
-            tt = prefill_tile_tokens(nq // nkv)
-            tile_req, tile_tok0, n_tiles = ctx.q_tiles(tt)
             tc = USE_TC_PREFILL and prefill_tc_supported(nq, nkv, head_dim, group.page_size)
+            tt = (prefill_tc_tile_tokens if tc else prefill_tile_tokens)(nq // nkv)
+            tile_req, tile_tok0, n_tiles = ctx.q_tiles(tt)
             (attention_prefill_tc if tc else attention_prefill)(
                 q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
                 ctx.q_start, ctx.q_len, ctx.kv_len, tile_req, tile_tok0, n_tiles, tt,

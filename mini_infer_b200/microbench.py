@@ -104,7 +104,7 @@ def attention_prefill(args, ops, device, flush) -> tuple[float, str]:
     q_start = torch.zeros(1, device=device, dtype=torch.int32)
     q_len = torch.full((1,), T, device=device, dtype=torch.int32)
     kv_len = torch.full((1,), T, device=device, dtype=torch.int32)
-    tile = ops.prefill_tile_tokens(nq // nkv)
+    tile = (ops.prefill_tc_tile_tokens if args.impl == "tc" else ops.prefill_tile_tokens)(nq // nkv)
     n_tiles = -(-T // tile)
     tile_req = torch.zeros(n_tiles, device=device, dtype=torch.int32)
     tile_tok0 = (torch.arange(n_tiles, device=device, dtype=torch.int32) * tile).contiguous()

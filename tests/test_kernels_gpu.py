@@ -327,7 +327,8 @@ def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, bo
     if boost is not None:
         boost(q, ks, kc, bt)
     q_start = [sum(q_lens[:i]) for i in range(len(q_lens))]
-    T_ = o.ATTENTION_TILE_TOKENS if kernel == "generic" else o.prefill_tile_tokens(nq // nkv)
+    T_ = {"generic": lambda: o.ATTENTION_TILE_TOKENS, "prefill_tc": lambda: o.prefill_tc_tile_tokens(nq // nkv)}.get(
+        kernel, lambda: o.prefill_tile_tokens(nq // nkv))()
     treq = [i for i, n in enumerate(q_lens) for _ in range(0, n, T_)]
     ttok = [t0 for n in q_lens for t0 in range(0, n, T_)]
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
