@@ -309,6 +309,16 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       segs.get(i, natural, tile, kc0, len);
       const bool whole = (len == kchunks);
       const int n = tile * TILE_ROWS + row;
+      // who shares this tile (worked out while the MMAs still run: the divisions are slow)
+      const long long t0 = (long long)tile * kchunks;
+      int c_first = 0, c_last = 0, first_slot = 0;
+      if (!whole) {
+        c_first = block_of_unit(total, t0, G);
+        c_last = block_of_unit(total, t0 + kchunks - 1, G);
+        // Every block after the tile's first one begins inside the tile, so the tile is its
+        // first segment (slot 0); the first block's is slot 0 only if it begins with the tile.
+        first_slot = c_first * 2 + (first_unit(total, c_first, G) == t0 ? 0 : 1);
+      }
       // the four warps leave together or not at all (they meet at named barriers below)
       if (!mbar_wait(&acc_full, i & 1, gu)) epilogue_stop = 1;
       asm volatile("bar.sync 1, 128;\n" ::: "memory");
@@ -347,15 +357,10 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // count this block in; the last one to arrive adds the partial tiles in block order
         __threadfence();
         asm volatile("bar.sync 1, 128;\n" ::: "memory");
-        const long long t0 = (long long)tile * kchunks;
-        const int c_first = block_of_unit(total, t0, G), c_last = block_of_unit(total, t0 + kchunks - 1, G);
         if (etid == 0) is_last = (atomicAdd(&counters[tile], 1) == c_last - c_first) ? 1 : 0;
         asm volatile("bar.sync 1, 128;\n" ::: "memory");
         if (is_last) {
           __threadfence();
-          // Every block after the tile's first one begins inside the tile, so the tile is its
-          // first segment (slot 0); the first block's is slot 0 only if it begins with the tile.
-          const int first_slot = c_first * 2 + (first_unit(total, c_first, G) == t0 ? 0 : 1);
           {
             // sixteen tokens and four blocks' partial tiles at a time: 64 independent loads are in
             // flight per thread; the additions still run in block order
