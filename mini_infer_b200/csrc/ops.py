@@ -685,7 +685,6 @@ def gemm_tma(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bf
     streaming ``w`` once through TMA (gemm_tma.cu); the result is bfloat16 or float32.  With
     ``swiglu`` the rows of ``w`` alternate gate, up and the result is ``[M, N / 2]``:
     ``silu(gate) * up`` computed on the fp32 accumulators in the product's epilogue."""
-    global launch_count
     _cuda(x, w)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tma: operands must be bfloat16")
@@ -702,7 +701,6 @@ def gemm_tma(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bf
         raise KernelError("gemm_tma: the gate/up epilogue needs an even number of rows")
     n_out = N // 2 if swiglu else N
     out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
-    launch_count += 1
     rc = lib.mi_gemm_tma(_ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), n_out, M, N, K,
                          _code(out_dtype), 1 if swiglu else 0, blocks, _ptr(partial), _ptr(count), _stream())
     _finish(lib, rc, "gemm_tma")
