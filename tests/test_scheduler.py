@@ -319,3 +319,41 @@ def test_lookahead_cancel_while_a_step_is_ahead():
     assert h.wait().finish_reason == "cancelled"
     assert other.wait().tokens == expected_tokens(1, 3, 8)
     assert runner.cache.num_requests == 0 and runner.cache.num_free_pages() == 64
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6])
+def test_lookahead_random_arrivals_match_the_plain_scheduler(seed):
+    """Requests of random lengths arrive at random moments into a pool so small that some are
+    preempted; some end on a stop token; with and without decode look-ahead every request gets
+    the same tokens and the same reason to finish, and every page comes back."""
+    import random
+
+    rng = random.Random(seed)
+    n = rng.randint(3, 7)
+    specs = [(rng.randint(1, 40), rng.randint(1, 25)) for _ in range(n)]          # (prompt length, max tokens)
+    arrive = sorted(rng.randint(0, 30) for _ in range(n))                        # step at which each is submitted
+    eos = {rid: rng.randint(0, m - 1) for rid, (_, m) in enumerate(specs) if rng.random() < 0.4}
+    pages = rng.randint(14, 28)
+
+    def run(lookahead):
+        runner = FeedbackRunner(pages, page_size=4, max_requests=4)
+        sched = ContinuousScheduler(runner, sampler=TensorSampler(dict(eos)), lookahead=lookahead, eos_token_ids=[0],
+                                    max_concurrent=4, chunk_size=16, max_tokens_per_step=24, decode_headroom_blocks=0)
+        handles, step, nxt = [], 0, 0
+        while nxt < n or any(not h.finished for h in handles):
+            while nxt < n and arrive[nxt] <= step:
+                p, m = specs[nxt]
+                handles.append(sched.submit(Request(prompt(p, base=37 * nxt), SamplingParams(), m)))
+                nxt += 1
+            sched.step()
+            step += 1
+            assert step < 2000, "the scheduler does not finish"
+        sched.run_until_done()
+        runner.cache.check()
+        assert runner.cache.num_requests == 0 and runner.cache.num_free_pages() == pages
+        return [(h.wait().tokens, h.wait().finish_reason) for h in handles], sched
+
+    plain, _ = run(False)
+    ahead, sched = run(True)
+    assert ahead == plain
+    assert sched.wasted_tokens <= len(eos)
