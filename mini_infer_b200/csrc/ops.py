@@ -485,8 +485,15 @@ USE_TC_PREFILL = os.environ.get("MINI_INFER_TC_PREFILL", "1") != "0"
 
 
 def prefill_tc_supported(nq: int, nkv: int, head_dim: int, page_size: int) -> bool:
-    """Whether the tcgen05 prefill kernel (attention_tc.cu) takes these sizes."""
-    return bool(_lib("attention_tc").mi_attention_prefill_tc_supported(nq, nkv, head_dim, page_size))
+    """Whether the tcgen05 prefill kernel (attention_tc.cu) takes these sizes: head size 64 or
+    128, a power-of-two page of 8 to 64 keys, a group size that divides 128.  (The same test as
+    the library's own ``mi_attention_prefill_tc_supported``, made here so that a model the
+    kernel does not take never compiles it.)"""
+    if head_dim not in (64, 128) or page_size < 8 or page_size > 64 or page_size & (page_size - 1):
+        return False
+    if nq <= 0 or nkv <= 0 or nq % nkv:
+        return False
+    return 128 % min(nq // nkv, 128) == 0
 
 
 def attention_prefill_tc(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, q_len, kv_len,

@@ -456,6 +456,13 @@ def test_attention_prefill_tcgen05_far_key_and_big_scores():
     assert not ops().prefill_tc_supported(6, 2, 48, 8)
     assert not ops().prefill_tc_supported(4, 4, 64, 4)
     assert not ops().prefill_tc_supported(3, 1, 128, 16)
+    # the Python-side test and the library's own agree
+    lib = ops()._lib("attention_tc")
+    for nq, nkv in [(1, 1), (4, 2), (6, 2), (32, 8), (3, 1), (64, 1), (256, 1), (5, 5), (4, 3)]:
+        for d in (16, 48, 64, 96, 128, 256):
+            for page in (1, 4, 8, 12, 16, 32, 64, 128):
+                assert ops().prefill_tc_supported(nq, nkv, d, page) == bool(
+                    lib.mi_attention_prefill_tc_supported(nq, nkv, d, page)), (nq, nkv, d, page)
 
 
 def test_attention_long_contexts():
