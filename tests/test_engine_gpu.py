@@ -244,7 +244,8 @@ def _register_toys():
     from mini_infer_b200.config import register_architecture
     from mini_infer_b200.models.llama import assemble as llama_assemble
     from mini_infer_b200.config import LlamaConfig
-    from mini_infer_b200.parts import (Mixer, ParamDecl, PartSpec, ScheduleEntry, StateNeed, register_mixer)
+    from mini_infer_b200.parts import (FeedForward, Mixer, ParamDecl, PartSpec, Position, ScheduleEntry, StateNeed,
+                                       register_feed_forward, register_mixer, register_position)
 
     class RunningMeanMixer(Mixer):
         """out_t = W * mean(x_0 .. x_t): its state is the running sum and the count."""
@@ -273,12 +274,65 @@ def _register_toys():
 
     register_mixer("toy_running_mean", RunningMeanMixer, replace=True)
 
+    class SoftRoutedExperts(FeedForward):
+        """sum_e softmax(x R^T)_e * down_e(silu(up_e x)): a router (fp32 logits and softmax) and
+        several experts of its own sizes; a feed-forward with routing, with plain torch ops."""
+
+        def param_decls(self):
+            H, I, E = self.param("hidden_size"), self.param("expert_size"), self.param("experts")
+            decls = {"router.weight": ParamDecl((E, H))}
+            for e in range(E):
+                decls[f"experts.{e}.up.weight"] = ParamDecl((I, H))
+                decls[f"experts.{e}.down.weight"] = ParamDecl((H, I))
+            return decls
+
+        def bind(self, tensors, dtype, device):
+            self.t = {k: v.to(dtype) for k, v in tensors.items()}
+
+        def forward(self, x, ctx):
+            gates = torch.softmax(x.float() @ self.t["router.weight"].float().T, dim=-1)
+            out = torch.zeros_like(x, dtype=torch.float32)
+            for e in range(self.param("experts")):
+                hidden = torch.nn.functional.silu((x @ self.t[f"experts.{e}.up.weight"].T).float()).to(x.dtype)
+                out += gates[:, e:e + 1] * (hidden @ self.t[f"experts.{e}.down.weight"].T).float()
+            return out.to(x.dtype)
+
+    register_feed_forward("toy_soft_experts", SoftRoutedExperts, replace=True)
+
+    class LearnedOffsets(Position):
+        """q and k get a learned vector added that depends on the position modulo a period:
+        another position encoding than rotation; keys are stored by the default store path."""
+
+        def param_decls(self):
+            return {"table": ParamDecl((self.param("period"), self.param("head_dim")))}
+
+        def bind(self, tensors, dtype, device):
+            self.table = tensors["table"].to(dtype)
+
+        def encode(self, qkv, nq, nkv, head_dim, ctx):
+            add = self.table[(ctx.positions.long() % self.param("period"))]          # [tokens, d]
+            heads = qkv[:, : (nq + nkv) * head_dim].view(qkv.shape[0], nq + nkv, head_dim)
+            heads += add[:, None, :]
+
+    register_position("toy_learned_offsets", LearnedOffsets, replace=True)
+
     def toy_state_assemble(cfg):
         spec = llama_assemble(cfg)
         layers = list(spec.layers)
         layers[0] = dataclasses.replace(
             layers[0], position=None,
             mixer=PartSpec("toy_running_mean", {"hidden_size": cfg.hidden_size}, prefix="model.layers.0.toy."))
+        return dataclasses.replace(spec, layers=tuple(layers))
+
+    def routed_assemble(cfg):
+        spec = llama_assemble(cfg)
+        layers = list(spec.layers)
+        layers[1] = dataclasses.replace(
+            layers[1],
+            feed_forward=PartSpec("toy_soft_experts", {"hidden_size": cfg.hidden_size, "expert_size": 40, "experts": 3},
+                                  prefix="model.layers.1.moe."),
+            position=PartSpec("toy_learned_offsets", {"head_dim": cfg.head_dim, "period": 7},
+                              prefix="model.layers.1.pos."))
         return dataclasses.replace(spec, layers=tuple(layers))
 
     def windowed_assemble(cfg):
@@ -297,9 +351,10 @@ def _register_toys():
     register_architecture("ToyStateLM", LlamaConfig.from_json, toy_state_assemble, replace=True)
     register_architecture("ToyWindowLM", LlamaConfig.from_json, windowed_assemble, replace=True)
     register_architecture("ToyLoopLM", LlamaConfig.from_json, looped_assemble, replace=True)
+    register_architecture("ToyRoutedLM", LlamaConfig.from_json, routed_assemble, replace=True)
 
 
-def plain_variant(state, raw, ids, *, windows=None, schedule=None, toy_layers=()):
+def plain_variant(state, raw, ids, *, windows=None, schedule=None, toy_layers=(), routed_layers=()):
     """The plain decoder with per-layer windows, a run order and toy layers (float64)."""
     cfg = P.normalise_config(raw)
     w = {k: v.double() for k, v in state.items()}
@@ -318,16 +373,29 @@ def plain_variant(state, raw, ids, *, windows=None, schedule=None, toy_layers=()
             mean = torch.cumsum(a, dim=0) / torch.arange(1, Tn + 1, dtype=torch.float64)[:, None]
             h = h + mean @ w[p + "toy.mix.weight"].T
         else:
-            q = P.apply_rope((a @ w[p + "self_attn.q_proj.weight"].T).view(Tn, nq, d), cos, sin)
+            if layer in routed_layers:       # learned offsets by position modulo the period, no rotation
+                table = w[p + "pos.table"]
+                add = table[torch.arange(Tn) % table.shape[0]][:, None, :]
+                encode = lambda t: t + add
+            else:
+                encode = lambda t: P.apply_rope(t, cos, sin)
+            q = encode((a @ w[p + "self_attn.q_proj.weight"].T).view(Tn, nq, d))
             if writes:
-                k = P.apply_rope((a @ w[p + "self_attn.k_proj.weight"].T).view(Tn, nkv, d), cos, sin)
+                k = encode((a @ w[p + "self_attn.k_proj.weight"].T).view(Tn, nkv, d))
                 v = (a @ w[p + "self_attn.v_proj.weight"].T).view(Tn, nkv, d)
                 kv_of[cache] = (k, v)
             k, v = kv_of[cache]
             o = P.causal_attention(q, k, v, 1 / math.sqrt(d), windows[layer])
             h = h + o.reshape(Tn, nq * d) @ w[p + "self_attn.o_proj.weight"].T
         b = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
-        h = h + P.swiglu(b, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+        if layer in routed_layers:
+            gates = torch.softmax(b @ w[p + "moe.router.weight"].T, dim=-1)
+            for e in range(gates.shape[1]):
+                hidden = P.silu(b @ w[p + f"moe.experts.{e}.up.weight"].T)
+                h = h + gates[:, e:e + 1] * (hidden @ w[p + f"moe.experts.{e}.down.weight"].T)
+        else:
+            h = h + P.swiglu(b, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                             w[p + "mlp.down_proj.weight"])
     z = P.rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else w["lm_head.weight"]
     return (z @ head.T).numpy()
@@ -340,7 +408,9 @@ def run_variant(arch, raw_base, tmp_path, dtype, page, plain_kwargs, num_blocks=
 
     _register_toys()
     raw = dict(raw_base, architectures=[arch])
-    folder = write_random_model(raw, str(tmp_path / arch), 5, std_overrides=PEAKED["A"])
+    # wide enough that a wrong offset, gate or expert would show in the logits
+    wide = dict(PEAKED["A"], **{"pos.table": 0.7, "router.weight": 0.5, "experts.": 0.08})
+    folder = write_random_model(raw, str(tmp_path / arch), 5, std_overrides=wide)
     state = load_state(folder)
     requests = {f"q{i}": prompt_ids("A", n, salt=200 + i) for i, n in enumerate([50, 3, 77, 31])}
     want = {r: plain_variant(state, raw, toks, **plain_kwargs) for r, toks in requests.items()}
@@ -365,6 +435,17 @@ def test_toy_mixer_with_state_of_its_own(dtype, tmp_path):
     runner = run_variant("ToyStateLM", TINY["A"], tmp_path, dtype, 16, {"toy_layers": (0,)})
     assert 0 in runner.cache.state_arenas and 1 not in runner.cache.state_arenas
     assert [g.layers for g in runner.cache.groups] == [(1,)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_routed_feed_forward_and_another_position_encoding(dtype, tmp_path):
+    """A feed-forward with a router and experts and a position encoding that is no rotation,
+    both defined here, take the place of a layer's SwiGLU and rotary parts: registered, built,
+    given their tensors by name, and stepped in mixed batches beside an ordinary layer."""
+    runner = run_variant("ToyRoutedLM", TINY["A"], tmp_path, dtype, 16, {"routed_layers": (1,)})
+    names = {t.name for t in runner.model.expected_tensors()}
+    assert "model.layers.1.moe.router.weight" in names and "model.layers.1.pos.table" in names
+    assert "model.layers.1.mlp.gate_proj.weight" not in names
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
