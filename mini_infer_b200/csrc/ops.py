@@ -658,9 +658,11 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch
 
 
 TMA_GEMM_MAX_ROWS = 128            # what gemm_tma.cu takes
-# ``linear`` routes inputs of up to this many rows to gemm_tma; measured on a B200 inside a
-# captured decode step (Llama 3.1 8B sizes) it is ahead of the library product up to 8 rows
-# (3.91 vs 4.15 ms per step at batch 8) and behind it from 16 rows on (4.39 vs 4.26 ms).
+# ``linear`` routes inputs of up to this many rows to gemm_tma.  Measured on a B200 inside a
+# captured decode step (Llama 3.1 8B sizes) the two products are within run-to-run noise of
+# each other up to 16 rows (batch 8: 3.97 vs 3.96 ms per step; batch 12: 4.10 vs 4.02 to
+# 4.18; batch 16: 4.35 vs 4.37) and the library product is ahead from 32 rows on (5.32 vs
+# 5.20; 64 rows: 7.65 vs 6.70).
 TMA_GEMM_DISPATCH_ROWS = 8
 USE_TMA_GEMM = os.environ.get("MINI_INFER_TMA_GEMM", "1") != "0"
 _tma_ws: dict[int, list[tuple[torch.Tensor, torch.Tensor]]] = {}
