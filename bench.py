@@ -55,6 +55,12 @@ LLAMA_8B = {
     "max_position_embeddings": 131072,
     "tie_word_embeddings": False,
 }
+# The same architecture at Llama 3.1 70B's layer sizes (a further measurement point,
+# ``--sizes 70b``; loading builds the merged matrices beside the checkpoint's, so the default
+# takes fewer layers than the model has and the line names both numbers).
+LLAMA_70B = dict(LLAMA_8B, hidden_size=8192, intermediate_size=28672, num_hidden_layers=80,
+                 num_attention_heads=64)
+SIZES = {"8b": ("Llama 3.1 8B", LLAMA_8B, 32), "70b": ("Llama 3.1 70B", LLAMA_70B, 20)}
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
 PAGE = 16
@@ -262,6 +268,83 @@ def time_e2e(runner, batch: int, context: int, steps: int, warmup: int) -> dict:
             "h2d_bytes_per_step": runner.stepper.last_h2d_bytes, "d2h_bytes_per_step": 4 * batch}
 
 
+def run_long_mixed(args) -> int:
+    """The long mixed workload: ``--requests`` requests started together, prompt lengths drawn
+    log-uniformly from [16, ``--max-prompt``], ``--generate`` greedy tokens each, a step budget
+    of 2048 tokens, admission by free pages.  Prints one JSON line of its own (total tokens a
+    second, step times, the pool's high-water mark, preemptions); it is no part of the
+    contract line.  Timed by the wall clock with a device synchronise on both sides."""
+    _, cfg, _ = SIZES[args.sizes]
+    layers = args.layers
+    token_bytes = 2 * layers * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+    num_blocks = int(args.pool_gb * 1e9 / (token_bytes * PAGE))
+    runner = build_runner(cfg, layers, num_blocks=num_blocks, max_requests=args.requests)
+    print(json.dumps(long_mixed(runner, args, num_blocks)))
+    return 0
+
+
+def long_mixed(runner, args, num_blocks: int) -> dict:
+    import math
+
+    import torch
+
+    from mini_infer_b200.engine import ContinuousScheduler, Request
+    from mini_infer_b200.sampling import SamplingParams
+
+    model_name, cfg, _ = SIZES[args.sizes]
+    layers = args.layers
+    gen = torch.Generator().manual_seed(11)
+    lo, hi = math.log(16.0), math.log(float(args.max_prompt))
+    lengths = [int(round(math.exp(lo + (hi - lo) * u))) for u in torch.rand(args.requests, generator=gen).tolist()]
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist() for n in lengths]
+    sched = ContinuousScheduler(runner, max_concurrent=args.requests, chunk_size=2048, max_tokens_per_step=2048,
+                                decode_headroom_blocks=8)
+    # Warm-up: one short request end to end, so that kernels are built and loaded.
+    sched.generate([Request(prompts[0][:64], SamplingParams(), max_tokens=4)])
+    clocks = ClockSampler()
+    clocks.start()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    handles = [sched.submit(Request(p, SamplingParams(), max_tokens=args.generate)) for p in prompts]
+    step_ms, step_tokens, high_water, last = [], [], 0.0, t0
+    while sched.step():
+        now = time.perf_counter()
+        step_ms.append(1000.0 * (now - last))
+        step_tokens.append(sum(len(e.tokens) for e in sched.last_step_entries))
+        high_water = max(high_water, sched.load_stats().kv_cache_usage)
+        last = now
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    clock_summary = clocks.stop()
+    results = [h.wait() for h in handles]
+    sched.stop()
+    runner.cache.check()
+    generated = sum(len(r.tokens) for r in results)
+    reasons: dict[str, int] = {}
+    for r in results:
+        reasons[r.finish_reason] = reasons.get(r.finish_reason, 0) + 1
+    ordered = sorted(step_ms)
+    decode_ms = sorted(ms for ms, n in zip(step_ms, step_tokens) if n <= args.requests)
+    line = {
+        "scenario": "long-mixed", "metric": "generated tokens a second, prefill included",
+        "value": round(generated / wall, 1), "unit": "tokens/s", "wall_s": round(wall, 3),
+        "prompt_tokens_per_s": round(sum(lengths) / wall, 1), "dtype": "bf16", "data": "synthetic",
+        "config": {"model": model_name.replace(" ", "-") + " sizes, random weights", "layers": layers,
+                   "layers_of_model": cfg["num_hidden_layers"], "requests": args.requests,
+                   "prompt_tokens": sum(lengths), "longest_prompt": max(lengths), "shortest_prompt": min(lengths),
+                   "generated_each": args.generate, "step_budget": 2048, "page_size": PAGE,
+                   "pool_pages": num_blocks, "pool_gb": args.pool_gb},
+        "steps": len(step_ms), "generated": generated, "finish_reasons": reasons,
+        "step_ms": {"p50": round(ordered[len(ordered) // 2], 3), "p90": round(ordered[len(ordered) * 9 // 10], 3),
+                    "max": round(ordered[-1], 3)},
+        "decode_step_ms_p50": round(decode_ms[len(decode_ms) // 2], 3) if decode_ms else None,
+        "pool_high_water": round(high_water, 4), "pool_in_use_after": runner.cache.usage(),
+        "preemptions": sched.preemptions, "tokens_computed_in_vain": sched.wasted_tokens,
+        "clocks": clock_summary,
+    }
+    return line
+
+
 def reference_arm(args) -> int:
     """The unmodified reference (installed under baseline/_ref) on the same metric: its own
     ``LlamaForCausalLM`` with random bf16 weights at the same sizes, its ``BlockPool`` /
@@ -383,56 +466,74 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=LLAMA_8B["num_hidden_layers"],
+    ap.add_argument("--sizes", default="8b", choices=sorted(SIZES), help="layer sizes of which model")
+    ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the model has (sizes unchanged), for small memory")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when decoding starts")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 and e2e measurements")
+    ap.add_argument("--scenario", default="decode", choices=["decode", "long-mixed"],
+                    help="decode: the contract line; long-mixed: many requests of very different lengths "
+                         "through the scheduler (a line of its own)")
+    ap.add_argument("--requests", type=int, default=64, help="long-mixed: requests started together")
+    ap.add_argument("--max-prompt", type=int, default=32768, help="long-mixed: longest prompt")
+    ap.add_argument("--generate", type=int, default=256, help="long-mixed: tokens generated per request")
+    ap.add_argument("--pool-gb", type=float, default=48.0, help="long-mixed: size of the key/value pool")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    model_name, cfg, default_layers = SIZES[args.sizes]
+    if args.layers is None:
+        args.layers = default_layers
     if args.impl == "reference":
+        if args.sizes != "8b" or args.scenario != "decode" or args.context != CONTEXT:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference arm measures the contract's "
+                              "configuration only (8B sizes, decode, 2048-token context)"}))
+            return 0
         return reference_arm(args)
+    if args.scenario == "long-mixed":
+        return run_long_mixed(args)
     warmup = max(3, args.warmup)
 
     import torch
 
     from mini_infer_b200.csrc import build as kernel_build
 
-    cfg, layers, batch = LLAMA_8B, args.layers, args.batch
+    layers, batch, context = args.layers, args.batch, args.context
     peaks = load_peaks()
     max_batch = batch if args.skip_points else max(batch, 64)
-    tokens_cap = max_batch * (CONTEXT + args.steps + warmup + 2 * batch + 64)
+    tokens_cap = max_batch * (context + args.steps + warmup + 2 * batch + 64)
     runner = build_runner(cfg, layers, num_blocks=tokens_cap // PAGE + 8, max_requests=max_batch)
 
     clocks = ClockSampler()
     clocks.start()
-    ms, launches = time_decode(runner, batch, CONTEXT, args.steps, warmup)
+    ms, launches = time_decode(runner, batch, context, args.steps, warmup)
     points, e2e, prefill = {}, None, None
     prefill_ms = time_prefill(runner, PREFILL_TOKENS, repeats=3, warmup=2)
     if not args.skip_points:
         for b in (1, 64):
-            pms, _ = time_decode(runner, b, CONTEXT, args.steps, warmup)
+            pms, _ = time_decode(runner, b, context, args.steps, warmup)
             points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
-        e2e = time_e2e(runner, batch, CONTEXT, args.steps, warmup)
+        e2e = time_e2e(runner, batch, context, args.steps, warmup)
     clock_summary = clocks.stop()
 
     value = batch * 1000.0 / ms
-    mean_ctx = CONTEXT + warmup + args.steps / 2.0
+    mean_ctx = context + warmup + args.steps / 2.0
     achieved = decode_bytes(cfg, layers, batch, mean_ctx) / (ms * 1e-3) / 1e9
     flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
     line = {
-        "metric": "decode tok/s @ batch 8, 2048-token context (Llama 3.1 8B layer sizes)",
+        "metric": f"decode tok/s @ batch {batch}, {context}-token context ({model_name} layer sizes)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": round(value / BASELINE_DECODE_TOK_S, 3), "dtype": "bf16", "data": "synthetic",
-        "impl": "ours",
+        "vs_baseline": round(value / BASELINE_DECODE_TOK_S, 3) if args.sizes == "8b" else None,
+        "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": {
-            "model": "Llama-3.1-8B sizes, random weights", "layers": layers,
+            "model": model_name.replace(" ", "-") + " sizes, random weights", "layers": layers,
             "layers_of_model": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"],
             "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-            "global_batch": batch, "seq_len": CONTEXT, "context_cap": 4096, "page_size": PAGE,
+            "global_batch": batch, "seq_len": context, "context_cap": max(4096, 2 * context), "page_size": PAGE,
             "prefill_tokens": PREFILL_TOKENS, "kv_dtype": "bf16", "parallelism": "single GPU",
             "l2": "inputs (weights) larger than L2, no flush", "peaks": peaks["source"],
         },

@@ -311,8 +311,9 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                         const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                         const int* __restrict__ block_table, int bt_stride, int page_size, int page_shift,
                         const int* __restrict__ q_start, const int* __restrict__ kv_len, int nq, int nkv,
-                        int d, float scale, int window, int n_splits, float* __restrict__ part_o,
-                        float* __restrict__ part_ml, int* __restrict__ counters, int* __restrict__ status) {
+                        int d, float scale, int window, int n_splits, const int* __restrict__ slice_chunks,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
+                        int* __restrict__ status) {
   // The next kernel's blocks may be scheduled.  This kernel reads the batch description and
   // the keys and values of earlier positions before it waits for the kernels ahead of it: the
   // description was uploaded before the step's first kernel, and the step's own kernels write
@@ -338,7 +339,11 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
   const int tok = q_start[b];
   const int lo = window > 0 ? max(0, kl - window) : 0;  // the query sits at position kl - 1
   const int c_first = lo / KCHUNK, c_end = (kl + KCHUNK - 1) / KCHUNK;
-  const int per_split = (c_end - c_first + n_splits - 1) / n_splits;
+  // A slice is the same number of chunks for every request when the caller planned one (a
+  // short request then fills fewer slices and a long one is cut into all of them); never
+  // fewer than this request needs to be covered by n_splits slices.
+  int per_split = (c_end - c_first + n_splits - 1) / n_splits;
+  if (slice_chunks) per_split = max(per_split, __ldg(slice_chunks));
   const int c0 = c_first + split * per_split;
   const int c1 = min(c_end, c0 + per_split);
   const int heads_here = min(DEC_HEADS, g - hb * DEC_HEADS);
@@ -927,11 +932,15 @@ extern "C" int mi_attention_decode_counters(int B, int nq, int nkv) {
 // Scratch: part_o holds B * nq * n_splits * d floats, part_ml holds B * nq * n_splits * 2 floats,
 // counters holds mi_attention_decode_counters(B, nq, nkv) ints that are zero on entry (the kernel
 // leaves them zero).  All three may be null when n_splits == 1.
-extern "C" int mi_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
-                                   const void* vcache, const int* block_table, int bt_stride, int page_size,
-                                   const int* q_start, const int* kv_len, int B, int nq, int nkv, int d,
-                                   float scale, int window, int n_splits, float* part_o, float* part_ml,
-                                   int* counters, cudaStream_t stream) {
+// slice_chunks (may be null) points at one int on the device, read when the kernel runs: the
+// number of 64-key chunks per slice, the same for every request.  Null cuts every request's
+// own span into n_splits equal slices.
+extern "C" int mi_attention_decode_sliced(const void* q, int q_stride, void* out, int out_stride,
+                                          const void* kcache, const void* vcache, const int* block_table,
+                                          int bt_stride, int page_size, const int* q_start, const int* kv_len,
+                                          int B, int nq, int nkv, int d, float scale, int window, int n_splits,
+                                          const int* slice_chunks, float* part_o, float* part_ml, int* counters,
+                                          cudaStream_t stream) {
   if (B <= 0) return 0;
   if (int rc = check_common(q, q_stride, out, out_stride, kcache, vcache, nq, nkv, d, page_size, window)) return rc;
   if (n_splits < 1 || n_splits > 64) MI_REFUSE("attention: n_splits must be in [1, 64], got %d", n_splits);
@@ -951,14 +960,24 @@ extern "C" int mi_attention_decode(const void* q, int q_stride, void* out, int o
     MI_LAUNCH((kern), grid, DEC_THREADS, smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,         \
                                            (const bf16*)kcache, (const bf16*)vcache, block_table,       \
                                            bt_stride, page_size, page_shift, q_start, kv_len, nq, nkv,  \
-                                           d, scale, window, n_splits, part_o, part_ml, counters,       \
-                                           wait_status_ptr());                                          \
+                                           d, scale, window, n_splits, slice_chunks, part_o, part_ml,   \
+                                           counters, wait_status_ptr());                                \
   } while (0)
   if (d <= 64) MI_DECODE(64);
   else if (d <= 128) MI_DECODE(128);
   else MI_DECODE(256);
 #undef MI_DECODE
   MI_RETURN_LAUNCH_STATUS();
+}
+
+extern "C" int mi_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
+                                   const void* vcache, const int* block_table, int bt_stride, int page_size,
+                                   const int* q_start, const int* kv_len, int B, int nq, int nkv, int d,
+                                   float scale, int window, int n_splits, float* part_o, float* part_ml,
+                                   int* counters, cudaStream_t stream) {
+  return mi_attention_decode_sliced(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride, page_size,
+                                    q_start, kv_len, B, nq, nkv, d, scale, window, n_splits, nullptr, part_o,
+                                    part_ml, counters, stream);
 }
 
 // Tokens per tile the prefill kernel wants for a group of g query heads per key/value head.

@@ -100,6 +100,10 @@ def _sig_attention_mma(lib: ctypes.CDLL) -> None:
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
         c_void_p, c_void_p]
+    lib.mi_attention_decode_sliced.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p]
     lib.mi_attention_decode_counters.argtypes = [c_int, c_int, c_int]
     lib.mi_attention_wait_status.argtypes = [c_int]
     lib.mi_attention_prefill.argtypes = [
@@ -365,6 +369,10 @@ def _sms(device: torch.device) -> int:
     return _sm_count[idx]
 
 
+def sm_count(device: torch.device) -> int:
+    return _sms(device)
+
+
 def decode_splits(n_requests: int, nq: int, nkv: int, max_kv_len: int, window: int, device) -> int:
     """How many slices of the keys each (request, key/value head) is cut into: enough blocks
     for about two per SM, but at least four 64-key chunks per slice (a slice costs a fixed
@@ -373,6 +381,44 @@ def decode_splits(n_requests: int, nq: int, nkv: int, max_kv_len: int, window: i
     span = min(max_kv_len, window + 63) if window else max_kv_len
     chunks = max(1, -(-span // 64))
     return max(1, min(2 * _sms(device) // blocks, chunks // 4, 64))
+
+
+DECODE_HEADS_PER_BLOCK = 8         # DEC_HEADS in attention_mma.cu
+# Slice counts a planned decode step may use (few values, so that few graphs are captured).
+DECODE_SLICE_COUNTS = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64)
+
+
+# Blocks per SM a planned decode step aims at: two when the requests are about equally long;
+# more (shorter slices) when the longest is over twice the mean, since blocks of very
+# different lengths leave a tail in which few SMs work.
+DECODE_BLOCKS_PER_SM = 2
+DECODE_BLOCKS_PER_SM_SKEWED = 4
+
+
+def decode_blocks_per_request(nq: int, nkv: int) -> int:
+    """Blocks the decode kernel starts per request and slice of keys."""
+    return nkv * ((nq // nkv + DECODE_HEADS_PER_BLOCK - 1) // DECODE_HEADS_PER_BLOCK)
+
+
+def decode_plan(kv_lens, window: int, blocks_per_request: int, sms: int) -> tuple[int, int]:
+    """``(slices, chunks per slice)`` for a decode step over requests of these lengths.
+
+    A slice is the same number of 64-key chunks for every request, sized so that all
+    requests together make about two blocks per SM and no slice is shorter than four chunks:
+    a request far longer than the others is cut into many slices while the short ones stay
+    whole, so no block is left with a multiple of the others' work.  For requests of equal
+    length this is ``decode_splits``' answer."""
+    chunks = []
+    for kl in kv_lens:
+        lo = max(0, kl - window) if window else 0
+        chunks.append(max(1, -(-kl // 64) - lo // 64))
+    longest = max(chunks)
+    skewed = longest * len(chunks) > 2 * sum(chunks)
+    per_sm = DECODE_BLOCKS_PER_SM_SKEWED if skewed else DECODE_BLOCKS_PER_SM
+    per = max(4, -(-sum(chunks) * blocks_per_request // (per_sm * sms)))
+    want = max(1, longest // per)
+    n = max(c for c in DECODE_SLICE_COUNTS if c <= want)
+    return n, -(-longest // n)
 
 
 def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq: int, nkv: int,
@@ -388,9 +434,11 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq:
     group = ctx.groups[cache.group]
     if q.dtype == torch.bfloat16:
         if ctx.decode_only:
+            planned = getattr(group, "decode_slices", 0)
             attention_decode(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
                              ctx.q_start, ctx.kv_len, ctx.n_requests, nq, nkv, head_dim, scale, window,
-                             decode_splits(ctx.n_requests, nq, nkv, ctx.max_kv_len, window, q.device))
+                             planned or decode_splits(ctx.n_requests, nq, nkv, ctx.max_kv_len, window, q.device),
+                             slice_chunks=group.decode_slice_chunks if planned else None)
         else:
             tc = USE_TC_PREFILL and prefill_tc_supported(nq, nkv, head_dim, group.page_size)
             tt = (prefill_tc_tile_tokens if tc else prefill_tile_tokens)(nq // nkv)
@@ -435,10 +483,15 @@ def _decode_counters(device: torch.device, n: int) -> torch.Tensor:
 
 
 def attention_decode(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, kv_len,
-                     n_requests, nq, nkv, head_dim, scale, window=0, n_splits=1) -> None:
+                     n_requests, nq, nkv, head_dim, scale, window=0, n_splits=1, slice_chunks=None) -> None:
     """bfloat16 decode attention: one query token per request, keys cut into ``n_splits``
-    slices whose partial results are merged through scratch memory (attention_mma.cu)."""
-    _cuda(q, out, kcache, vcache, block_table, q_start, kv_len)
+    slices whose partial results are merged through scratch memory (attention_mma.cu).
+    ``slice_chunks`` (an int32 tensor of one element on the device, read when the kernel
+    runs) makes every slice that many 64-key chunks for all requests; without it every
+    request's own keys are cut into ``n_splits`` equal slices."""
+    _cuda(q, out, kcache, vcache, block_table, q_start, kv_len, slice_chunks)
+    if slice_chunks is not None and (slice_chunks.dtype != torch.int32 or slice_chunks.numel() < 1):
+        raise KernelError("attention_decode: slice_chunks must be an int32 tensor of one element")
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_decode: bfloat16 only")
     _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, page_size,
@@ -449,11 +502,11 @@ def attention_decode(q, q_stride, out, kcache, vcache, block_table, page_size, q
         part_o = torch.empty((n_requests * nq * n_splits, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n_requests * nq * n_splits, 2), dtype=torch.float32, device=q.device)
         counters = _decode_counters(q.device, lib.mi_attention_decode_counters(int(n_requests), nq, nkv))
-    rc = lib.mi_attention_decode(
+    rc = lib.mi_attention_decode_sliced(
         _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_table),
         block_table.stride(0), int(page_size), _ptr(q_start), _ptr(kv_len), int(n_requests), nq, nkv,
-        head_dim, float(scale), int(window), int(n_splits), _ptr(part_o), _ptr(part_ml), _ptr(counters),
-        _stream())
+        head_dim, float(scale), int(window), int(n_splits), _ptr(slice_chunks), _ptr(part_o), _ptr(part_ml),
+        _ptr(counters), _stream())
     _finish(lib, rc, "attention_decode")
 
 

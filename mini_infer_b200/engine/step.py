@@ -58,7 +58,7 @@ class GraphSlot:
 class StepRunner:
     """``cuda_graph=True`` replays decode-only steps (every request brings one token and
     wants its logits) as captured CUDA graphs, one per (batch size, block-table width
-    bucket); the reference keeps such graphs per batch bucket
+    bucket, number of key slices); the reference keeps such graphs per batch bucket
     (``engine/paged_decode_graph.py:67-225``).  Everything else runs kernel by kernel."""
 
     GRAPH_WIDTH_BUCKET = 64           # block tables of a captured step grow in steps of 64 pages
@@ -72,7 +72,9 @@ class StepRunner:
         self.device = model.device
         self.dtype = model.dtype
         self.vocab_size = model.spec.vocab_size
-        self.tile_sizes = sorted(model.plan_needs().q_tile_tokens)
+        needs = model.plan_needs()
+        self.tile_sizes = sorted(needs.q_tile_tokens)
+        self.decode_blocks_per_request = needs.decode_blocks_per_request
         self.max_positions = model.spec.max_positions
         self.steps_run = 0
         self.last_h2d_bytes = 0
@@ -142,6 +144,15 @@ class StepRunner:
                 flat.extend([-1] * (width - len(t)))
             parts.append((f"table{gi}", flat))
             parts.append((f"slots{gi}", plan.token_slots[gi]))
+        # Decode-only steps of a mixer that cuts keys into slices: how many, and how long
+        # (one int per group on the device, so that a captured step follows the lengths).
+        decode_only = all(n == 1 for n in q_len)
+        slices: list[int] = [0] * len(self.cache.groups)
+        if decode_only and self.decode_blocks_per_request > 0 and self.dtype == torch.bfloat16:
+            for gi, g in enumerate(self.cache.groups):
+                slices[gi], per = ops.decode_plan(kv_len, g.window or 0, self.decode_blocks_per_request,
+                                                  ops.sm_count(self.device))
+                parts.append((f"slice{gi}", [per]))
         tile_counts: dict[int, int] = {}
         for n in self.tile_sizes:
             treq: list[int] = []
@@ -167,7 +178,7 @@ class StepRunner:
                 host_np[o:o + n] = lst
         slot = None
         if graphed:
-            key = (B, tuple(widths))
+            key = (B, tuple(widths), tuple(slices))
             slot = self._graphs.get(key)
             if slot is None:
                 slot = GraphSlot(widths=list(widths),
@@ -188,6 +199,7 @@ class StepRunner:
             groups.append(GroupView(
                 page_size=self.cache.page_size, window=g.window,
                 block_table=view(f"table{gi}").view(B, widths[gi]), slots=view(f"slots{gi}"),
+                decode_slices=slices[gi], decode_slice_chunks=view(f"slice{gi}") if slices[gi] else None,
             ))
         ctx = StepContext(
             dtype=self.dtype, device=self.device, n_tokens=M, n_requests=B,
@@ -196,7 +208,7 @@ class StepRunner:
             host_q_start=q_start, host_q_len=list(q_len), host_kv_len=kv_len,
             host_state_slot=list(plan.state_slots), groups=groups,
             tiles={n: (view(f"tile_req{n}"), view(f"tile_tok{n}"), tile_counts[n]) for n in self.tile_sizes},
-            decode_only=all(n == 1 for n in q_len),
+            decode_only=decode_only,
             # a captured step must not depend on the lengths of the day: it is planned for
             # the longest context its block tables can hold
             max_kv_len=(max(widths) * self.cache.page_size) if graphed else max(kv_len),

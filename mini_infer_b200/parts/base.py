@@ -69,9 +69,14 @@ class PlanNeeds:
 
     ``q_tile_tokens``: for each value n, a list of tiles of at most n consecutive query
     tokens of one request (``StepContext.q_tiles(n)``).
+    ``decode_blocks_per_request``: how many thread blocks a decode step of this mixer starts
+    per request before its keys are cut into slices; a value above zero makes the planner
+    decide the slices of each cache group from the requests' lengths
+    (``GroupView.decode_slices``, ``GroupView.decode_slice_chunks``).
     """
 
     q_tile_tokens: frozenset[int] = frozenset()
+    decode_blocks_per_request: int = 0
 
 
 # ----------------------------------------------------------------------------- step context
@@ -85,6 +90,8 @@ class GroupView:
     window: int | None
     block_table: torch.Tensor          # [requests, max_pages] page ids of this group
     slots: torch.Tensor                # [tokens] flat slot (page * page_size + offset) per new token
+    decode_slices: int = 0             # decode-only steps: slices the keys are cut into (0: not planned)
+    decode_slice_chunks: torch.Tensor | None = None   # [1] int32: 64-key chunks per slice
 
 
 @dataclass

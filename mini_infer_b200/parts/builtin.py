@@ -182,7 +182,8 @@ class GroupedQueryAttention(Mixer):
         return KVNeed(self.nkv, self.d, self.window)
 
     def plan_needs(self):
-        return PlanNeeds(ops.attention_tile_sizes(self.nq // self.nkv))
+        return PlanNeeds(ops.attention_tile_sizes(self.nq // self.nkv),
+                         ops.decode_blocks_per_request(self.nq, self.nkv))
 
     def bind(self, tensors, dtype, device):
         qkv = torch.cat(

@@ -117,9 +117,12 @@ class DecoderModel:
 
     def plan_needs(self) -> PlanNeeds:
         tiles: set[int] = set()
+        decode_blocks = 0
         for b in self.blocks:
-            tiles |= set(b.mixer.plan_needs().q_tile_tokens)
-        return PlanNeeds(frozenset(tiles))
+            needs = b.mixer.plan_needs()
+            tiles |= set(needs.q_tile_tokens)
+            decode_blocks = max(decode_blocks, needs.decode_blocks_per_request)
+        return PlanNeeds(frozenset(tiles), decode_blocks)
 
     # ------------------------------------------------------------------ binding
 

@@ -318,7 +318,7 @@ def as_pages(c, page):
 
 
 def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, boost=None, kernel="generic",
-                  n_splits=1):
+                  n_splits=1, slice_chunks=None):
     o = ops()
     kc, vc, bt, ks, vs = build_paged(kv_lens, nkv, d, page, dtype, seed)
     M = sum(q_lens)
@@ -351,7 +351,8 @@ def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, bo
     else:
         assert all(n == 1 for n in q_lens)
         o.attention_decode(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), page, i32(q_start),
-                           i32(kv_lens), len(q_lens), nq, nkv, d, scale, window, n_splits)
+                           i32(kv_lens), len(q_lens), nq, nkv, d, scale, window, n_splits,
+                           slice_chunks=None if slice_chunks is None else i32([slice_chunks]))
     if kernel != "generic":
         assert o.attention_wait_status() == 0, "a kernel gave up waiting for its copies"
     want = torch.empty(M, nq, d, dtype=torch.float64)
@@ -486,6 +487,21 @@ def test_attention_decode_split_keys(nq, nkv, d, page, n_splits):
     got, want = run_attention([1] * len(kv_lens), kv_lens, nq, nkv, d, page, torch.bfloat16, seed=nq + 7,
                               kernel="decode", n_splits=n_splits)
     assert torch.isfinite(got).all()
+    assert (got - want).abs().max().item() <= BF16_BOUND
+
+
+@pytest.mark.parametrize("n_splits,slice_chunks", [(4, 9), (8, 4), (5, 1), (64, 1), (3, 100), (12, 3)])
+def test_attention_decode_slices_of_one_length(n_splits, slice_chunks):
+    """Slices of the same number of chunks for every request: requests far shorter than the
+    longest fill one slice and leave the others empty; a slice length too short to cover the
+    longest request with the slices at hand is lengthened by the kernel, never obeyed."""
+    kv_lens = [2100, 1, 64, 65, 300, 17, 640]
+    got, want = run_attention([1] * len(kv_lens), kv_lens, 8, 2, 64, 16, torch.bfloat16, seed=31,
+                              kernel="decode", n_splits=n_splits, slice_chunks=slice_chunks)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max().item() <= BF16_BOUND
+    got, want = run_attention([1, 1, 1], [500, 64, 7], 8, 2, 64, 16, torch.bfloat16, window=100, seed=9,
+                              kernel="decode", n_splits=n_splits, slice_chunks=slice_chunks)
     assert (got - want).abs().max().item() <= BF16_BOUND
 
 
