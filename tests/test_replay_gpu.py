@@ -173,3 +173,38 @@ def test_captured_decode_steps_match_plain(which, dtype, model_dirs, plain):
         bad = T.first_bad(got[rid], want[rid], TOL[dtype] * scale)
         assert bad is None, f"{dtype}: request {rid} first differs at position {bad}"
     runner.cache.check()
+
+
+def test_one_long_request_among_short_ones_is_decoded_in_slices(model_dirs):
+    """Decode steps of a batch whose longest request (1,540 tokens) is many times the others
+    (40 and 200): the planner cuts the keys into slices of one length, so the long request
+    fills several and the short ones one; eight captured steps against the plain
+    implementation, in the middle of which the slice length grows."""
+    from mini_infer_b200.engine import ModelRunner
+
+    which, dtype, n_decode = "C", "bfloat16", 8
+    requests = {"long": prompt_ids(which, 1540, salt=7), "short": prompt_ids(which, 40, salt=8),
+                "mid": prompt_ids(which, 200, salt=9)}
+    steps = []
+    for rid, toks in requests.items():
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": toks[:-n_decode], "want": []}], "end": []})
+    for i in range(n_decode):
+        steps.append({"step": len(steps), "end": [],
+                      "entries": [{"id": rid, "tokens": [toks[len(toks) - n_decode + i]], "want": [0]}
+                                  for rid, toks in requests.items()]})
+    steps[-1]["end"] = list(requests)
+    ps = PAGE_SIZE[which]
+    runner = ModelRunner.from_pretrained(model_dirs[which], dtype=dtype, block_size=ps,
+                                         num_blocks=T.max_tokens_needed(steps) // ps, max_requests=4,
+                                         cuda_graph=True)
+    for st in runner.cache.storage:
+        st.fill_(float("nan"))
+    got = T.collect(steps, T.replay_in_process(runner, steps), TINY[which]["vocab_size"])
+    slices = [key[2][0] for key in runner.stepper._graphs]
+    assert slices and min(slices) > 1, f"the long request was not cut into slices: {slices}"
+    want = T.plain_logits(load_state(model_dirs[which]), TINY[which], requests)
+    scale = max(1.0, max(float(np.abs(want[r]).max()) for r in want))
+    for rid in requests:
+        bad = T.first_bad(got[rid], want[rid][-n_decode:], TOL[dtype] * scale)
+        assert bad is None, f"request {rid} first differs at decoded token {bad}"
+    runner.cache.check()
