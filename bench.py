@@ -152,14 +152,11 @@ def build_runner(cfg: dict, layers: int, num_blocks: int, max_requests: int):
     import torch
 
     from mini_infer_b200.engine import ModelRunner
-    from mini_infer_b200.weights import random_state_dict
 
     raw = dict(cfg, num_hidden_layers=layers)
-    state = random_state_dict(raw, seed=0, gain_std=0.0, device="cuda")
-    runner = ModelRunner.from_state_dict(raw, state, device="cuda:0", dtype="bfloat16",
-                                         num_blocks=num_blocks, block_size=PAGE, max_requests=max_requests,
-                                         cuda_graph=True)
-    del state
+    runner = ModelRunner.from_random(raw, seed=0, gain_std=0.0, device="cuda:0", dtype="bfloat16",
+                                     num_blocks=num_blocks, block_size=PAGE, max_requests=max_requests,
+                                     cuda_graph=True)
     torch.cuda.empty_cache()
     return runner
 

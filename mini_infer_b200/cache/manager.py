@@ -17,6 +17,13 @@ for all requests of the step at once, before anything is launched: either every 
 there and the plan is returned, or ``OutOfPages`` is raised and nothing has changed.
 ``free_request`` returns everything.
 
+*Block tables on the device.*  Each group has one int32 table ``[max_requests, table_width]``
+on the device, a row per request slot.  The host keeps the authoritative tables; a plan
+records only the pages it has just handed out as ``(slot, index, page)`` triples, which the
+step uploads with its descriptors and scatters into the device table before its first kernel
+reads it.  What a step sends to the device therefore does not grow with the context.  Entries
+of pages that a window has given back are left as they are: no kernel looks below a window.
+
 *State slots.*  A mixer with a per-request state of fixed size gets an arena
 ``[max_requests, *shape]`` per cache layer; a request's row is its slot, zeroed on
 admission.  Llama has no such state; the arena exists for mixers that do.
@@ -100,7 +107,6 @@ class AppendPlan:
     start: list[int]                     # tokens held before the step, per request
     counts: list[int]                    # new tokens per request
     token_slots: list[list[int]]         # per group: flat slot of every new token (all requests)
-    tables: list[list[list[int]]]        # per group: per request: page ids (with -1)
 
 
 def group_needs(needs: Sequence) -> list[GroupSpec]:
@@ -128,6 +134,7 @@ class CacheManager:
         max_requests: int,
         dtype: torch.dtype = torch.bfloat16,
         device: torch.device | str | None = None,
+        max_request_tokens: int | None = None,
     ) -> None:
         if page_size <= 0:
             raise CacheError(f"page size must be positive, got {page_size}")
@@ -146,6 +153,7 @@ class CacheManager:
             if len(pages) != len(self.groups):
                 raise CacheError(f"{len(self.groups)} groups but {len(pages)} page counts")
         self.pools = [PagePool(n) for n in pages]
+        self._windowed = [gi for gi, g in enumerate(self.groups) if g.window is not None]
         self._requests: dict[Hashable, _Request] = {}
         self._free_slots = list(range(max_requests - 1, -1, -1))
 
@@ -155,14 +163,28 @@ class CacheManager:
             for li, layer in enumerate(g.layers):
                 self.layer_place[layer] = (gi, li)
 
+        # Width of a request's block table: no request holds more pages than its group's pool
+        # has, nor more than the longest sequence the caller allows.
+        # (A windowed group hands pages back, so its requests may be longer than its pool: its
+        # tables are as wide as the longest sequence, 65,536 pages when the caller names none.)
+        cap = None if max_request_tokens is None else -(-int(max_request_tokens) // page_size)
+        self.table_width = []
+        for g, n in zip(self.groups, pages):
+            widest = n if g.window is None else max(n, 65536 if cap is None else cap)
+            self.table_width.append(max(1, widest if cap is None else min(widest, cap)))
+        # pages handed out since the last take_table_updates(): flat (slot, index, page) triples
+        self._table_updates: list[list[int]] = [[] for _ in self.groups]
+
         self.storage: list[torch.Tensor] = []
+        self.block_tables: list[torch.Tensor] = []
         self.state_arenas: dict[int, torch.Tensor] = {}
         if self.device is not None:
-            for g, n in zip(self.groups, pages):
+            for g, n, width in zip(self.groups, pages, self.table_width):
                 self.storage.append(
                     torch.zeros((len(g.layers), 2, n, g.kv_heads, page_size, g.head_dim),
                                 dtype=dtype, device=self.device)
                 )
+                self.block_tables.append(torch.full((max_requests, width), -1, dtype=torch.int32, device=self.device))
             for need in self.needs:
                 if need.state is not None:
                     self.state_arenas[need.index] = torch.zeros(
@@ -188,6 +210,19 @@ class CacheManager:
 
     def slot(self, rid: Hashable) -> int:
         return self._get(rid).slot
+
+    def table(self, rid: Hashable, group: int = 0) -> list[int]:
+        """A copy of a request's block table in ``group`` (page ids; -1 where a window gave
+        the page back)."""
+        return list(self._get(rid).tables[group])
+
+    def take_table_updates(self) -> list[list[int]]:
+        """Per group, the ``(slot, index, page)`` triples (flat) of every page handed out since
+        the last call, in the order they were handed out.  Whoever runs steps on the device
+        must scatter them into ``block_tables`` before the step's kernels run."""
+        out = self._table_updates
+        self._table_updates = [[] for _ in self.groups]
+        return out
 
     def _get(self, rid: Hashable) -> _Request:
         try:
@@ -237,12 +272,11 @@ class CacheManager:
         need = [0] * len(self.groups)
         for rid, n_new in entries:
             req = self._get(rid)
-            total = req.length + n_new
-            for gi in range(len(self.groups)):
-                have = len(req.tables[gi])
-                want = -(-total // self.page_size)
-                back = max(0, self._window_release_count(gi, req.length) - req.released[gi])
-                need[gi] += max(0, want - have) - back
+            want = -(-(req.length + n_new) // self.page_size)
+            for gi, g in enumerate(self.groups):
+                need[gi] += max(0, want - len(req.tables[gi]))
+                if g.window is not None:
+                    need[gi] -= max(0, self._window_release_count(gi, req.length) - req.released[gi])
         return need
 
     def can_append(self, entries: Iterable[tuple[Hashable, int]]) -> bool:
@@ -265,13 +299,21 @@ class CacheManager:
                 raise OutOfPages(
                     f"group {gi} needs {n} more pages, {pool.num_free} of {pool.num_pages} are free"
                 )
-        plan = AppendPlan([], [], [], [], [[] for _ in self.groups], [[] for _ in self.groups])
+        room = min(self.table_width, default=0) * self.page_size
+        for rid, n_new in entries:
+            if self.groups and self._requests[rid].length + n_new > room:
+                raise CacheError(
+                    f"request {rid!r} would hold {self._requests[rid].length + n_new} tokens; a block table "
+                    f"takes {room}"
+                )
+        plan = AppendPlan([], [], [], [], [[] for _ in self.groups])
         ps = self.page_size
         # pages that have fallen out of a window go back first, for every request of the
         # step, so that the allocations below may use them
-        for rid, _ in entries:
+        for rid, _ in entries if self._windowed else ():
             req = self._requests[rid]
-            for gi, pool in enumerate(self.pools):
+            for gi in self._windowed:
+                pool = self.pools[gi]
                 table = req.tables[gi]
                 upto = min(self._window_release_count(gi, req.length), len(table))
                 for idx in range(req.released[gi], upto):
@@ -288,12 +330,17 @@ class CacheManager:
             plan.counts.append(n_new)
             for gi, pool in enumerate(self.pools):
                 table = req.tables[gi]
+                updates = self._table_updates[gi]
                 while len(table) * ps < total:
-                    table.append(pool.allocate())
+                    page = pool.allocate()
+                    updates.extend((req.slot, len(table), page))
+                    table.append(page)
                 slots = plan.token_slots[gi]
-                for p in range(start, total):
-                    slots.append(table[p // ps] * ps + p % ps)
-                plan.tables[gi].append(list(table))
+                if n_new == 1:
+                    slots.append(table[start // ps] * ps + start % ps)
+                else:
+                    for p in range(start, total):
+                        slots.append(table[p // ps] * ps + p % ps)
             req.length = total
         return plan
 

@@ -25,59 +25,77 @@ from typing import Any, Mapping
 from .registry import ConfigError
 
 
+LLAMA3_FIELDS = (
+    ("factor", float),
+    ("low_freq_factor", float),
+    ("high_freq_factor", float),
+    ("original_max_position_embeddings", int),
+)
+
+
 @dataclass(frozen=True)
 class Llama3RopeScaling:
-    """The ``rope_type: "llama3"`` frequency rescale (reference
-    ``models/blocks/rope.py:171-197``)."""
+    """The four numbers of a ``"llama3"`` rotary rescale: frequencies whose wavelength is
+    longer than ``original_max_position_embeddings / low_freq_factor`` are divided by
+    ``factor``, those shorter than ``... / high_freq_factor`` are kept, the band between is
+    blended (what the numbers mean: reference ``models/blocks/rope.py:200-225``)."""
 
     factor: float
     low_freq_factor: float
     high_freq_factor: float
     original_max_position_embeddings: int
 
-    def __post_init__(self) -> None:
+    def problems(self) -> list[str]:
+        """Why these numbers cannot describe a rescale (empty: they can)."""
+        found = []
         if not self.factor > 0:
-            raise ConfigError(f"llama3 rope factor must be positive, got {self.factor}")
-        if not self.high_freq_factor > self.low_freq_factor:
-            raise ConfigError(
-                "llama3 rope needs high_freq_factor > low_freq_factor, got "
-                f"{self.high_freq_factor} <= {self.low_freq_factor}"
-            )
+            found.append(f"factor={self.factor} is not positive")
+        if not self.low_freq_factor < self.high_freq_factor:
+            found.append(f"low_freq_factor={self.low_freq_factor} is not below "
+                         f"high_freq_factor={self.high_freq_factor}")
         if not self.original_max_position_embeddings > 0:
-            raise ConfigError(
-                "llama3 rope original_max_position_embeddings must be positive, got "
-                f"{self.original_max_position_embeddings}"
-            )
+            found.append(f"original_max_position_embeddings={self.original_max_position_embeddings} "
+                         "is not positive")
+        return found
+
+    def __post_init__(self) -> None:
+        found = self.problems()
+        if found:
+            raise ConfigError("bad llama3 rope scaling: " + "; ".join(found))
+
+
+def _llama3_from(section: Mapping[str, Any]) -> Llama3RopeScaling:
+    absent = [key for key, _ in LLAMA3_FIELDS if section.get(key) is None]
+    if absent:
+        raise ConfigError(f"a llama3 rope scaling needs {', '.join(absent)}; config.json gives only "
+                          f"{', '.join(sorted(section)) or 'nothing'}")
+    return Llama3RopeScaling(**{key: kind(section[key]) for key, kind in LLAMA3_FIELDS})
+
+
+# rope type (as config.json spells it) -> how its section becomes a scaling (None: no rescale)
+ROPE_TYPES = {
+    "default": lambda section: None,
+    "llama3": _llama3_from,
+}
 
 
 def read_rope_parameters(raw: Mapping[str, Any]) -> tuple[float, Llama3RopeScaling | None]:
-    """``(rope_theta, llama3 scaling or None)`` from raw ``config.json`` keys."""
-    params = raw.get("rope_parameters") or raw.get("rope_scaling") or {}
-    if not isinstance(params, Mapping):
-        raise ConfigError(f"rope_scaling must be an object, got {params!r}")
-    if "rope_theta" in params:
-        theta = float(params["rope_theta"])
-    else:
-        theta = float(raw.get("rope_theta") or 10000.0)
-    rope_type = params.get("rope_type") or params.get("type") or "default"
-    if rope_type == "default":
-        return theta, None
-    if rope_type == "llama3":
-        try:
-            scaling = Llama3RopeScaling(
-                factor=float(params["factor"]),
-                low_freq_factor=float(params["low_freq_factor"]),
-                high_freq_factor=float(params["high_freq_factor"]),
-                original_max_position_embeddings=int(params["original_max_position_embeddings"]),
-            )
-        except KeyError as missing:
-            raise ConfigError(
-                f"llama3 rope parameters are missing {missing}; got {sorted(params)}"
-            ) from None
-        return theta, scaling
-    raise NotImplementedError(
-        f"rope_type={rope_type!r} is not supported; only 'default' and 'llama3' are"
-    )
+    """``(rope_theta, scaling or None)``.  The rotary settings sit in a section named
+    ``rope_parameters`` (newer files) or ``rope_scaling``; its type is spelled ``rope_type`` or
+    ``type``; ``rope_theta`` may sit inside the section or at the top level (the reference
+    reads the same places, ``models/blocks/rope.py:228-269``)."""
+    section: Any = {}
+    for name in ("rope_parameters", "rope_scaling"):
+        if raw.get(name):
+            section = raw[name]
+            break
+    if not isinstance(section, Mapping):
+        raise ConfigError(f"the rope section of config.json must be an object, got {section!r}")
+    theta = section.get("rope_theta", raw.get("rope_theta"))
+    kind = section.get("rope_type") or section.get("type") or "default"
+    if kind not in ROPE_TYPES:
+        raise NotImplementedError(f"rope type {kind!r}: this engine knows {sorted(ROPE_TYPES)}")
+    return float(theta or 10000.0), ROPE_TYPES[kind](section)
 
 
 def _required(raw: Mapping[str, Any], key: str, kind: type):

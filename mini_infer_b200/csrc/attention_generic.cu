@@ -14,7 +14,8 @@
 //   kcache, vcache [pages, nkv, page_size, d]: the page_size keys of a page lie together
 //                  per key/value head; the 16-byte chunks of a row are permuted by the key's
 //                  in-page offset (mi_swizzled in common.cuh)
-//   block_table [requests, bt_stride] page ids;  q_start / q_len / kv_len [requests]
+//   block_table [rows, bt_stride] page ids; request b uses row table_rows[b] (row b when
+//                  table_rows is null);  q_start / q_len / kv_len [requests]
 //   tile_req / tile_tok0 [tiles]: request and first token (within the portion) of a tile
 #include "common.cuh"
 
@@ -28,7 +29,8 @@ template <typename T, int DMAX>
 __global__ void __launch_bounds__(NTHREADS)
 attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
                          const T* __restrict__ kcache, const T* __restrict__ vcache,
-                         const int* __restrict__ block_table, int bt_stride, int page_size,
+                         const int* __restrict__ block_table, int bt_stride,
+                         const int* __restrict__ table_rows, int page_size,
                          const int* __restrict__ q_start, const int* __restrict__ q_len,
                          const int* __restrict__ kv_len, const int* __restrict__ tile_req,
                          const int* __restrict__ tile_tok0, int nq, int nkv, int d, float scale,
@@ -49,6 +51,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   const int kvh = h / (nq / nkv);
   const int b = tile_req[tile], tok0 = tile_tok0[tile];
   const int ql = q_len[b], kl = kv_len[b], qs = q_start[b];
+  const int trow = table_rows ? table_rows[b] : b;   // the request's row of the block table
   const int rows = min(BQ, ql - tok0);
   const int p0 = kl - ql + tok0;  // absolute position of the tile's first query
   const int j_end = p0 + rows;    // one past the last visible key
@@ -75,7 +78,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
       const int j = j0 + tid;
       int base = -1;
       if (j >= j_lo && j < j_end) {
-        const int page = block_table[(size_t)b * bt_stride + j / page_size];
+        const int page = block_table[(size_t)trow * bt_stride + j / page_size];
         base = (page * nkv + kvh) * page_size + j % page_size;
       }
       rowbase[tid] = base;
@@ -159,7 +162,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 
 template <typename T, int DMAX>
 static int launch(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
-                  const void* vcache, const int* block_table, int bt_stride, int page_size,
+                  const void* vcache, const int* block_table, int bt_stride, const int* table_rows, int page_size,
                   const int* q_start, const int* q_len, const int* kv_len, const int* tile_req,
                   const int* tile_tok0, int n_tiles, int nq, int nkv, int d, float scale, int window,
                   cudaStream_t stream) {
@@ -172,7 +175,7 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
   }
   dim3 grid(n_tiles, nq);
   MI_LAUNCH((kern), grid, NTHREADS, smem, stream, (const T*)q, q_stride, (T*)out, out_stride, (const T*)kcache,
-                                         (const T*)vcache, block_table, bt_stride, page_size, q_start,
+                                         (const T*)vcache, block_table, bt_stride, table_rows, page_size, q_start,
                                          q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, scale, window);
   return 0;
 }
@@ -181,7 +184,7 @@ extern "C" int mi_attention_generic_tile_tokens() { return BQ; }
 
 extern "C" int mi_attention_generic(const void* q, int q_stride, void* out, int out_stride,
                                     const void* kcache, const void* vcache, const int* block_table,
-                                    int bt_stride, int page_size, const int* q_start,
+                                    int bt_stride, const int* table_rows, int page_size, const int* q_start,
                                     const int* q_len, const int* kv_len, const int* tile_req,
                                     const int* tile_tok0, int n_tiles, int nq, int nkv, int d,
                                     float scale, int window, int dtype, cudaStream_t stream) {
@@ -196,7 +199,7 @@ extern "C" int mi_attention_generic(const void* q, int q_stride, void* out, int 
   int rc;
 #define MI_GO(T, DMAX)                                                                              \
   rc = launch<T, DMAX>(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride,        \
-                       page_size, q_start, q_len, kv_len, tile_req, tile_tok0, n_tiles, nq, nkv, d, \
+                       table_rows, page_size, q_start, q_len, kv_len, tile_req, tile_tok0, n_tiles, nq, nkv, d, \
                        scale, window, stream)
   if (dtype == MI_DTYPE_F32) {
     if (d <= 64) MI_GO(float, 64);

@@ -309,7 +309,8 @@ template <int DMAX>
 __global__ void __launch_bounds__(DEC_THREADS)
 attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                         const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
-                        const int* __restrict__ block_table, int bt_stride, int page_size, int page_shift,
+                        const int* __restrict__ block_table, int bt_stride, const int* __restrict__ table_rows,
+                        int page_size, int page_shift,
                         const int* __restrict__ q_start, const int* __restrict__ kv_len, int nq, int nkv,
                         int d, float scale, int window, int n_splits, const int* __restrict__ slice_chunks,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
@@ -348,11 +349,16 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
   const int c1 = min(c_end, c0 + per_split);
   const int heads_here = min(DEC_HEADS, g - hb * DEC_HEADS);
   const int head0 = kvh * g + hb * DEC_HEADS;
-  const int* table = block_table + (size_t)b * bt_stride;
+  const int* table = block_table + (size_t)(table_rows ? table_rows[b] : b) * bt_stride;
 
   if (status && *reinterpret_cast<volatile int*>(status)) return;   // an earlier block gave up waiting
-  if (c0 >= c1) {  // nothing for this split (only possible with n_splits > 1)
+  if (c0 >= c1) {  // nothing for this slice: the request is shorter than the slices before it, or empty
     mi_pdl_wait();
+    if (n_splits == 1) {   // a request that holds no key at all: its output rows are zero, no scratch exists
+      bf16* orow = out + (size_t)tok * out_stride + (size_t)head0 * d;
+      for (int k = tid; k < heads_here * d; k += DEC_THREADS) orow[k] = __float2bfloat16_rn(0.f);
+      return;
+    }
     for (int r = tid; r < heads_here; r += DEC_THREADS) {
       float* ml = part_ml + ((size_t)(b * nq + head0 + r) * n_splits + split) * 2;
       ml[0] = -INFINITY;
@@ -608,7 +614,8 @@ template <int DMAX>
 __global__ void __launch_bounds__(PrefillShape<DMAX>::THREADS, PrefillShape<DMAX>::BLOCKS_PER_SM)
 attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                          const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
-                         const int* __restrict__ block_table, int bt_stride, int page_size, int page_shift,
+                         const int* __restrict__ block_table, int bt_stride, const int* __restrict__ table_rows,
+                        int page_size, int page_shift,
                          const int* __restrict__ q_start, const int* __restrict__ q_len,
                          const int* __restrict__ kv_len, const int* __restrict__ tile_req,
                          const int* __restrict__ tile_tok0, int nq, int nkv, int d, float scale, int window,
@@ -639,7 +646,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   const int hi = p_first + ntok;  // one past the last key any row of the tile sees
   const int lo = window > 0 ? max(0, p_first - window + 1) : 0;
   const int heads_here = min(gb, g - hb * gb);
-  const int* table = block_table + (size_t)b * bt_stride;
+  const int* table = block_table + (size_t)(table_rows ? table_rows[b] : b) * bt_stride;
 
   if (status && *reinterpret_cast<volatile int*>(status)) return;   // an earlier block gave up waiting
   // row R of the tile: token tok0 + R / gb, head kvh * g + hb * gb + R % gb
@@ -890,9 +897,14 @@ static __device__ int g_wait_status;
 #define MI_MAX_DEVICES 64
 static int* g_wait_status_ptr[MI_MAX_DEVICES];
 
+// A word the host shares among its kernel libraries (mi_set_status_word), per device; null:
+// this library's own word above.
+static int* g_status_word_host[MI_MAX_DEVICES];
+
 static int* wait_status_ptr() {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MI_MAX_DEVICES) return nullptr;
+  if (g_status_word_host[dev]) return g_status_word_host[dev];
   if (!g_wait_status_ptr[dev]) {
     int* p = nullptr;
     if (cudaGetSymbolAddress((void**)&p, g_wait_status) != cudaSuccess) return nullptr;
@@ -901,14 +913,21 @@ static int* wait_status_ptr() {
   return g_wait_status_ptr[dev];
 }
 
+// Report give-ups of this library's kernels on the current device into `device_word` (an int in
+// device memory that the caller owns and keeps alive; null: back to the library's own word).
+extern "C" int mi_set_status_word(int* device_word) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MI_MAX_DEVICES) MI_REFUSE("status word: bad device");
+  g_status_word_host[dev] = device_word;
+  return 0;
+}
+
 // 1 if a kernel of this library gave up waiting for a copy since the last reset (synchronises).
 extern "C" int mi_attention_wait_status(int reset) {
   int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_wait_status, sizeof(int)) != cudaSuccess) return -1;
-  if (reset && v) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_wait_status, &zero, sizeof(int));
-  }
+  int* word = wait_status_ptr();
+  if (!word || cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (reset && v) cudaMemset(word, 0, sizeof(int));
   return v;
 }
 
@@ -937,7 +956,8 @@ extern "C" int mi_attention_decode_counters(int B, int nq, int nkv) {
 // own span into n_splits equal slices.
 extern "C" int mi_attention_decode_sliced(const void* q, int q_stride, void* out, int out_stride,
                                           const void* kcache, const void* vcache, const int* block_table,
-                                          int bt_stride, int page_size, const int* q_start, const int* kv_len,
+                                          int bt_stride, const int* table_rows, int page_size, const int* q_start,
+                                          const int* kv_len,
                                           int B, int nq, int nkv, int d, float scale, int window, int n_splits,
                                           const int* slice_chunks, float* part_o, float* part_ml, int* counters,
                                           cudaStream_t stream) {
@@ -946,6 +966,9 @@ extern "C" int mi_attention_decode_sliced(const void* q, int q_stride, void* out
   if (n_splits < 1 || n_splits > 64) MI_REFUSE("attention: n_splits must be in [1, 64], got %d", n_splits);
   const int page_shift = shift_of(page_size);
   if (n_splits > 1 && (!part_o || !part_ml || !counters)) MI_REFUSE("attention: split results need scratch memory");
+  // the merge reads (max, sum) pairs as one 8-byte load
+  if (n_splits > 1 && (!mi_aligned(part_o, 4) || !mi_aligned(part_ml, 8) || !mi_aligned(counters, 4)))
+    MI_REFUSE("attention: scratch must be aligned (part_o and counters to 4 bytes, part_ml to 8)");
   const int g = nq / nkv, hblocks = (g + DEC_HEADS - 1) / DEC_HEADS;
   if (B > 65535 || nkv * hblocks > 65535) MI_REFUSE("attention: batch or head count too large for one launch");
   const size_t smem = (size_t)(2 * DEC_STAGES * KCHUNK) * d * sizeof(bf16);
@@ -959,7 +982,7 @@ extern "C" int mi_attention_decode_sliced(const void* q, int q_stride, void* out
     }                                                                                                   \
     MI_LAUNCH((kern), grid, DEC_THREADS, smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,         \
                                            (const bf16*)kcache, (const bf16*)vcache, block_table,       \
-                                           bt_stride, page_size, page_shift, q_start, kv_len, nq, nkv,  \
+                                           bt_stride, table_rows, page_size, page_shift, q_start, kv_len, nq, nkv,  \
                                            d, scale, window, n_splits, slice_chunks, part_o, part_ml,   \
                                            counters, wait_status_ptr());                                \
   } while (0)
@@ -975,7 +998,7 @@ extern "C" int mi_attention_decode(const void* q, int q_stride, void* out, int o
                                    const int* q_start, const int* kv_len, int B, int nq, int nkv, int d,
                                    float scale, int window, int n_splits, float* part_o, float* part_ml,
                                    int* counters, cudaStream_t stream) {
-  return mi_attention_decode_sliced(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride, page_size,
+  return mi_attention_decode_sliced(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride, nullptr, page_size,
                                     q_start, kv_len, B, nq, nkv, d, scale, window, n_splits, nullptr, part_o,
                                     part_ml, counters, stream);
 }
@@ -987,8 +1010,8 @@ extern "C" int mi_attention_prefill_tile_tokens(int g) {
 }
 
 extern "C" int mi_attention_prefill(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
-                                    const void* vcache, const int* block_table, int bt_stride, int page_size,
-                                    const int* q_start, const int* q_len, const int* kv_len,
+                                    const void* vcache, const int* block_table, int bt_stride, const int* table_rows,
+                                    int page_size, const int* q_start, const int* q_len, const int* kv_len,
                                     const int* tile_req, const int* tile_tok0, int n_tiles, int tile_tokens,
                                     int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
@@ -1011,7 +1034,7 @@ extern "C" int mi_attention_prefill(const void* q, int q_stride, void* out, int 
     }                                                                                                   \
     MI_LAUNCH((kern), grid, PrefillShape<DMAX>::THREADS, smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, \
                                            (const bf16*)kcache, (const bf16*)vcache, block_table,       \
-                                           bt_stride, page_size, page_shift, q_start, q_len, kv_len,    \
+                                           bt_stride, table_rows, page_size, page_shift, q_start, q_len, kv_len,    \
                                            tile_req, tile_tok0, nq, nkv, d, scale, window, gb,          \
                                            PROWS / gb, wait_status_ptr());                              \
   } while (0)
@@ -1044,7 +1067,10 @@ extern "C" int mi_attention_decode_noalloc(const void* q, int q_stride, void* ou
   if (B <= 0) return 0;
   if (nq <= 0 || d <= 0 || n_splits < 1) MI_REFUSE("attention (no allocation): bad sizes");
   const size_t slots = (size_t)B * nq * n_splits;
-  const size_t n_counters = (size_t)mi_attention_decode_counters(B, nq, nkv > 0 ? nkv : 1);
+  // The arrival counters come first, rounded up to a multiple of four (16 bytes), so that the
+  // partial results behind them start on a 16-byte boundary and the (max, sum) pairs behind
+  // those (slots * d floats further, d a multiple of 16) on an 8-byte one.
+  const size_t n_counters = ((size_t)mi_attention_decode_counters(B, nq, nkv > 0 ? nkv : 1) + 3) & ~(size_t)3;
   const size_t need = slots * ((size_t)d + 2) + n_counters;
   if (need > (size_t)MI_ATTENTION_NOALLOC_MAX_FLOATS)
     MI_REFUSE("attention (no allocation): %zu floats of scratch needed (B=%d, heads=%d, slices=%d, head size=%d), "
@@ -1066,8 +1092,8 @@ extern "C" int mi_attention_decode_noalloc(const void* q, int q_stride, void* ou
     }
     g_noalloc_device_ptr[dev] = p;
   }
-  // the arrival counters come first and must be zero when the kernel starts; the array keeps
-  // whatever the last call left (a call that was cut short could leave a count behind)
+  // the arrival counters must be zero when the kernel starts; the array keeps whatever the
+  // last call left (a call that was cut short could leave a count behind)
   int* counters = reinterpret_cast<int*>(g_noalloc_device_ptr[dev]);
   float* part_o = g_noalloc_device_ptr[dev] + n_counters;
   float* part_ml = part_o + slots * (size_t)d;

@@ -11,8 +11,9 @@
 // The scratch is one file-scope `static __device__` array of
 // MI_ATTENTION_NOALLOC_MAX_FLOATS floats (4 MiB).  Every GPU on which the library is loaded
 // holds that array until the process exits.  A call needs B * nq * n_splits * (d + 2) floats
-// of it plus one arrival counter per (request, group of 8 query heads), and is refused, with a
-// message, when that is more than the array holds.
+// of it plus one arrival counter per (request, key/value head, group of 8 query heads), the
+// counters rounded up to a multiple of four so that everything behind them stays aligned, and
+// is refused, with a message, when that is more than the array holds.
 //
 // What a caller has to know:
 //   * The first call on a device looks up the array's device address (with that device

@@ -34,6 +34,12 @@ MI_DEFINE_ERROR_API()
 #define RESCALE_LOG2 8.0f   // how far (in powers of two) a score may exceed the running reference before O is rescaled
 
 static __device__ int g_tc_status;
+// Where a give-up is reported: this library's own word above, or a word the host shares among
+// its kernel libraries (mi_set_status_word) so that one small copy per step tells it about all.
+static __device__ int* g_status_word;
+#define MI_MAX_DEVICES 64
+static int* g_status_word_host[MI_MAX_DEVICES];
+__device__ __forceinline__ void report_give_up() { atomicExch(g_status_word ? g_status_word : &g_tc_status, 1); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
@@ -59,7 +65,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 1023) == 1023 && *give_up) return false;   // another role of this block gave up
   }
-  atomicExch(&g_tc_status, 1);
+  report_give_up();
   *give_up = 1;
   return false;
 }
@@ -177,7 +183,8 @@ enum {
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
-                            const int* __restrict__ block_table, int bt_stride, int page_size, int page_shift,
+                            const int* __restrict__ block_table, int bt_stride, const int* __restrict__ table_rows,
+                            int page_size, int page_shift,
                             const int* __restrict__ q_start, const int* __restrict__ q_len,
                             const int* __restrict__ kv_len, const int* __restrict__ tile_req,
                             const int* __restrict__ tile_tok0, int nq, int nkv, int d, float scale, int window,
@@ -254,7 +261,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     // as its scores are computed, a value stage only after the second product: the two rings
     // run independently, each as far ahead as its own stages allow.
     const bool is_v = warp == 10;
-    const int* table = block_table + (size_t)b * bt_stride;
+    const int* table = block_table + (size_t)(table_rows ? table_rows[b] : b) * bt_stride;
     const int ppc = KC >> page_shift;   // pages per chunk
     const CUtensorMap* map = is_v ? &map_v : &map_k;
     unsigned char* ring = is_v ? Vs : Ks;
@@ -509,13 +516,25 @@ static bool make_cache_map(CUtensorMap* map, const void* base, long long rows, i
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Report give-ups of this library's kernels on the current device into `device_word` (an int in
+// device memory that the caller owns and keeps alive; null: back to the library's own word).
+extern "C" int mi_set_status_word(int* device_word) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MI_MAX_DEVICES) MI_REFUSE("status word: bad device");
+  cudaError_t e = cudaMemcpyToSymbol(g_status_word, &device_word, sizeof(int*));
+  if (e != cudaSuccess) return (int)e;
+  g_status_word_host[dev] = device_word;
+  return 0;
+}
+
+// Non-zero when a block gave up a bounded wait since the last reset (synchronises the device).
 extern "C" int mi_attention_tc_status(int reset) {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
-  if (reset && v) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
-  }
+  int dev = -1, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MI_MAX_DEVICES) return -1;
+  int* word = g_status_word_host[dev];
+  if (!word && cudaGetSymbolAddress((void**)&word, g_tc_status) != cudaSuccess) return -1;
+  if (cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (reset && v) cudaMemset(word, 0, sizeof(int));
   return v;
 }
 
@@ -539,7 +558,7 @@ extern "C" int mi_attention_prefill_tc_tile_tokens(int g) {
 // cache; tiles are mi_attention_prefill_tc_tile_tokens(g) tokens.
 extern "C" int mi_attention_prefill_tc(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
                                        const void* vcache, long long n_pages, const int* block_table, int bt_stride,
-                                       int page_size, const int* q_start, const int* q_len, const int* kv_len,
+                                       const int* table_rows, int page_size, const int* q_start, const int* q_len, const int* kv_len,
                                        const int* tile_req, const int* tile_tok0, int n_tiles, int tile_tokens,
                                        int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
@@ -568,7 +587,7 @@ extern "C" int mi_attention_prefill_tc(const void* q, int q_stride, void* out, i
   if (e != cudaSuccess) return (int)e;
   dim3 grid(n_tiles, nkv * hblocks);
   MI_LAUNCH((kern), grid, TC_THREADS, smem, stream, map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride,
-            block_table, bt_stride, page_size, page_shift, q_start, q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, scale,
+            block_table, bt_stride, table_rows, page_size, page_shift, q_start, q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, scale,
             window, gb, NTILE * ROWS / gb);
   MI_RETURN_LAUNCH_STATUS();
 }

@@ -36,7 +36,6 @@ LIBRARIES: dict[str, tuple[list[str], list[str], list[str]]] = {
     "attention_generic": (["attention_generic.cu"], ["common.cuh"], []),
     "sampling": (["sampling.cu"], ["common.cuh"], []),
     "attention_mma": (["attention_mma.cu"], ["common.cuh", "attention_noalloc.h"], []),
-    "gemm_skinny": (["gemm_skinny.cu"], ["common.cuh"], []),
     "gemm_tma": (["gemm_tma.cu"], ["common.cuh"], []),
     "attention_tc": (["attention_tc.cu"], ["common.cuh"], []),
 }
@@ -164,6 +163,13 @@ def compile_library(name: str, *, force: bool = False, verbose: bool = True) -> 
                     pass
                 raise KernelBuildError(f"nvcc failed for {name} (exit {proc.returncode}):\n{output}")
             os.replace(tmp, out)
+            # builds of older versions of the sources are of no use any more
+            for stale in os.listdir(os.path.dirname(out)):
+                if stale.startswith(f"libmi_{name}_") and stale.endswith(".so") and stale != os.path.basename(out):
+                    try:
+                        os.unlink(os.path.join(os.path.dirname(out), stale))
+                    except OSError:
+                        pass
             if verbose:
                 _say(f"compiled {name} in {time.time() - t0:.1f} s")
             return out

@@ -1,5 +1,6 @@
 // Row-wise kernels of the decoder: token embedding, (residual add +) RMS norm,
-// rotary position encoding fused with the key/value page write, SiLU-and-multiply.
+// rotary position encoding fused with the key/value page write, SiLU-and-multiply; and the
+// scatter of new page ids into the block tables.
 //
 // All arithmetic is fp32; T is the storage type of activations (float or bf16).
 // The residual stream is always stored in fp32.  Each kernel accepts any width;
@@ -52,6 +53,38 @@ extern "C" int mi_embedding(const void* table, const int* ids, void* out, int M,
   } else {
     MI_REFUSE("embedding: unknown dtype %d", dtype);
   }
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------
+// Block-table updates: table[slot, index] = page for each of *count triples (slot, index,
+// page) in `updates` (at most `capacity` of them; a negative slot is skipped).  A step runs
+// this before its first kernel, with the pages the host has just handed out.
+//
+// Kernels further down the stream may read the block tables before they wait for the
+// kernels ahead of them (decode attention starts its copies early), so this kernel lets its
+// dependents start only when its writes are done and visible, not at its beginning as the
+// other kernels do.
+// ---------------------------------------------------------------------------
+__global__ void table_update_kernel(int* __restrict__ table, int stride, int rows,
+                                    const int* __restrict__ updates, const int* __restrict__ count,
+                                    int capacity) {
+  mi_pdl_wait();
+  const int n = min(*count, capacity);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int slot = updates[3 * i], index = updates[3 * i + 1];
+    if (slot >= 0 && slot < rows && index >= 0 && index < stride) table[(size_t)slot * stride + index] = updates[3 * i + 2];
+  }
+  __threadfence();
+  __syncthreads();
+  mi_pdl_launch_dependents();
+}
+
+extern "C" int mi_table_update(int* table, int stride, int rows, const int* updates, const int* count,
+                               int capacity, cudaStream_t stream) {
+  if (capacity <= 0) return 0;
+  if (stride <= 0 || rows <= 0) MI_REFUSE("table_update: bad table shape %d x %d", rows, stride);
+  MI_LAUNCH((table_update_kernel), 1, 256, 0, stream, table, stride, rows, updates, count, capacity);
   MI_RETURN_LAUNCH_STATUS();
 }
 

@@ -42,6 +42,12 @@ MI_DEFINE_ERROR_API()
 #define SPIN_LIMIT (1 << 22)
 
 static __device__ int g_gemm_tma_status;
+// Where a give-up is reported: this library's own word above, or a word the host shares among
+// its kernel libraries (mi_set_status_word) so that one small copy per step tells it about all.
+static __device__ int* g_status_word;
+#define MI_MAX_DEVICES 64
+static int* g_status_word_host[MI_MAX_DEVICES];
+__device__ __forceinline__ void report_give_up() { atomicExch(g_status_word ? g_status_word : &g_gemm_tma_status, 1); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -68,7 +74,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 1023) == 1023 && *give_up) return false;   // another role of this block gave up
   }
-  atomicExch(&g_gemm_tma_status, 1);
+  report_give_up();
   *give_up = 1;
   return false;
 }
@@ -460,13 +466,25 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, lon
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Report give-ups of this library's kernels on the current device into `device_word` (an int in
+// device memory that the caller owns and keeps alive; null: back to the library's own word).
+extern "C" int mi_set_status_word(int* device_word) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MI_MAX_DEVICES) MI_REFUSE("status word: bad device");
+  cudaError_t e = cudaMemcpyToSymbol(g_status_word, &device_word, sizeof(int*));
+  if (e != cudaSuccess) return (int)e;
+  g_status_word_host[dev] = device_word;
+  return 0;
+}
+
+// Non-zero when a block gave up a bounded wait since the last reset (synchronises the device).
 extern "C" int mi_gemm_tma_status(int reset) {
-  int v = 0;
-  cudaMemcpyFromSymbol(&v, g_gemm_tma_status, sizeof(int));
-  if (reset && v) {
-    int z = 0;
-    cudaMemcpyToSymbol(g_gemm_tma_status, &z, sizeof(int));
-  }
+  int dev = -1, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MI_MAX_DEVICES) return -1;
+  int* word = g_status_word_host[dev];
+  if (!word && cudaGetSymbolAddress((void**)&word, g_gemm_tma_status) != cudaSuccess) return -1;
+  if (cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (reset && v) cudaMemset(word, 0, sizeof(int));
   return v;
 }
 

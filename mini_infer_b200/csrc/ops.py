@@ -56,7 +56,18 @@ def _finish(lib: ctypes.CDLL, rc: int, what: str) -> None:
     launch_count += 1
 
 
+class KernelWaitError(KernelError):
+    """A kernel gave up one of its bounded waits: what it wrote since is not to be trusted."""
+
+
 _configured: set[str] = set()
+
+# Libraries whose kernels have bounded waits.  Their give-ups are reported into one int32 word
+# per device (``status_word``), which the engine copies to the host with every step's result;
+# on their own the libraries would each keep a word that only a synchronising call can read.
+_WAITING_LIBRARIES = ("attention_mma", "attention_tc", "gemm_tma")
+_status_words: dict[int, torch.Tensor] = {}
+_status_shared: set[tuple[str, int]] = set()
 
 
 def _lib(name: str) -> ctypes.CDLL:
@@ -67,6 +78,48 @@ def _lib(name: str) -> ctypes.CDLL:
     return lib
 
 
+def _device_index(device: torch.device) -> int:
+    return device.index if device.index is not None else torch.cuda.current_device()
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The int32 word (on ``device``) that the kernels with bounded waits set to 1 when a wait
+    gave up.  Zero means every such kernel launched through this module has waited out its
+    copies; the engine reads it with each step's tokens."""
+    idx = _device_index(device)
+    word = _status_words.get(idx)
+    if word is None:
+        word = _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return word
+
+
+def _waiting_lib(name: str, device: torch.device) -> ctypes.CDLL:
+    """``_lib`` for a library with bounded waits: the first use on a device points the
+    library's give-up reports at that device's shared status word."""
+    lib = _lib(name)
+    idx = _device_index(device)
+    if (name, idx) not in _status_shared:
+        with torch.cuda.device(idx):
+            rc = lib.mi_set_status_word(_ptr(status_word(device)))
+        if rc != 0:
+            raise KernelError(f"{name}: cannot share the status word: {lib.mi_error_message().decode()}")
+        _status_shared.add((name, idx))
+    return lib
+
+
+def recover_from_wait_failure(device: torch.device) -> None:
+    """After a give-up: clear the status word and the arrival counters that the interrupted
+    kernels may have left non-zero (they are zero between calls otherwise).  Synchronises."""
+    torch.cuda.synchronize(device)
+    status_word(device).zero_()
+    idx = _device_index(device)
+    for buf in _decode_counter_bufs.get(idx, []):
+        buf.zero_()
+    for _partials, counters in _tma_ws.get(idx, []):
+        counters.zero_()
+    torch.cuda.synchronize(device)
+
+
 def _sig_elementwise(lib: ctypes.CDLL) -> None:
     lib.mi_embedding.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     lib.mi_add_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -75,6 +128,7 @@ def _sig_elementwise(lib: ctypes.CDLL) -> None:
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     lib.mi_silu_mul.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     lib.mi_silu_mul_pairs.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.mi_table_update.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
 
 
 def _sig_gemm_f32(lib: ctypes.CDLL) -> None:
@@ -84,7 +138,7 @@ def _sig_gemm_f32(lib: ctypes.CDLL) -> None:
 
 def _sig_attention_generic(lib: ctypes.CDLL) -> None:
     lib.mi_attention_generic.argtypes = [
-        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
         c_float, c_int, c_int, c_void_p]
     lib.mi_attention_generic_tile_tokens.restype = c_int
@@ -101,23 +155,18 @@ def _sig_attention_mma(lib: ctypes.CDLL) -> None:
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
         c_void_p, c_void_p]
     lib.mi_attention_decode_sliced.argtypes = [
-        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
         c_void_p, c_void_p]
     lib.mi_attention_decode_counters.argtypes = [c_int, c_int, c_int]
     lib.mi_attention_wait_status.argtypes = [c_int]
+    lib.mi_set_status_word.argtypes = [c_void_p]
     lib.mi_attention_prefill.argtypes = [
-        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
         c_float, c_int, c_void_p]
     lib.mi_attention_prefill_tile_tokens.argtypes = [c_int]
     lib.mi_attention_prefill_tile_tokens.restype = c_int
-
-
-def _sig_gemm_skinny(lib: ctypes.CDLL) -> None:
-    lib.mi_gemm_skinny.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                   c_int, c_int, c_void_p, c_void_p, c_void_p]
-    lib.mi_gemm_skinny_plan.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)]
 
 
 def _sig_gemm_tma(lib: ctypes.CDLL) -> None:
@@ -126,21 +175,22 @@ def _sig_gemm_tma(lib: ctypes.CDLL) -> None:
     lib.mi_gemm_tma_workspace.argtypes = [c_int, c_int, c_int, ctypes.POINTER(ctypes.c_longlong),
                                           ctypes.POINTER(c_int)]
     lib.mi_gemm_tma_status.argtypes = [c_int]
+    lib.mi_set_status_word.argtypes = [c_void_p]
 
 
 def _sig_attention_tc(lib: ctypes.CDLL) -> None:
     lib.mi_attention_prefill_tc.argtypes = [
-        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int,
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_int,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
         c_void_p]
     lib.mi_attention_prefill_tc_supported.argtypes = [c_int, c_int, c_int, c_int]
     lib.mi_attention_tc_status.argtypes = [c_int]
+    lib.mi_set_status_word.argtypes = [c_void_p]
 
 
 _SIGNATURES = {
     "attention_tc": _sig_attention_tc,
     "gemm_tma": _sig_gemm_tma,
-    "gemm_skinny": _sig_gemm_skinny,
     "attention_mma": _sig_attention_mma,
     "elementwise": _sig_elementwise,
     "gemm_f32": _sig_gemm_f32,
@@ -257,6 +307,21 @@ def rope_write(
                            _ptr(vcache), M, nq, nkv, head_dim, rotary_dim, page_size, _code(qkv.dtype),
                            _stream())
     _finish(lib, rc, "rope")
+
+
+def table_update(table: torch.Tensor, updates: torch.Tensor, count: torch.Tensor, capacity: int) -> None:
+    """Scatter new page ids into a block table: ``table[slot, index] = page`` for the first
+    ``count[0]`` (at most ``capacity``) triples ``(slot, index, page)`` of ``updates``; all int32
+    on the device.  ``count`` is read when the kernel runs, so a captured step can replay it."""
+    _cuda(table, updates, count)
+    if table.dtype != torch.int32 or table.dim() != 2 or not table.is_contiguous():
+        raise KernelError("table_update: the table must be a contiguous int32 matrix")
+    if updates.dtype != torch.int32 or updates.numel() < 3 * capacity or count.dtype != torch.int32 or count.numel() < 1:
+        raise KernelError("table_update: updates must hold 3 * capacity int32 values and count one")
+    lib = _lib("elementwise")
+    rc = lib.mi_table_update(_ptr(table), table.shape[1], table.shape[0], _ptr(updates), _ptr(count),
+                             int(capacity), _stream())
+    _finish(lib, rc, "table_update")
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, pairs: bool = False) -> torch.Tensor:
@@ -438,7 +503,8 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq:
             attention_decode(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
                              ctx.q_start, ctx.kv_len, ctx.n_requests, nq, nkv, head_dim, scale, window,
                              planned or decode_splits(ctx.n_requests, nq, nkv, ctx.max_kv_len, window, q.device),
-                             slice_chunks=group.decode_slice_chunks if planned else None)
+                             slice_chunks=group.decode_slice_chunks if planned else None,
+                             table_rows=group.table_rows)
         else:
             tc = USE_TC_PREFILL and prefill_tc_supported(nq, nkv, head_dim, group.page_size)
             tt = (prefill_tc_tile_tokens if tc else prefill_tile_tokens)(nq // nkv)
@@ -446,17 +512,17 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq:
             (attention_prefill_tc if tc else attention_prefill)(
                 q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
                 ctx.q_start, ctx.q_len, ctx.kv_len, tile_req, tile_tok0, n_tiles, tt,
-                nq, nkv, head_dim, scale, window)
+                nq, nkv, head_dim, scale, window, table_rows=group.table_rows)
         return
     tile_req, tile_tok0, n_tiles = ctx.q_tiles(ATTENTION_TILE_TOKENS)
     attention_generic(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
                       ctx.q_start, ctx.q_len, ctx.kv_len, tile_req, tile_tok0, n_tiles,
-                      nq, nkv, head_dim, scale, window)
+                      nq, nkv, head_dim, scale, window, table_rows=group.table_rows)
 
 
 def _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, page_size, ints):
     for name, t in ints:
-        if t.dtype != torch.int32:
+        if t is not None and t.dtype != torch.int32:
             raise KernelError(f"attention: {name} must be int32")
     if kcache.dtype != q.dtype or vcache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, out and caches must share a dtype")
@@ -466,7 +532,7 @@ def _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim
     if out.dim() != 2 or out.shape[1] != nq * head_dim or not out.is_contiguous():
         raise KernelError("attention: out must be contiguous [tokens, nq * d]")
     if block_table.dim() != 2 or block_table.stride(1) != 1:
-        raise KernelError("attention: block_table must be [requests, pages] with unit inner stride")
+        raise KernelError("attention: block_table must be [rows, pages] with unit inner stride")
 
 
 # Arrival counters of the split-key decode kernel, per device: zero between calls (the kernel
@@ -483,28 +549,31 @@ def _decode_counters(device: torch.device, n: int) -> torch.Tensor:
 
 
 def attention_decode(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, kv_len,
-                     n_requests, nq, nkv, head_dim, scale, window=0, n_splits=1, slice_chunks=None) -> None:
+                     n_requests, nq, nkv, head_dim, scale, window=0, n_splits=1, slice_chunks=None,
+                     table_rows=None) -> None:
     """bfloat16 decode attention: one query token per request, keys cut into ``n_splits``
     slices whose partial results are merged through scratch memory (attention_mma.cu).
+    Request ``b`` reads row ``table_rows[b]`` of ``block_table`` (row ``b`` without ``table_rows``).
     ``slice_chunks`` (an int32 tensor of one element on the device, read when the kernel
     runs) makes every slice that many 64-key chunks for all requests; without it every
     request's own keys are cut into ``n_splits`` equal slices."""
-    _cuda(q, out, kcache, vcache, block_table, q_start, kv_len, slice_chunks)
+    _cuda(q, out, kcache, vcache, block_table, q_start, kv_len, slice_chunks, table_rows)
     if slice_chunks is not None and (slice_chunks.dtype != torch.int32 or slice_chunks.numel() < 1):
         raise KernelError("attention_decode: slice_chunks must be an int32 tensor of one element")
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_decode: bfloat16 only")
     _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, page_size,
-                          (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len)))
+                          (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len),
+                           ("table_rows", table_rows)))
     part_o = part_ml = counters = None
-    lib = _lib("attention_mma")
+    lib = _waiting_lib("attention_mma", q.device)
     if n_splits > 1:
         part_o = torch.empty((n_requests * nq * n_splits, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n_requests * nq * n_splits, 2), dtype=torch.float32, device=q.device)
         counters = _decode_counters(q.device, lib.mi_attention_decode_counters(int(n_requests), nq, nkv))
     rc = lib.mi_attention_decode_sliced(
         _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_table),
-        block_table.stride(0), int(page_size), _ptr(q_start), _ptr(kv_len), int(n_requests), nq, nkv,
+        block_table.stride(0), _ptr(table_rows), int(page_size), _ptr(q_start), _ptr(kv_len), int(n_requests), nq, nkv,
         head_dim, float(scale), int(window), int(n_splits), _ptr(slice_chunks), _ptr(part_o), _ptr(part_ml),
         _ptr(counters), _stream())
     _finish(lib, rc, "attention_decode")
@@ -517,18 +586,20 @@ def attention_wait_status(reset: bool = True) -> int:
 
 
 def attention_prefill(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, q_len, kv_len,
-                      tile_req, tile_tok0, n_tiles, tile_tokens, nq, nkv, head_dim, scale, window=0) -> None:
+                      tile_req, tile_tok0, n_tiles, tile_tokens, nq, nkv, head_dim, scale, window=0,
+                      table_rows=None) -> None:
     """bfloat16 attention of query portions of any length over the paged cache (attention_mma.cu)."""
-    _cuda(q, out, kcache, vcache, block_table, q_start, q_len, kv_len, tile_req, tile_tok0)
+    _cuda(q, out, kcache, vcache, block_table, q_start, q_len, kv_len, tile_req, tile_tok0, table_rows)
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill: bfloat16 only")
     _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, page_size,
                           (("block_table", block_table), ("q_start", q_start), ("q_len", q_len),
-                           ("kv_len", kv_len), ("tile_req", tile_req), ("tile_tok0", tile_tok0)))
-    lib = _lib("attention_mma")
+                           ("kv_len", kv_len), ("tile_req", tile_req), ("tile_tok0", tile_tok0),
+                           ("table_rows", table_rows)))
+    lib = _waiting_lib("attention_mma", q.device)
     rc = lib.mi_attention_prefill(
         _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_table),
-        block_table.stride(0), int(page_size), _ptr(q_start), _ptr(q_len), _ptr(kv_len), _ptr(tile_req),
+        block_table.stride(0), _ptr(table_rows), int(page_size), _ptr(q_start), _ptr(q_len), _ptr(kv_len), _ptr(tile_req),
         _ptr(tile_tok0), int(n_tiles), int(tile_tokens), nq, nkv, head_dim, float(scale), int(window),
         _stream())
     _finish(lib, rc, "attention_prefill")
@@ -550,19 +621,21 @@ def prefill_tc_supported(nq: int, nkv: int, head_dim: int, page_size: int) -> bo
 
 
 def attention_prefill_tc(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, q_len, kv_len,
-                         tile_req, tile_tok0, n_tiles, tile_tokens, nq, nkv, head_dim, scale, window=0) -> None:
+                         tile_req, tile_tok0, n_tiles, tile_tokens, nq, nkv, head_dim, scale, window=0,
+                         table_rows=None) -> None:
     """bfloat16 attention of query portions over the paged cache on tcgen05 (attention_tc.cu);
     same arguments as ``attention_prefill``."""
-    _cuda(q, out, kcache, vcache, block_table, q_start, q_len, kv_len, tile_req, tile_tok0)
+    _cuda(q, out, kcache, vcache, block_table, q_start, q_len, kv_len, tile_req, tile_tok0, table_rows)
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill_tc: bfloat16 only")
     _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, page_size,
                           (("block_table", block_table), ("q_start", q_start), ("q_len", q_len),
-                           ("kv_len", kv_len), ("tile_req", tile_req), ("tile_tok0", tile_tok0)))
-    lib = _lib("attention_tc")
+                           ("kv_len", kv_len), ("tile_req", tile_req), ("tile_tok0", tile_tok0),
+                           ("table_rows", table_rows)))
+    lib = _waiting_lib("attention_tc", q.device)
     rc = lib.mi_attention_prefill_tc(
         _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), int(kcache.shape[0]),
-        _ptr(block_table), block_table.stride(0), int(page_size), _ptr(q_start), _ptr(q_len), _ptr(kv_len),
+        _ptr(block_table), block_table.stride(0), _ptr(table_rows), int(page_size), _ptr(q_start), _ptr(q_len), _ptr(kv_len),
         _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), int(tile_tokens), nq, nkv, head_dim, float(scale),
         int(window), _stream())
     _finish(lib, rc, "attention_prefill_tc")
@@ -593,16 +666,18 @@ def attention_generic(
     head_dim: int,
     scale: float,
     window: int = 0,
+    table_rows: torch.Tensor | None = None,
 ) -> None:
     """Causal attention of query portions over the paged cache (see attention_generic.cu).
 
     ``q`` is any tensor whose element ``(token t, head h, k)`` lies at
     ``t * q_stride + h * head_dim + k`` from its first element.
     """
-    _cuda(q, out, kcache, vcache, block_table, q_start, q_len, kv_len, tile_req, tile_tok0)
+    _cuda(q, out, kcache, vcache, block_table, q_start, q_len, kv_len, tile_req, tile_tok0, table_rows)
     for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len),
-                    ("kv_len", kv_len), ("tile_req", tile_req), ("tile_tok0", tile_tok0)):
-        if t.dtype != torch.int32:
+                    ("kv_len", kv_len), ("tile_req", tile_req), ("tile_tok0", tile_tok0),
+                    ("table_rows", table_rows)):
+        if t is not None and t.dtype != torch.int32:
             raise KernelError(f"attention: {name} must be int32")
     if kcache.dtype != q.dtype or vcache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, out and caches must share a dtype")
@@ -618,7 +693,7 @@ def attention_generic(
         raise KernelError("attention: the kernel's tile size differs from ATTENTION_TILE_TOKENS")
     rc = lib.mi_attention_generic(
         _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
-        _ptr(block_table), block_table.stride(0), int(page_size), _ptr(q_start), _ptr(q_len),
+        _ptr(block_table), block_table.stride(0), _ptr(table_rows), int(page_size), _ptr(q_start), _ptr(q_len),
         _ptr(kv_len), _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), nq, nkv, head_dim,
         float(scale), int(window), _code(q.dtype), _stream())
     _finish(lib, rc, "attention")
@@ -652,61 +727,6 @@ def sample(
                        _ptr(top_k), _ptr(top_p), _ptr(seed_lo), _ptr(seed_hi), _ptr(draw_index),
                        _ptr(out), _stream())
     _finish(lib, rc, "sample")
-    return out
-
-
-SKINNY_MAX_ROWS = 16
-USE_SKINNY_GEMM = False
-
-
-# Scratch of the K-sliced weight-streaming product, per device: partial sums and the arrival
-# counters (zero between calls).  A workspace is never freed once handed out: a captured CUDA
-# graph may hold its address.
-_SKINNY_PARTIAL_FLOATS = 10 * 1024 * 1024
-_SKINNY_COUNTERS = 4096
-_skinny_ws: dict[int, list[tuple[torch.Tensor, torch.Tensor]]] = {}
-_skinny_plans: dict[tuple[int, int, int, int], int] = {}
-
-
-def _skinny_workspace(device: torch.device, floats: int, counters: int) -> tuple[torch.Tensor, torch.Tensor]:
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    stack = _skinny_ws.setdefault(idx, [])
-    if not stack or stack[-1][0].numel() < floats or stack[-1][1].numel() < counters:
-        stack.append((
-            torch.empty(max(floats, _SKINNY_PARTIAL_FLOATS), dtype=torch.float32, device=device),
-            torch.zeros(max(counters, _SKINNY_COUNTERS), dtype=torch.int32, device=device),
-        ))
-    return stack[-1]
-
-
-def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-                k_slices: int | None = None) -> torch.Tensor:
-    """``x [M <= 16, K] @ w [N, K]^T`` for bfloat16 operands, streaming ``w`` once
-    (gemm_skinny.cu); the result is bfloat16 or float32.  ``k_slices`` (default: the
-    kernel's own plan) cuts K across blocks when ``w`` has too few rows to fill the GPU."""
-    _cuda(x, w)
-    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
-        raise KernelError("gemm_skinny: operands must be bfloat16")
-    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1] or x.stride(1) != 1 or w.stride(1) != 1:
-        raise KernelError(f"gemm_skinny: shapes {tuple(x.shape)} x {tuple(w.shape)}^T do not match")
-    M, K = x.shape
-    N = w.shape[0]
-    lib = _lib("gemm_skinny")
-    if k_slices is None:
-        key = (M, N, K, _sms(x.device))
-        k_slices = _skinny_plans.get(key)
-        if k_slices is None:
-            rows, slices = c_int(0), c_int(0)
-            lib.mi_gemm_skinny_plan(M, N, K, key[3], ctypes.byref(rows), ctypes.byref(slices))
-            k_slices = _skinny_plans[key] = int(slices.value)
-    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    partial = counters = None
-    if k_slices > 1:
-        partial, counters = _skinny_workspace(x.device, k_slices * M * N, -(-N // 64))
-    rc = lib.mi_gemm_skinny(_ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0) if M > 1 else K,
-                            w.stride(0) if N > 1 else K, N, _code(out_dtype), int(k_slices),
-                            _ptr(partial), _ptr(counters), _stream())
-    _finish(lib, rc, "gemm_skinny")
     return out
 
 
@@ -754,7 +774,7 @@ def gemm_tma(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bf
         raise KernelError(f"gemm_tma: shapes {tuple(x.shape)} x {tuple(w.shape)}^T do not match")
     M, K = x.shape
     N = w.shape[0]
-    lib = _lib("gemm_tma")
+    lib = _waiting_lib("gemm_tma", x.device)
     blocks = _sms(x.device)
     floats, counters = ctypes.c_longlong(0), c_int(0)
     lib.mi_gemm_tma_workspace(M, N, blocks, ctypes.byref(floats), ctypes.byref(counters))
@@ -773,13 +793,6 @@ def gemm_tma_status(reset: bool = True) -> int:
     """Non-zero when a block of the streaming product gave up a bounded wait since the last
     reset (its output is then wrong).  Synchronises the device."""
     return int(_lib("gemm_tma").mi_gemm_tma_status(1 if reset else 0))
-
-
-def _skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    M, K = x.shape
-    return (M <= SKINNY_MAX_ROWS and K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1
-            and (M == 1 or x.stride(0) % 8 == 0) and (w.shape[0] == 1 or w.stride(0) % 8 == 0)
-            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor) -> torch.Tensor:
@@ -804,7 +817,6 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     weight-streaming tcgen05 kernel of gemm_tma.cu, which starts streaming weights while the
     kernel before it still runs; other bfloat16 operands use the library product with fp32
     accumulation, as the reference does for every linear layer (``distributed/linear.py:167``).
-    The CUDA-core kernel of gemm_skinny.cu stays available as ``gemm_skinny``.
     ``out_dtype=float32`` keeps the accumulator's precision in the result (used for logits).
     """
     global _MM_OUT_DTYPE, launch_count
@@ -819,8 +831,6 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
         raise KernelError(f"linear: unsupported output dtype {out_dtype}")
     if USE_TMA_GEMM and x.shape[0] <= TMA_GEMM_DISPATCH_ROWS and gemm_tma_ok(x, w):
         return gemm_tma(x, w, out_dtype or torch.bfloat16)
-    if USE_SKINNY_GEMM and _skinny_ok(x, w):
-        return gemm_skinny(x, w, out_dtype or torch.bfloat16)
     launch_count += 1
     if out_dtype in (None, torch.bfloat16):
         return torch.mm(x, w.t())

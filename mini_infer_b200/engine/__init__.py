@@ -3,6 +3,7 @@
 from .runner import ModelRunner  # noqa: F401
 from .scheduler import (  # noqa: F401
     ContinuousScheduler,
+    EngineFaultError,
     EngineNotRunningError,
     GenerationResult,
     Request,

@@ -56,6 +56,7 @@ class ModelRunner:
         self.cache = CacheManager(
             model.cache_needs(), page_size=block_size, num_pages=num_blocks,
             max_requests=max_requests, dtype=self.dtype, device=self.device,
+            max_request_tokens=model.spec.max_positions,
         )
         self.stepper = StepRunner(model, self.cache, cuda_graph=cuda_graph)
         self.vocab_size = model.spec.vocab_size
@@ -91,6 +92,24 @@ class ModelRunner:
         return cls(model, cfg, num_blocks=num_blocks, block_size=block_size, max_requests=max_requests,
                    cuda_graph=cuda_graph)
 
+    @classmethod
+    def from_random(cls, raw_config: Mapping[str, Any], seed: int, *, device="cuda:0", dtype="bfloat16",
+                    num_blocks: int = DEFAULT_NUM_BLOCKS, block_size: int = DEFAULT_BLOCK_SIZE,
+                    max_requests: int = 64, cuda_graph: bool = False, std: float = 0.02,
+                    gain_std: float = 0.1, std_overrides: Mapping[str, float] | None = None) -> "ModelRunner":
+        """Build from a raw configuration mapping with the random weights of ``seed`` (the ones
+        ``write_random_model`` writes), drawn on the device part by part: a model of tens of
+        gigabytes needs neither a file nor host memory, and nothing exists twice."""
+        from ..weights.random_init import bind_random
+
+        device = require_cuda(device)
+        tdtype = resolve_dtype(dtype)
+        arch, cfg = load_config(raw_config)
+        model = DecoderModel(arch.assemble(cfg))
+        bind_random(model, seed, tdtype, device, std=std, gain_std=gain_std, std_overrides=std_overrides)
+        return cls(model, cfg, num_blocks=num_blocks, block_size=block_size, max_requests=max_requests,
+                   cuda_graph=cuda_graph)
+
     # -- requests -----------------------------------------------------------------------
 
     def add_request(self, rid) -> int:
@@ -104,3 +123,19 @@ class ModelRunner:
 
     def step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> StepResult:
         return self.stepper.step(entries, device_tokens)
+
+    # -- health -------------------------------------------------------------------------
+
+    def health_word(self) -> torch.Tensor:
+        """An int32 tensor of one element on the device: non-zero once a kernel has given up one
+        of its bounded waits (its output, and everything computed from it, is then invalid).  A
+        scheduler copies it to the host together with each step's tokens."""
+        from ..csrc import ops
+
+        return ops.status_word(self.device)
+
+    def reset_health(self) -> None:
+        """Clear the word and whatever the interrupted kernels left behind (synchronises)."""
+        from ..csrc import ops
+
+        ops.recover_from_wait_failure(self.device)

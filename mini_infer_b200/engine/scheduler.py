@@ -21,6 +21,10 @@ decodes, finishes and frees.  Names follow the reference (``ContinuousScheduler`
   it has generated, keeping its sampling seed and token count, so it continues the same
   sequence later.  (The reference cancels the youngest request instead, ``:373-445``.)  A
   request that cannot fit even alone is finished as ``"cancelled"``.
+* **Faults.**  With every step's tokens the scheduler reads the runner's health word (set by
+  a kernel that gave up a bounded wait).  If it is set, the step's requests are finished as
+  ``"cancelled"`` with their pages given back, the runner is reset, and ``EngineFaultError``
+  is raised; nothing sampled from that step is handed out.
 * **Finishing.**  ``"stop"`` when the sampled id is an end-of-sequence id (it is not
   emitted), ``"length"`` after ``max_tokens`` tokens or at the model's last position.
   A finished request's pages go back before the next step is planned.
@@ -44,6 +48,12 @@ from .step import StepEntry
 
 class EngineNotRunningError(RuntimeError):
     pass
+
+
+class EngineFaultError(RuntimeError):
+    """A step's kernels reported that they gave up waiting for their copies: the tokens of that
+    step are worthless.  The step's requests are finished as ``"cancelled"``, the runner's
+    health is reset, and the error is raised to whoever drives the engine."""
 
 
 @dataclasses.dataclass
@@ -141,6 +151,7 @@ class _InFlightStep:
     host: object                      # the same ids on their way to (pinned) host memory
     ready: object                     # event recorded after that copy (None: the copy was synchronous)
     t0: float
+    health: object = None             # the runner's health word on its way to the host (None: the runner has none)
 
 
 class ContinuousScheduler:
@@ -328,9 +339,13 @@ class ContinuousScheduler:
                 [rr.seed for rr in wanting],
                 [len(rr.generated) for rr in wanting],
             )
+            health = self._queue_health_read()
             ids = [int(t) for t in (ids.tolist() if hasattr(ids, "tolist") else ids)]
         else:
+            health = self._queue_health_read()
             ids = []
+        self._check_health(health, owners)
+        emitted: list = []
         with self._lock:
             for rr, e in zip(owners, entries):
                 if rr.state is RequestState.PREFILLING:
@@ -340,7 +355,7 @@ class ContinuousScheduler:
                 else:
                     rr.next_token = None
             for rr, tok in zip(wanting, ids):
-                self._consume(rr, tok)
+                self._consume(rr, tok, emitted=emitted)
             if self.trace_out is not None:
                 n_pre = sum(1 for e in entries if len(e.tokens) > 1)
                 phase = "decode" if n_pre == 0 else ("prefill" if n_pre == len(entries) else "mixed")
@@ -350,7 +365,50 @@ class ContinuousScheduler:
                     "args": {"B": len(entries), "phase": phase,
                              "total_q": sum(len(e.tokens) for e in entries)},
                 })
+        self._emit(emitted)
         return True
+
+    # ------------------------------------------------------------------ health
+
+    def _queue_health_read(self):
+        """Start a copy of the runner's health word to the host, behind the step just launched
+        (None when the runner has no such word)."""
+        word_of = getattr(self.runner, "health_word", None)
+        word = word_of() if word_of is not None else None
+        if word is None:
+            return None
+        if getattr(word, "is_cuda", False):
+            import torch
+
+            host = torch.empty(word.shape, dtype=word.dtype, pin_memory=True)
+            host.copy_(word, non_blocking=True)
+            return host
+        return word
+
+    def _check_health(self, health, owners) -> None:
+        """Called once the step's results are on the host.  A set word means that the step's
+        tokens are worthless: its requests end as ``"cancelled"`` and the error goes up."""
+        if health is None or not int(health[0]):
+            return
+        self._drain(check=False)
+        with self._lock:
+            for rr in owners:
+                rr.in_flight_after_done = False
+                if rr.state is not RequestState.DONE:
+                    self._retire(rr, "cancelled")
+                else:
+                    self._release(rr)
+        reset = getattr(self.runner, "reset_health", None)
+        if reset is not None:
+            reset()
+        raise EngineFaultError("a kernel gave up waiting for its copies; the step's tokens were discarded, "
+                               f"{len(owners)} requests were cancelled and the runner was reset")
+
+    def _emit(self, emitted) -> None:
+        """Streaming callbacks run outside the scheduler's lock: a callback may cancel its own
+        request, submit another one or ask for the load without deadlocking the engine."""
+        for callback, token in emitted:
+            callback(token)
 
     # ------------------------------------------------------------------ decode look-ahead
 
@@ -384,14 +442,17 @@ class ContinuousScheduler:
         if isinstance(sampled, torch.Tensor) and sampled.is_cuda:
             host = torch.empty(sampled.shape, dtype=sampled.dtype, pin_memory=True)
             host.copy_(sampled, non_blocking=True)
+            health = self._queue_health_read()
             ready = torch.cuda.Event()
             ready.record(torch.cuda.current_stream(sampled.device))
         else:
             host = sampled
+            health = self._queue_health_read()
         with self._lock:
             for rr in owners:
                 rr.next_token = None
-        return _InFlightStep(entries=entries, owners=owners, sampled=sampled, host=host, ready=ready, t0=t0)
+        return _InFlightStep(entries=entries, owners=owners, sampled=sampled, host=host, ready=ready, t0=t0,
+                             health=health)
 
     def _launch_ahead(self, cur: _InFlightStep) -> _InFlightStep | None:
         """The step after ``cur`` for the requests that are known to go on (none has reached
@@ -428,13 +489,16 @@ class ContinuousScheduler:
         entries = [StepEntry(rr.rid, [0], [0]) for rr in owners]
         return self._launch(entries, owners, tokens.to(torch.int32))
 
-    def _collect(self, cur: _InFlightStep) -> None:
+    def _collect(self, cur: _InFlightStep, check: bool = True) -> None:
         """Read a launched step's tokens and hand them to their requests."""
         if cur.ready is not None:
             cur.ready.synchronize()
+        if check:
+            self._check_health(cur.health, cur.owners)
         ids = [int(t) for t in (cur.host.tolist() if hasattr(cur.host, "tolist") else cur.host)]
         nxt = self._inflight
         ahead = set(id(rr) for rr in nxt.owners) if nxt is not None else set()
+        emitted: list = []
         with self._lock:
             for rr, tok in zip(cur.owners, ids):
                 if rr.in_flight_after_done:
@@ -444,19 +508,32 @@ class ContinuousScheduler:
                     self.wasted_tokens += 1
                     self._release(rr)
                     continue
-                self._consume(rr, tok, still_in_flight=id(rr) in ahead)
+                self._consume(rr, tok, still_in_flight=id(rr) in ahead, emitted=emitted)
             if self.trace_out is not None:
                 self._trace.append({
                     "name": "step", "ph": "X", "pid": 0, "tid": 0, "ts": cur.t0 * 1e6,
                     "dur": (time.time() - cur.t0) * 1e6,
                     "args": {"B": len(cur.entries), "phase": "decode", "total_q": len(cur.entries)},
                 })
+        self._emit(emitted)
 
-    def _drain(self) -> None:
-        """Read back whatever was launched ahead (used before the engine stops)."""
+    def _drain(self, check: bool = True) -> None:
+        """Read back whatever was launched ahead (used before the engine stops).  Without
+        ``check`` (after a fault) the steps are waited for and their tokens thrown away."""
         while self._inflight is not None:
             cur, self._inflight = self._inflight, None
-            self._collect(cur)
+            if check:
+                self._collect(cur)
+                continue
+            if cur.ready is not None:
+                cur.ready.synchronize()
+            with self._lock:
+                for rr in cur.owners:
+                    if rr.in_flight_after_done:
+                        rr.in_flight_after_done = False
+                        self._release(rr)
+                    elif rr.state is not RequestState.DONE:
+                        self._retire(rr, "cancelled")
 
     # ------------------------------------------------------------------ internals (lock held)
 
@@ -564,18 +641,19 @@ class ContinuousScheduler:
         if rr.rid in self.cache:
             self.cache.free_request(rr.rid)
 
-    def _consume(self, rr: RunningRequest, token: int, still_in_flight: bool = False) -> None:
+    def _consume(self, rr: RunningRequest, token: int, still_in_flight: bool = False, emitted: list | None = None) -> None:
         """A sampled token: emit it, or finish the request (reference ``:847-860``).  With
         ``still_in_flight`` a step launched ahead holds the request: if it ends here, its
-        pages stay until that step has been read."""
+        pages stay until that step has been read.  The request's streaming callback is not
+        called here (the lock is held) but noted in ``emitted`` for ``_emit``."""
         if token in self.eos_token_ids:
             self._retire(rr, "stop", still_in_flight)
             return
         rr.generated.append(token)
         rr.next_token = token
         self.tokens_generated += 1
-        if rr.on_token is not None:
-            rr.on_token(token)
+        if rr.on_token is not None and emitted is not None:
+            emitted.append((rr.on_token, token))
         held = self.cache.length(rr.rid) - (1 if still_in_flight else 0)   # without the token launched ahead
         if len(rr.generated) >= rr.request.max_tokens:
             self._retire(rr, "length", still_in_flight)

@@ -72,11 +72,13 @@ class PlanNeeds:
     ``decode_blocks_per_request``: how many thread blocks a decode step of this mixer starts
     per request before its keys are cut into slices; a value above zero makes the planner
     decide the slices of each cache group from the requests' lengths
-    (``GroupView.decode_slices``, ``GroupView.decode_slice_chunks``).
+    (``GroupView.decode_slices``, ``GroupView.decode_slice_chunks``), for the compute dtypes in
+    ``decode_slice_dtypes`` (the mixer knows which of its kernels cut keys into slices).
     """
 
     q_tile_tokens: frozenset[int] = frozenset()
     decode_blocks_per_request: int = 0
+    decode_slice_dtypes: frozenset = frozenset()
 
 
 # ----------------------------------------------------------------------------- step context
@@ -88,8 +90,9 @@ class GroupView:
 
     page_size: int
     window: int | None
-    block_table: torch.Tensor          # [requests, max_pages] page ids of this group
+    block_table: torch.Tensor          # [request slots, max_pages] page ids of this group, resident on the device
     slots: torch.Tensor                # [tokens] flat slot (page * page_size + offset) per new token
+    table_rows: torch.Tensor | None = None   # [requests] row of block_table of each request (None: its index)
     decode_slices: int = 0             # decode-only steps: slices the keys are cut into (0: not planned)
     decode_slice_chunks: torch.Tensor | None = None   # [1] int32: 64-key chunks per slice
 
@@ -131,6 +134,9 @@ class StepContext:
     tiles: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = field(default_factory=dict)
     decode_only: bool = False          # every request brings exactly one token
     max_kv_len: int = 0
+    # per cache group: (triples, count, capacity) of the page ids the step scatters into the
+    # block tables before its first kernel (the step runner's business, not a part's)
+    table_updates: list = field(default_factory=list)
 
     def q_tiles(self, tokens: int) -> tuple[torch.Tensor, torch.Tensor, int]:
         """``(tile_request, tile_first_token, n_tiles)`` for tiles of ``tokens`` tokens."""
@@ -148,6 +154,11 @@ class StepContext:
 
 class Part:
     kind: ClassVar[str] = ""
+    # A captured step replays the device work of ``forward`` without running its Python again.
+    # A part whose ``forward`` reads the host lists of the StepContext, synchronises with the
+    # device or changes Python state sets this to False; steps of its model then always run
+    # kernel by kernel.
+    graph_safe: ClassVar[bool] = True
 
     def __init__(self, spec: PartSpec) -> None:
         self.spec = spec

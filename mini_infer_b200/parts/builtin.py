@@ -85,28 +85,30 @@ class RMSNorm(Norm):
 
 def rotary_inv_freq(head_dim: int, theta: float, rotary_dim: int | None = None,
                     scaling: dict | None = None) -> torch.Tensor:
-    """fp32 inverse frequencies ``theta^(-2i/d)``, optionally with the llama3 rescale.
+    """fp32 rotation frequencies ``theta^(-2i/d)``, optionally with the llama3 rescale.
 
-    The rescale keeps short wavelengths, divides long ones by ``factor`` and blends in
-    between (reference ``models/blocks/rope.py:200-225``); operations are applied in that
-    file's order so the fp32 table comes out bit-equal.
+    The rescale sorts frequencies by wavelength into three bands: short waves (below
+    ``L / high_freq_factor``, ``L`` the original context length) are kept, long waves (above
+    ``L / low_freq_factor``) are slowed down by ``factor``, and the band between is a blend of
+    both that is linear in ``L / wavelength``.  Every intermediate is fp32 and the
+    operations run in the order of the reference's ``models/blocks/rope.py:200-225``, so
+    the table comes out bit-equal to the reference's (a test compares them).
     """
-    rot = head_dim if rotary_dim is None else rotary_dim
-    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / head_dim))
+    width = head_dim if rotary_dim is None else rotary_dim
+    exponent = torch.arange(0, width, 2, dtype=torch.float32) / head_dim
+    freq = 1.0 / (theta ** exponent)
     if scaling is None:
-        return inv
-    factor = float(scaling["factor"])
-    low = float(scaling["low_freq_factor"])
-    high = float(scaling["high_freq_factor"])
-    old_len = int(scaling["original_max_position_embeddings"])
-    low_wavelen = old_len / low
-    high_wavelen = old_len / high
-    wavelen = 2 * math.pi / inv
-    scaled = torch.where(wavelen > low_wavelen, inv / factor, inv)
-    smooth = (old_len / wavelen - low) / (high - low)
-    smoothed = (1 - smooth) * scaled / factor + smooth * scaled
-    medium = ~(wavelen < high_wavelen) * ~(wavelen > low_wavelen)
-    return torch.where(medium, smoothed, scaled)
+        return freq
+    slow_down = float(scaling["factor"])
+    low, high = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+    context = int(scaling["original_max_position_embeddings"])
+    wave = 2 * math.pi / freq
+    is_long, is_short = wave > context / low, wave < context / high
+    slowed = torch.where(is_long, freq / slow_down, freq)
+    blend = (context / wave - low) / (high - low)          # 0 at the long edge, 1 at the short edge
+    blended = (1 - blend) * slowed / slow_down + blend * slowed
+    in_between = ~is_short * ~is_long
+    return torch.where(in_between, blended, slowed)
 
 
 class RotaryPosition(Position):
@@ -182,8 +184,10 @@ class GroupedQueryAttention(Mixer):
         return KVNeed(self.nkv, self.d, self.window)
 
     def plan_needs(self):
+        # only the bfloat16 decode kernel cuts keys into slices
         return PlanNeeds(ops.attention_tile_sizes(self.nq // self.nkv),
-                         ops.decode_blocks_per_request(self.nq, self.nkv))
+                         ops.decode_blocks_per_request(self.nq, self.nkv),
+                         frozenset({torch.bfloat16}))
 
     def bind(self, tensors, dtype, device):
         qkv = torch.cat(

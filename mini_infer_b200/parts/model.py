@@ -118,16 +118,24 @@ class DecoderModel:
     def plan_needs(self) -> PlanNeeds:
         tiles: set[int] = set()
         decode_blocks = 0
+        slice_dtypes: set = set()
         for b in self.blocks:
             needs = b.mixer.plan_needs()
             tiles |= set(needs.q_tile_tokens)
             decode_blocks = max(decode_blocks, needs.decode_blocks_per_request)
-        return PlanNeeds(frozenset(tiles), decode_blocks)
+            slice_dtypes |= set(needs.decode_slice_dtypes)
+        return PlanNeeds(frozenset(tiles), decode_blocks, frozenset(slice_dtypes))
+
+    def graph_safe(self) -> bool:
+        """Whether a step of this model may be captured as a CUDA graph (every part says so)."""
+        return all(p.graph_safe for p in self.all_parts())
 
     # ------------------------------------------------------------------ binding
 
-    def bind(self, tensors: dict[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
-        """Give every part its tensors (``tensors`` is keyed by full checkpoint name)."""
+    def bind(self, tensors, dtype: torch.dtype, device: torch.device) -> None:
+        """Give every part its tensors.  ``tensors`` is anything indexed by full checkpoint
+        name: a dict, or a source that fetches a tensor when it is asked for (parts are bound
+        one after the other, so such a source keeps peak memory at the model plus one part)."""
         def local_view(part: Part) -> dict[str, torch.Tensor]:
             return {local: tensors[part.spec.tensor_name(local)] for local in part.param_decls()}
 

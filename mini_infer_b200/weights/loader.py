@@ -69,22 +69,30 @@ def check_names(model, names_and_shapes: dict[str, tuple[int, ...]], where: str 
         raise WeightLoadError("\n".join(lines), missing, unexpected, mismatched)
 
 
+class TensorSource:
+    """Tensors by full checkpoint name, fetched when asked for and not kept: ``model.bind`` takes
+    one part's tensors at a time, so a part's own copies (a merged projection, say) are built
+    while only that part's checkpoint tensors are on the device, and peak memory is the model
+    plus one part, not twice the model.  (The reference loads shard by shard for the same
+    reason, ``models/loader.py:188-215``.)"""
+
+    def __init__(self, fetch) -> None:
+        self._fetch = fetch
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        return self._fetch(name)
+
+
 def load_weights(model, model_dir: str | os.PathLike, dtype: torch.dtype, device) -> None:
-    """Read ``model_dir``'s safetensors into ``model`` (a ``DecoderModel``)."""
+    """Read ``model_dir``'s safetensors into ``model`` (a ``DecoderModel``), part by part."""
     device = torch.device(device)
     with Checkpoint(os.fspath(model_dir)) as ckpt:
         check_names(model, {n: ckpt.shape(n) for n in ckpt.names()}, where=os.fspath(model_dir))
-        tensors: dict[str, torch.Tensor] = {}
-        for e in model.expected_tensors():
-            tensors[e.name] = to_engine_dtype(ckpt.read(e.name), dtype).to(device)
-    model.bind(tensors, dtype, device)
+        model.bind(TensorSource(lambda name: to_engine_dtype(ckpt.read(name), dtype).to(device)), dtype, device)
 
 
 def bind_state_dict(model, state: dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
     """Bind tensors already in memory (same checks and dtype policy as ``load_weights``)."""
     device = torch.device(device)
     check_names(model, {n: tuple(t.shape) for n, t in state.items()}, where="the given tensors")
-    tensors = {
-        e.name: to_engine_dtype(state[e.name], dtype).to(device) for e in model.expected_tensors()
-    }
-    model.bind(tensors, dtype, device)
+    model.bind(TensorSource(lambda name: to_engine_dtype(state[name], dtype).to(device)), dtype, device)

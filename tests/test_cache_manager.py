@@ -41,12 +41,16 @@ def test_block_tables_positions_and_slots():
     cm.add_request("b")
     plan = cm.plan_append([("a", 6), ("b", 1)])
     assert plan.start == [0, 0] and plan.counts == [6, 1]
-    ta, tb = plan.tables[0]
+    ta, tb = cm.table("a"), cm.table("b")
+    # the plan carries only what is new: (slot, index, page) of every page it handed out
+    assert cm.take_table_updates() == [[cm.slot("a"), 0, ta[0], cm.slot("a"), 1, ta[1], cm.slot("b"), 0, tb[0]]]
     assert len(ta) == 2 and len(tb) == 1 and len(set(ta + tb)) == 3
     assert plan.token_slots[0] == [ta[0] * 4 + i for i in range(4)] + [ta[1] * 4, ta[1] * 4 + 1] + [tb[0] * 4]
     plan2 = cm.plan_append([("b", 3), ("a", 3)])          # any order, positions come from the cache
     assert plan2.start == [1, 6]
     assert plan2.token_slots[0][:3] == [tb[0] * 4 + 1, tb[0] * 4 + 2, tb[0] * 4 + 3]
+    assert cm.take_table_updates() == [[cm.slot("a"), 2, cm.table("a")[2]]]   # b stayed inside its page
+    assert cm.take_table_updates() == [[]]
     assert cm.length("a") == 9 and cm.length("b") == 4
     cm.check()
     cm.free_request("a")
@@ -97,7 +101,7 @@ def test_groups_have_pages_of_their_own_and_windows_give_pages_back():
     for step in range(14):
         plan = cm.plan_append([("a", 3)])
         cm.check()
-        table = plan.tables[1][0]
+        table = cm.table("a", 1)
         held.append(sum(1 for p in table if p >= 0))
         length = cm.length("a")
         # every position a later query can see (the last window-1 keys and itself) has a page
@@ -177,3 +181,47 @@ def test_random_orders_never_lose_or_duplicate_a_page(seed):
         cm.free_request(rid)
     cm.check()
     assert all(cm.num_free_pages(g) == 12 for g in range(len(cm.groups)))
+
+
+def test_table_updates_replay_to_the_host_tables_under_random_orders():
+    """Scattering the (slot, index, page) triples in order into a table per slot, as the device
+    does, gives every live request its host table (entries a window gave back aside)."""
+    rng = random.Random(3)
+    kinds = needs(KVNeed(2, 16), KVNeed(2, 16, window=9))
+    cm = CacheManager(kinds, page_size=4, num_pages=[24, 8], max_requests=4, max_request_tokens=400)
+    assert cm.table_width == [24, 100]
+    device = [dict() for _ in cm.groups]            # (slot, index) -> page
+    live, next_id = [], 0
+    for _ in range(300):
+        action = rng.random()
+        if action < 0.3 and cm.num_free_slots:
+            cm.add_request(next_id)
+            live.append(next_id)
+            next_id += 1
+        elif action < 0.45 and live:
+            cm.free_request(live.pop(rng.randrange(len(live))))
+        elif live:
+            entries = [(rid, rng.choice([1, 1, 2, 7])) for rid in rng.sample(live, rng.randint(1, len(live)))]
+            if cm.can_append(entries):
+                cm.plan_append(entries)
+        for gi, flat in enumerate(cm.take_table_updates()):
+            assert len(flat) % 3 == 0
+            for i in range(0, len(flat), 3):
+                device[gi][(flat[i], flat[i + 1])] = flat[i + 2]
+        for rid in live:
+            for gi in range(len(cm.groups)):
+                for idx, page in enumerate(cm.table(rid, gi)):
+                    if page >= 0:
+                        assert device[gi][(cm.slot(rid), idx)] == page
+
+
+def test_a_request_longer_than_its_block_table_is_refused():
+    cm = CacheManager(full(), page_size=4, num_pages=64, max_requests=2, max_request_tokens=20)
+    assert cm.table_width == [5]
+    cm.add_request("a")
+    cm.plan_append([("a", 19)])
+    with pytest.raises(CacheError, match="block table"):
+        cm.plan_append([("a", 2)])
+    assert cm.length("a") == 19
+    cm.plan_append([("a", 1)])
+    cm.check()

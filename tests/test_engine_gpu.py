@@ -19,7 +19,6 @@ from tiny_configs import PAGE_SIZE, TINY, load_state, prompt_ids
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-TOL = {"float32": 1e-4, "bfloat16": 3e-2}
 
 
 # ----------------------------------------------------------------------------- generation
@@ -183,6 +182,7 @@ def test_attention_part_alone_in_portions(dtype):
     outs, pos = [], 0
     for n in (7, 1, 2, 19, 16):
         ctx, _, _, _ = runner.plan([StepEntry("r", [0] * n, [])])
+        runner.apply_table_updates(ctx)
         gi, k, v = cache.layer_kv(0)
         out = mixer.forward(x[pos:pos + n].to(DEV).to(dtype), ctx, LayerCache(group=gi, k=k, v=v), rope)
         outs.append(out.float().cpu())
@@ -191,7 +191,7 @@ def test_attention_part_alone_in_portions(dtype):
     cfg = {"num_attention_heads": nq, "num_key_value_heads": nkv, "head_dim": d}
     cos, sin = P.rope_cos_sin(list(range(Tn)), P.rope_inv_freq(d, 1234.0, None), torch.float64)
     want = P.attention_block(x.double(), {k: t.double() for k, t in w.items()}, "", cfg, cos, sin)
-    bound = (1e-4 if dtype == torch.float32 else 3e-2) * max(1.0, want.abs().max().item())
+    bound = (1e-4 if dtype == torch.float32 else 1e-2) * want.abs().max().item()
     assert (got - want).abs().max().item() <= bound
 
 
@@ -202,7 +202,7 @@ def test_feed_forward_norm_embedding_head_parts_alone(dtype):
     dev = torch.device(DEV)
     H, I, V, M = 136, 200, 333, 9
     g = torch.Generator().manual_seed(1)
-    rel = 1e-4 if dtype == torch.float32 else 3e-2
+    rel = 1e-4 if dtype == torch.float32 else 1e-2
     ffn = build_part("feed_forward", PartSpec("swiglu", {"hidden_size": H, "intermediate_size": I}))
     w = {n: (torch.randn(*d.shape, generator=g) * 0.1).to(torch.bfloat16) for n, d in ffn.param_decls().items()}
     ffn.bind({n: t.to(DEV) for n, t in w.items()}, dtype, dev)
@@ -210,7 +210,7 @@ def test_feed_forward_norm_embedding_head_parts_alone(dtype):
     got = ffn.forward(x.to(DEV).to(dtype), None).float().cpu().double()
     want = P.swiglu(x.double(), w["gate_proj.weight"].double(), w["up_proj.weight"].double(),
                     w["down_proj.weight"].double())
-    assert (got - want).abs().max().item() <= rel * max(1.0, want.abs().max().item())
+    assert (got - want).abs().max().item() <= rel * want.abs().max().item()
 
     norm = build_part("norm", PartSpec("rmsnorm", {"hidden_size": H, "eps": 3e-4}))
     gain = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
@@ -272,7 +272,27 @@ def _register_toys():
                 st[H] = counts[-1]
             return out
 
+    RunningMeanMixer.graph_safe = False      # it reads the host lists of the step: never captured
     register_mixer("toy_running_mean", RunningMeanMixer, replace=True)
+
+    class RunningMeanOnDevice(RunningMeanMixer):
+        """The same mixer with a decode path that touches device tensors only (rows gathered and
+        scattered by the step's slot indices), so a captured step may replay it."""
+
+        graph_safe = True
+
+        def forward(self, x, ctx, cache, position):
+            if not ctx.decode_only:
+                return super().forward(x, ctx, cache, position)
+            H = self.param("hidden_size")
+            slots = ctx.state_slot.long()
+            st = cache.state.index_select(0, slots)
+            sums = st[:, :H] + x.float()
+            counts = st[:, H] + 1.0
+            cache.state.index_copy_(0, slots, torch.cat([sums, counts[:, None]], dim=1))
+            return ((sums / counts[:, None]) @ self.w.T).to(x.dtype)
+
+    register_mixer("toy_running_mean_device", RunningMeanOnDevice, replace=True)
 
     class SoftRoutedExperts(FeedForward):
         """sum_e softmax(x R^T)_e * down_e(silu(up_e x)): a router (fp32 logits and softmax) and
@@ -316,12 +336,12 @@ def _register_toys():
 
     register_position("toy_learned_offsets", LearnedOffsets, replace=True)
 
-    def toy_state_assemble(cfg):
+    def toy_state_assemble(cfg, kind="toy_running_mean"):
         spec = llama_assemble(cfg)
         layers = list(spec.layers)
         layers[0] = dataclasses.replace(
             layers[0], position=None,
-            mixer=PartSpec("toy_running_mean", {"hidden_size": cfg.hidden_size}, prefix="model.layers.0.toy."))
+            mixer=PartSpec(kind, {"hidden_size": cfg.hidden_size}, prefix="model.layers.0.toy."))
         return dataclasses.replace(spec, layers=tuple(layers))
 
     def routed_assemble(cfg):
@@ -349,6 +369,8 @@ def _register_toys():
             ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2), ScheduleEntry(1, 0, writes_cache=False)))
 
     register_architecture("ToyStateLM", LlamaConfig.from_json, toy_state_assemble, replace=True)
+    register_architecture("ToyStateOnDeviceLM", LlamaConfig.from_json,
+                          lambda cfg: toy_state_assemble(cfg, "toy_running_mean_device"), replace=True)
     register_architecture("ToyWindowLM", LlamaConfig.from_json, windowed_assemble, replace=True)
     register_architecture("ToyLoopLM", LlamaConfig.from_json, looped_assemble, replace=True)
     register_architecture("ToyRoutedLM", LlamaConfig.from_json, routed_assemble, replace=True)
@@ -401,7 +423,22 @@ def plain_variant(state, raw, ids, *, windows=None, schedule=None, toy_layers=()
     return (z @ head.T).numpy()
 
 
-def run_variant(arch, raw_base, tmp_path, dtype, page, plain_kwargs, num_blocks=None):
+def cut_prefill_then_decode(requests, n_decode):
+    """Every request's prompt in a step of its own (no logits), then ``n_decode`` steps in which
+    all of them bring one token: the steps a captured graph replays."""
+    steps = []
+    for rid, toks in requests.items():
+        steps.append({"step": len(steps), "end": [],
+                      "entries": [{"id": rid, "tokens": toks[:-n_decode], "want": [len(toks) - n_decode - 1]}]})
+    for i in range(n_decode):
+        steps.append({"step": len(steps), "end": [],
+                      "entries": [{"id": rid, "tokens": [toks[len(toks) - n_decode + i]], "want": [0]}
+                                  for rid, toks in requests.items()]})
+    steps[-1]["end"] = list(requests)
+    return steps
+
+
+def run_variant(arch, raw_base, tmp_path, dtype, page, plain_kwargs, num_blocks=None, cuda_graph=False):
     from mini_infer_b200.engine import ModelRunner
     from mini_infer_b200.weights import write_random_model
     from tiny_configs import PEAKED
@@ -412,18 +449,22 @@ def run_variant(arch, raw_base, tmp_path, dtype, page, plain_kwargs, num_blocks=
     wide = dict(PEAKED["A"], **{"pos.table": 0.7, "router.weight": 0.5, "experts.": 0.08})
     folder = write_random_model(raw, str(tmp_path / arch), 5, std_overrides=wide)
     state = load_state(folder)
-    requests = {f"q{i}": prompt_ids("A", n, salt=200 + i) for i, n in enumerate([50, 3, 77, 31])}
+    requests = {f"q{i}": prompt_ids("A", n, salt=200 + i) for i, n in enumerate([50, 13 if cuda_graph else 3, 77, 31])}
     want = {r: plain_variant(state, raw, toks, **plain_kwargs) for r, toks in requests.items()}
-    steps = T.cut_mixed(requests, n_decode=9)
+    n_decode = 12
+    steps = cut_prefill_then_decode(requests, n_decode) if cuda_graph else T.cut_mixed(requests, n_decode=9)
     runner = ModelRunner.from_pretrained(folder, dtype=dtype, block_size=page,
-                                         num_blocks=num_blocks or T.max_tokens_needed(steps) // page, max_requests=4)
+                                         num_blocks=num_blocks or T.max_tokens_needed(steps) // page, max_requests=4,
+                                         cuda_graph=cuda_graph)
     for st in runner.cache.storage:
         st.fill_(float("nan"))
     got = T.collect(steps, T.replay_in_process(runner, steps), raw["vocab_size"])
     runner.cache.check()
-    scale = max(1.0, max(float(np.abs(want[r]).max()) for r in want))
+    scale = max(float(np.abs(want[r]).max()) for r in want)
     for r in requests:
-        bad = T.first_bad(got[r], want[r], TOL[dtype] * scale)
+        # with graphs the trace asks for the last prompt position and the decoded ones only
+        ref = want[r][-(n_decode + 1):] if cuda_graph else want[r]
+        bad = T.first_bad(got[r], ref, T.tolerance(dtype, scale))
         assert bad is None, f"{arch}/{dtype}: request {r} first differs at position {bad}"
     return runner
 
@@ -435,6 +476,29 @@ def test_toy_mixer_with_state_of_its_own(dtype, tmp_path):
     runner = run_variant("ToyStateLM", TINY["A"], tmp_path, dtype, 16, {"toy_layers": (0,)})
     assert 0 in runner.cache.state_arenas and 1 not in runner.cache.state_arenas
     assert [g.layers for g in runner.cache.groups] == [(1,)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_stateful_mixers_and_captured_steps(dtype, tmp_path):
+    """``cuda_graph=True`` with mixers that keep a state of their own.  One whose decode path
+    runs on device tensors only is captured and replayed, and its state advances exactly once
+    per step, the first step of a kind included (that step runs kernel by kernel and is then
+    captured without being run again).  One that reads the step's host lists says so
+    (``graph_safe = False``): its model is never captured and still gives the right logits."""
+    runner = run_variant("ToyStateOnDeviceLM", TINY["A"], tmp_path, dtype, 16, {"toy_layers": (0,)}, cuda_graph=True)
+    assert sum(slot.replays for slot in runner.stepper._graphs.values()) >= 10
+    runner = run_variant("ToyStateLM", TINY["A"], tmp_path, dtype, 16, {"toy_layers": (0,)}, cuda_graph=True)
+    assert not runner.stepper.cuda_graph and not runner.stepper._graphs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_windowed_layers_in_captured_steps(dtype, tmp_path):
+    """Decode steps of a model with windowed and full layers (two cache groups, the windowed
+    one handing pages back while it decodes) replayed as captured graphs."""
+    runner = run_variant("ToyWindowLM", TINY["A"], tmp_path, dtype, 4, {"windows": [11, None]},
+                         num_blocks=[48, 80], cuda_graph=True)
+    assert sum(slot.replays for slot in runner.stepper._graphs.values()) >= 10
+    assert [(g.layers, g.window) for g in runner.cache.groups] == [((0,), 11), ((1,), None)]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

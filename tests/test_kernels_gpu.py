@@ -204,33 +204,6 @@ def test_gemm_f32_is_not_reduced_precision():
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(1, 1000, 64), (3, 50, 176), (8, 4096, 4096), (9, 320, 192), (16, 513, 4104),
-                                   (5, 128256, 256), (8, 16, 8)])
-def test_gemm_skinny(M, N, K, out_dtype):
-    x = rnd(M, K, dtype=torch.bfloat16, seed=20)
-    w = rnd(N, K, dtype=torch.bfloat16, seed=21, scale=0.1)
-    out = ops().gemm_skinny(x.to(DEV), w.to(DEV), out_dtype)
-    want = x.double() @ w.double().T
-    bound = (1e-5 if out_dtype == torch.float32 else 1 / 128) * max(1.0, want.abs().max().item())
-    assert out.dtype == out_dtype
-    assert (out.cpu().double() - want).abs().max().item() <= bound
-
-
-@pytest.mark.parametrize("k_slices", [1, 2, 3, 7])
-def test_gemm_skinny_k_slices_agree(k_slices):
-    """Cutting K across blocks (partial sums in scratch memory, the last block adds them up)
-    gives the same result on every call, whatever the arrival order."""
-    M, N, K = 8, 200, 14336
-    x = rnd(M, K, dtype=torch.bfloat16, seed=24).to(DEV)
-    w = rnd(N, K, dtype=torch.bfloat16, seed=25, scale=0.05).to(DEV)
-    want = x.double().cpu() @ w.double().cpu().T
-    first = ops().gemm_skinny(x, w, torch.float32, k_slices=k_slices)
-    assert (first.cpu().double() - want).abs().max().item() <= 1e-4 * max(1.0, want.abs().max().item())
-    for _ in range(5):
-        assert torch.equal(ops().gemm_skinny(x, w, torch.float32, k_slices=k_slices), first)
-
-
-@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("M,N,K", [(1, 1000, 64), (3, 50, 176), (8, 4096, 4096), (9, 320, 192), (16, 513, 4104),
                                    (5, 128256, 256), (8, 16, 8), (17, 6144, 1024), (64, 264, 14336),
                                    (128, 520, 1032)])
 def test_gemm_tma(M, N, K, out_dtype):

@@ -23,7 +23,7 @@ def _checksum(state):
     return h.hexdigest()
 
 
-@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("which", ["A", "B", "C"])
 def test_plain_matches_reference_golden(which, model_dirs):
     gold = np.load(os.path.join(GOLDEN, f"tiny_{which}.npz"))
     state = load_state(model_dirs[which])
@@ -38,12 +38,34 @@ def test_plain_matches_reference_golden(which, model_dirs):
     assert np.abs(logits64 - gold["logits"]).max() <= 1e-4 * max(1.0, scale)
 
 
-@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("which", ["A", "B", "C"])
 def test_inv_freq_bit_equal_to_reference(which):
+    """Both the plain implementation's table and the product's own (the one the rotary kernel
+    is given) equal the reference's fp32 table bit for bit."""
+    from mini_infer_b200.config import load_config
+    from mini_infer_b200.parts.builtin import rotary_inv_freq
+
     gold = np.load(os.path.join(GOLDEN, f"tiny_{which}.npz"))
     cfg = P.normalise_config(TINY[which])
     mine = P.rope_inv_freq(cfg["head_dim"], cfg["_theta"], cfg["_scaling"]).numpy()
     assert np.array_equal(mine, gold["inv_freq"])
+    arch, typed = load_config(TINY[which])
+    position = arch.assemble(typed).layers[0].position
+    product = rotary_inv_freq(position.params["head_dim"], position.params["theta"],
+                              position.params.get("rotary_dim"), position.params.get("scaling"))
+    assert product.dtype == torch.float32
+    assert np.array_equal(product.numpy(), gold["inv_freq"])
+
+
+def test_inv_freq_check_values():
+    """Configuration A's table (theta 1e4, head size 16, llama3 factor 8, low 1, high 4, original
+    length 64): one frequency kept, two blended, five divided by 8."""
+    from mini_infer_b200.parts.builtin import rotary_inv_freq
+
+    cfg = P.normalise_config(TINY["A"])
+    want = [1.0, 2.4438e-01, 1.3042e-02, 3.9528e-03, 1.2500e-03, 3.9528e-04, 1.2500e-04, 3.9528e-05]
+    for table in (P.rope_inv_freq(16, 10000.0, cfg["_scaling"]), rotary_inv_freq(16, 10000.0, None, cfg["_scaling"])):
+        assert np.allclose(table.numpy(), want, rtol=1e-4)
 
 
 def test_llama3_rescale_has_three_bands():

@@ -357,3 +357,52 @@ def test_lookahead_random_arrivals_match_the_plain_scheduler(seed):
     ahead, sched = run(True)
     assert ahead == plain
     assert sched.wasted_tokens <= len(eos)
+
+
+def test_a_kernel_that_gave_up_waiting_cancels_the_step_and_raises():
+    """The runner's health word is read with every step's tokens.  When it is set the tokens of
+    that step are thrown away, its requests end as cancelled with their pages back, the runner
+    is reset, and the error reaches whoever drives the engine; afterwards the engine works."""
+    import torch
+
+    from mini_infer_b200.engine.scheduler import EngineFaultError
+
+    runner, sched = make(max_tokens_per_step=64, chunk_size=64)
+    word = torch.zeros(1, dtype=torch.int32)
+    resets = []
+    runner.health_word = lambda: word
+    runner.reset_health = lambda: (resets.append(True), word.zero_())
+    handles = [sched.submit(Request(prompt(n), SamplingParams(), 6)) for n in (5, 9)]
+    assert sched.step() and sched.step()
+    emitted_before = [len(h._rr.generated) for h in handles]
+    word.fill_(1)                                  # "a wait gave up" during the next step
+    with pytest.raises(EngineFaultError, match="gave up"):
+        sched.step()
+    assert resets == [True] and int(word[0]) == 0
+    assert all(h.finished and h.wait().finish_reason == "cancelled" for h in handles)
+    assert [len(h.wait().tokens) for h in handles] == emitted_before      # nothing from the bad step
+    assert runner.cache.num_requests == 0 and runner.cache.num_free_pages() == 64
+    runner.cache.check()
+    res = sched.generate([Request(prompt(4), SamplingParams(), 3)])[0]
+    assert res.finish_reason == "length" and len(res.tokens) == 3
+
+
+def test_streaming_callback_may_call_back_into_the_scheduler():
+    """Callbacks run outside the scheduler's lock: one that cancels its own request, asks for
+    the load and submits another request does not deadlock."""
+    runner, sched = make(max_tokens_per_step=64, chunk_size=64)
+    seen, later = [], []
+
+    def on_token(tok):
+        seen.append(tok)
+        assert sched.load_stats().block_size == 4
+        if len(seen) == 3:
+            later.append(sched.submit(Request(prompt(2), SamplingParams(), 2)))
+            handle.cancel()
+
+    handle = sched.submit(Request(prompt(7), SamplingParams(), 50), on_token=on_token)
+    sched.run_until_done()
+    res = handle.wait()
+    assert res.finish_reason == "cancelled" and res.tokens == seen and len(seen) == 3
+    assert later[0].wait().finish_reason == "length"
+    assert runner.cache.num_requests == 0

@@ -119,3 +119,55 @@ def test_random_weights_are_seeded_and_shaped(tmp_path):
         model = model_for(TINY_B)
         check_names(model, {n: ck.shape(n) for n in ck.names()})
         assert ck.dtype("model.embed_tokens.weight") == torch.bfloat16
+
+
+def test_random_generator_is_counter_based_and_exact():
+    """The stream of a tensor depends on (seed, name, element index) only: the integer hash
+    agrees with the same formula on Python integers (so nothing hangs on how a device wraps
+    int64 products), a tensor drawn in pieces equals the tensor drawn at once, and the values
+    are normal with the asked width."""
+    from mini_infer_b200.weights import random_init as R
+
+    key = R.tensor_seed(5, "model.layers.0.mlp.up_proj.weight")
+    assert key == R.tensor_seed(5, "model.layers.0.mlp.up_proj.weight") != R.tensor_seed(6, "model.layers.0.mlp.up_proj.weight")
+    index = torch.tensor([0, 1, 2, 12345, 2 ** 31, 2 ** 40 + 17], dtype=torch.int64)
+    got = R.hash_bits(key, index).tolist()
+    for i, g in zip(index.tolist(), got):
+        assert g & ((1 << 64) - 1) == R.hash_bits_exact(key, i)
+    whole = R.standard_normal(key, 0, 5000)
+    pieces = torch.cat([R.standard_normal(key, 0, 1234), R.standard_normal(key, 1234, 5000 - 1234)])
+    assert torch.equal(whole, pieces)
+    z = R.standard_normal(key, 0, 200_000)
+    assert abs(z.mean().item()) < 0.01 and abs(z.std().item() - 1.0) < 0.01
+    assert abs((z ** 4).mean().item() - 3.0) < 0.1                      # a normal's fourth moment
+    assert abs(((z.abs() > 1.959964).double().mean().item()) - 0.05) < 0.003
+    assert abs((z[:-1] * z[1:]).mean().item()) < 0.01                   # neighbours do not correlate
+    # the series used instead of library functions are accurate to a few ulps
+    x = torch.rand(10_000, dtype=torch.float64) * 4e9 + 0.5
+    assert (R._log_of(x) - torch.log(x)).abs().max().item() < 1e-13
+    a = torch.linspace(0, 3.141592653589793 / 2, 10_001, dtype=torch.float64)
+    assert (R._sin_quarter(a) - torch.sin(a)).abs().max().item() < 1e-14
+    # a tensor larger than one chunk is drawn chunk by chunk and comes out the same
+    t = R.random_tensor(1, "t", (3, 70_001), "matrix", std=0.02, gain_std=0.1)
+    old, R._CHUNK = R._CHUNK, 4096
+    try:
+        assert torch.equal(R.random_tensor(1, "t", (3, 70_001), "matrix", std=0.02, gain_std=0.1), t)
+    finally:
+        R._CHUNK = old
+    g = R.random_tensor(1, "g", (1000,), "gain", std=0.02, gain_std=0.1)
+    assert abs(g.mean().item() - 1.0) < 0.02 and abs(g.std().item() - 0.1) < 0.02
+
+
+@pytest.mark.gpu
+def test_random_weights_are_the_same_on_cpu_and_gpu():
+    """Bit for bit, in float32 and in bfloat16, for a matrix of odd size and a gain."""
+    from mini_infer_b200.weights import random_init as R
+
+    for shape, role in (((513, 1031), "matrix"), ((4097,), "gain"), ((1 << 22) + 5, "matrix")):
+        shape = shape if isinstance(shape, tuple) else (shape,)
+        for dtype in (torch.float32, torch.bfloat16):
+            cpu = R.random_tensor(7, "w", shape, role, std=0.02, gain_std=0.1, dtype=dtype)
+            gpu = R.random_tensor(7, "w", shape, role, std=0.02, gain_std=0.1, dtype=dtype, device="cuda:0")
+            assert torch.equal(cpu, gpu.cpu()), (shape, role, dtype)
+    key = R.tensor_seed(7, "w")
+    assert torch.equal(R.standard_normal(key, 10, 100_000), R.standard_normal(key, 10, 100_000, "cuda:0").cpu())

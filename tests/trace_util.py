@@ -180,6 +180,17 @@ def max_err(got: dict[str, np.ndarray], want: dict[str, np.ndarray]) -> tuple[fl
     return err, scale
 
 
+# Largest allowed |logit difference|.  float32: rounding of a few hundred fp32 operations,
+# relative to max(1, largest |reference logit|).  bfloat16: one percent of the largest
+# |reference logit| itself, with no floor: activations are rounded to 8 bits of mantissa about
+# six times per layer, which gives errors of a few thousandths of the logit scale at these
+# depths (0.3 to 0.5 percent observed), while a wrong key, position or page gives tens of percent.
+def tolerance(dtype: str, largest_logit: float) -> float:
+    if dtype == "float32":
+        return 1e-4 * max(1.0, largest_logit)
+    return 1e-2 * largest_logit
+
+
 def first_bad(got: np.ndarray, want: np.ndarray, tol: float) -> int | None:
     bad = np.nonzero(np.abs(got - want).max(axis=1) > tol)[0]
     return int(bad[0]) if bad.size else None
