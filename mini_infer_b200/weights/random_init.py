@@ -10,9 +10,9 @@ engine, a float32 engine and a plain fp32 implementation all see exactly the sam
 
 *The same numbers on every device.*  An element's value depends on nothing but the seed, the
 tensor's name and the element's index, and it is computed with integer arithmetic and with
-float64 additions, multiplications, divisions and square roots only, each a separate,
-correctly rounded operation: the logarithm, the sine and the cosine of the Box-Muller
-transform are evaluated by their own short series here instead of by a math library, whose
+float64 additions, multiplications and divisions only, each a separate, correctly rounded
+operation: the logarithm, the square root and the sine of the Box-Muller transform are
+evaluated by their own short series and iterations here instead of by a math library, whose
 results differ between a CPU and a GPU in the last bit.  So a tensor drawn on a GPU (a
 benchmark's 16 GB of weights never exist on the host) is bit for bit the tensor the CPU
 draws, and a plain implementation on the CPU can be handed weights made on the device.
@@ -102,6 +102,17 @@ def _log_of(x: torch.Tensor) -> torch.Tensor:
     return e.to(torch.float64) * _LN2 + 2.0 * s * acc
 
 
+def _sqrt_of(x: torch.Tensor) -> torch.Tensor:
+    """Square root of positive float64 numbers by Newton's iteration from a guess made on the
+    bit pattern (halving the exponent): divisions, additions and halvings only, so every
+    device takes the same steps to the same bits.  (A library square root is not used: the
+    CPU's and the GPU's were seen to differ in the last bit.)"""
+    y = ((x.view(torch.int64) >> 1) + (1023 << 51)).view(torch.float64)       # within a few percent
+    for _ in range(6):
+        y = (y + x / y) * 0.5
+    return y
+
+
 def _sin_quarter(x: torch.Tensor) -> torch.Tensor:
     """``sin x`` for ``0 <= x <= pi / 2`` as its Taylor polynomial (exact operations only)."""
     x2 = x * x
@@ -122,7 +133,7 @@ def standard_normal(key: int, start: int, count: int, device="cpu") -> torch.Ten
     hi = _shr(z, 32)
     lo = z & 0xFFFF_FFFF
     log_u = _log_of(hi.to(torch.float64) + 0.5) - 32.0 * _LN2
-    radius = torch.sqrt(log_u * -2.0)
+    radius = _sqrt_of(log_u * -2.0)
     turn = (lo + (1 << 30)) & 0xFFFF_FFFF            # a quarter turn further: cos -> sin
     quadrant = turn >> 30
     within = turn & ((1 << 30) - 1)

@@ -147,6 +147,8 @@ def test_random_generator_is_counter_based_and_exact():
     assert (R._log_of(x) - torch.log(x)).abs().max().item() < 1e-13
     a = torch.linspace(0, 3.141592653589793 / 2, 10_001, dtype=torch.float64)
     assert (R._sin_quarter(a) - torch.sin(a)).abs().max().item() < 1e-14
+    r = torch.rand(10_000, dtype=torch.float64) * 45 + 1e-10
+    assert ((R._sqrt_of(r) - torch.sqrt(r)).abs() / torch.sqrt(r)).max().item() < 1e-15
     # a tensor larger than one chunk is drawn chunk by chunk and comes out the same
     t = R.random_tensor(1, "t", (3, 70_001), "matrix", std=0.02, gain_std=0.1)
     old, R._CHUNK = R._CHUNK, 4096
