@@ -16,6 +16,11 @@ A "step" is one decode step of a batch of 8 requests, each holding 2,048 tokens 
 ``points``     decode tokens/s at batch 1 and 64;
 ``clocks``     SM clocks and throttle reasons sampled during the timed regions.
 
+``--scenario serving`` is the workload the reference published numbers for (1,024-token
+prompts, 128 generated tokens, five single requests and one batch of 16, through the
+scheduler's engine thread; ``scripts/bench/modal_model_metrics.py:59-63,126-204``), for either
+arm, as a line of its own.
+
 Weights are far larger than L2, so nothing is flushed between timed iterations
 (``config.l2``).  The engine is single-GPU: ``--gpus N`` with N > 1 prints one line and
 exits with status 2.
@@ -56,11 +61,12 @@ LLAMA_8B = {
     "tie_word_embeddings": False,
 }
 # The same architecture at Llama 3.1 70B's layer sizes (a further measurement point,
-# ``--sizes 70b``; loading builds the merged matrices beside the checkpoint's, so the default
-# takes fewer layers than the model has and the line names both numbers).
+# ``--sizes 70b``: 141 GB of weights, drawn on the device part by part; ``--context 4096`` is
+# the context the benchmark's description names for it).
 LLAMA_70B = dict(LLAMA_8B, hidden_size=8192, intermediate_size=28672, num_hidden_layers=80,
                  num_attention_heads=64)
-SIZES = {"8b": ("Llama 3.1 8B", LLAMA_8B, 32), "70b": ("Llama 3.1 70B", LLAMA_70B, 20)}
+SIZES = {"8b": ("Llama 3.1 8B", LLAMA_8B, 32), "70b": ("Llama 3.1 70B", LLAMA_70B, 80)}
+POINTS = {"8b": (1, 64), "70b": (1,)}      # further batch sizes measured beside the headline's
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
 PAGE = 16
@@ -364,22 +370,33 @@ def reference_arm(args) -> int:
     return 0
 
 
-def _reference_measure(args, ref: str) -> dict:
+class _IdTokenizer:
+    """Stands in for a text tokenizer where the reference's scheduler wants one: a prompt is its
+    token ids written as decimal numbers."""
+
+    eos_token_id = -1
+
+    def encode(self, text):
+        return [int(t) for t in text.split()]
+
+    def decode(self, ids):
+        return " ".join(str(int(i)) for i in ids)
+
+
+def _reference_runner(ref: str, layers: int, num_blocks: int, prefill_graph: bool):
+    """The reference's own model, pool and runner at the benchmark's sizes, random bf16 weights."""
     os.environ.setdefault("HF_HUB_OFFLINE", "1")
     os.environ.setdefault("TRANSFORMERS_OFFLINE", "1")
-    sys.path.insert(0, ref)
+    if ref not in sys.path:
+        sys.path.insert(0, ref)
     from types import SimpleNamespace
 
     import torch
     from mini_infer.cache.block_pool import BlockPool
     from mini_infer.cache.packed_attention import effective_attention_backend
-    from mini_infer.cache.paged_kv_cache import PagedKVCache
     from mini_infer.engine.model_runner import ModelRunner
-    from mini_infer.engine.sampler import SamplingParams, sample_tokens
     from mini_infer.models.llama.llama import LlamaConfig, LlamaForCausalLM
 
-    warmup = max(3, args.warmup)
-    batch, steps, layers = args.batch, args.steps, args.layers
     raw = dict(LLAMA_8B, num_hidden_layers=layers)
     cfg = LlamaConfig.from_hf(SimpleNamespace(**raw))
     torch.manual_seed(0)
@@ -396,15 +413,190 @@ def _reference_measure(args, ref: str) -> dict:
             if prm.dim() == 2:
                 prm.normal_(0.0, 0.02)
     backend = "flashinfer" if effective_attention_backend("flashinfer", "cuda", None) == "flashinfer" else "flash_attn"
-    tokens_cap = batch * (CONTEXT + steps + warmup + 64)
-    pool = BlockPool(num_blocks=tokens_cap // PAGE + 8, block_size=PAGE, num_layers=cfg.num_hidden_layers,
+    pool = BlockPool(num_blocks=num_blocks, block_size=PAGE, num_layers=cfg.num_hidden_layers,
                      num_kv_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim, dtype=torch.bfloat16,
                      device="cuda", attention_backend=backend)
-    runner = ModelRunner(model=model, tokenizer=None, device="cuda", block_pool=pool)
-    graph = False
-    if backend == "flashinfer":
-        runner.enable_decode_graph()
-        graph = True
+    runner = ModelRunner(model=model, tokenizer=_IdTokenizer(), device="cuda", block_pool=pool)
+    graphs = []
+    if backend == "flashinfer":          # the reference's published configuration (its decode and prefill graphs)
+        for name, enable in (("decode", runner.enable_decode_graph),
+                             ("prefill", runner.enable_prefill_graph if prefill_graph else None)):
+            if enable is None:
+                continue
+            try:
+                enable()
+                graphs.append(name)
+            except (ValueError, AttributeError):
+                pass
+    return runner, cfg, backend, graphs
+
+
+def _serving_numbers(run_together, single_requests: int, concurrency: int, out_tokens: int) -> dict:
+    """The reference's published workload (``scripts/bench/modal_model_metrics.py:126-204``):
+    warm-up, then ``single_requests`` requests one after the other (median time to the first
+    token, median decode speed after it) and one batch of ``concurrency`` started together
+    (tokens a second over the batch's wall time, median time to the first token)."""
+    for index in (100, 101):
+        run_together([index], 16)
+    run_together(list(range(200, 200 + concurrency)), 16)
+    single = [run_together([index], out_tokens)[0] for index in range(single_requests)]
+    batch = run_together(list(range(10, 10 + concurrency)), out_tokens)
+    wall = max(r["times"][-1] for r in batch) - min(r["submit"] for r in batch)
+    total = sum(len(r["times"]) for r in batch)
+    return {
+        "single": {
+            "ttft_ms": round(statistics.median((r["times"][0] - r["submit"]) * 1000 for r in single), 2),
+            "decode_tok_s": round(statistics.median((len(r["times"]) - 1) / (r["times"][-1] - r["times"][0])
+                                                    for r in single), 1),
+            "requests": single_requests,
+        },
+        "batch": {
+            "concurrency": concurrency, "throughput_tok_s": round(total / wall, 1),
+            "ttft_p50_ms": round(statistics.median((r["times"][0] - r["submit"]) * 1000 for r in batch), 2),
+            "mean_output_tokens": round(total / len(batch), 1),
+        },
+    }
+
+
+SERVING_PROMPT, SERVING_OUTPUT, SERVING_SINGLE, SERVING_CONCURRENCY = 1024, 128, 5, 16
+
+
+def _serving_prompt(index: int, vocab: int) -> list[int]:
+    import torch
+
+    gen = torch.Generator().manual_seed(5000 + index)
+    return torch.randint(0, vocab, (SERVING_PROMPT,), generator=gen).tolist()
+
+
+def serving_ours(args) -> dict:
+    import torch
+
+    from mini_infer_b200.engine import ContinuousScheduler, Request
+    from mini_infer_b200.sampling import SamplingParams
+
+    _, cfg, _ = SIZES[args.sizes]
+    # 2048 pages of 16 tokens hold 16 requests of 1,152 tokens with room to spare (the reference's pool)
+    runner = build_runner(cfg, args.layers, num_blocks=2048, max_requests=SERVING_CONCURRENCY)
+    sched = ContinuousScheduler(runner, max_concurrent=SERVING_CONCURRENCY)
+    sched.start()
+
+    def run_together(indices, max_tokens):
+        records = [{} for _ in indices]
+        handles = []
+        for rec, index in zip(records, indices):
+            rec["submit"] = time.perf_counter()
+            rec["times"] = []
+            handles.append(sched.submit(Request(_serving_prompt(index, cfg["vocab_size"]), SamplingParams(), max_tokens),
+                                        on_token=lambda tok, rec=rec: rec["times"].append(time.perf_counter())))
+        for h in handles:
+            h.wait(timeout=600)
+        return records
+
+    clocks = ClockSampler()
+    clocks.start()
+    try:
+        numbers = _serving_numbers(run_together, SERVING_SINGLE, SERVING_CONCURRENCY, SERVING_OUTPUT)
+    finally:
+        sched.stop()
+    torch.cuda.synchronize()
+    numbers["clocks"] = clocks.stop()
+    numbers["path"] = "paged cache, own kernels, captured decode steps, decode look-ahead"
+    return numbers
+
+
+def serving_reference(args, ref: str) -> dict:
+    import threading
+
+    runner, cfg, backend, graphs = _reference_runner(ref, args.layers, num_blocks=2048, prefill_graph=True)
+    from mini_infer.engine.sampler import SamplingParams
+    from mini_infer.scheduler import ContinuousScheduler, Request
+
+    sched = ContinuousScheduler(runner, max_concurrent=SERVING_CONCURRENCY)
+    sched.start()
+    tok = _IdTokenizer()
+
+    def one(index, max_tokens, rec):
+        request = Request(prompt=tok.decode(_serving_prompt(index, cfg.vocab_size)),
+                          sampling_params=SamplingParams(), max_tokens=max_tokens)
+        rec["submit"] = time.perf_counter()
+        rec["times"] = []
+        handle = sched.submit(request)
+        while True:
+            step = handle.get_step(timeout=600)
+            if step.failed:
+                raise RuntimeError(f"request {index} failed")
+            rec["times"].extend([time.perf_counter()] * step.num_tokens)
+            if step.finish_reason is not None:
+                break
+
+    def run_together(indices, max_tokens):
+        records = [{} for _ in indices]
+        threads = [threading.Thread(target=one, args=(i, max_tokens, r)) for i, r in zip(indices, records)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        if any(not r.get("times") for r in records):
+            raise RuntimeError("a request of the reference arm produced nothing")
+        return records
+
+    clocks = ClockSampler()
+    clocks.start()
+    try:
+        numbers = _serving_numbers(run_together, SERVING_SINGLE, SERVING_CONCURRENCY, SERVING_OUTPUT)
+    finally:
+        sched.stop()
+    numbers["clocks"] = clocks.stop()
+    numbers["path"] = f"paged, {backend} attention, graphs: {', '.join(graphs) or 'none'}"
+    return numbers
+
+
+def run_serving(args) -> int:
+    model_name, cfg, _ = SIZES[args.sizes]
+    line = {"scenario": "serving", "impl": args.impl,
+            "metric": "reference-shaped serving: time to first token, single-request decode tok/s, tok/s of 16 together",
+            "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (uniform token ids, no end-of-sequence id)",
+            "config": {"model": model_name.replace(" ", "-") + " sizes, random weights", "layers": args.layers,
+                       "layers_of_model": cfg["num_hidden_layers"], "prompt_tokens": SERVING_PROMPT,
+                       "output_tokens": SERVING_OUTPUT, "single_requests": SERVING_SINGLE,
+                       "concurrency": SERVING_CONCURRENCY, "page_size": PAGE, "pool_pages": 2048},
+            "published_by_the_reference": {"single_decode_tok_s": 276.0, "batch_throughput_tok_s": 2668.0,
+                                           "ttft_ms": 34.0, "where": "docs/benchmarks/2026-11-05-model-metrics.md:55"}}
+    if args.impl == "reference":
+        ref = os.path.join(ROOT, "baseline", "_ref")
+        if not os.path.isdir(os.path.join(ref, "mini_infer")):
+            print(json.dumps({"impl": "reference", "scenario": "serving",
+                              "unavailable": "the reference is not installed under baseline/_ref"}))
+            return 0
+        try:
+            line.update(serving_reference(args, ref))
+        except Exception as e:  # noqa: BLE001
+            line = {"impl": "reference", "scenario": "serving",
+                    "unavailable": f"{type(e).__name__}: {str(e)[:300]}".replace("\n", " ")}
+    else:
+        line.update(serving_ours(args))
+    if "batch" in line:
+        line["value"] = line["batch"]["throughput_tok_s"]
+    print(json.dumps(line))
+    return 0
+
+
+def _reference_measure(args, ref: str) -> dict:
+    import threading
+
+    import torch
+
+    warmup = max(3, args.warmup)
+    batch, steps, layers = args.batch, args.steps, args.layers
+    tokens_cap = batch * (CONTEXT + 2 * (steps + warmup) + 128)
+    runner, cfg, backend, graphs = _reference_runner(ref, layers, num_blocks=tokens_cap // PAGE + 8 * batch + 8,
+                                                     prefill_graph=False)
+    from mini_infer.cache.paged_kv_cache import PagedKVCache
+    from mini_infer.engine.sampler import SamplingParams, sample_tokens
+    from mini_infer.scheduler import ContinuousScheduler, Request
+
+    graph = "decode" in graphs
+    pool = runner.block_pool
     cache = PagedKVCache(pool)
     for _ in range(batch):
         cache.add_request_slot()
@@ -435,12 +627,40 @@ def _reference_measure(args, ref: str) -> dict:
     end.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(end) / steps
-    # end to end: host ids in, sampled ids read back every step
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        ids = one(ids).tolist()
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
+    cache.free()
+    del cache
+    # End to end through the reference's own scheduler (its engine thread, its sampling on the
+    # device with ids read a step late): `batch` requests of CONTEXT prompt tokens are submitted
+    # together; once every one of them has produced `warmup` tokens the clock runs until every
+    # one has produced `steps` more.  Host token ids in (the prompts), sampled ids out per step.
+    sched = ContinuousScheduler(runner, max_concurrent=batch)
+    sched.start()
+    tok = _IdTokenizer()
+    want = warmup + steps
+    stamps: list[list[float]] = [[] for _ in range(batch)]
+
+    def follow(i):
+        handle = sched.submit(Request(prompt=tok.decode(prompts[i]), sampling_params=SamplingParams(),
+                                      max_tokens=want + 4))
+        while True:
+            step = handle.get_step(timeout=600)
+            if step.failed:
+                raise RuntimeError("a request of the reference arm failed")
+            stamps[i].extend([time.perf_counter()] * step.num_tokens)
+            if step.finish_reason is not None:
+                break
+
+    threads = [threading.Thread(target=follow, args=(i,)) for i in range(batch)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    sched.stop()
+    if any(len(st) < want for st in stamps):
+        raise RuntimeError("the reference's scheduler produced fewer tokens than asked for")
+    t_a = max(st[warmup - 1] for st in stamps)
+    t_b = max(st[want - 1] for st in stamps)
+    dt = t_b - t_a
     value = batch * 1000.0 / ms
     return {
         "metric": "decode tok/s @ batch 8, 2048-token context (Llama 3.1 8B layer sizes)",
@@ -450,7 +670,8 @@ def _reference_measure(args, ref: str) -> dict:
         "config": {"model": "Llama-3.1-8B sizes, random weights", "layers": layers,
                    "layers_of_model": LLAMA_8B["num_hidden_layers"], "global_batch": batch, "seq_len": CONTEXT,
                    "page_size": PAGE, "attention_backend": backend, "cuda_graph": graph,
-                   "parallelism": "single GPU", "l2": "inputs (weights) larger than L2, no flush"},
+                   "parallelism": "single GPU", "l2": "inputs (weights) larger than L2, no flush",
+                   "e2e_path": "the reference's ContinuousScheduler (engine thread, asynchronous sampling)"},
         "e2e": {"value": round(batch * steps / dt, 2), "unit": "tokens/s", "ms_per_step": round(1000.0 * dt / steps, 3),
                 "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 8 * batch},
         "clocks": clocks.stop(),
@@ -469,9 +690,10 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when decoding starts")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 and e2e measurements")
-    ap.add_argument("--scenario", default="decode", choices=["decode", "long-mixed"],
+    ap.add_argument("--scenario", default="decode", choices=["decode", "long-mixed", "serving"],
                     help="decode: the contract line; long-mixed: many requests of very different lengths "
-                         "through the scheduler (a line of its own)")
+                         "through the scheduler (a line of its own); serving: the reference's published "
+                         "workload, 1024 tokens in and 128 out, single requests and 16 together (a line of its own)")
     ap.add_argument("--requests", type=int, default=64, help="long-mixed: requests started together")
     ap.add_argument("--max-prompt", type=int, default=32768, help="long-mixed: longest prompt")
     ap.add_argument("--generate", type=int, default=256, help="long-mixed: tokens generated per request")
@@ -483,6 +705,12 @@ def main() -> int:
     model_name, cfg, default_layers = SIZES[args.sizes]
     if args.layers is None:
         args.layers = default_layers
+    if args.scenario == "serving":
+        if args.impl == "reference" and args.sizes != "8b":
+            print(json.dumps({"impl": "reference", "scenario": "serving",
+                              "unavailable": "the reference arm runs the 8B sizes only"}))
+            return 0
+        return run_serving(args)
     if args.impl == "reference":
         if args.sizes != "8b" or args.scenario != "decode" or args.context != CONTEXT:
             print(json.dumps({"impl": "reference", "unavailable": "the reference arm measures the contract's "
@@ -499,7 +727,8 @@ def main() -> int:
 
     layers, batch, context = args.layers, args.batch, args.context
     peaks = load_peaks()
-    max_batch = batch if args.skip_points else max(batch, 64)
+    point_batches = () if args.skip_points else POINTS[args.sizes]
+    max_batch = max((batch, *point_batches))
     tokens_cap = max_batch * (context + args.steps + warmup + 2 * batch + 64)
     runner = build_runner(cfg, layers, num_blocks=tokens_cap // PAGE + 8, max_requests=max_batch)
 
@@ -509,7 +738,7 @@ def main() -> int:
     points, e2e, prefill = {}, None, None
     prefill_ms = time_prefill(runner, PREFILL_TOKENS, repeats=3, warmup=2)
     if not args.skip_points:
-        for b in (1, 64):
+        for b in point_batches:
             pms, _ = time_decode(runner, b, context, args.steps, warmup)
             points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
         e2e = time_e2e(runner, batch, context, args.steps, warmup)

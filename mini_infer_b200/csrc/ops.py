@@ -111,12 +111,13 @@ def recover_from_wait_failure(device: torch.device) -> None:
     """After a give-up: clear the status word and the arrival counters that the interrupted
     kernels may have left non-zero (they are zero between calls otherwise).  Synchronises."""
     torch.cuda.synchronize(device)
-    status_word(device).zero_()
-    idx = _device_index(device)
-    for buf in _decode_counter_bufs.get(idx, []):
-        buf.zero_()
-    for _partials, counters in _tma_ws.get(idx, []):
-        counters.zero_()
+    with torch.inference_mode():      # the buffers were made inside a step, which runs in inference mode
+        status_word(device).zero_()
+        idx = _device_index(device)
+        for buf in _decode_counter_bufs.get(idx, []):
+            buf.zero_()
+        for _partials, counters in _tma_ws.get(idx, []):
+            counters.zero_()
     torch.cuda.synchronize(device)
 
 

@@ -342,8 +342,9 @@ class ContinuousScheduler:
             health = self._queue_health_read()
             ids = [int(t) for t in (ids.tolist() if hasattr(ids, "tolist") else ids)]
         else:
-            health = self._queue_health_read()
-            ids = []
+            # nothing is read back from this step, so nothing waits for it here; the health
+            # word stays set once it is, and the next step that hands out tokens reads it
+            health, ids = None, []
         self._check_health(health, owners)
         emitted: list = []
         with self._lock:

@@ -127,6 +127,37 @@ def test_decode_lookahead_gives_the_same_tokens(model_dirs, cuda_graph):
     assert "stop" in ahead_why and sched.wasted_tokens >= 1
 
 
+def test_engine_thread_streams_the_same_tokens(model_dirs):
+    """The engine loop on a thread of its own (``start`` / ``stop``): requests submitted from
+    this thread while it runs, tokens streamed through callbacks, the runner's health word read
+    with every step; same tokens as the plain implementation."""
+    from mini_infer_b200.engine import ContinuousScheduler, ModelRunner, Request
+    from mini_infer_b200.sampling import SamplingParams
+
+    which = "C"
+    state = load_state(model_dirs[which])
+    prompts = [prompt_ids(which, n, salt=20 + i) for i, n in enumerate([30, 5, 70])]
+    want = [P.greedy_generate(state, TINY[which], p, 12) for p in prompts]
+    for dtype, graph in (("float32", False), ("bfloat16", True)):
+        runner = ModelRunner.from_pretrained(model_dirs[which], dtype=dtype, block_size=16, num_blocks=32,
+                                             max_requests=4, cuda_graph=graph)
+        sched = ContinuousScheduler(runner, chunk_size=32, max_tokens_per_step=48)
+        sched.start()
+        try:
+            streamed = [[] for _ in prompts]
+            handles = [sched.submit(Request(p, SamplingParams(), 12), on_token=streamed[i].append)
+                       for i, p in enumerate(prompts)]
+            results = [h.wait(timeout=300) for h in handles]
+        finally:
+            sched.stop()
+        assert [r.tokens for r in results] == streamed
+        assert all(r.finish_reason == "length" for r in results)
+        if dtype == "float32":
+            assert streamed == want
+        assert int(runner.health_word().item()) == 0
+        assert runner.cache.num_requests == 0 and runner.cache.num_free_pages() == 32
+
+
 def test_preemption_by_recompute_gives_the_same_tokens(model_dirs):
     from mini_infer_b200.engine import ContinuousScheduler, ModelRunner, Request
     from mini_infer_b200.sampling import SamplingParams
