@@ -586,6 +586,434 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                            n_splits, head0, heads_here);
 }
 
+// ------------------------------------------------------------------------------- decode, balanced
+//
+// The same arithmetic with the work cut evenly.  attention_decode_kernel gives every (request,
+// head group) the same number of key slices; when requests differ in length, or when the
+// number of blocks that comes out does not fill the GPU's block slots evenly, some SMs stream
+// a multiple of what others do.  Here the 64-key chunks of all (request, head group) units are
+// numbered in one row, unit after unit, and each of G persistent blocks takes an equal
+// contiguous stretch of that row, whatever the lengths are: one long request among short ones
+// is spread over many blocks, many short ones share a block.  A block walks its stretch unit
+// by unit; for a unit it holds completely it writes the output; otherwise it parks its partial
+// result and adds the chunks it did to the unit's counter, and the block that brings the
+// counter to the unit's chunk count merges the stretches in block order.  The copy warp runs
+// ahead across unit boundaries, so the ring of stages never drains inside a block.
+//
+// Scratch: slot (unit + block) is unique and increases along the row, so part_o holds
+// (units + G) * 8 * d floats, part_ml (units + G) * 8 * 2, counters one int per unit (zero
+// between calls).  No host-side plan: the blocks work the stretches out from kv_len themselves.
+
+// Position i of the row -> request b, unit u within the request, chunk c_rel within the unit.
+__device__ __forceinline__ void balanced_locate(long long i, const int* cum, int B, int U, int& b, int& u,
+                                                int& c_rel, int& n_b) {
+  int lo = 0, hi = B - 1;
+  while (lo < hi) {   // the largest b with cum[b] * U <= i (requests without chunks are passed over)
+    const int mid = (lo + hi + 1) >> 1;
+    if ((long long)cum[mid] * U <= i) lo = mid;
+    else hi = mid - 1;
+  }
+  b = lo;
+  n_b = cum[b + 1] - cum[b];
+  const long long r = i - (long long)cum[b] * U;
+  u = (int)(r / n_b);
+  c_rel = (int)(r - (long long)u * n_b);
+}
+
+// The stretches g_first .. g_last of one unit into its output row (head r of the unit's group,
+// this thread's columns cgrp, cgrp + 16, ...), in block order.  Out of line: its many loads in
+// flight need registers that the main loop's accumulators would otherwise have to share.
+template <int DMAX>
+__device__ __noinline__ void balanced_merge_unit(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                 int unit, int g_first, int g_last, int r, int cgrp, int d,
+                                                 bf16* __restrict__ orow) {
+  const float2* ml = reinterpret_cast<const float2*>(part_ml);
+  float mm = -INFINITY, LL = 0.f, acc[DMAX / 16];
+#pragma unroll
+  for (int k = 0; k < DMAX / 16; ++k) acc[k] = 0.f;
+  if (g_last - g_first < 8 && DMAX <= 128) {
+    // Few stretches (the usual case): everything this thread needs is asked for before any of it
+    // is used, so the merge costs one round trip to the L2.
+    float2 v[8];
+    float po[8][DMAX <= 128 ? DMAX / 16 : 1];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const bool live = g_first + k <= g_last;
+      const size_t slot = ((size_t)unit + g_first + k) * DEC_HEADS + r;
+      v[k] = live ? __ldcg(ml + slot) : make_float2(-INFINITY, 0.f);
+#pragma unroll
+      for (int c = 0; c < (DMAX <= 128 ? DMAX / 16 : 1); ++c)
+        po[k][c] = (live && cgrp + 16 * c < d) ? __ldcg(part_o + slot * d + cgrp + 16 * c) : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) mm = fmaxf(mm, v[k].x);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float fk = (v[k].x == -INFINITY) ? 0.f : exp2f(v[k].x - mm);
+      LL += v[k].y * fk;
+#pragma unroll
+      for (int c = 0; c < (DMAX <= 128 ? DMAX / 16 : 1); ++c) acc[c] += fk != 0.f ? fk * po[k][c] : 0.f;
+    }
+  } else {
+    for (int gb = g_first; gb <= g_last; gb += 8) {   // eight stretches' (max, sum) in flight at a time
+      float2 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        v[k] = gb + k <= g_last ? __ldcg(ml + ((size_t)unit + gb + k) * DEC_HEADS + r) : make_float2(-INFINITY, 0.f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) mm = fmaxf(mm, v[k].x);
+    }
+    for (int gb = g_first; gb <= g_last; gb += 4) {   // four stretches' columns in flight at a time
+      float2 v[4];
+      float po[4][DMAX / 16];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const bool live = gb + k <= g_last;
+        const size_t slot = ((size_t)unit + gb + k) * DEC_HEADS + r;
+        v[k] = live ? __ldcg(ml + slot) : make_float2(-INFINITY, 0.f);
+#pragma unroll
+        for (int c = 0; c < DMAX / 16; ++c)
+          po[k][c] = (live && cgrp + 16 * c < d) ? __ldcg(part_o + slot * d + cgrp + 16 * c) : 0.f;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float fk = (v[k].x == -INFINITY) ? 0.f : exp2f(v[k].x - mm);
+        LL += v[k].y * fk;
+#pragma unroll
+        for (int c = 0; c < DMAX / 16; ++c) acc[c] += fk != 0.f ? fk * po[k][c] : 0.f;
+      }
+    }
+  }
+  const float inv = LL > 0.f ? 1.f / LL : 0.f;
+#pragma unroll
+  for (int c = 0; c < DMAX / 16; ++c)
+    if (cgrp + 16 * c < d) orow[cgrp + 16 * c] = __float2bfloat16_rn(acc[c] * inv);
+}
+
+template <int DMAX>
+__global__ void __launch_bounds__(DEC_THREADS, DMAX <= 128 ? 2 : 1)
+attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+                                 const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                                 const int* __restrict__ block_table, int bt_stride,
+                                 const int* __restrict__ table_rows, int page_size, int page_shift,
+                                 const int* __restrict__ q_start, const int* __restrict__ kv_len, int B, int nq,
+                                 int nkv, int d, float scale, int window, int min_chunks,
+                                 float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
+                                 int* __restrict__ status) {
+  mi_pdl_launch_dependents();   // (what this kernel may touch before it waits: see attention_decode_kernel)
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                      // [DEC_STAGES][64][d]
+  bf16* Vs = Ks + DEC_STAGES * KCHUNK * d;                           // [DEC_STAGES][64][d]
+  float* merge_o = reinterpret_cast<float*>(Vs + DEC_STAGES * KCHUNK * d);   // [4][DEC_HEADS][d]
+  int* cum = reinterpret_cast<int*>(merge_o + 4 * DEC_HEADS * d);    // [B + 1] chunks of the requests before b
+  const int swz_mask = mi_swizzle_mask(d, 2);
+  __shared__ float merge_m[4][DEC_HEADS], merge_l[4][DEC_HEADS];
+  __shared__ __align__(8) uint64_t bars[DEC_STAGES], empty[DEC_STAGES];
+  __shared__ int is_last;
+  __shared__ volatile int dead;   // a warp gave up waiting for a copy: everybody leaves at the next common point
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int qd = lane >> 2, t4 = lane & 3;
+  const int g = nq / nkv;
+  const int hblocks = (g + DEC_HEADS - 1) / DEC_HEADS;
+  const int U = nkv * hblocks;
+  if (tid == 0) dead = 0;
+
+  // chunks per request, and their running sum (one warp; B is at most a few hundred)
+  for (int b = tid; b < B; b += DEC_THREADS) {
+    const int kl = kv_len[b];
+    const int lo = window > 0 ? max(0, kl - window) : 0;   // (a window skips the chunks below it)
+    cum[b + 1] = (kl + KCHUNK - 1) / KCHUNK - lo / KCHUNK;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int b0 = 0; b0 < B; b0 += 32) {
+      int v = b0 + lane < B ? cum[b0 + lane + 1] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += up;
+      }
+      if (b0 + lane < B) cum[b0 + lane + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+    if (lane == 0) cum[0] = 0;
+  }
+  __syncthreads();
+  const long long W = (long long)cum[B] * U;
+  // a stretch shorter than min_chunks costs more in set-up and merging than it spreads
+  int G = (int)min((long long)gridDim.x, max((long long)1, W / max(1, min_chunks)));
+  // Requests of one length, and fewer units than blocks: a block count that is a multiple of
+  // the unit count makes every stretch a whole fraction of one unit (no block straddles two
+  // units, every unit has the same number of stretches), which costs fewer partial results
+  // than the last few blocks would bring.
+  {
+    const long long units = (long long)B * U;
+    const int n0 = cum[1];
+    if (units < G && W == units * n0) G = (int)(units * (G / units));
+  }
+  if ((int)blockIdx.x >= G) return;
+  if (status && *reinterpret_cast<volatile int*>(status)) return;   // an earlier block gave up waiting
+  const long long i0 = W * blockIdx.x / G, i1 = W * (blockIdx.x + 1) / G;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES; ++i) {
+      mbar_init(&bars[i], 1);
+      mbar_init(&empty[i], 4);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  if (warp == 4) {
+    // the copy warp: walks the stretch chunk by chunk and keeps the ring full
+    PageLoader loader;
+    const int pieces = 2 * (KCHUNK / PageLoader::piece_rows(page_size, page_shift));
+    bool ok = true, waited = false;
+    int it = 0;
+    for (long long i = i0; i < i1 && ok;) {
+      int b, u, c_rel, n_b;
+      balanced_locate(i, cum, B, U, b, u, c_rel, n_b);
+      const int seg = (int)min((long long)(n_b - c_rel), i1 - i);
+      const int kvh = u / hblocks;
+      const int kl = kv_len[b];
+      const int lo = window > 0 ? max(0, kl - window) : 0;
+      const int* table = block_table + (size_t)(table_rows ? table_rows[b] : b) * bt_stride;
+      for (int s = 0; s < seg && ok; ++s, ++it) {
+        const int c = lo / KCHUNK + c_rel + s, st = it % DEC_STAGES;
+        if (it >= DEC_STAGES)
+          ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty[st], ((it / DEC_STAGES) - 1) & 1, status));
+        if (!ok) break;
+        if (!waited && (c + 1) * KCHUNK >= kl) {   // the chunk with the newest position: written by this step
+          mi_pdl_wait();
+          waited = true;
+        }
+        if (lane == 0) mbar_expect_tx(&bars[st], PageLoader::chunk_bytes(c, lo, kl, d, page_size, page_shift));
+        __syncwarp();
+        for (int t0 = 0; t0 < pieces; t0 += 32) {
+          loader.t = t0 + lane;
+          loader.fetch(table, page_size, page_shift, c, lo, kl);
+          loader.issue(Ks + st * KCHUNK * d, Vs + st * KCHUNK * d, kcache, vcache, page_size, page_shift, c, nkv, kvh,
+                       d, &bars[st]);
+        }
+      }
+      i += seg;
+    }
+    return;
+  }
+
+  mi_pdl_wait();   // the queries come from the kernel before this one
+  const int ksteps = d >> 4;
+  const float sc = scale * LOG2E;
+  const int src0 = (2 * t4) * 4 + (qd >> 1), src1 = (2 * t4 + 1) * 4 + (qd >> 1);
+  const bool odd_head = qd & 1;
+  const int r = tid >> 4, cgrp = tid & 15;   // the merges' layout: 8 heads x 16 threads
+  int it = 0;
+  bool warp_dead = false;   // this warp's wait ran out: it keeps in step with the others but computes nothing more
+  for (long long i = i0; i < i1;) {
+    int b, u, c_rel, n_b;
+    balanced_locate(i, cum, B, U, b, u, c_rel, n_b);
+    const int seg = (int)min((long long)(n_b - c_rel), i1 - i);
+    const int unit = b * U + u;
+    const int kvh = u / hblocks, hb = u - kvh * hblocks;
+    const int heads_here = min(DEC_HEADS, g - hb * DEC_HEADS);
+    const int head0 = kvh * g + hb * DEC_HEADS;
+    const int kl = kv_len[b], tok = q_start[b];
+    const int lo = window > 0 ? max(0, kl - window) : 0;
+
+    // Q as the B operand: lane (qd, t4) holds head qd, dims ks*16 + 2*t4 + {0,1} and + 8
+    uint32_t qb[DMAX / 16][2];
+    {
+      const bf16* qrow = q + (size_t)tok * q_stride + (size_t)(head0 + qd) * d;
+#pragma unroll
+      for (int ks = 0; ks < DMAX / 16; ++ks) {
+        qb[ks][0] = qb[ks][1] = 0u;
+        if (ks < ksteps && qd < heads_here) {
+          qb[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
+          qb[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t4);
+        }
+      }
+    }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[DMAX / 16][4];
+#pragma unroll
+    for (int k = 0; k < DMAX / 16; ++k) o[k][0] = o[k][1] = o[k][2] = o[k][3] = 0.f;
+
+    for (int s = 0; s < seg; ++s, ++it) {
+      const int c = lo / KCHUNK + c_rel + s, buf = it % DEC_STAGES;
+      const bool arrived =
+          !warp_dead && __all_sync(0xffffffffu, mbar_wait_bounded(&bars[buf], (it / DEC_STAGES) & 1, status));
+      if (!arrived && !warp_dead) {
+        warp_dead = true;
+        if (lane == 0) dead = 1;
+      }
+      zero_masked_values<NTHREADS, true>(Vs + buf * KCHUNK * d, c, lo, kl, d);
+      const int key0 = c * KCHUNK + warp * 16;
+      const int kr = lane & 15, vr = (lane & 7) + (lane >> 4) * 8;
+      const int ksw = inpage_of(key0 + kr, page_size, page_shift) & swz_mask;
+      const int vsw = inpage_of(key0 + vr, page_size, page_shift) & swz_mask;
+      const bf16* Kb = Ks + buf * KCHUNK * d + (warp * 16 + kr) * d;
+      const bf16* Vb = Vs + buf * KCHUNK * d + (warp * 16 + vr) * d;
+      if (arrived && key0 < kl && key0 + 16 > lo) {   // (the arithmetic of attention_decode_kernel)
+        constexpr int GROUP = (DMAX / 16) < 8 ? (DMAX / 16) : 8;
+        float sa[4] = {0.f, 0.f, 0.f, 0.f}, s_odd[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int g0 = 0; g0 < DMAX / 16; g0 += GROUP) {
+          uint32_t kf[GROUP][4];
+#pragma unroll
+          for (int k = 0; k < GROUP; ++k)
+            if (g0 + k < ksteps) ldmatrix_x4(kf[k], Kb + ((((g0 + k) * 2 + (lane >> 4)) ^ ksw) << 3));
+#pragma unroll
+          for (int k = 0; k < GROUP; ++k)
+            if (g0 + k < ksteps) {
+              if (k & 1) mma_bf16(s_odd, kf[k], qb[g0 + k][0], qb[g0 + k][1]);
+              else mma_bf16(sa, kf[k], qb[g0 + k][0], qb[g0 + k][1]);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sa[e] += s_odd[e];
+        uint32_t vf[GROUP][4];
+#pragma unroll
+        for (int k = 0; k < GROUP; ++k)
+          if (k < ksteps) ldmatrix_x4_trans(vf[k], Vb + (((k * 2 + ((lane >> 3) & 1)) ^ vsw) << 3));
+        const int j0 = key0 + qd, j1 = j0 + 8;
+        const bool ok0 = j0 < kl && j0 >= lo, ok1 = j1 < kl && j1 >= lo;
+        sa[0] = ok0 ? sa[0] * sc : -INFINITY;
+        sa[1] = ok0 ? sa[1] * sc : -INFINITY;
+        sa[2] = ok1 ? sa[2] * sc : -INFINITY;
+        sa[3] = ok1 ? sa[3] * sc : -INFINITY;
+        float alpha[2], p[4];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          float mx = fmaxf(sa[hh], sa[2 + hh]);
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+          const float m_new = fmaxf(m_run[hh], mx);
+          alpha[hh] = exp2f(m_run[hh] - m_new);
+          p[hh] = exp2f(sa[hh] - m_new);
+          p[2 + hh] = exp2f(sa[2 + hh] - m_new);
+          m_run[hh] = m_new;
+          l_run[hh] = l_run[hh] * alpha[hh] + (p[hh] + p[2 + hh]);
+        }
+        if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+          for (int k = 0; k < DMAX / 16; ++k) {
+            o[k][0] *= alpha[0]; o[k][1] *= alpha[1];
+            o[k][2] *= alpha[0]; o[k][3] *= alpha[1];
+          }
+        }
+        const uint32_t p_lo = pack_bf16(p[0], p[1]), p_hi = pack_bf16(p[2], p[3]);
+        const uint32_t x0 = __shfl_sync(0xffffffffu, p_lo, src0), x1 = __shfl_sync(0xffffffffu, p_lo, src1);
+        const uint32_t y0 = __shfl_sync(0xffffffffu, p_hi, src0), y1 = __shfl_sync(0xffffffffu, p_hi, src1);
+        const uint32_t sel = odd_head ? 0x7632u : 0x5410u;
+        const uint32_t pb0 = __byte_perm(x0, x1, sel), pb1 = __byte_perm(y0, y1, sel);
+#pragma unroll
+        for (int k = 0; k < GROUP; ++k)
+          if (k < ksteps) mma_bf16(o[k], vf[k], pb0, pb1);
+#pragma unroll
+        for (int g0 = GROUP; g0 < DMAX / 16; g0 += GROUP) {
+#pragma unroll
+          for (int k = 0; k < GROUP; ++k)
+            if (g0 + k < ksteps) ldmatrix_x4_trans(vf[k], Vb + ((((g0 + k) * 2 + ((lane >> 3) & 1)) ^ vsw) << 3));
+#pragma unroll
+          for (int k = 0; k < GROUP; ++k)
+            if (g0 + k < ksteps) mma_bf16(o[g0 + k], vf[k], pb0, pb1);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[buf]);   // this warp is done with the stage
+    }
+
+    // the four warps' shares of this stretch into one (m, l, O)
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      float l = l_run[hh];
+      l += __shfl_xor_sync(0xffffffffu, l, 4);
+      l += __shfl_xor_sync(0xffffffffu, l, 8);
+      l += __shfl_xor_sync(0xffffffffu, l, 16);
+      if (qd == 0) {
+        merge_m[warp][2 * t4 + hh] = m_run[hh];
+        merge_l[warp][2 * t4 + hh] = l;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < DMAX / 16; ++k)
+      if (k < ksteps) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          merge_o[((size_t)warp * DEC_HEADS + 2 * t4 + (e & 1)) * d + k * 16 + qd + 8 * (e >> 1)] = o[k][e];
+      }
+    consumer_barrier(NTHREADS);
+    if (dead) break;   // (status is set; the output is invalid) all four warps see the same value here
+    float m = -INFINITY, L = 0.f, f[4];
+    if (r < heads_here) {
+      m = merge_m[0][r];
+#pragma unroll
+      for (int w = 1; w < 4; ++w) m = fmaxf(m, merge_m[w][r]);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        f[w] = (merge_m[w][r] == -INFINITY) ? 0.f : exp2f(merge_m[w][r] - m);
+        L += merge_l[w][r] * f[w];
+      }
+    }
+    const bool whole = seg == n_b;   // this block held the whole unit: no scratch, no counter
+    const int head = head0 + r;
+    if (r < heads_here) {
+      if (whole) {
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        bf16* orow = out + (size_t)tok * out_stride + (size_t)head * d;
+        for (int k = cgrp; k < d; k += 16) {
+          float acc = 0.f;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) acc += f[w] * merge_o[((size_t)w * DEC_HEADS + r) * d + k];
+          orow[k] = __float2bfloat16_rn(acc * inv);
+        }
+      } else {
+        const size_t slot = ((size_t)unit + blockIdx.x) * DEC_HEADS + r;
+        float* po = part_o + slot * d;
+        for (int k = cgrp; k < d; k += 16) {
+          float acc = 0.f;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) acc += f[w] * merge_o[((size_t)w * DEC_HEADS + r) * d + k];
+          po[k] = acc;
+        }
+        if (cgrp == 0) {
+          part_ml[slot * 2] = m;
+          part_ml[slot * 2 + 1] = L;
+        }
+      }
+    }
+    if (!whole) {
+      // count this stretch's chunks in; whoever completes the unit merges its stretches in block order
+      __threadfence();
+      consumer_barrier(NTHREADS);
+      if (tid == 0) is_last = (atomicAdd(&counters[unit], seg) + seg == n_b) ? 1 : 0;
+      consumer_barrier(NTHREADS);
+      if (is_last) {
+        __threadfence();
+        const long long start = (long long)cum[b] * U + (long long)u * n_b;
+        const int g_first = (int)(((start + 1) * G - 1) / W), g_last = (int)(((start + n_b) * G - 1) / W);
+        if (r < heads_here)
+          balanced_merge_unit<DMAX>(part_o, part_ml, unit, g_first, g_last, r, cgrp, d,
+                                    out + (size_t)tok * out_stride + (size_t)head * d);
+        if (tid == 0) counters[unit] = 0;   // ready for the next call
+      }
+    }
+    consumer_barrier(NTHREADS);   // merge_o, merge_m and is_last may be written again
+    i += seg;
+  }
+  // a request that holds no key at all has no chunk in the row: its output rows are zero
+  if (blockIdx.x == 0)
+    for (int b = 0; b < B; ++b)
+      if (cum[b + 1] == cum[b]) {
+        bf16* orow = out + (size_t)q_start[b] * out_stride;
+        for (int k = tid; k < nq * d; k += NTHREADS) orow[k] = __float2bfloat16_rn(0.f);
+      }
+}
+
 // ------------------------------------------------------------------------------- prefill
 
 // 2^x as one instruction of the special-function unit (2 ulp, results below 2^-126 are 0):
@@ -1001,6 +1429,62 @@ extern "C" int mi_attention_decode(const void* q, int q_stride, void* out, int o
   return mi_attention_decode_sliced(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride, nullptr, page_size,
                                     q_start, kv_len, B, nq, nkv, d, scale, window, n_splits, nullptr, part_o,
                                     part_ml, counters, stream);
+}
+
+static size_t balanced_smem_bytes(int B, int d) {   // the ring, the warps' merge buffer, the running sum of chunks
+  return (size_t)(2 * DEC_STAGES * KCHUNK) * d * sizeof(bf16) + (size_t)4 * DEC_HEADS * d * sizeof(float) +
+         (size_t)(B + 1) * sizeof(int);
+}
+
+// Blocks the balanced decode kernel should be started with on a GPU of `sms` SMs, and the
+// scratch it needs for B requests: floats of part_o and part_ml, ints of counters (zero before
+// the first call; the kernel leaves them zero).
+extern "C" int mi_attention_decode_balanced_scratch(int B, int nq, int nkv, int d, int sms, int* grid,
+                                                    long long* o_floats, long long* ml_floats, int* counter_ints) {
+  if (B <= 0 || nq <= 0 || nkv <= 0 || nq % nkv || d <= 0 || sms <= 0) MI_REFUSE("attention: bad sizes");
+  const int g = nq / nkv, hblocks = (g + DEC_HEADS - 1) / DEC_HEADS, units = B * nkv * hblocks;
+  const size_t smem = balanced_smem_bytes(B, d);
+  // two blocks share an SM when both fit its 228 KB (each also takes 1 KB of reserve and its static part)
+  *grid = sms * (2 * (smem + 1024 + 512) <= 228 * 1024 ? 2 : 1);
+  *o_floats = (long long)(units + *grid) * DEC_HEADS * d;
+  *ml_floats = (long long)(units + *grid) * DEC_HEADS * 2;
+  *counter_ints = units;
+  return 0;
+}
+
+// Decode attention with the keys of all requests spread evenly over `grid` persistent blocks
+// (attention_decode_balanced_kernel); scratch as mi_attention_decode_balanced_scratch says.
+extern "C" int mi_attention_decode_balanced(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
+                                            const void* vcache, const int* block_table, int bt_stride,
+                                            const int* table_rows, int page_size, const int* q_start,
+                                            const int* kv_len, int B, int nq, int nkv, int d, float scale, int window,
+                                            int grid, float* part_o, float* part_ml, int* counters,
+                                            cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (int rc = check_common(q, q_stride, out, out_stride, kcache, vcache, nq, nkv, d, page_size, window)) return rc;
+  if (grid <= 0 || !part_o || !part_ml || !counters) MI_REFUSE("attention: the balanced kernel needs its grid and scratch");
+  if (!mi_aligned(part_o, 4) || !mi_aligned(part_ml, 8) || !mi_aligned(counters, 4))
+    MI_REFUSE("attention: scratch must be aligned (part_o and counters to 4 bytes, part_ml to 8)");
+  if (B > 16384) MI_REFUSE("attention: %d requests in one decode step", B);
+  const int page_shift = shift_of(page_size);
+  const size_t smem = balanced_smem_bytes(B, d);
+#define MI_DECODE_BAL(DMAX)                                                                               \
+  do {                                                                                                    \
+    auto kern = attention_decode_balanced_kernel<DMAX>;                                                   \
+    if (smem > 40 * 1024) {                                                                               \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return (int)e;                                                                \
+    }                                                                                                     \
+    MI_LAUNCH((kern), grid, DEC_THREADS, smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,  \
+              (const bf16*)kcache, (const bf16*)vcache, block_table, bt_stride, table_rows, page_size,    \
+              page_shift, q_start, kv_len, B, nq, nkv, d, scale, window, 4, part_o, part_ml, counters,    \
+              wait_status_ptr());                                                                         \
+  } while (0)
+  if (d <= 64) MI_DECODE_BAL(64);
+  else if (d <= 128) MI_DECODE_BAL(128);
+  else MI_DECODE_BAL(256);
+#undef MI_DECODE_BAL
+  MI_RETURN_LAUNCH_STATUS();
 }
 
 // Tokens per tile the prefill kernel wants for a group of g query heads per key/value head.

@@ -160,6 +160,12 @@ def _sig_attention_mma(lib: ctypes.CDLL) -> None:
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
         c_void_p, c_void_p]
     lib.mi_attention_decode_counters.argtypes = [c_int, c_int, c_int]
+    lib.mi_attention_decode_balanced_scratch.argtypes = [c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int),
+                                                         ctypes.POINTER(ctypes.c_longlong),
+                                                         ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(c_int)]
+    lib.mi_attention_decode_balanced.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+        c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.mi_attention_wait_status.argtypes = [c_int]
     lib.mi_set_status_word.argtypes = [c_void_p]
     lib.mi_attention_prefill.argtypes = [
@@ -440,7 +446,8 @@ def sm_count(device: torch.device) -> int:
 
 
 def decode_splits(n_requests: int, nq: int, nkv: int, max_kv_len: int, window: int, device) -> int:
-    """How many slices of the keys each (request, key/value head) is cut into: enough blocks
+    """For the sliced decode kernel (``attention_decode``), which the engine itself no longer
+    uses: how many slices of the keys each (request, key/value head) is cut into: enough blocks
     for about two per SM, but at least four 64-key chunks per slice (a slice costs a fixed
     prologue and a merge, measured at roughly ten chunks' worth of time)."""
     blocks = n_requests * nkv * ((nq // nkv + 7) // 8)
@@ -449,63 +456,22 @@ def decode_splits(n_requests: int, nq: int, nkv: int, max_kv_len: int, window: i
     return max(1, min(2 * _sms(device) // blocks, chunks // 4, 64))
 
 
-DECODE_HEADS_PER_BLOCK = 8         # DEC_HEADS in attention_mma.cu
-# Slice counts a planned decode step may use (few values, so that few graphs are captured).
-DECODE_SLICE_COUNTS = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64)
-
-
-# Blocks per SM a planned decode step aims at: two when the requests are about equally long;
-# more (shorter slices) when the longest is over twice the mean, since blocks of very
-# different lengths leave a tail in which few SMs work.
-DECODE_BLOCKS_PER_SM = 2
-DECODE_BLOCKS_PER_SM_SKEWED = 4
-
-
-def decode_blocks_per_request(nq: int, nkv: int) -> int:
-    """Blocks the decode kernel starts per request and slice of keys."""
-    return nkv * ((nq // nkv + DECODE_HEADS_PER_BLOCK - 1) // DECODE_HEADS_PER_BLOCK)
-
-
-def decode_plan(kv_lens, window: int, blocks_per_request: int, sms: int) -> tuple[int, int]:
-    """``(slices, chunks per slice)`` for a decode step over requests of these lengths.
-
-    A slice is the same number of 64-key chunks for every request, sized so that all
-    requests together make about two blocks per SM and no slice is shorter than four chunks:
-    a request far longer than the others is cut into many slices while the short ones stay
-    whole, so no block is left with a multiple of the others' work.  For requests of equal
-    length this is ``decode_splits``' answer."""
-    chunks = []
-    for kl in kv_lens:
-        lo = max(0, kl - window) if window else 0
-        chunks.append(max(1, -(-kl // 64) - lo // 64))
-    longest = max(chunks)
-    skewed = longest * len(chunks) > 2 * sum(chunks)
-    per_sm = DECODE_BLOCKS_PER_SM_SKEWED if skewed else DECODE_BLOCKS_PER_SM
-    per = max(4, -(-sum(chunks) * blocks_per_request // (per_sm * sms)))
-    want = max(1, longest // per)
-    n = max(c for c in DECODE_SLICE_COUNTS if c <= want)
-    return n, -(-longest // n)
-
-
 def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq: int, nkv: int,
               head_dim: int, scale: float, window: int = 0) -> None:
     """Attention of this step's queries over one cache layer.
 
     ``cache`` is a ``LayerCache`` (its ``k``/``v`` pages and group index), ``ctx`` the
     ``StepContext`` (block tables, lengths, query tiles).  float32 runs the CUDA-core kernel;
-    bfloat16 runs the tensor-core kernels: split-key decode when every request brings one
-    token, otherwise the tcgen05 prefill kernel where it takes the sizes and the mma.sync
+    bfloat16 runs the tensor-core kernels: the balanced decode kernel when every request brings
+    one token, otherwise the tcgen05 prefill kernel where it takes the sizes and the mma.sync
     prefill kernel elsewhere.
     """
     group = ctx.groups[cache.group]
     if q.dtype == torch.bfloat16:
         if ctx.decode_only:
-            planned = getattr(group, "decode_slices", 0)
-            attention_decode(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
-                             ctx.q_start, ctx.kv_len, ctx.n_requests, nq, nkv, head_dim, scale, window,
-                             planned or decode_splits(ctx.n_requests, nq, nkv, ctx.max_kv_len, window, q.device),
-                             slice_chunks=group.decode_slice_chunks if planned else None,
-                             table_rows=group.table_rows)
+            attention_decode_balanced(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
+                                      ctx.q_start, ctx.kv_len, ctx.n_requests, nq, nkv, head_dim, scale, window,
+                                      table_rows=group.table_rows)
         else:
             tc = USE_TC_PREFILL and prefill_tc_supported(nq, nkv, head_dim, group.page_size)
             tt = (prefill_tc_tile_tokens if tc else prefill_tile_tokens)(nq // nkv)
@@ -577,6 +543,47 @@ def attention_decode(q, q_stride, out, kcache, vcache, block_table, page_size, q
         block_table.stride(0), _ptr(table_rows), int(page_size), _ptr(q_start), _ptr(kv_len), int(n_requests), nq, nkv,
         head_dim, float(scale), int(window), int(n_splits), _ptr(slice_chunks), _ptr(part_o), _ptr(part_ml),
         _ptr(counters), _stream())
+    _finish(lib, rc, "attention_decode")
+
+
+# Scratch of the balanced decode kernel, per device: partial results, their (max, sum) pairs and
+# the per-unit chunk counters (zero between calls).  Never freed once handed out: a captured
+# CUDA graph may hold the addresses.
+_balanced_ws: dict[int, list[tuple[torch.Tensor, torch.Tensor, torch.Tensor]]] = {}
+
+
+def _balanced_workspace(device: torch.device, o_floats: int, ml_floats: int, counters: int):
+    idx = _device_index(device)
+    stack = _balanced_ws.setdefault(idx, [])
+    if not stack or stack[-1][0].numel() < o_floats or stack[-1][1].numel() < ml_floats or stack[-1][2].numel() < counters:
+        stack.append((torch.empty(max(o_floats, 1 << 20), dtype=torch.float32, device=device),
+                      torch.empty(max(ml_floats, 1 << 14), dtype=torch.float32, device=device),
+                      torch.zeros(max(counters, 4096), dtype=torch.int32, device=device)))
+    return stack[-1]
+
+
+def attention_decode_balanced(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, kv_len,
+                              n_requests, nq, nkv, head_dim, scale, window=0, table_rows=None) -> None:
+    """bfloat16 decode attention with the keys of all requests spread evenly over persistent
+    blocks, whatever the requests' lengths (attention_decode_balanced_kernel): no plan from the
+    host, the blocks read the lengths themselves."""
+    _cuda(q, out, kcache, vcache, block_table, q_start, kv_len, table_rows)
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_decode: bfloat16 only")
+    _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, page_size,
+                          (("block_table", block_table), ("q_start", q_start), ("kv_len", kv_len),
+                           ("table_rows", table_rows)))
+    lib = _waiting_lib("attention_mma", q.device)
+    grid, o_floats, ml_floats, counters = c_int(0), ctypes.c_longlong(0), ctypes.c_longlong(0), c_int(0)
+    rc = lib.mi_attention_decode_balanced_scratch(int(n_requests), nq, nkv, head_dim, _sms(q.device), ctypes.byref(grid),
+                                                  ctypes.byref(o_floats), ctypes.byref(ml_floats), ctypes.byref(counters))
+    if rc != 0:
+        raise KernelError("attention_decode: " + lib.mi_error_message().decode("utf-8", "replace"))
+    part_o, part_ml, count = _balanced_workspace(q.device, int(o_floats.value), int(ml_floats.value), int(counters.value))
+    rc = lib.mi_attention_decode_balanced(
+        _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_table),
+        block_table.stride(0), _ptr(table_rows), int(page_size), _ptr(q_start), _ptr(kv_len), int(n_requests), nq, nkv,
+        head_dim, float(scale), int(window), int(grid.value), _ptr(part_o), _ptr(part_ml), _ptr(count), _stream())
     _finish(lib, rc, "attention_decode")
 
 

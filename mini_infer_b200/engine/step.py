@@ -68,7 +68,6 @@ class HostPlan:
     state_slots: list[int]
     rows: list[tuple[Hashable, int]]
     decode_only: bool
-    slices: list[int]                  # per group: key slices of a planned decode step (0: not planned)
     update_capacity: list[int]         # per group: triples the buffer has room for
     overflow: list[list[int]]          # per group: triples that did not fit a captured step's fixed room
     tile_counts: dict[int, int]
@@ -76,8 +75,9 @@ class HostPlan:
 
 class StepRunner:
     """``cuda_graph=True`` replays decode-only steps (every request brings one token and
-    wants its logits) as captured CUDA graphs, one per (batch size, number of key slices);
-    the reference keeps such graphs per batch bucket (``engine/paged_decode_graph.py:67-225``).
+    wants its logits) as captured CUDA graphs, one per batch size (the lengths, the pages and
+    how decode attention spreads its keys over blocks are all read from device memory when the
+    graph runs); the reference keeps such graphs per batch bucket (``engine/paged_decode_graph.py:67-225``).
     Everything else runs kernel by kernel, and so does every step of a model one of whose parts
     is not ``graph_safe``.
 
@@ -96,9 +96,6 @@ class StepRunner:
         self.vocab_size = model.spec.vocab_size
         needs = model.plan_needs()
         self.tile_sizes = sorted(needs.q_tile_tokens)
-        # a mixer that cuts a decode step's keys into slices lets the planner decide them
-        self.decode_blocks_per_request = (needs.decode_blocks_per_request
-                                          if self.dtype in needs.decode_slice_dtypes else 0)
         self.max_positions = model.spec.max_positions
         self.sm_count = ops.sm_count(self.device) if self.device is not None and self.device.type == "cuda" else 148
         self.steps_run = 0
@@ -166,7 +163,6 @@ class StepRunner:
         ]
         n_groups = len(self.cache.groups)
         capacity, overflow = [0] * n_groups, [[] for _ in range(n_groups)]
-        slices: list[int] = [0] * n_groups
         for gi, g in enumerate(self.cache.groups):
             parts.append((f"slots{gi}", plan.token_slots[gi]))
             flat = updates[gi]
@@ -179,12 +175,6 @@ class StepRunner:
                 capacity[gi] = len(flat) // 3
                 parts.append((f"updates{gi}", flat))
             parts.append((f"update_count{gi}", [len(flat) // 3]))
-            # Decode-only steps of a mixer that cuts keys into slices: how many, and how long
-            # (one int per group on the device, so that a captured step follows the lengths).
-            if decode_only and self.decode_blocks_per_request > 0:
-                slices[gi], per = ops.decode_plan(kv_len, g.window or 0, self.decode_blocks_per_request,
-                                                  self.sm_count)
-                parts.append((f"slice{gi}", [per]))
         tile_counts: dict[int, int] = {}
         for n in self.tile_sizes:
             if decode_only:
@@ -212,7 +202,7 @@ class StepRunner:
                 buffer[o:o + n] = lst
         return HostPlan(buffer=buffer, offsets=offsets, n_tokens=M, q_start=q_start, q_len=list(q_len),
                         kv_len=kv_len, state_slots=list(plan.state_slots), rows=rows, decode_only=decode_only,
-                        slices=slices, update_capacity=capacity, overflow=overflow, tile_counts=tile_counts)
+                        update_capacity=capacity, overflow=overflow, tile_counts=tile_counts)
 
     def plan(self, entries: Sequence[StepEntry], graphed: bool = False):
         """Reserve pages and put the step's descriptors on the device (one copy).
@@ -225,7 +215,7 @@ class StepRunner:
         host.numpy()[:] = hp.buffer
         slot = None
         if graphed:
-            key = (B, tuple(hp.slices))
+            key = (B,)
             slot = self._graphs.get(key)
             if slot is None:
                 slot = GraphSlot(device_buffer=torch.empty(host.numel(), dtype=torch.int32, device=self.device))
@@ -251,7 +241,6 @@ class StepRunner:
             groups.append(GroupView(
                 page_size=self.cache.page_size, window=g.window,
                 block_table=self.cache.block_tables[gi], slots=view(f"slots{gi}"), table_rows=state_slot,
-                decode_slices=hp.slices[gi], decode_slice_chunks=view(f"slice{gi}") if hp.slices[gi] else None,
             ))
         ctx = StepContext(
             dtype=self.dtype, device=self.device, n_tokens=hp.n_tokens, n_requests=B,

@@ -85,15 +85,27 @@ def attention_decode(args, ops, device, flush) -> tuple[float, str]:
     out = torch.empty(args.batch, nq * d, device=device, dtype=torch.bfloat16)
     q_start = torch.arange(args.batch, device=device, dtype=torch.int32)
     kv_len = torch.full((args.batch,), args.context, device=device, dtype=torch.int32)
-    splits = args.splits or ops.decode_splits(args.batch, nq, nkv, args.context, 0, device)
+    if args.skew:      # lengths from context / skew up to context, so that requests differ widely
+        lens = [max(1, int(args.context / args.skew ** (i / max(1, args.batch - 1)))) for i in range(args.batch)]
+        kv_len = torch.tensor(lens, device=device, dtype=torch.int32)
+    total = int(kv_len.sum().item())
+    nbytes = 2 * total * nkv * d * 2
+    if args.impl == "sliced":
+        splits = args.splits or ops.decode_splits(args.batch, nq, nkv, args.context, 0, device)
+
+        def run():
+            ops.attention_decode(qkv, qkv.stride(0), out, kcache, vcache, table, args.page, q_start, kv_len,
+                                 args.batch, nq, nkv, d, 1.0 / math.sqrt(d), 0, splits)
+
+        us = _time(run, args.iters, args.warmup, flush)
+        return us, f"{splits} key slices, {nbytes / us / 1e6:.2f} TB/s of keys and values"
 
     def run():
-        ops.attention_decode(qkv, qkv.stride(0), out, kcache, vcache, table, args.page, q_start, kv_len,
-                             args.batch, nq, nkv, d, 1.0 / math.sqrt(d), 0, splits)
+        ops.attention_decode_balanced(qkv, qkv.stride(0), out, kcache, vcache, table, args.page, q_start, kv_len,
+                                      args.batch, nq, nkv, d, 1.0 / math.sqrt(d), 0)
 
     us = _time(run, args.iters, args.warmup, flush)
-    nbytes = 2 * args.batch * args.context * nkv * d * 2
-    return us, f"{splits} key slices, {nbytes / us / 1e6:.2f} TB/s of keys and values"
+    return us, f"balanced over persistent blocks, {nbytes / us / 1e6:.2f} TB/s of keys and values"
 
 
 def attention_prefill(args, ops, device, flush) -> tuple[float, str]:
@@ -217,13 +229,18 @@ def main(argv=None) -> int:
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--top-k", type=int, default=0)
     ap.add_argument("--top-p", type=float, default=1.0)
-    ap.add_argument("--impl", choices=["tc", "mma"], default="tc",
-                    help="attention_prefill: the tcgen05 kernel or the mma.sync kernel")
+    ap.add_argument("--impl", choices=["tc", "mma", "balanced", "sliced"], default=None,
+                    help="attention_prefill: the tcgen05 kernel (default) or the mma.sync kernel; attention_decode: "
+                         "keys spread evenly over persistent blocks (default) or equal slices per request")
+    ap.add_argument("--skew", type=float, default=0.0,
+                    help="attention_decode: request lengths from context / skew up to context (0: all equal)")
     ap.add_argument("--timer", choices=["device", "events"], default="device",
                     help="device: kernel durations from the profiler's records; events: CUDA events around the call")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)
+    if args.impl is None:
+        args.impl = "balanced" if args.kernel == "attention_decode" else "tc"
     if not torch.cuda.is_available():
         print("microbench needs a GPU", file=sys.stderr)
         return 2

@@ -69,16 +69,9 @@ class PlanNeeds:
 
     ``q_tile_tokens``: for each value n, a list of tiles of at most n consecutive query
     tokens of one request (``StepContext.q_tiles(n)``).
-    ``decode_blocks_per_request``: how many thread blocks a decode step of this mixer starts
-    per request before its keys are cut into slices; a value above zero makes the planner
-    decide the slices of each cache group from the requests' lengths
-    (``GroupView.decode_slices``, ``GroupView.decode_slice_chunks``), for the compute dtypes in
-    ``decode_slice_dtypes`` (the mixer knows which of its kernels cut keys into slices).
     """
 
     q_tile_tokens: frozenset[int] = frozenset()
-    decode_blocks_per_request: int = 0
-    decode_slice_dtypes: frozenset = frozenset()
 
 
 # ----------------------------------------------------------------------------- step context
@@ -93,8 +86,6 @@ class GroupView:
     block_table: torch.Tensor          # [request slots, max_pages] page ids of this group, resident on the device
     slots: torch.Tensor                # [tokens] flat slot (page * page_size + offset) per new token
     table_rows: torch.Tensor | None = None   # [requests] row of block_table of each request (None: its index)
-    decode_slices: int = 0             # decode-only steps: slices the keys are cut into (0: not planned)
-    decode_slice_chunks: torch.Tensor | None = None   # [1] int32: 64-key chunks per slice
 
 
 @dataclass

@@ -184,10 +184,7 @@ class GroupedQueryAttention(Mixer):
         return KVNeed(self.nkv, self.d, self.window)
 
     def plan_needs(self):
-        # only the bfloat16 decode kernel cuts keys into slices
-        return PlanNeeds(ops.attention_tile_sizes(self.nq // self.nkv),
-                         ops.decode_blocks_per_request(self.nq, self.nkv),
-                         frozenset({torch.bfloat16}))
+        return PlanNeeds(ops.attention_tile_sizes(self.nq // self.nkv))
 
     def bind(self, tensors, dtype, device):
         qkv = torch.cat(

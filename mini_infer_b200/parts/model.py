@@ -117,14 +117,9 @@ class DecoderModel:
 
     def plan_needs(self) -> PlanNeeds:
         tiles: set[int] = set()
-        decode_blocks = 0
-        slice_dtypes: set = set()
         for b in self.blocks:
-            needs = b.mixer.plan_needs()
-            tiles |= set(needs.q_tile_tokens)
-            decode_blocks = max(decode_blocks, needs.decode_blocks_per_request)
-            slice_dtypes |= set(needs.decode_slice_dtypes)
-        return PlanNeeds(frozenset(tiles), decode_blocks, frozenset(slice_dtypes))
+            tiles |= set(b.mixer.plan_needs().q_tile_tokens)
+        return PlanNeeds(frozenset(tiles))
 
     def graph_safe(self) -> bool:
         """Whether a step of this model may be captured as a CUDA graph (every part says so)."""

@@ -2,8 +2,8 @@
 query heads over 8 key/value heads of 128, intermediate 14336, vocabulary 128256, llama3
 rotary scaling with an original context of 8192, pages of 16.
 
-At these sizes the kernels take paths the tiny configurations never reach: the decode
-planner's slices for 32/8 heads, the streaming product cut stream-K fashion over a
+At these sizes the kernels take paths the tiny configurations never reach: decode attention's
+stretches for 32/8 heads, the streaming product cut stream-K fashion over a
 28672 x 4096 gate/up matrix with its activation epilogue, a 128256-row head, the tcgen05
 prefill attention, and positions past the original context length.  The float32 engine is
 compared with the plain implementation under the four cuttings, the bfloat16 engine with the

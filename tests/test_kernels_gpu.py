@@ -321,6 +321,15 @@ def run_attention(q_lens, kv_lens, nq, nkv, d, page, dtype, window=0, seed=0, bo
            i32(q_lens), i32(kv_lens), i32(treq), i32(ttok), len(treq), T_, nq, nkv, d, scale, window)
         if kernel == "prefill_tc":
             assert o.attention_tc_status() == 0, "a block of the tcgen05 kernel gave up a wait"
+    elif kernel == "balanced":
+        assert all(n == 1 for n in q_lens)
+        # the requests' rows of the block table in another order than the requests, as in the engine
+        order = list(reversed(range(len(q_lens))))
+        table = torch.full((len(q_lens) + 2, bt.shape[1]), -1, dtype=torch.int32)
+        for i, row in enumerate(order):
+            table[row] = bt[i]
+        o.attention_decode_balanced(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), table.to(DEV), page, i32(q_start),
+                                    i32(kv_lens), len(q_lens), nq, nkv, d, scale, window, table_rows=i32(order))
     else:
         assert all(n == 1 for n in q_lens)
         o.attention_decode(wide, wide.stride(0), out, kc.to(DEV), vc.to(DEV), bt.to(DEV), page, i32(q_start),
@@ -476,6 +485,38 @@ def test_attention_decode_slices_of_one_length(n_splits, slice_chunks):
     got, want = run_attention([1, 1, 1], [500, 64, 7], 8, 2, 64, 16, torch.bfloat16, window=100, seed=9,
                               kernel="decode", n_splits=n_splits, slice_chunks=slice_chunks)
     assert (got - want).abs().max().item() <= BF16_BOUND
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(32, 8, 128, 16), (6, 2, 48, 8), (3, 3, 16, 4), (40, 2, 64, 16), (5, 1, 256, 16),
+                                            (24, 1, 128, 32)])
+def test_attention_decode_balanced(nq, nkv, d, page):
+    """The balanced decode kernel: requests of very different lengths (one key, a chunk's edge,
+    thousands), so that some blocks hold several whole units, some a stretch of one unit, and a
+    long unit is merged from many stretches; a request without any key among them."""
+    kv_lens = [1, 64, 65, 700, 17, 2048 if d <= 128 else 300, 3, 129, 5000 if d <= 64 else 130]
+    got, want = run_attention([1] * len(kv_lens), kv_lens, nq, nkv, d, page, torch.bfloat16, seed=nq + 11, kernel="balanced")
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max().item() <= BF16_BOUND
+    # the same twice more with other lengths: the counters were left at zero
+    for seed, lens in ((3, [40000 if d <= 64 else 9000]), (4, [300, 300, 300, 300]), (5, [5, 9, 2, 1, 1, 1, 130])):
+        got, want = run_attention([1] * len(lens), lens, nq, nkv, d, page, torch.bfloat16, seed=seed, kernel="balanced")
+        assert (got - want).abs().max().item() <= BF16_BOUND
+
+
+@pytest.mark.parametrize("window", [1, 30, 64, 200])
+def test_attention_decode_balanced_window_and_far_key(window):
+    got, want = run_attention([1, 1, 1], [500, 64, 7], 8, 2, 64, 16, torch.bfloat16, window=window, seed=9, kernel="balanced")
+    assert (got - want).abs().max().item() <= BF16_BOUND
+    nq, nkv, d, page = 4, 1, 32, 16
+    for target in (0, 15, 16, 63, 64, 257, 700, 703):
+        def boost(q, ks, kc, bt, target=target):
+            ks[0][target] = 0
+            ks[0][target, 0, 0] = 8.0
+            kc[bt[0, target // page] * page + target % page] = ks[0][target]
+            q[-1] = 0
+            q[-1, :, 0] = 40.0
+        got, want = run_attention([1], [704], nq, nkv, d, page, torch.bfloat16, seed=5, boost=boost, kernel="balanced")
+        assert (got - want).abs().max().item() <= BF16_BOUND
 
 
 @pytest.mark.parametrize("window", [1, 30, 64, 200])
