@@ -47,7 +47,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   const int swz_mask = mi_swizzle_mask(d, (int)sizeof(T));
 
   const int tid = threadIdx.x;
-  const int tile = blockIdx.x, h = blockIdx.y;
+  const int tile = blockIdx.x / nq, h = blockIdx.x - tile * nq;   // all heads of a tile, then the next tile (the caller lists long tiles first)
   const int kvh = h / (nq / nkv);
   const int b = tile_req[tile], tok0 = tile_tok0[tile];
   const int ql = q_len[b], kl = kv_len[b], qs = q_start[b];
@@ -173,7 +173,7 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  dim3 grid(n_tiles, nq);
+  dim3 grid((unsigned)(n_tiles * nq));
   MI_LAUNCH((kern), grid, NTHREADS, smem, stream, (const T*)q, q_stride, (T*)out, out_stride, (const T*)kcache,
                                          (const T*)vcache, block_table, bt_stride, table_rows, page_size, q_start,
                                          q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, scale, window);
@@ -193,7 +193,7 @@ extern "C" int mi_attention_generic(const void* q, int q_stride, void* out, int 
     MI_REFUSE("attention: head size %d is not a multiple of 16 in [16, 256]", d);
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0)
     MI_REFUSE("attention: %d query heads cannot share %d key/value heads", nq, nkv);
-  if (nq > 65535) MI_REFUSE("attention: too many heads (%d)", nq);
+  if ((long long)n_tiles * nq > 0x7fffffffLL) MI_REFUSE("attention: too many blocks for one launch");
   if (page_size <= 0 || window < 0) MI_REFUSE("attention: bad page size %d or window %d", page_size, window);
   if (!mi_aligned(kcache, 16) || !mi_aligned(vcache, 16)) MI_REFUSE("attention: cache must be 16-byte aligned");
   int rc;

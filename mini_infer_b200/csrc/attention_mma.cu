@@ -1062,11 +1062,12 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   const int qd = lane >> 2, t4 = lane & 3;
   const int g = nq / nkv;
   const int hblocks = (g + gb - 1) / gb;
-  // Blocks start in the order of their index.  Tiles are listed in token order and, with a
-  // causal mask, the later a tile the more keys it walks: take them last first, so that the
-  // long ones do not end up alone in the last wave.
-  const int tile = gridDim.x - 1 - blockIdx.x;
-  const int kvh = blockIdx.y / hblocks, hb = blockIdx.y - kvh * hblocks;
+  // Blocks start in the order of their index.  The caller lists the tiles with the most keys
+  // first, and all head groups of a tile come before the next tile, so the longest blocks of
+  // the whole launch start first and the short ones fill the gaps at the end.
+  const int n_hg = nkv * hblocks;
+  const int tile = blockIdx.x / n_hg, hg = blockIdx.x - tile * n_hg;
+  const int kvh = hg / hblocks, hb = hg - kvh * hblocks;
   const int b = tile_req[tile], tok0 = tile_tok0[tile];
   const int ql = q_len[b], kl = kv_len[b], qs = q_start[b];
   const int ntok = min(tt, ql - tok0);
@@ -1505,10 +1506,10 @@ extern "C" int mi_attention_prefill(const void* q, int q_stride, void* out, int 
   const int gb = g < PROWS ? g : PROWS;
   if (tile_tokens != PROWS / gb) MI_REFUSE("attention: tiles of %d tokens, the kernel wants %d", tile_tokens, PROWS / gb);
   const int hblocks = (g + gb - 1) / gb;
-  if (nkv * hblocks > 65535) MI_REFUSE("attention: too many heads for one launch");
+  if ((long long)n_tiles * nkv * hblocks > 0x7fffffffLL) MI_REFUSE("attention: too many blocks for one launch");
   const size_t smem = smem_bytes(PROWS, d);
   const int page_shift = shift_of(page_size);
-  dim3 grid(n_tiles, nkv * hblocks);
+  dim3 grid((unsigned)(n_tiles * nkv * hblocks));
 #define MI_PREFILL(DMAX)                                                                                \
   do {                                                                                                  \
     auto kern = attention_prefill_kernel<DMAX>;                                                         \

@@ -206,8 +206,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = nq / nkv;
   const int hblocks = (g + gb - 1) / gb;
-  const int tile = gridDim.x - 1 - blockIdx.x;     // longest tiles first (causal)
-  const int kvh = blockIdx.y / hblocks, hb = blockIdx.y - kvh * hblocks;
+  // Blocks start in the order of their index.  The caller lists the tiles with the most keys
+  // first, and all head groups of a tile come before the next tile, so the longest blocks of
+  // the whole launch start first and the short ones fill the gaps at the end.
+  const int n_hg = nkv * hblocks;
+  const int tile = blockIdx.x / n_hg, hg = blockIdx.x - tile * n_hg;
+  const int kvh = hg / hblocks, hb = hg - kvh * hblocks;
   const int b = tile_req[tile], tok0 = tile_tok0[tile];
   const int ql = q_len[b], kl = kv_len[b], qs = q_start[b];
   const int ntok = min(tt, ql - tok0);
@@ -585,7 +589,9 @@ extern "C" int mi_attention_prefill_tc(const void* q, int q_stride, void* out, i
   auto kern = attention_prefill_tc_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid(n_tiles, nkv * hblocks);
+  const long long n_blocks = (long long)n_tiles * nkv * hblocks;
+  if (n_blocks > 0x7fffffffLL) MI_REFUSE("attention_tc: too many blocks for one launch");
+  dim3 grid((unsigned)n_blocks);
   MI_LAUNCH((kern), grid, TC_THREADS, smem, stream, map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride,
             block_table, bt_stride, table_rows, page_size, page_shift, q_start, q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, scale,
             window, gb, NTILE * ROWS / gb);

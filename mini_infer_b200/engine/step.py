@@ -181,11 +181,13 @@ class StepRunner:
                 treq: Sequence[int] = range(B)
                 ttok: Sequence[int] = [0] * B
             else:
-                treq, ttok = [], []
-                for i in range(B):
-                    for t0 in range(0, q_len[i], n):
-                        treq.append(i)
-                        ttok.append(t0)
+                # Tiles with the most keys to walk come first: the attention kernels start their
+                # blocks in this order, so the long ones are under way when the short ones fill
+                # what is left (a tile of tokens t0.. of request i sees its keys up to the tile's end).
+                tiles = [(i, t0) for i in range(B) for t0 in range(0, q_len[i], n)]
+                tiles.sort(key=lambda it: -(kv_len[it[0]] - q_len[it[0]] + min(q_len[it[0]], it[1] + n)))
+                treq = [i for i, _ in tiles]
+                ttok = [t0 for _, t0 in tiles]
             tile_counts[n] = len(treq)
             parts.append((f"tile_req{n}", treq))
             parts.append((f"tile_tok{n}", ttok))

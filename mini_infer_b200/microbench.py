@@ -119,7 +119,8 @@ def attention_prefill(args, ops, device, flush) -> tuple[float, str]:
     tile = (ops.prefill_tc_tile_tokens if args.impl == "tc" else ops.prefill_tile_tokens)(nq // nkv)
     n_tiles = -(-T // tile)
     tile_req = torch.zeros(n_tiles, device=device, dtype=torch.int32)
-    tile_tok0 = (torch.arange(n_tiles, device=device, dtype=torch.int32) * tile).contiguous()
+    # the tiles with the most keys first, as the engine's step plan lists them
+    tile_tok0 = (torch.arange(n_tiles - 1, -1, -1, device=device, dtype=torch.int32) * tile).contiguous()
 
     kernel = ops.attention_prefill_tc if args.impl == "tc" else ops.attention_prefill
 

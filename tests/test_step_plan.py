@@ -66,7 +66,8 @@ def test_layout_of_a_mixed_step_and_of_a_captured_one():
     assert view(hp, "positions") == list(range(37)) + [0]
     assert view(hp, "state_slot") == [cache.slot("a"), cache.slot("b")]
     assert view(hp, "update_count0") == [4] and hp.update_capacity == [4]      # three pages for a, one for b
-    assert view(hp, "tile_req16") == [0, 0, 0, 1] and view(hp, "tile_tok16") == [0, 16, 32, 0]
+    # tiles with the most keys first: a's last tile sees 37 keys, then 32, 16, and b's one key
+    assert view(hp, "tile_req16") == [0, 0, 0, 1] and view(hp, "tile_tok16") == [32, 16, 0, 0]
     # a captured step: fixed room for one new page per request; what is unused is marked -1
     hp = runner.host_plan([StepEntry("a", [3], [0]), StepEntry("b", [4], [0])], graphed=True)
     assert hp.decode_only and hp.update_capacity == [2] and view(hp, "update_count0") == [0]
