@@ -8,9 +8,11 @@
 //            offset, which is exactly the 128-byte-swizzle pattern of the tensor cores' shared
 //            memory operands, so un-swizzled box copies of [page_size keys x 64 dims] land in
 //            the canonical layout: K as a K-major operand, V as an MN-major one.
-//   warps 9, 11  one thread each issues tcgen05.mma: S = Q K^T (128 x 64, fp32 in tensor memory, two
-//            buffers so that the next chunk's scores are computed while this one's softmax
-//            runs) and O += P V (128 x d, fp32 in tensor memory).
+//   warps 9, 12, 11, 13  one thread each issues tcgen05.mma for one tile and one product: S = Q K^T
+//            (128 x 64, fp32 in tensor memory, two buffers so that the next chunk's scores are
+//            computed while this one's softmax runs) and O += P V (128 x d, fp32 in tensor
+//            memory; P is read from tensor memory, where the softmax warps leave it as bf16
+//            over the first half of the chunk's score buffer).
 //   warps 0-7  softmax, four warps per tile, one row per thread: read the row of S from tensor memory, mask what
 //            the row must not see, keep the running maximum and sum in registers (fp32, log2
 //            domain), rescale O in tensor memory when the maximum moved, write P (bf16) into
@@ -28,7 +30,7 @@ MI_DEFINE_ERROR_API()
 
 #define ROWS 128
 #define KC 64            // keys per chunk
-#define TC_THREADS 384   // eight softmax warps, key copies, first product, value copies, second product
+#define TC_THREADS 512   // four groups of four warps: softmax of tile 0, softmax of tile 1, copies and issuers (two groups)
 #define SPIN_LIMIT (1 << 22)
 #define LOG2E 1.4426950408889634f
 #define RESCALE_LOG2 8.0f   // how far (in powers of two) a score may exceed the running reference before O is rescaled
@@ -100,8 +102,13 @@ __device__ __forceinline__ uint32_t idesc_bf16(int m, int n, int b_mn) {
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
-      "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
-      : "memory");
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate));
+}
+// the same with the A operand in tensor memory (row i in lane i, two 16-bit elements of k per column)
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate));
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
@@ -156,6 +163,17 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
       "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
       : "memory");
 }
+__device__ __forceinline__ void tmem_st32_bits(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]),
+      "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
+      "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -173,10 +191,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 #define NTILE 2    // query tiles of 128 rows per block
 enum {
   B_KFULL = 0, B_VFULL = NSTAGE, B_KEMPTY = 2 * NSTAGE, B_VEMPTY = 3 * NSTAGE,
-  B_SFULL = 4 * NSTAGE,               // [tile][2 buffers]
-  B_SEMPTY = 4 * NSTAGE + 4,          // [tile][2 buffers], the four softmax warps of the tile arrive
-  B_PFULL = 4 * NSTAGE + 8,           // [tile], the four softmax warps arrive
-  B_PVDONE = 4 * NSTAGE + 10,         // [tile]
+  B_SFULL = 4 * NSTAGE,               // [tile][2 buffers]: the scores of a chunk are in tensor memory
+  B_PFULL = 4 * NSTAGE + 4,           // [tile][2 buffers]: its probabilities are (the four softmax warps arrive)
+  B_PVDONE = 4 * NSTAGE + 8,          // [tile][2 buffers]: its second product has finished, the buffer is free
   B_COUNT = 4 * NSTAGE + 12
 };
 
@@ -196,8 +213,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const uint32_t tile_bytes = KC * 128 * halves;   // one K or V chunk: [half][64 keys][128 B]
   const uint32_t q_bytes = ROWS * 128 * halves;    // one query tile: [half][128 rows][128 B]
   unsigned char* Qs = smem;                        // [NTILE][q tile]
-  unsigned char* Ps = Qs + NTILE * q_bytes;        // [NTILE][128 rows][128 B]
-  unsigned char* Ks = Ps + NTILE * ROWS * 128;     // [NSTAGE][tile]
+  unsigned char* Ks = Qs + NTILE * q_bytes;        // [NSTAGE][tile]
   unsigned char* Vs = Ks + NSTAGE * tile_bytes;    // [NSTAGE][tile]
   __shared__ __align__(8) uint64_t bars[B_COUNT];
   __shared__ uint32_t tmem_base_holder;
@@ -225,7 +241,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   if (tid == 0) {
     for (int i = 0; i < B_COUNT; ++i)   // the softmax warps arrive one thread each
-      mbar_init(&bars[i], (i >= B_SEMPTY && i < B_PVDONE) ? 4 : 1);
+      mbar_init(&bars[i], (i >= B_PFULL && i < B_PVDONE) ? 4 : (i >= B_KEMPTY && i < B_SFULL) ? NTILE : 1);
     give_up = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -256,7 +272,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_holder;
-  // tensor memory: S of tile t, buffer sb at columns (2 t + sb) * 64; O of tile t at 256 + 128 t
+  // Registers: the launch gives every thread 128; the softmax warps, which hold a row of 64 scores
+  // each, take 192, the copy and issuer warps keep 64 (whole groups of four warps at a time).
+#define REGS_GIVE() asm volatile("setmaxnreg.dec.sync.aligned.u32 64;\n")
+#define REGS_TAKE() asm volatile("setmaxnreg.inc.sync.aligned.u32 192;\n")
+  // tensor memory: S of tile t, buffer sb at columns (2 t + sb) * 64, whose first 32 columns then
+  // hold the chunk's probabilities as bf16 pairs (the second product reads them from there: they
+  // never pass through shared memory); O of tile t at 256 + 128 t
 
   if (warp == 8 || warp == 10) {
     // The copy warps, one for keys and one for values: lane p owns page p of the chunk (its id
@@ -264,6 +286,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     // costs one round trip to the block table, not one per page.  A key stage is free as soon
     // as its scores are computed, a value stage only after the second product: the two rings
     // run independently, each as far ahead as its own stages allow.
+    REGS_GIVE();
     const bool is_v = warp == 10;
     const int* table = block_table + (size_t)(table_rows ? table_rows[b] : b) * bt_stride;
     const int ppc = KC >> page_shift;   // pages per chunk
@@ -293,58 +316,63 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       }
       page = next_page;
     }
-  } else if (warp == 9) {
-    // The first product's issuer: S[t][it & 1] = Q_t K^T for both tiles, ahead of the softmax.
-    // Operand descriptors are built once; a tile, a stage, a half or a k step only adds to the
-    // address field.
+  } else if (warp == 9 || warp == 12) {
+    // The first product's issuers, one thread per tile: S[t][it & 1] = Q_t K^T, ahead of the
+    // softmax.  One thread issues a tcgen05.mma every 60 to 120 cycles whatever its shape; a
+    // thread per tile and product keeps the tensor pipe fed and lets the tiles run out of step.
+    // Operand descriptors are built once; a stage, a half or a k step only adds to the address.
+    REGS_GIVE();
     if (lane == 0) {
+      const int t = warp == 9 ? 0 : 1;
       const uint32_t idesc_qk = idesc_bf16(ROWS, KC, 0);
-      const uint64_t q_desc = desc_sw128(smem_u32(Qs), 0), k_desc = desc_sw128(smem_u32(Ks), 0);
-      bool ok = true;
-      for (int it = 0; it < n_chunks && ok; ++it) {
+      const uint64_t qd = desc_sw128(smem_u32(Qs + t * q_bytes), 0), k_desc = desc_sw128(smem_u32(Ks), 0);
+      for (int it = 0; it < n_chunks; ++it) {
         const int st = it % NSTAGE, round = it / NSTAGE, sb = it & 1, sround = it >> 1;
         if (!mbar_wait(&bars[B_KFULL + st], round & 1, gu)) break;
+        // the score buffer also held the probabilities of chunk it - 2: free once their product is done
+        if (sround > 0 && !mbar_wait(&bars[B_PVDONE + 2 * t + sb], (sround - 1) & 1, gu)) break;
+        tc_fence_after();
         const uint64_t kd = k_desc + ((st * tile_bytes) >> 4);
-        for (int t = 0; t < NTILE; ++t) {
-          if (sround > 0 && !mbar_wait(&bars[B_SEMPTY + 2 * t + sb], (sround - 1) & 1, gu)) { ok = false; break; }
-          tc_fence_after();
-          const uint64_t qd = q_desc + ((t * q_bytes) >> 4);
-          for (int h = 0; h < halves; ++h)
+        for (int h = 0; h < halves; ++h)
 #pragma unroll
-            for (int k = 0; k < 4; ++k)   // 16 of the 64 dims of a half per MMA: 32 bytes along the row
-              umma(tmem + (2 * t + sb) * KC, qd + ((h * (ROWS * 128) + k * 32) >> 4),
-                   kd + ((h * (KC * 128) + k * 32) >> 4), idesc_qk, (h | k) ? 1u : 0u);
-          umma_commit(&bars[B_SFULL + 2 * t + sb]);
-        }
-        if (ok) umma_commit(&bars[B_KEMPTY + st]);
+          for (int k = 0; k < 4; ++k)   // 16 of the 64 dims of a half per MMA: 32 bytes along the row
+            umma(tmem + (2 * t + sb) * KC, qd + ((h * (ROWS * 128) + k * 32) >> 4),
+                 kd + ((h * (KC * 128) + k * 32) >> 4), idesc_qk, (h | k) ? 1u : 0u);
+        umma_commit(&bars[B_SFULL + 2 * t + sb]);
+        umma_commit(&bars[B_KEMPTY + st]);   // the stage is free when both tiles' issuers have said so
       }
     }
-  } else if (warp == 11) {
-    // The second product's issuer: O_t += P_t V as soon as a tile's probabilities are published.
+  } else if (warp == 11 || warp == 13) {
+    // The second product's issuers, one thread per tile: O_t += P_t V as soon as the tile's
+    // probabilities are published (A operand: the probabilities in tensor memory, 8 columns for
+    // 16 keys).
+    REGS_GIVE();
     if (lane == 0) {
+      const int t = warp == 11 ? 0 : 1;
       const uint32_t idesc_pv = idesc_bf16(ROWS, d, 1);
-      const uint64_t p_desc = desc_sw128(smem_u32(Ps), 0), v_desc = desc_sw128(smem_u32(Vs), KC * 128);
-      bool ok = true;
-      for (int it = 0; it < n_chunks && ok; ++it) {
-        const int st = it % NSTAGE, round = it / NSTAGE;
+      const uint64_t v_desc = desc_sw128(smem_u32(Vs), KC * 128);
+      for (int it = 0; it < n_chunks; ++it) {
+        const int st = it % NSTAGE, round = it / NSTAGE, sb = it & 1, sround = it >> 1;
         if (!mbar_wait(&bars[B_VFULL + st], round & 1, gu)) break;
+        if (!mbar_wait(&bars[B_PFULL + 2 * t + sb], sround & 1, gu)) break;
+        tc_fence_after();
         const uint64_t vd = v_desc + ((st * tile_bytes) >> 4);
-        for (int t = 0; t < NTILE; ++t) {
-          if (!mbar_wait(&bars[B_PFULL + t], it & 1, gu)) { ok = false; break; }
-          tc_fence_after();
-          const uint64_t pd = p_desc + ((t * (ROWS * 128)) >> 4);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)   // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
-            umma(tmem + 256 + t * 128, pd + ((k * 32) >> 4), vd + ((k * 2048) >> 4), idesc_pv, (it > 0 || k > 0) ? 1u : 0u);
-          umma_commit(&bars[B_PVDONE + t]);
-        }
-        if (ok) umma_commit(&bars[B_VEMPTY + st]);
+        for (int k = 0; k < 4; ++k)   // 16 keys per MMA: 8 columns of P, two 8-key groups of V
+          umma_ts(tmem + 256 + t * 128, tmem + (2 * t + sb) * KC + k * 8, vd + ((k * 2048) >> 4), idesc_pv,
+                  (it > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&bars[B_PVDONE + 2 * t + sb]);
+        umma_commit(&bars[B_VEMPTY + st]);
       }
     }
+  } else if (warp >= 14) {
+    // two warps without a role: they fill the fourth group of four, which hands over its registers
+    REGS_GIVE();
   } else {
     // softmax: warps 0-3 own tile 0, warps 4-7 tile 1; one thread per row (TMEM lane).  The two
     // groups run out of step with each other, so one computes exponentials while the other
     // waits for its scores or publishes its probabilities.
+    REGS_TAKE();
     const int t = warp >> 2, r = tid & (ROWS - 1), R = t * ROWS + r;
     const int tk = R / gb, mem = R - tk * gb;
     const bool rvalid = tk < ntok && mem < heads_here;
@@ -354,7 +382,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int t_first = p_first + (t * ROWS) / gb, t_last = min(hi - 1, p_first + (t * ROWS + ROWS - 1) / gb);
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tmem_o = tmem + 256 + t * 128;
-    unsigned char* Pt = Ps + t * (ROWS * 128);
     const float sc = scale * LOG2E;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
@@ -375,9 +402,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           s[32 + i] = __uint_as_float(rb[i]);
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[B_SEMPTY + 2 * t + sb]);   // the scores are in registers
       const bool interior = key0 + KC - 1 <= t_first && key0 >= (window > 0 ? max(0, t_last - window + 1) : 0) && key0 >= lo;
       if (!interior || !rvalid) {
 #pragma unroll
@@ -415,10 +439,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       }
       m_run = m_new;
       l_run = l_run * alpha + sum;
-      // the tile's P buffer and its O are free once its previous second product has finished
-      if (it > 0 && !warp_wait(&bars[B_PVDONE + t], (it - 1) & 1, gu)) { ok = false; break; }
-      tc_fence_after();
+      // O may be touched once the tile's previous second product has finished (the probabilities
+      // go into this chunk's own score buffer, which nothing else uses until its product is done)
       if (it > 0 && moved) {
+        if (!warp_wait(&bars[B_PVDONE + 2 * t + (sb ^ 1)], ((it - 1) >> 1) & 1, gu)) { ok = false; break; }
+        tc_fence_after();
         for (int c32 = 0; c32 < d; c32 += 32) {
           float o32[32];
           tmem_ld32(tmem_o + lane_addr + c32, o32);
@@ -428,23 +453,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         }
         tmem_st_wait();
       }
-      // P as bf16 into the swizzled K-major tile: row r, 16-byte chunk cc holds keys 8cc .. 8cc+7
+      // P as bf16 pairs over the first 32 columns of the chunk's score buffer: column j of this
+      // thread's lane holds keys 2j and 2j + 1
       {
-        unsigned char* prow_ptr = Pt + r * 128;
+        uint32_t pk[32];
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-          uint4 v;
-          v.x = pack_bf16(s[8 * cc], s[8 * cc + 1]);
-          v.y = pack_bf16(s[8 * cc + 2], s[8 * cc + 3]);
-          v.z = pack_bf16(s[8 * cc + 4], s[8 * cc + 5]);
-          v.w = pack_bf16(s[8 * cc + 6], s[8 * cc + 7]);
-          *reinterpret_cast<uint4*>(prow_ptr + ((cc ^ (r & 7)) << 4)) = v;
-        }
+        for (int j = 0; j < 32; ++j) pk[j] = pack_bf16(s[2 * j], s[2 * j + 1]);
+        tmem_st32_bits(tmem + lane_addr + (2 * t + sb) * KC, pk);
+        tmem_st_wait();
       }
       // value rows of keys nobody may see can hold anything (pages never written, stale rows):
-      // clear them, 0 * NaN is NaN.  Only a request's first and last chunks have such rows; tile
-      // 0 does it (its second product is always issued before tile 1's).
-      if (t == 0 && (key0 < lo || key0 + KC > hi)) {
+      // clear them, 0 * NaN is NaN.  Only a request's first and last chunks have such rows.  Each
+      // tile does it before it publishes its probabilities (the tiles' second products are
+      // issued independently; both write the same zeros).
+      if (key0 < lo || key0 + KC > hi) {
         if (!warp_wait(&bars[B_VFULL + st], round & 1, gu)) { ok = false; break; }
         unsigned char* vt = Vs + st * tile_bytes;
         for (int idx = r; idx < KC * halves * 8; idx += ROWS) {
@@ -452,14 +474,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           if (key0 + j < lo || key0 + j >= hi)
             *reinterpret_cast<uint4*>(vt + (rest >> 3) * (KC * 128) + j * 128 + ((rest & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
         }
+        fence_async_smem();   // plain stores that the tensor core reads
       }
-      fence_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[B_PFULL + t]);
+      if (lane == 0) mbar_arrive(&bars[B_PFULL + 2 * t + sb]);
     }
     // the output: O / l
-    if (ok && n_chunks > 0 && warp_wait(&bars[B_PVDONE + t], (n_chunks - 1) & 1, gu)) {
+    if (ok && n_chunks > 0 && warp_wait(&bars[B_PVDONE + 2 * t + ((n_chunks - 1) & 1)], ((n_chunks - 1) >> 1) & 1, gu)) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       bf16* orow = out + (size_t)(qs + tok0 + tk) * out_stride + (size_t)(kvh * g + hb * gb + mem) * d;
@@ -585,7 +607,7 @@ extern "C" int mi_attention_prefill_tc(const void* q, int q_stride, void* out, i
   if (!make_cache_map(&map_k, kcache, rows, d, page_size) || !make_cache_map(&map_v, vcache, rows, d, page_size))
     MI_REFUSE("attention_tc: the driver refused a tensor map");
   const int halves = d / 64;
-  const size_t smem = (size_t)NTILE * ROWS * 128 * halves + NTILE * ROWS * 128 + 2 * NSTAGE * (size_t)KC * 128 * halves + 1024;
+  const size_t smem = (size_t)NTILE * ROWS * 128 * halves + 2 * NSTAGE * (size_t)KC * 128 * halves + 1024;
   auto kern = attention_prefill_tc_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;

@@ -112,8 +112,7 @@ __device__ __forceinline__ uint32_t umma_idesc_bf16(int m, int n) {
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
-      "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
-      : "memory");
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate));
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
