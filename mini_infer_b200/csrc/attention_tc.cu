@@ -30,7 +30,6 @@ MI_DEFINE_ERROR_API()
 
 #define ROWS 128
 #define KC 64            // keys per chunk
-#define TC_THREADS 512   // four groups of four warps: softmax of tile 0, softmax of tile 1, copies and issuers (two groups)
 #define SPIN_LIMIT (1 << 22)
 #define LOG2E 1.4426950408889634f
 #define RESCALE_LOG2 8.0f   // how far (in powers of two) a score may exceed the running reference before O is rescaled
@@ -187,8 +186,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // barriers of the block, in one array
-#define NSTAGE 3   // chunks of keys and values in flight
-#define NTILE 2    // query tiles of 128 rows per block
+#ifndef NTILE
+#define NTILE 1    // query tiles of 128 rows per block
+#endif
+#define NSTAGE (NTILE == 1 ? 2 : 3)   // chunks of keys and values in flight
+// Warps come in groups of four (registers move between whole groups): per tile one group of
+// softmax warps and one group of copy and issuer warps.
+#define TC_THREADS (256 * NTILE)
+#define W_SOFT (4 * NTILE)      // the softmax warps are 0 .. W_SOFT - 1, four per tile
+#define W_KCOPY (W_SOFT + 0)
+#define W_QK0 (W_SOFT + 1)      // also allocates and frees the tensor memory
+#define W_VCOPY (W_SOFT + 2)
+#define W_PV0 (W_SOFT + 3)
+#define W_QK1 (W_SOFT + 4)      // with two tiles
+#define W_PV1 (W_SOFT + 5)
+#define TM_COLS (256 * NTILE)   // tensor memory columns: per tile two score buffers of 64 and O of 128
+#define TM_O (128 * NTILE)      // O of tile t at TM_O + 128 t
 enum {
   B_KFULL = 0, B_VFULL = NSTAGE, B_KEMPTY = 2 * NSTAGE, B_VEMPTY = 3 * NSTAGE,
   B_SFULL = 4 * NSTAGE,               // [tile][2 buffers]: the scores of a chunk are in tensor memory
@@ -197,7 +210,7 @@ enum {
   B_COUNT = 4 * NSTAGE + 12
 };
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, 2 / NTILE)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                             const int* __restrict__ block_table, int bt_stride, const int* __restrict__ table_rows,
@@ -245,9 +258,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     give_up = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 9) {
+  if (warp == W_QK0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_holder)),
-                 "r"(512)
+                 "r"(TM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
@@ -278,16 +291,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #define REGS_TAKE() asm volatile("setmaxnreg.inc.sync.aligned.u32 192;\n")
   // tensor memory: S of tile t, buffer sb at columns (2 t + sb) * 64, whose first 32 columns then
   // hold the chunk's probabilities as bf16 pairs (the second product reads them from there: they
-  // never pass through shared memory); O of tile t at 256 + 128 t
+  // never pass through shared memory); O of tile t at TM_O + 128 t
 
-  if (warp == 8 || warp == 10) {
+  if (warp == W_KCOPY || warp == W_VCOPY) {
     // The copy warps, one for keys and one for values: lane p owns page p of the chunk (its id
     // is fetched one chunk ahead, all lanes at once) and issues that page's boxes, so a chunk
     // costs one round trip to the block table, not one per page.  A key stage is free as soon
     // as its scores are computed, a value stage only after the second product: the two rings
     // run independently, each as far ahead as its own stages allow.
     REGS_GIVE();
-    const bool is_v = warp == 10;
+    const bool is_v = warp == W_VCOPY;
     const int* table = block_table + (size_t)(table_rows ? table_rows[b] : b) * bt_stride;
     const int ppc = KC >> page_shift;   // pages per chunk
     const CUtensorMap* map = is_v ? &map_v : &map_k;
@@ -316,14 +329,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       }
       page = next_page;
     }
-  } else if (warp == 9 || warp == 12) {
+  } else if (warp == W_QK0 || warp == W_QK1) {
     // The first product's issuers, one thread per tile: S[t][it & 1] = Q_t K^T, ahead of the
     // softmax.  One thread issues a tcgen05.mma every 60 to 120 cycles whatever its shape; a
     // thread per tile and product keeps the tensor pipe fed and lets the tiles run out of step.
     // Operand descriptors are built once; a stage, a half or a k step only adds to the address.
     REGS_GIVE();
     if (lane == 0) {
-      const int t = warp == 9 ? 0 : 1;
+      const int t = warp == W_QK0 ? 0 : 1;
       const uint32_t idesc_qk = idesc_bf16(ROWS, KC, 0);
       const uint64_t qd = desc_sw128(smem_u32(Qs + t * q_bytes), 0), k_desc = desc_sw128(smem_u32(Ks), 0);
       for (int it = 0; it < n_chunks; ++it) {
@@ -342,13 +355,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         umma_commit(&bars[B_KEMPTY + st]);   // the stage is free when both tiles' issuers have said so
       }
     }
-  } else if (warp == 11 || warp == 13) {
+  } else if (warp == W_PV0 || warp == W_PV1) {
     // The second product's issuers, one thread per tile: O_t += P_t V as soon as the tile's
     // probabilities are published (A operand: the probabilities in tensor memory, 8 columns for
     // 16 keys).
     REGS_GIVE();
     if (lane == 0) {
-      const int t = warp == 11 ? 0 : 1;
+      const int t = warp == W_PV0 ? 0 : 1;
       const uint32_t idesc_pv = idesc_bf16(ROWS, d, 1);
       const uint64_t v_desc = desc_sw128(smem_u32(Vs), KC * 128);
       for (int it = 0; it < n_chunks; ++it) {
@@ -359,13 +372,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const uint64_t vd = v_desc + ((st * tile_bytes) >> 4);
 #pragma unroll
         for (int k = 0; k < 4; ++k)   // 16 keys per MMA: 8 columns of P, two 8-key groups of V
-          umma_ts(tmem + 256 + t * 128, tmem + (2 * t + sb) * KC + k * 8, vd + ((k * 2048) >> 4), idesc_pv,
+          umma_ts(tmem + TM_O + t * 128, tmem + (2 * t + sb) * KC + k * 8, vd + ((k * 2048) >> 4), idesc_pv,
                   (it > 0 || k > 0) ? 1u : 0u);
         umma_commit(&bars[B_PVDONE + 2 * t + sb]);
         umma_commit(&bars[B_VEMPTY + st]);
       }
     }
-  } else if (warp >= 14) {
+  } else if (warp >= W_SOFT) {
     // two warps without a role: they fill the fourth group of four, which hands over its registers
     REGS_GIVE();
   } else {
@@ -381,7 +394,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     // the tile's own range of tokens: chunks past its last row's position are skipped wholesale
     const int t_first = p_first + (t * ROWS) / gb, t_last = min(hi - 1, p_first + (t * ROWS + ROWS - 1) / gb);
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tmem_o = tmem + 256 + t * 128;
+    const uint32_t tmem_o = tmem + TM_O + t * 128;
     const float sc = scale * LOG2E;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
@@ -504,9 +517,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == W_QK0) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base_holder), "r"(512) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base_holder), "r"(TM_COLS) : "memory");
   }
 }
 

@@ -420,10 +420,13 @@ def prefill_tile_tokens(group: int) -> int:
     return 128 // min(group, 128)
 
 
+PREFILL_TC_TILES = 1      # 128-row tiles per block of the tcgen05 prefill kernel (NTILE in attention_tc.cu)
+
+
 def prefill_tc_tile_tokens(group: int) -> int:
-    """Tokens per tile of the tcgen05 prefill kernel: two tiles of 128 rows of (token, head
-    in group) per block (attention_tc.cu)."""
-    return 256 // min(group, 128)
+    """Tokens per block of the tcgen05 prefill kernel: tiles of 128 rows of (token, head in
+    group) (attention_tc.cu)."""
+    return 128 * PREFILL_TC_TILES // min(group, 128)
 
 
 def attention_tile_sizes(group: int) -> frozenset[int]:
