@@ -1,22 +1,27 @@
 // Prefill attention over the paged cache on the fifth-generation tensor cores.
 //
-// One block takes two tiles of 128 rows (tokens x the query heads that share one key/value
-// head) and walks the request's keys in chunks of 64, each chunk loaded once for both tiles:
+// One block takes NTILE tiles of 128 rows (tokens x the query heads that share one key/value
+// head) and walks the request's keys in chunks of 64.  As built (NTILE 1) a block has one tile
+// and eight warps and two blocks share an SM, each with half of the tensor memory; with NTILE 2
+// one block of sixteen warps has two tiles and loads every chunk once for both (measured
+// slower: 676 against 594 us at 8192 tokens).  Per tile:
 //
-//   warps 8, 10  issue TMA copies of key and value pages into a two-stage ring.  The
+//   two copy warps  issue TMA copies of key and value pages into a ring of stages.  The
 //            cache stores every row with its 16-byte chunks permuted by the key's in-page
 //            offset, which is exactly the 128-byte-swizzle pattern of the tensor cores' shared
 //            memory operands, so un-swizzled box copies of [page_size keys x 64 dims] land in
 //            the canonical layout: K as a K-major operand, V as an MN-major one.
-//   warps 9, 12, 11, 13  one thread each issues tcgen05.mma for one tile and one product: S = Q K^T
-//            (128 x 64, fp32 in tensor memory, two buffers so that the next chunk's scores are
-//            computed while this one's softmax runs) and O += P V (128 x d, fp32 in tensor
-//            memory; P is read from tensor memory, where the softmax warps leave it as bf16
-//            over the first half of the chunk's score buffer).
-//   warps 0-7  softmax, four warps per tile, one row per thread: read the row of S from tensor memory, mask what
+//   two issuer warps  one thread each issues the tcgen05.mma of one product: S = Q K^T (128 x 64,
+//            fp32 in tensor memory, two buffers so that the next chunk's scores are computed
+//            while this one's softmax runs) and O += P V (128 x d, fp32 in tensor memory; P is
+//            the A operand and is read from tensor memory, where the softmax warps leave it as
+//            bf16 over the first half of the chunk's score buffer).
+//   four softmax warps  one row per thread: read the row of S from tensor memory, mask what
 //            the row must not see, keep the running maximum and sum in registers (fp32, log2
-//            domain), rescale O in tensor memory when the maximum moved, write P (bf16) into
-//            shared memory as the K-major A operand of the second product.
+//            domain), rescale O in tensor memory when the maximum moved, write P (bf16) back
+//            into tensor memory.  They are what the kernel waits for (64 exponentials a row and
+//            chunk on the special-function unit, about 1,800 cycles a chunk), so they get the
+//            registers of the other warps (setmaxnreg) and the two-wide fp32 instructions.
 //
 // Takes head sizes 64 and 128, power-of-two page sizes from 8 to 64, any group size that
 // divides 128; the mma.sync kernel of attention_mma.cu takes everything else.
@@ -179,6 +184,31 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// The softmax warps are bound by the number of instructions they issue, so the row's arithmetic
+// uses the two-wide fp32 instructions and the three-input maximum of this architecture.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t pair_of(float lo, float hi) {
+  uint64_t p;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(p) : "f"(lo), "f"(hi));
+  return p;
+}
+__device__ __forceinline__ void unpair(uint64_t p, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {   // a * b + c on both halves
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -421,14 +451,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         for (int j = 0; j < 64; ++j)
           if (!(rvalid && key0 + j <= prow && key0 + j >= lorow)) s[j] = -INFINITY;
       }
-      float mx8[8];
+      float mx4[4];   // four independent chains of three-input maxima
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        mx8[i] = fmaxf(fmaxf(fmaxf(s[8 * i], s[8 * i + 1]), fmaxf(s[8 * i + 2], s[8 * i + 3])),
-                       fmaxf(fmaxf(s[8 * i + 4], s[8 * i + 5]), fmaxf(s[8 * i + 6], s[8 * i + 7])));
+      for (int i = 0; i < 4; ++i) {
+        float m = fmaxf(s[16 * i], s[16 * i + 1]);
+#pragma unroll
+        for (int j = 2; j < 16; j += 2) m = max3(m, s[16 * i + j], s[16 * i + j + 1]);
+        mx4[i] = m;
       }
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * sc;   // sc > 0
+      const float mx = fmaxf(max3(mx4[0], mx4[1], mx4[2]), mx4[3]) * sc;   // sc > 0
       // The exponents are taken relative to m_run, which follows the true running maximum
       // lazily: it moves (and O and l are rescaled) only when some row of the warp found a
       // score more than 2^RESCALE_LOG2 above it.  Probabilities may then exceed 1 by that
@@ -439,13 +470,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       float alpha = 1.f, sum = 0.f;
       if (m_new != -INFINITY) {
         alpha = fast_exp2(m_run - m_new);
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint64_t sc2 = pair_of(sc, sc), mneg2 = pair_of(-m_new, -m_new);
+        uint64_t acc[2] = {pair_of(0.f, 0.f), pair_of(0.f, 0.f)};
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          s[j] = fast_exp2(fmaf(s[j], sc, -m_new));
-          sum4[j & 3] += s[j];
+        for (int j = 0; j < 64; j += 2) {
+          float x0, x1;
+          unpair(fma2(pair_of(s[j], s[j + 1]), sc2, mneg2), x0, x1);
+          s[j] = fast_exp2(x0);
+          s[j + 1] = fast_exp2(x1);
+          acc[(j >> 1) & 1] = add2(acc[(j >> 1) & 1], pair_of(s[j], s[j + 1]));
         }
-        sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        float a0, a1;
+        unpair(add2(acc[0], acc[1]), a0, a1);
+        sum = a0 + a1;
       } else {
 #pragma unroll
         for (int j = 0; j < 64; ++j) s[j] = 0.f;
