@@ -298,16 +298,29 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   // rows 0..127 in tile 0 and 128..255 in tile 1, into the swizzled K-major layout; rows that
   // do not exist are zero
   {
-    const int units = d >> 3;   // 16-byte chunks per row
-    for (int idx = tid; idx < NTILE * ROWS * units; idx += TC_THREADS) {
-      const int R = idx / units, u = idx - R * units;
-      const int tk = R / gb, mem = R - tk * gb;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (tk < ntok && mem < heads_here)
-        v = *reinterpret_cast<const uint4*>(q + (size_t)(qs + tok0 + tk) * q_stride +
-                                            (size_t)(kvh * g + hb * gb + mem) * d + u * 8);
-      const int t = R / ROWS, r = R - t * ROWS, half = u >> 3, c = u & 7;
-      *reinterpret_cast<uint4*>(Qs + t * q_bytes + half * (ROWS * 128) + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+    // every thread keeps one 16-byte column u and walks the rows: all of its loads are in flight
+    // before the first store (d and the group size are powers of two, so the indices are shifts)
+    const int ushift = d == 128 ? 4 : 3, gshift = __ffs(gb) - 1;
+    const int u = tid & ((1 << ushift) - 1), r0 = tid >> ushift, rstep = TC_THREADS >> ushift;
+    const int half = u >> 3, c = u & 7;
+    constexpr int PASSES = NTILE * ROWS / (TC_THREADS >> 4);   // with d 128; half as many with d 64
+    uint4 v[PASSES];
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+      const int R = r0 + k * rstep;
+      const int tk = R >> gshift, mem = R & (gb - 1);
+      v[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (R < NTILE * ROWS && tk < ntok && mem < heads_here)
+        v[k] = *reinterpret_cast<const uint4*>(q + (size_t)(qs + tok0 + tk) * q_stride +
+                                               (size_t)(kvh * g + hb * gb + mem) * d + u * 8);
+    }
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+      const int R = r0 + k * rstep;
+      if (R < NTILE * ROWS) {
+        const int t = R / ROWS, r = R & (ROWS - 1);
+        *reinterpret_cast<uint4*>(Qs + t * q_bytes + half * (ROWS * 128) + r * 128 + ((c ^ (r & 7)) << 4)) = v[k];
+      }
     }
     fence_async_smem();
   }
