@@ -78,6 +78,33 @@ def _paged_cache(batch: int, context: int, nkv: int, d: int, page: int, device):
     return kcache, vcache, table
 
 
+def _library_attention(q_lens, kv_lens, nq, nkv, d, page, device):
+    """The same attention through FlashInfer's paged prefill wrapper, the library call the
+    reference project makes for every attention layer (cache/flashinfer_backend.py:289-349:
+    one ``plan`` per step, ``run`` per layer): a bar to compare with, never a product path.
+    Returns ``run()`` or raises ImportError."""
+    import flashinfer
+
+    pages = [-(-n // page) for n in kv_lens]
+    n_pages = sum(pages)
+    kcache = torch.randn(n_pages, page, nkv, d, device=device, dtype=torch.bfloat16)
+    vcache = torch.randn_like(kcache)
+    q = torch.randn(sum(q_lens), nq, d, device=device, dtype=torch.bfloat16)
+    qo_indptr = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=device)
+    kv_indptr = torch.tensor([0] + list(torch.tensor(pages).cumsum(0)), dtype=torch.int32, device=device)
+    kv_indices = torch.randperm(n_pages, device=device).to(torch.int32)
+    last = torch.tensor([(n - 1) % page + 1 for n in kv_lens], dtype=torch.int32, device=device)
+    workspace = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    wrapper = flashinfer.BatchPrefillWithPagedKVCacheWrapper(workspace, "NHD")
+    wrapper.plan(qo_indptr, kv_indptr, kv_indices, last, nq, nkv, d, page, causal=True, pos_encoding_mode="NONE",
+                 sm_scale=1.0 / math.sqrt(d), q_data_type=torch.bfloat16, kv_data_type=torch.bfloat16)
+
+    def run():
+        wrapper.run(q, (kcache, vcache))
+
+    return run
+
+
 def attention_decode(args, ops, device, flush) -> tuple[float, str]:
     nq, nkv, d = args.heads, args.kv_heads, args.head_dim
     kcache, vcache, table = _paged_cache(args.batch, args.context, nkv, d, args.page, device)
@@ -90,6 +117,10 @@ def attention_decode(args, ops, device, flush) -> tuple[float, str]:
         kv_len = torch.tensor(lens, device=device, dtype=torch.int32)
     total = int(kv_len.sum().item())
     nbytes = 2 * total * nkv * d * 2
+    if args.impl == "library":
+        run = _library_attention([1] * args.batch, kv_len.tolist(), nq, nkv, d, args.page, device)
+        us = _time(run, args.iters, args.warmup, flush)
+        return us, f"FlashInfer's paged prefill wrapper on one query token per request, {nbytes / us / 1e6:.2f} TB/s of keys and values"
     if args.impl == "sliced":
         splits = args.splits or ops.decode_splits(args.batch, nq, nkv, args.context, 0, device)
 
@@ -122,6 +153,10 @@ def attention_prefill(args, ops, device, flush) -> tuple[float, str]:
     # the tiles with the most keys first, as the engine's step plan lists them
     tile_tok0 = (torch.arange(n_tiles - 1, -1, -1, device=device, dtype=torch.int32) * tile).contiguous()
 
+    flops = 4.0 * nq * d * T * (T + 1) / 2     # causal: QK^T and PV over the visible half
+    if args.impl == "library":
+        us = _time(_library_attention([T], [T], nq, nkv, d, args.page, device), args.iters, args.warmup, flush)
+        return us, f"FlashInfer's paged prefill wrapper, {flops / us / 1e6:.1f} TFLOP/s (causal flops)"
     kernel = ops.attention_prefill_tc if args.impl == "tc" else ops.attention_prefill
 
     def run():
@@ -129,7 +164,6 @@ def attention_prefill(args, ops, device, flush) -> tuple[float, str]:
                tile_req, tile_tok0, n_tiles, tile, nq, nkv, d, 1.0 / math.sqrt(d), 0)
 
     us = _time(run, args.iters, args.warmup, flush)
-    flops = 4.0 * nq * d * T * (T + 1) / 2     # causal: QK^T and PV over the visible half
     return us, f"{flops / us / 1e6:.1f} TFLOP/s (causal flops)"
 
 
@@ -230,9 +264,10 @@ def main(argv=None) -> int:
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--top-k", type=int, default=0)
     ap.add_argument("--top-p", type=float, default=1.0)
-    ap.add_argument("--impl", choices=["tc", "mma", "balanced", "sliced"], default=None,
+    ap.add_argument("--impl", choices=["tc", "mma", "balanced", "sliced", "library"], default=None,
                     help="attention_prefill: the tcgen05 kernel (default) or the mma.sync kernel; attention_decode: "
-                         "keys spread evenly over persistent blocks (default) or equal slices per request")
+                         "keys spread evenly over persistent blocks (default) or equal slices per request; "
+                         "library: FlashInfer's paged prefill wrapper on the same shapes, for comparison")
     ap.add_argument("--skew", type=float, default=0.0,
                     help="attention_decode: request lengths from context / skew up to context (0: all equal)")
     ap.add_argument("--timer", choices=["device", "events"], default="device",
