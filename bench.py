@@ -577,6 +577,10 @@ def run_serving(args) -> int:
         line.update(serving_ours(args))
     if "batch" in line:
         line["value"] = line["batch"]["throughput_tok_s"]
+        # both schedulers run with their own defaults, as the reference's script runs its own
+        line["config"]["prompt_portion"] = ("256 tokens per request and step (the reference's default chunk_size)"
+                                            if args.impl == "reference" else
+                                            "up to the step's 2048-token budget, oldest request first (this engine's default)")
     print(json.dumps(line))
     return 0
 

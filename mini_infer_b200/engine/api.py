@@ -1,7 +1,7 @@
 """The Python entry point, in the reference's manner (``README.md:108-131``):
 
     runner = ModelRunner.from_pretrained(model_dir, dtype="bfloat16", num_blocks=1024, block_size=16)
-    scheduler = ContinuousScheduler(runner, max_concurrent=16, chunk_size=256)
+    scheduler = ContinuousScheduler(runner, max_concurrent=16)
     result = scheduler.run(Request(prompt=[1, 2, 3], sampling_params=SamplingParams(), max_tokens=32))
     result.tokens, result.finish_reason
 
@@ -19,7 +19,7 @@ from .scheduler import ContinuousScheduler, GenerationResult, Request
 
 def generate(runner: ModelRunner, prompts: Sequence[Sequence[int]], *, max_tokens: int = 16,
              sampling_params: SamplingParams | Sequence[SamplingParams] | None = None,
-             max_concurrent: int = 16, chunk_size: int = 256, max_tokens_per_step: int = 2048,
+             max_concurrent: int = 16, chunk_size: int | None = None, max_tokens_per_step: int = 2048,
              decode_headroom_blocks: int = 8, eos_token_ids: Sequence[int] = ()) -> list[GenerationResult]:
     """Generate for every prompt (token ids) with continuous batching; results in order."""
     if sampling_params is None:

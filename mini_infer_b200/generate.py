@@ -49,7 +49,8 @@ def main(argv=None) -> int:
     ap.add_argument("--num-blocks", type=int, default=int(env.get("MINI_INFER_NUM_BLOCKS", 1024)))
     ap.add_argument("--block-size", type=int, default=int(env.get("MINI_INFER_BLOCK_SIZE", 16)))
     ap.add_argument("--max-concurrent", type=int, default=16)
-    ap.add_argument("--chunk-size", type=int, default=256)
+    ap.add_argument("--chunk-size", type=int, default=None,
+                    help="most prompt tokens one request feeds in a step (default: the step's token budget)")
     ap.add_argument("--max-tokens-per-step", type=int, default=2048)
     ap.add_argument("--decode-headroom-blocks", type=int, default=8)
     ap.add_argument("--eos-token-id", type=int, action="append", default=[])

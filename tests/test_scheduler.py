@@ -88,6 +88,16 @@ def test_generates_and_frees_everything():
         assert runner.fed[rid] == prompt(n) + results[rid].tokens[:-1]
 
 
+def test_without_a_chunk_size_prompts_are_fed_oldest_first_and_whole_where_they_fit():
+    runner, sched = make(max_tokens_per_step=64, decode_headroom_blocks=0)
+    sched.generate([Request(prompt(40), max_tokens=1), Request(prompt(40), max_tokens=1),
+                    Request(prompt(40), max_tokens=1)])
+    # step 0: the first prompt whole, the second gets what the budget leaves; step 1: its rest, then the third
+    assert [(r, n) for r, n, _, _ in runner.log[0]] == [(0, 40), (1, 24)]
+    assert [(r, n) for r, n, _, _ in runner.log[1]] == [(1, 16), (2, 40)]
+    assert len(runner.log) == 2
+
+
 def test_token_budget_decoders_first_then_portions_in_order():
     runner, sched = make(max_tokens_per_step=10, chunk_size=6, decode_headroom_blocks=0)
     sched.generate([Request(prompt(3), max_tokens=30), Request(prompt(20), max_tokens=2),
