@@ -57,19 +57,32 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
+// One try: the thread sleeps in hardware until the phase completes (it is woken at once) or
+// until about WAIT_HINT_NS have passed.  Without the hint a try comes back after a few hundred
+// cycles and the waiting warps' polling takes issue slots from the warps that work.
+#define WAIT_HINT_NS 20000u
+#define WAIT_LIMIT_NS 2000000000ull   // a wait gives up after two seconds
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(WAIT_HINT_NS)
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* give_up) {
-  for (int it = 0; it < SPIN_LIMIT; ++it) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (int it = 0; it < SPIN_LIMIT; ++it) {   // bounded both in tries and in time
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 1023) == 1023 && *give_up) return false;   // another role of this block gave up
+    if (*give_up) return false;   // another role of this block gave up
+    if (global_ns() - t0 > WAIT_LIMIT_NS) break;
   }
   report_give_up();
   *give_up = 1;
