@@ -477,41 +477,64 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         for (int j = 0; j < 64; ++j)
           if (!(rvalid && key0 + j <= prow && key0 + j >= lorow)) s[j] = -INFINITY;
       }
-      float mx4[4];   // four independent chains of three-input maxima
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float m = fmaxf(s[16 * i], s[16 * i + 1]);
-#pragma unroll
-        for (int j = 2; j < 16; j += 2) m = max3(m, s[16 * i + j], s[16 * i + j + 1]);
-        mx4[i] = m;
-      }
-      const float mx = fmaxf(max3(mx4[0], mx4[1], mx4[2]), mx4[3]) * sc;   // sc > 0
       // The exponents are taken relative to m_run, which follows the true running maximum
       // lazily: it moves (and O and l are rescaled) only when some row of the warp found a
       // score more than 2^RESCALE_LOG2 above it.  Probabilities may then exceed 1 by that
       // factor, which fp32 sums and bf16 products hold without loss; the result is the same
       // quotient, and rescaling O in tensor memory becomes rare instead of the rule.
-      const bool moved = __any_sync(0xffffffffu, mx > m_run + RESCALE_LOG2);
-      const float m_new = moved ? fmaxf(m_run, mx) : m_run;
-      float alpha = 1.f, sum = 0.f;
-      if (m_new != -INFINITY) {
-        alpha = fast_exp2(m_run - m_new);
-        const uint64_t sc2 = pair_of(sc, sc), mneg2 = pair_of(-m_new, -m_new);
+      // So the exponentials need not wait for the chunk's maximum: they are computed against
+      // the reference as it stands while the maximum is being found (the two streams of
+      // instructions use different pipes and interleave), and only when the reference has to
+      // move, or a row has none yet, are they computed again against the new one.
+      const uint64_t sc2 = pair_of(sc, sc);
+      uint32_t pk[32];   // the probabilities as bf16 pairs: column j of this thread's lane holds keys 2j and 2j + 1
+      float sum = 0.f, mx4[4];
+      const bool ahead = __all_sync(0xffffffffu, m_run != -INFINITY);
+      if (ahead) {
+        const uint64_t mneg2 = pair_of(-m_run, -m_run);
         uint64_t acc[2] = {pair_of(0.f, 0.f), pair_of(0.f, 0.f)};
 #pragma unroll
         for (int j = 0; j < 64; j += 2) {
           float x0, x1;
           unpair(fma2(pair_of(s[j], s[j + 1]), sc2, mneg2), x0, x1);
-          s[j] = fast_exp2(x0);
-          s[j + 1] = fast_exp2(x1);
-          acc[(j >> 1) & 1] = add2(acc[(j >> 1) & 1], pair_of(s[j], s[j + 1]));
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          acc[(j >> 1) & 1] = add2(acc[(j >> 1) & 1], pair_of(p0, p1));
+          pk[j >> 1] = pack_bf16(p0, p1);
+          mx4[j >> 4] = (j & 15) ? max3(mx4[j >> 4], s[j], s[j + 1]) : fmaxf(s[j], s[j + 1]);
         }
         float a0, a1;
         unpair(add2(acc[0], acc[1]), a0, a1);
         sum = a0 + a1;
       } else {
 #pragma unroll
-        for (int j = 0; j < 64; ++j) s[j] = 0.f;
+        for (int j = 0; j < 64; j += 2)   // four independent chains of three-input maxima
+          mx4[j >> 4] = (j & 15) ? max3(mx4[j >> 4], s[j], s[j + 1]) : fmaxf(s[j], s[j + 1]);
+      }
+      const float mx = fmaxf(max3(mx4[0], mx4[1], mx4[2]), mx4[3]) * sc;   // sc > 0
+      const bool moved = __any_sync(0xffffffffu, mx > m_run + RESCALE_LOG2);
+      const float m_new = moved ? fmaxf(m_run, mx) : m_run;
+      float alpha = 1.f;
+      if (!ahead || moved) {   // (the same for the whole warp)
+        sum = 0.f;
+        if (m_new != -INFINITY) {
+          alpha = fast_exp2(m_run - m_new);
+          const uint64_t mneg2 = pair_of(-m_new, -m_new);
+          uint64_t acc[2] = {pair_of(0.f, 0.f), pair_of(0.f, 0.f)};
+#pragma unroll
+          for (int j = 0; j < 64; j += 2) {
+            float x0, x1;
+            unpair(fma2(pair_of(s[j], s[j + 1]), sc2, mneg2), x0, x1);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            acc[(j >> 1) & 1] = add2(acc[(j >> 1) & 1], pair_of(p0, p1));
+            pk[j >> 1] = pack_bf16(p0, p1);
+          }
+          float a0, a1;
+          unpair(add2(acc[0], acc[1]), a0, a1);
+          sum = a0 + a1;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) pk[j] = 0u;
+        }
       }
       m_run = m_new;
       l_run = l_run * alpha + sum;
@@ -529,15 +552,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         }
         tmem_st_wait();
       }
-      // P as bf16 pairs over the first 32 columns of the chunk's score buffer: column j of this
-      // thread's lane holds keys 2j and 2j + 1
-      {
-        uint32_t pk[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) pk[j] = pack_bf16(s[2 * j], s[2 * j + 1]);
-        tmem_st32_bits(tmem + lane_addr + (2 * t + sb) * KC, pk);
-        tmem_st_wait();
-      }
+      // P over the first 32 columns of the chunk's score buffer
+      tmem_st32_bits(tmem + lane_addr + (2 * t + sb) * KC, pk);
+      tmem_st_wait();
       // value rows of keys nobody may see can hold anything (pages never written, stale rows):
       // clear them, 0 * NaN is NaN.  Only a request's first and last chunks have such rows.  Each
       // tile does it before it publishes its probabilities (the tiles' second products are
