@@ -248,11 +248,7 @@ def test_linear_library_and_streaming_kernels_agree():
     w = rnd(300, 264, dtype=torch.bfloat16, seed=22, scale=0.1).to(DEV)
     x = rnd(40, 264, dtype=torch.bfloat16, seed=23).to(DEV)
     big = ops().linear(x, w).float()              # library product
-    ops().USE_SKINNY_GEMM = True
-    try:
-        small = torch.cat([ops().linear(x[i:i + 8].contiguous(), w).float() for i in range(0, 40, 8)])
-    finally:
-        ops().USE_SKINNY_GEMM = False
+    small = torch.cat([ops().linear(x[i:i + 8].contiguous(), w).float() for i in range(0, 40, 8)])
     assert (big - small).abs().max().item() <= 1 / 64 * max(1.0, big.abs().max().item())
     assert ops().linear(x[:4].contiguous(), w, out_dtype=torch.float32).dtype == torch.float32
     assert ops().linear(x, w, out_dtype=torch.float32).dtype == torch.float32
