@@ -105,6 +105,19 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+// two bf16 pairs (x1 in `lo`, their partners x2 in `hi`) rotated by the angles whose sines and cosines follow sn, cn
+__device__ __forceinline__ void rotate_words(uint32_t& lo, uint32_t& hi, const float* __restrict__ sn,
+                                             const float* __restrict__ cn) {
+  const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lo));
+  const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hi));
+  float a0, a1, b0, b1;
+  mi_rotate(x1.x, x2.x, sn[0], cn[0], a0, b0);
+  mi_rotate(x1.y, x2.y, sn[1], cn[1], a1, b1);
+  lo = pack_bf16(a0, a1);
+  hi = pack_bf16(b0, b1);
+}
+// the same for every state space: plain stores to global memory that a bulk copy reads next
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
 
 __device__ __forceinline__ int inpage_of(int j, int page_size, int page_shift) {
@@ -690,8 +703,9 @@ __device__ __noinline__ void balanced_merge_unit(const float* __restrict__ part_
     if (cgrp + 16 * c < d) orow[cgrp + 16 * c] = __float2bfloat16_rn(acc[c] * inv);
 }
 
-template <int DMAX>
-__global__ void __launch_bounds__(DEC_THREADS, DMAX <= 128 ? 2 : 1)
+#define BAL_THREADS (NTHREADS + 64)   // four consumer warps, the copy warp, the store warp (ROPE only)
+template <int DMAX, bool ROPE>
+__global__ void __launch_bounds__(ROPE ? BAL_THREADS : DEC_THREADS, DMAX <= 128 ? 2 : 1)
 attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                                  const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                                  const int* __restrict__ block_table, int bt_stride,
@@ -699,7 +713,12 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
                                  const int* __restrict__ q_start, const int* __restrict__ kv_len, int B, int nq,
                                  int nkv, int d, float scale, int window, int min_chunks,
                                  float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
-                                 int* __restrict__ status) {
+                                 int* __restrict__ status, const float* __restrict__ rope_cs, int store_kv) {
+  // ROPE (the head size is then DMAX exactly): rope_cs holds per query token [d / 2] sines then
+  // [d / 2] cosines of its rotary angles; q arrives un-rotated and is rotated here, in registers; and with store_kv
+  // the block that comes to a request's newest chunk first rotates the new key, writes it and
+  // the new value into their page (they follow q in the token's row: q heads, k heads, v heads)
+  // and only then copies the chunk.  One kernel and one kernel boundary less per layer.
   mi_pdl_launch_dependents();   // (what this kernel may touch before it waits: see attention_decode_kernel)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                      // [DEC_STAGES][64][d]
@@ -708,7 +727,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
   int* cum = reinterpret_cast<int*>(merge_o + 4 * DEC_HEADS * d);    // [B + 1] chunks of the requests before b
   const int swz_mask = mi_swizzle_mask(d, 2);
   __shared__ float merge_m[4][DEC_HEADS], merge_l[4][DEC_HEADS];
-  __shared__ __align__(8) uint64_t bars[DEC_STAGES], empty[DEC_STAGES];
+  __shared__ __align__(8) uint64_t bars[DEC_STAGES], empty[DEC_STAGES], stored;
   __shared__ int is_last;
   __shared__ volatile int dead;   // a warp gave up waiting for a copy: everybody leaves at the next common point
 
@@ -720,7 +739,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
   if (tid == 0) dead = 0;
 
   // chunks per request, and their running sum (one warp; B is at most a few hundred)
-  for (int b = tid; b < B; b += DEC_THREADS) {
+  for (int b = tid; b < B; b += (ROPE ? BAL_THREADS : DEC_THREADS)) {
     const int kl = kv_len[b];
     const int lo = window > 0 ? max(0, kl - window) : 0;   // (a window skips the chunks below it)
     cum[b + 1] = (kl + KCHUNK - 1) / KCHUNK - lo / KCHUNK;
@@ -763,6 +782,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
       mbar_init(&bars[i], 1);
       mbar_init(&empty[i], 4);
     }
+    mbar_init(&stored, 1);
     fence_mbar_init();
   }
   __syncthreads();
@@ -771,7 +791,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
     // the copy warp: walks the stretch chunk by chunk and keeps the ring full
     PageLoader loader;
     const int pieces = 2 * (KCHUNK / PageLoader::piece_rows(page_size, page_shift));
-    bool ok = true, waited = false;
+    bool ok = true, waited = false, stored_seen = false;
     int it = 0;
     for (long long i = i0; i < i1 && ok;) {
       int b, u, c_rel, n_b;
@@ -786,9 +806,18 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
         if (it >= DEC_STAGES)
           ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty[st], ((it / DEC_STAGES) - 1) & 1, status));
         if (!ok) break;
-        if (!waited && (c + 1) * KCHUNK >= kl) {   // the chunk with the newest position: written by this step
-          mi_pdl_wait();
-          waited = true;
+        if ((c + 1) * KCHUNK >= kl) {   // the chunk with the newest position: written by this step
+          if (!waited) {
+            mi_pdl_wait();
+            waited = true;
+          }
+          if (ROPE && store_kv && !stored_seen) {
+            // the other warps have rotated and stored the newest keys and values of this block's requests
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&stored, 0, status));
+            if (!ok) break;
+            fence_proxy_async_all();
+            stored_seen = true;
+          }
         }
         if (lane == 0) mbar_expect_tx(&bars[st], PageLoader::chunk_bytes(c, lo, kl, d, page_size, page_shift));
         __syncwarp();
@@ -801,6 +830,55 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
       }
       i += seg;
     }
+    return;
+  }
+
+  if (ROPE && warp == 5) {
+    // The store warp (only when this kernel rotates and stores by itself): the newest key
+    // (rotated) and value of every request whose last chunk this block reads go into their
+    // pages, beside the other warps' work and long before the copy warp gets there.  Blocks
+    // that read the same chunk (other head groups of the key/value head) write the same bytes.
+    if (!store_kv) return;
+    mi_pdl_wait();
+    const int half = d >> 1, n_rot = half >> 3, cpr = d >> 3, per_unit = n_rot + cpr;
+    for (long long i = i0; i < i1;) {
+      int b, u, c_rel, n_b;
+      balanced_locate(i, cum, B, U, b, u, c_rel, n_b);
+      const int seg = (int)min((long long)(n_b - c_rel), i1 - i);
+      if (c_rel + seg == n_b) {
+        const int kvh = u / hblocks, kl = kv_len[b], tok = q_start[b], pos = kl - 1;
+        const int* table = block_table + (size_t)(table_rows ? table_rows[b] : b) * bt_stride;
+        const int page = table[page_shift >= 0 ? (pos >> page_shift) : (pos / page_size)];
+        const int off = inpage_of(pos, page_size, page_shift), swz = off & swz_mask;
+        const bf16* krow = q + (size_t)tok * q_stride + (size_t)(nq + kvh) * d;
+        const bf16* vrow = krow + (size_t)nkv * d;
+        const size_t row = (((size_t)page * nkv + kvh) * page_size + off) * d;
+        bf16* kdst = const_cast<bf16*>(kcache) + row;
+        bf16* vdst = const_cast<bf16*>(vcache) + row;
+        const float* cs = rope_cs + (size_t)tok * d;
+        for (int item = lane; item < per_unit; item += 32) {
+          if (item < n_rot) {
+            uint4 a = *reinterpret_cast<const uint4*>(krow + item * 8);
+            uint4 bb = *reinterpret_cast<const uint4*>(krow + half + item * 8);
+            const float* sn = cs + item * 8;
+            const float* cn = cs + half + item * 8;
+            rotate_words(a.x, bb.x, sn + 0, cn + 0);
+            rotate_words(a.y, bb.y, sn + 2, cn + 2);
+            rotate_words(a.z, bb.z, sn + 4, cn + 4);
+            rotate_words(a.w, bb.w, sn + 6, cn + 6);
+            *reinterpret_cast<uint4*>(kdst + ((item ^ swz) << 3)) = a;
+            *reinterpret_cast<uint4*>(kdst + (((n_rot + item) ^ swz) << 3)) = bb;
+          } else {
+            const int j = item - n_rot;
+            *reinterpret_cast<uint4*>(vdst + ((j ^ swz) << 3)) = *reinterpret_cast<const uint4*>(vrow + j * 8);
+          }
+        }
+      }
+      i += seg;
+    }
+    fence_proxy_async_all();   // a bulk copy reads these plain stores next
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&stored);
     return;
   }
 
@@ -834,6 +912,18 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
           qb[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
           qb[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t4);
         }
+      }
+      if (ROPE && qd < heads_here) {
+        // dims below d / 2 pair with the same lane's dims d / 2 further on: DMAX / 32 k steps further on
+        const float* cs = rope_cs + (size_t)tok * d;
+        constexpr int HK = DMAX / 32;
+#pragma unroll
+        for (int ks = 0; ks < HK; ++ks)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int i0 = ks * 16 + e * 8 + 2 * t4;
+            rotate_words(qb[ks][e], qb[ks + HK][e], cs + i0, cs + DMAX / 2 + i0);
+          }
       }
     }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
@@ -1460,8 +1550,10 @@ extern "C" int mi_attention_decode_balanced(const void* q, int q_stride, void* o
                                             const int* table_rows, int page_size, const int* q_start,
                                             const int* kv_len, int B, int nq, int nkv, int d, float scale, int window,
                                             int grid, float* part_o, float* part_ml, int* counters,
-                                            cudaStream_t stream) {
+                                            const float* rope_cs, int store_kv, cudaStream_t stream) {
   if (B <= 0) return 0;
+  if (rope_cs && ((d != 64 && d != 128 && d != 256) || !mi_aligned(rope_cs, 4)))
+    MI_REFUSE("attention: rotating inside the decode kernel needs a head size of 64, 128 or 256, got %d", d);
   if (int rc = check_common(q, q_stride, out, out_stride, kcache, vcache, nq, nkv, d, page_size, window)) return rc;
   if (grid <= 0 || !part_o || !part_ml || !counters) MI_REFUSE("attention: the balanced kernel needs its grid and scratch");
   if (!mi_aligned(part_o, 4) || !mi_aligned(part_ml, 8) || !mi_aligned(counters, 4))
@@ -1469,21 +1561,25 @@ extern "C" int mi_attention_decode_balanced(const void* q, int q_stride, void* o
   if (B > 16384) MI_REFUSE("attention: %d requests in one decode step", B);
   const int page_shift = shift_of(page_size);
   const size_t smem = balanced_smem_bytes(B, d);
-#define MI_DECODE_BAL(DMAX)                                                                               \
+#define MI_DECODE_BAL(DMAX, ROPE)                                                                         \
   do {                                                                                                    \
-    auto kern = attention_decode_balanced_kernel<DMAX>;                                                   \
+    auto kern = attention_decode_balanced_kernel<DMAX, ROPE>;                                             \
     if (smem > 40 * 1024) {                                                                               \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return (int)e;                                                                \
     }                                                                                                     \
-    MI_LAUNCH((kern), grid, DEC_THREADS, smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,  \
-              (const bf16*)kcache, (const bf16*)vcache, block_table, bt_stride, table_rows, page_size,    \
-              page_shift, q_start, kv_len, B, nq, nkv, d, scale, window, 4, part_o, part_ml, counters,    \
-              wait_status_ptr());                                                                         \
+    MI_LAUNCH((kern), grid, ROPE ? BAL_THREADS : DEC_THREADS, smem, stream, (const bf16*)q, q_stride,     \
+              (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, block_table, bt_stride,   \
+              table_rows, page_size, page_shift, q_start, kv_len, B, nq, nkv, d, scale, window, 4, part_o, \
+              part_ml, counters, wait_status_ptr(), rope_cs, store_kv);                                   \
   } while (0)
-  if (d <= 64) MI_DECODE_BAL(64);
-  else if (d <= 128) MI_DECODE_BAL(128);
-  else MI_DECODE_BAL(256);
+  if (rope_cs) {
+    if (d == 64) MI_DECODE_BAL(64, true);
+    else if (d == 128) MI_DECODE_BAL(128, true);
+    else MI_DECODE_BAL(256, true);
+  } else if (d <= 64) MI_DECODE_BAL(64, false);
+  else if (d <= 128) MI_DECODE_BAL(128, false);
+  else MI_DECODE_BAL(256, false);
 #undef MI_DECODE_BAL
   MI_RETURN_LAUNCH_STATUS();
 }

@@ -172,4 +172,12 @@ __device__ __forceinline__ int mi_swizzled(int k, int t, int mask, int epc) {
   return (((k / epc) ^ (t & mask)) * epc) + (k % epc);
 }
 
+// One rotation of the rotary encoding in fp32, every operation rounded on its own (never
+// contracted into a fused multiply-add), so that every kernel that rotates gives the same bits:
+// (y1, y2) = (x1 c - x2 s, x2 c + x1 s).
+__device__ __forceinline__ void mi_rotate(float x1, float x2, float s, float c, float& y1, float& y2) {
+  y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
+  y2 = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
+}
+
 static inline bool mi_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

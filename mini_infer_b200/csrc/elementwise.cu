@@ -260,8 +260,10 @@ __global__ void rope_write_kernel(T* __restrict__ qkv, const int* __restrict__ p
         sincosf(p * inv_freq[i], &s, &c);
         const float x1 = mi_to_float(head[i]);
         const float x2 = mi_to_float(head[i + half]);
-        const T y1 = mi_from_float<T>(x1 * c - x2 * s);
-        const T y2 = mi_from_float<T>(x2 * c + x1 * s);
+        float r1, r2;
+        mi_rotate(x1, x2, s, c, r1, r2);
+        const T y1 = mi_from_float<T>(r1);
+        const T y2 = mi_from_float<T>(r2);
         head[i] = y1;
         head[i + half] = y2;
         if (dst) {
@@ -338,9 +340,7 @@ __global__ void rope_write_chunks_kernel(T* __restrict__ qkv, const int* __restr
         b.get(x2);
 #pragma unroll
         for (int i = 0; i < E; ++i) {
-          const float s = rope_sc[j * E + i], c = rope_sc[half + j * E + i];
-          y1[i] = x1[i] * c - x2[i] * s;
-          y2[i] = x2[i] * c + x1[i] * s;
+          mi_rotate(x1[i], x2[i], rope_sc[j * E + i], rope_sc[half + j * E + i], y1[i], y2[i]);
         }
         a.set(y1);
         b.set(y2);
@@ -363,6 +363,24 @@ __global__ void rope_write_chunks_kernel(T* __restrict__ qkv, const int* __restr
       a.store(dst + ((j ^ swz) * E));
     }
   }
+}
+
+// Sines and cosines of every token's rotary angles, for kernels that rotate on their own (decode
+// attention rotates its query and the new key itself): out [M, 2 half] fp32, row t = [half]
+// sines then [half] cosines of pos[t] * inv_freq[i], computed as the kernels above compute them.
+__global__ void rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq,
+                                  float* __restrict__ out, int half) {
+  mi_pdl_enter();
+  const float p = (float)pos[blockIdx.x];
+  float* row = out + (size_t)blockIdx.x * 2 * half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(p * inv_freq[i], &row[i], &row[half + i]);
+}
+
+extern "C" int mi_rope_table(const int* pos, const float* inv_freq, float* out, int M, int half, cudaStream_t stream) {
+  if (M <= 0 || half <= 0) return 0;
+  if (!pos || !inv_freq || !out) MI_REFUSE("rope table: positions, frequencies and the output are required");
+  MI_LAUNCH((rope_table_kernel), M, half < 128 ? ((half + 31) / 32 * 32) : 128, 0, stream, pos, inv_freq, out, half);
+  MI_RETURN_LAUNCH_STATUS();
 }
 
 extern "C" int mi_rope_write(void* qkv, const int* pos, const float* inv_freq, const int* slot,

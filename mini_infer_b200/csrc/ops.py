@@ -130,6 +130,7 @@ def _sig_elementwise(lib: ctypes.CDLL) -> None:
     lib.mi_silu_mul.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     lib.mi_silu_mul_pairs.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     lib.mi_table_update.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
+    lib.mi_rope_table.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
 
 
 def _sig_gemm_f32(lib: ctypes.CDLL) -> None:
@@ -165,7 +166,7 @@ def _sig_attention_mma(lib: ctypes.CDLL) -> None:
                                                          ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(c_int)]
     lib.mi_attention_decode_balanced.argtypes = [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-        c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+        c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     lib.mi_attention_wait_status.argtypes = [c_int]
     lib.mi_set_status_word.argtypes = [c_void_p]
     lib.mi_attention_prefill.argtypes = [
@@ -459,23 +460,57 @@ def decode_splits(n_requests: int, nq: int, nkv: int, max_kv_len: int, window: i
     return max(1, min(2 * _sms(device) // blocks, chunks // 4, 64))
 
 
+FUSE_DECODE_ROPE = os.environ.get("MINI_INFER_FUSE_ROPE", "1") != "0"
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """``[tokens, 2 * len(inv_freq)]`` fp32: per token the sines, then the cosines, of
+    ``position * inv_freq``, computed as the rotary kernels compute them (elementwise.cu)."""
+    _cuda(positions, inv_freq)
+    if positions.dtype != torch.int32 or inv_freq.dtype != torch.float32:
+        raise KernelError("rope_table: int32 positions and fp32 frequencies")
+    half = inv_freq.numel()
+    out = torch.empty((positions.numel(), 2 * half), dtype=torch.float32, device=positions.device)
+    lib = _lib("elementwise")
+    rc = lib.mi_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(out), positions.numel(), half, _stream())
+    _finish(lib, rc, "rope_table")
+    return out
+
+
+FUSE_DECODE_ROPE_MAX_REQUESTS = 16
+
+
+def decode_rope_fusable(q_dtype: torch.dtype, head_dim: int, decode_only: bool, n_requests: int) -> bool:
+    """Whether ``attention`` should rotate q and store the new key and value itself (the decode
+    kernel of bfloat16 steps in which every request brings one token).  Measured inside the
+    captured step at Llama 3.1 8B sizes: one kernel boundary less per layer is worth 0.5 % at
+    batch 8; at batch 64 the separate kernel is 1 % faster (while it runs, the attention kernel's
+    copy warps are already fetching pages), hence the limit."""
+    return (FUSE_DECODE_ROPE and decode_only and q_dtype == torch.bfloat16 and head_dim in (64, 128, 256)
+            and n_requests <= FUSE_DECODE_ROPE_MAX_REQUESTS)
+
+
 def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq: int, nkv: int,
-              head_dim: int, scale: float, window: int = 0) -> None:
+              head_dim: int, scale: float, window: int = 0, rope_table: torch.Tensor | None = None) -> None:
     """Attention of this step's queries over one cache layer.
 
     ``cache`` is a ``LayerCache`` (its ``k``/``v`` pages and group index), ``ctx`` the
     ``StepContext`` (block tables, lengths, query tiles).  float32 runs the CUDA-core kernel;
     bfloat16 runs the tensor-core kernels: the balanced decode kernel when every request brings
     one token, otherwise the tcgen05 prefill kernel where it takes the sizes and the mma.sync
-    prefill kernel elsewhere.
+    prefill kernel elsewhere.  ``rope_table`` (only where ``decode_rope_fusable``): q, k, v are
+    un-rotated and not yet stored; the decode kernel does both.
     """
     group = ctx.groups[cache.group]
     if q.dtype == torch.bfloat16:
         if ctx.decode_only:
             attention_decode_balanced(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
                                       ctx.q_start, ctx.kv_len, ctx.n_requests, nq, nkv, head_dim, scale, window,
-                                      table_rows=group.table_rows)
+                                      table_rows=group.table_rows, rope_table=rope_table,
+                                      store_kv=bool(cache.writes))
         else:
+            if rope_table is not None:
+                raise KernelError("attention: only the decode kernel rotates and stores by itself")
             tc = USE_TC_PREFILL and prefill_tc_supported(nq, nkv, head_dim, group.page_size)
             tt = (prefill_tc_tile_tokens if tc else prefill_tile_tokens)(nq // nkv)
             tile_req, tile_tok0, n_tiles = ctx.q_tiles(tt)
@@ -566,11 +601,18 @@ def _balanced_workspace(device: torch.device, o_floats: int, ml_floats: int, cou
 
 
 def attention_decode_balanced(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, kv_len,
-                              n_requests, nq, nkv, head_dim, scale, window=0, table_rows=None) -> None:
+                              n_requests, nq, nkv, head_dim, scale, window=0, table_rows=None,
+                              rope_table: torch.Tensor | None = None, store_kv: bool = True) -> None:
     """bfloat16 decode attention with the keys of all requests spread evenly over persistent
     blocks, whatever the requests' lengths (attention_decode_balanced_kernel): no plan from the
-    host, the blocks read the lengths themselves."""
-    _cuda(q, out, kcache, vcache, block_table, q_start, kv_len, table_rows)
+    host, the blocks read the lengths themselves.  With ``rope_table`` (``rope_table()`` of the
+    step's positions) q, k and v come as the projection left them (one row per token: q heads, k
+    heads, v heads): the kernel rotates q itself and, with ``store_kv``, rotates the new key and
+    writes it and the new value into their page before it reads them."""
+    _cuda(q, out, kcache, vcache, block_table, q_start, kv_len, table_rows, rope_table)
+    if rope_table is not None and (rope_table.dtype != torch.float32 or not rope_table.is_contiguous()
+                                   or rope_table.shape[-1] != head_dim):
+        raise KernelError("attention_decode: the rotary table must be contiguous fp32 [tokens, head_dim]")
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_decode: bfloat16 only")
     _check_attention_args(q, out, kcache, vcache, block_table, nq, nkv, head_dim, page_size,
@@ -586,7 +628,8 @@ def attention_decode_balanced(q, q_stride, out, kcache, vcache, block_table, pag
     rc = lib.mi_attention_decode_balanced(
         _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_table),
         block_table.stride(0), _ptr(table_rows), int(page_size), _ptr(q_start), _ptr(kv_len), int(n_requests), nq, nkv,
-        head_dim, float(scale), int(window), int(grid.value), _ptr(part_o), _ptr(part_ml), _ptr(count), _stream())
+        head_dim, float(scale), int(window), int(grid.value), _ptr(part_o), _ptr(part_ml), _ptr(count),
+        _ptr(rope_table), 1 if store_kv else 0, _stream())
     _finish(lib, rc, "attention_decode")
 
 

@@ -288,6 +288,7 @@ class StepRunner:
 
     def _run(self, ctx: StepContext, caches, want, n_want: int) -> torch.Tensor:
         """The device work of a step: the new page ids into the block tables, then the model."""
+        ctx.scratch.clear()   # what the parts share within a step is made anew in every run (and in a capture)
         self.apply_table_updates(ctx)
         return self.model.forward(ctx, caches, want, n_want)
 

@@ -131,9 +131,14 @@ def attention_decode(args, ops, device, flush) -> tuple[float, str]:
         us = _time(run, args.iters, args.warmup, flush)
         return us, f"{splits} key slices, {nbytes / us / 1e6:.2f} TB/s of keys and values"
 
+    rope = None
+    if args.rope:   # the kernel rotates q and stores the new key and value itself
+        inv_freq = (1.0 / (10000.0 ** (torch.arange(0, d, 2, device=device, dtype=torch.float32) / d))).contiguous()
+        rope = ops.rope_table((kv_len - 1).to(torch.int32), inv_freq)
+
     def run():
         ops.attention_decode_balanced(qkv, qkv.stride(0), out, kcache, vcache, table, args.page, q_start, kv_len,
-                                      args.batch, nq, nkv, d, 1.0 / math.sqrt(d), 0)
+                                      args.batch, nq, nkv, d, 1.0 / math.sqrt(d), 0, rope_table=rope)
 
     us = _time(run, args.iters, args.warmup, flush)
     return us, f"balanced over persistent blocks, {nbytes / us / 1e6:.2f} TB/s of keys and values"
@@ -268,6 +273,8 @@ def main(argv=None) -> int:
                     help="attention_prefill: the tcgen05 kernel (default) or the mma.sync kernel; attention_decode: "
                          "keys spread evenly over persistent blocks (default) or equal slices per request; "
                          "library: FlashInfer's paged prefill wrapper on the same shapes, for comparison")
+    ap.add_argument("--rope", action="store_true",
+                    help="attention_decode: give the kernel un-rotated q, k, v and the rotary table (it rotates and stores itself)")
     ap.add_argument("--skew", type=float, default=0.0,
                     help="attention_decode: request lengths from context / skew up to context (0: all equal)")
     ap.add_argument("--timer", choices=["device", "events"], default="device",

@@ -128,6 +128,9 @@ class StepContext:
     # per cache group: (triples, count, capacity) of the page ids the step scatters into the
     # block tables before its first kernel (the step runner's business, not a part's)
     table_updates: list = field(default_factory=list)
+    # what parts of different layers share within one step (a table that depends on the step's
+    # positions only, say): filled by whoever needs it first
+    scratch: dict = field(default_factory=dict)
 
     def q_tiles(self, tokens: int) -> tuple[torch.Tensor, torch.Tensor, int]:
         """``(tile_request, tile_first_token, n_tiles)`` for tiles of ``tokens`` tokens."""

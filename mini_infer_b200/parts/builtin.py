@@ -126,10 +126,24 @@ class RotaryPosition(Position):
         self.inv_freq = rotary_inv_freq(
             d, float(self.param("theta")), self.rotary_dim, self.spec.params.get("scaling")
         ).to(device)
+        # layers with the same frequencies share one table per step
+        self._table_key = (d, self.rotary_dim, float(self.param("theta")), repr(self.spec.params.get("scaling")))
 
     def encode(self, qkv, nq, nkv, head_dim, ctx):
         ops.rope_write(qkv, nq, nkv, head_dim, positions=ctx.positions, inv_freq=self.inv_freq,
                        rotary_dim=self.rotary_dim)
+
+    def step_table(self, ctx, head_dim):
+        """Sines and cosines of this step's positions for a mixer that rotates by itself, or
+        None where that is not possible (a rotary width below the head size).  Layers share one
+        table per step: it depends on the positions and the frequencies only."""
+        if self.rotary_dim != head_dim:
+            return None
+        key = ("rope_table", self._table_key)
+        table = ctx.scratch.get(key)
+        if table is None:
+            table = ctx.scratch[key] = ops.rope_table(ctx.positions, self.inv_freq)
+        return table
 
     def rotate_and_store(self, qkv, nq, nkv, head_dim, ctx, cache):
         if cache.writes and cache.k is not None:
@@ -197,13 +211,20 @@ class GroupedQueryAttention(Mixer):
     def forward(self, x, ctx: StepContext, cache: LayerCache, position):
         nq, nkv, d = self.nq, self.nkv, self.d
         qkv = self.qkv_proj(x)
-        if position is not None:
+        table = None
+        if (position is not None and cache.k is not None and hasattr(position, "step_table")
+                and ops.decode_rope_fusable(x.dtype, d, ctx.decode_only, ctx.n_requests)):
+            table = position.step_table(ctx, d)   # the decode kernel rotates q and stores the new k, v itself
+        if table is not None:
+            pass
+        elif position is not None:
             position.rotate_and_store(qkv, nq, nkv, d, ctx, cache)
         elif cache.writes:
             ops.rope_write(qkv, nq, nkv, d, slots=ctx.groups[cache.group].slots,
                            kcache=cache.k, vcache=cache.v)
         out = torch.empty((ctx.n_tokens, nq * d), dtype=x.dtype, device=x.device)
-        ops.attention(qkv, qkv.stride(0), out, cache, ctx, nq, nkv, d, self.scale, self.window or 0)
+        ops.attention(qkv, qkv.stride(0), out, cache, ctx, nq, nkv, d, self.scale, self.window or 0,
+                      rope_table=table)
         return self.o_proj(out)
 
 

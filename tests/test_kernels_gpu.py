@@ -499,6 +499,58 @@ def test_attention_decode_balanced(nq, nkv, d, page):
         assert (got - want).abs().max().item() <= BF16_BOUND
 
 
+@pytest.mark.parametrize("nq,nkv,d,page", [(32, 8, 128, 16), (8, 2, 64, 8), (6, 3, 128, 16), (5, 1, 256, 32), (4, 4, 64, 16),
+                                            (24, 1, 128, 32)])
+def test_attention_decode_rotates_and_stores_by_itself(nq, nkv, d, page):
+    """The decode kernel given the projection's raw q, k, v and the step's rotary table against
+    the two-kernel route (rotate and store, then attend): the same output and the same cache,
+    bit for bit, with requests whose newest token lies at a page's first slot, at a chunk's edge,
+    deep inside a long context, and alone."""
+    o = ops()
+    kv_lens = [1, 64, 65, 700, page + 1, 2048 if d <= 128 else 300, 129]
+    B = len(kv_lens)
+    kc, vc, bt, ks, vs = build_paged(kv_lens, nkv, d, page, torch.bfloat16, seed=nq + 50)
+    g = torch.Generator().manual_seed(nq + 51)
+    qkv = torch.randn(B, (nq + 2 * nkv) * d, generator=g).to(torch.bfloat16).to(DEV)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV)
+    positions = torch.tensor([L - 1 for L in kv_lens], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([int(bt[i, (L - 1) // page]) * page + (L - 1) % page for i, L in enumerate(kv_lens)],
+                         dtype=torch.int32, device=DEV)
+    q_start = torch.arange(B, dtype=torch.int32, device=DEV)
+    kv_len = torch.tensor(kv_lens, dtype=torch.int32, device=DEV)
+    btd = bt.to(DEV)
+    scale = d ** -0.5
+
+    def caches():
+        return as_pages(kc, page).to(DEV), as_pages(vc, page).to(DEV)
+
+    # two kernels
+    k1, v1 = caches()
+    qkv1 = qkv.clone()
+    o.rope_write(qkv1, nq, nkv, d, positions=positions, inv_freq=inv_freq, rotary_dim=d, slots=slots, kcache=k1, vcache=v1)
+    out1 = torch.full((B, nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.attention_decode_balanced(qkv1, qkv1.stride(0), out1, k1, v1, btd, page, q_start, kv_len, B, nq, nkv, d, scale)
+    # one kernel
+    k2, v2 = caches()
+    table = o.rope_table(positions, inv_freq)
+    out2 = torch.full((B, nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.attention_decode_balanced(qkv.clone(), qkv.stride(0), out2, k2, v2, btd, page, q_start, kv_len, B, nq, nkv, d, scale,
+                                rope_table=table, store_kv=True)
+    torch.cuda.synchronize()
+    assert o.attention_wait_status() == 0
+    assert torch.isfinite(out2).all()
+    assert torch.equal(out1, out2)
+    # the written rows are the same (everything else in the pool is NaN or untouched and equal bit for bit)
+    assert torch.equal(k1.view(torch.int16), k2.view(torch.int16))
+    assert torch.equal(v1.view(torch.int16), v2.view(torch.int16))
+    # without storing: q is rotated, the cache is left as it was (a layer that reads another layer's cache)
+    k3, v3 = k1.clone(), v1.clone()
+    out3 = torch.full((B, nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.attention_decode_balanced(qkv.clone(), qkv.stride(0), out3, k3, v3, btd, page, q_start, kv_len, B, nq, nkv, d, scale,
+                                rope_table=table, store_kv=False)
+    assert torch.equal(out3, out1) and torch.equal(k3.view(torch.int16), k1.view(torch.int16))
+
+
 @pytest.mark.parametrize("window", [1, 30, 64, 200])
 def test_attention_decode_balanced_window_and_far_key(window):
     got, want = run_attention([1, 1, 1], [500, 64, 7], 8, 2, 64, 16, torch.bfloat16, window=window, seed=9, kernel="balanced")
