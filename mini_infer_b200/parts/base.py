@@ -186,6 +186,13 @@ class Position(Part):
     def encode(self, qkv: torch.Tensor, nq: int, nkv: int, head_dim: int, ctx: StepContext) -> None:
         raise NotImplementedError
 
+    def step_table(self, ctx: StepContext, head_dim: int) -> torch.Tensor | None:
+        """For an encoding that is a rotation of the half layout (dim ``j`` with ``j + head_dim /
+        2``): fp32 ``[tokens, head_dim]``, per token the sines then the cosines of its angles, so
+        that a mixer whose kernel rotates by itself can skip ``rotate_and_store``.  None (the
+        default): the encoding goes through ``rotate_and_store``."""
+        return None
+
     def rotate_and_store(self, qkv: torch.Tensor, nq: int, nkv: int, head_dim: int,
                          ctx: StepContext, cache: LayerCache) -> None:
         from ..csrc import ops

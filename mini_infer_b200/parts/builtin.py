@@ -212,7 +212,7 @@ class GroupedQueryAttention(Mixer):
         nq, nkv, d = self.nq, self.nkv, self.d
         qkv = self.qkv_proj(x)
         table = None
-        if (position is not None and cache.k is not None and hasattr(position, "step_table")
+        if (position is not None and cache.k is not None
                 and ops.decode_rope_fusable(x.dtype, d, ctx.decode_only, ctx.n_requests)):
             table = position.step_table(ctx, d)   # the decode kernel rotates q and stores the new k, v itself
         if table is not None:
