@@ -469,7 +469,7 @@ def cut_prefill_then_decode(requests, n_decode):
     return steps
 
 
-def run_variant(arch, raw_base, tmp_path, dtype, page, plain_kwargs, num_blocks=None, cuda_graph=False):
+def run_variant(arch, raw_base, tmp_path, dtype, page, plain_kwargs, num_blocks=None, cuda_graph=False, which="A"):
     from mini_infer_b200.engine import ModelRunner
     from mini_infer_b200.weights import write_random_model
     from tiny_configs import PEAKED
@@ -477,10 +477,10 @@ def run_variant(arch, raw_base, tmp_path, dtype, page, plain_kwargs, num_blocks=
     _register_toys()
     raw = dict(raw_base, architectures=[arch])
     # wide enough that a wrong offset, gate or expert would show in the logits
-    wide = dict(PEAKED["A"], **{"pos.table": 0.7, "router.weight": 0.5, "experts.": 0.08})
+    wide = dict(PEAKED[which], **{"pos.table": 0.7, "router.weight": 0.5, "experts.": 0.08})
     folder = write_random_model(raw, str(tmp_path / arch), 5, std_overrides=wide)
     state = load_state(folder)
-    requests = {f"q{i}": prompt_ids("A", n, salt=200 + i) for i, n in enumerate([50, 13 if cuda_graph else 3, 77, 31])}
+    requests = {f"q{i}": prompt_ids(which, n, salt=200 + i) for i, n in enumerate([50, 13 if cuda_graph else 3, 77, 31])}
     want = {r: plain_variant(state, raw, toks, **plain_kwargs) for r, toks in requests.items()}
     n_decode = 12
     steps = cut_prefill_then_decode(requests, n_decode) if cuda_graph else T.cut_mixed(requests, n_decode=9)
@@ -550,6 +550,22 @@ def test_layers_with_and_without_a_window_have_pages_of_their_own(dtype, tmp_pat
     runner = run_variant("ToyWindowLM", TINY["A"], tmp_path, dtype, 4, {"windows": [11, None]},
                          num_blocks=[48, 80])
     assert [(g.layers, g.window) for g in runner.cache.groups] == [((0,), 11), ((1,), None)]
+
+
+def test_decode_kernel_that_rotates_by_itself_in_windowed_and_shared_cache_layers(tmp_path):
+    """At a head size the decode kernel takes (64), captured decode-only bfloat16 steps leave the
+    rotation of q and the storing of the newest key and value to the attention kernel: with a
+    windowed layer (its pages handed back while it decodes), and with a layer that only reads
+    another layer's cache (q is rotated, nothing is stored)."""
+    from mini_infer_b200.csrc import ops
+
+    assert ops.decode_rope_fusable(torch.bfloat16, TINY["C"]["head_dim"], True, 4)
+    runner = run_variant("ToyWindowLM", TINY["C"], tmp_path / "w", "bfloat16", 16, {"windows": [11, None]},
+                         num_blocks=[48, 80], cuda_graph=True, which="C")
+    assert sum(slot.replays for slot in runner.stepper._graphs.values()) >= 10
+    runner = run_variant("ToyLoopLM", TINY["C"], tmp_path / "l", "bfloat16", 16,
+                         {"schedule": [(0, 0, True), (1, 1, True), (0, 2, True), (1, 0, False)]}, cuda_graph=True, which="C")
+    assert sum(slot.replays for slot in runner.stepper._graphs.values()) >= 10
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
