@@ -461,6 +461,7 @@ def decode_splits(n_requests: int, nq: int, nkv: int, max_kv_len: int, window: i
 
 
 FUSE_DECODE_ROPE = os.environ.get("MINI_INFER_FUSE_ROPE", "1") != "0"
+SPLIT_MIXED_STEPS = os.environ.get("MINI_INFER_SPLIT_MIXED", "1") != "0"
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
@@ -514,6 +515,13 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq:
             tc = USE_TC_PREFILL and prefill_tc_supported(nq, nkv, head_dim, group.page_size)
             tt = (prefill_tc_tile_tokens if tc else prefill_tile_tokens)(nq // nkv)
             tile_req, tile_tok0, n_tiles = ctx.q_tiles(tt)
+            if SPLIT_MIXED_STEPS and ctx.n_single and tt in ctx.tiles_multi:
+                # a mixed step: the single tokens through the decode kernel (their keys spread over
+                # all blocks), the prompt portions through the prefill kernel; disjoint rows of `out`
+                attention_decode_balanced(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
+                                          ctx.single_q_start, ctx.single_kv_len, ctx.n_single, nq, nkv, head_dim,
+                                          scale, window, table_rows=ctx.single_rows)
+                tile_req, tile_tok0, n_tiles = ctx.tiles_multi[tt]
             (attention_prefill_tc if tc else attention_prefill)(
                 q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
                 ctx.q_start, ctx.q_len, ctx.kv_len, tile_req, tile_tok0, n_tiles, tt,

@@ -124,6 +124,33 @@ class ModelRunner:
     def step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> StepResult:
         return self.stepper.step(entries, device_tokens)
 
+    def capture_decode_steps(self, max_batch: int) -> int:
+        """Capture the decode step of every batch size up to ``max_batch`` that has no graph yet
+        (a step of a new size otherwise runs kernel by kernel and is captured when it first
+        occurs, some 40 ms in the middle of serving).  Uses requests of its own that hold one
+        token each and gives their pages back; needs that many free pages and request slots.
+        Returns the number of graphs captured; 0 when steps are not captured at all."""
+        if not self.stepper.cuda_graph:
+            return 0
+        made = 0
+        max_batch = min(max_batch, self.cache.max_requests - self.cache.num_requests)
+        for b in range(1, max_batch + 1):
+            slot = self.stepper._graphs.get((b,))
+            if slot is not None and slot.graph is not None:
+                continue
+            rids = [("__capture__", i) for i in range(b)]
+            for r in rids:
+                self.cache.add_request(r)
+            try:
+                if not self.cache.can_append([(r, 1) for r in rids]):
+                    break
+                self.stepper.step([StepEntry(r, [0], [0]) for r in rids])   # runs kernel by kernel once, then records
+                made += 1
+            finally:
+                for r in rids:
+                    self.cache.free_request(r)
+        return made
+
     # -- health -------------------------------------------------------------------------
 
     def health_word(self) -> torch.Tensor:

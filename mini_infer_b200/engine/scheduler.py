@@ -264,11 +264,15 @@ class ContinuousScheduler:
         while self.step():
             pass
 
-    def start(self) -> None:
-        """Run the engine loop on a thread of its own until ``stop``."""
+    def start(self, capture_decode_steps: bool = True) -> None:
+        """Run the engine loop on a thread of its own until ``stop``.  A runner that replays
+        captured decode steps captures those of every batch size up to ``max_concurrent`` first
+        (under a second in all), so that no request meets a capture in the middle of serving."""
         if self._thread is not None:
             return
         self._stop.clear()
+        if capture_decode_steps and hasattr(self.runner, "capture_decode_steps") and not self._live:
+            self.runner.capture_decode_steps(self.max_concurrent)
 
         def loop() -> None:
             try:

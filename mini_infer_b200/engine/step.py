@@ -71,6 +71,8 @@ class HostPlan:
     update_capacity: list[int]         # per group: triples the buffer has room for
     overflow: list[list[int]]          # per group: triples that did not fit a captured step's fixed room
     tile_counts: dict[int, int]
+    n_single: int = 0                  # a mixed step's requests that bring one token
+    multi_counts: dict[int, int] = field(default_factory=dict)   # tiles of the others, per tile size
 
 
 class StepRunner:
@@ -175,7 +177,18 @@ class StepRunner:
                 capacity[gi] = len(flat) // 3
                 parts.append((f"updates{gi}", flat))
             parts.append((f"update_count{gi}", [len(flat) // 3]))
+        # In a mixed step the requests that bring a single token can go to the decode kernel,
+        # which spreads their keys over all blocks (as one tile of the prefill kernels such a
+        # request is one block per head group walking its whole context alone); the tiles of the
+        # others are listed a second time without them.
+        singles = [] if decode_only else [i for i in range(B) if q_len[i] == 1]
+        if len(singles) == B:
+            singles = []
+        parts.append(("single_q_start", [q_start[i] for i in singles]))
+        parts.append(("single_kv_len", [kv_len[i] for i in singles]))
+        parts.append(("single_rows", [plan.state_slots[i] for i in singles]))
         tile_counts: dict[int, int] = {}
+        multi_counts: dict[int, int] = {}
         for n in self.tile_sizes:
             if decode_only:
                 treq: Sequence[int] = range(B)
@@ -191,6 +204,11 @@ class StepRunner:
             tile_counts[n] = len(treq)
             parts.append((f"tile_req{n}", treq))
             parts.append((f"tile_tok{n}", ttok))
+            if singles:
+                keep = [j for j, i in enumerate(treq) if q_len[i] > 1]
+                multi_counts[n] = len(keep)
+                parts.append((f"multi_req{n}", [treq[j] for j in keep]))
+                parts.append((f"multi_tok{n}", [ttok[j] for j in keep]))
 
         offsets: dict[str, tuple[int, int]] = {}
         total = 0
@@ -204,7 +222,8 @@ class StepRunner:
                 buffer[o:o + n] = lst
         return HostPlan(buffer=buffer, offsets=offsets, n_tokens=M, q_start=q_start, q_len=list(q_len),
                         kv_len=kv_len, state_slots=list(plan.state_slots), rows=rows, decode_only=decode_only,
-                        update_capacity=capacity, overflow=overflow, tile_counts=tile_counts)
+                        update_capacity=capacity, overflow=overflow, tile_counts=tile_counts,
+                        n_single=len(singles), multi_counts=multi_counts)
 
     def plan(self, entries: Sequence[StepEntry], graphed: bool = False):
         """Reserve pages and put the step's descriptors on the device (one copy).
@@ -252,6 +271,9 @@ class StepRunner:
             host_state_slot=hp.state_slots, groups=groups,
             tiles={n: (view(f"tile_req{n}"), view(f"tile_tok{n}"), hp.tile_counts[n]) for n in self.tile_sizes},
             decode_only=hp.decode_only,
+            n_single=hp.n_single,
+            single_q_start=view("single_q_start"), single_kv_len=view("single_kv_len"), single_rows=view("single_rows"),
+            tiles_multi={n: (view(f"multi_req{n}"), view(f"multi_tok{n}"), hp.multi_counts[n]) for n in hp.multi_counts},
             # a captured step must not depend on the lengths of the day: it is planned for
             # the longest context its block tables can hold
             max_kv_len=(max(self.cache.table_width, default=1) * self.cache.page_size) if graphed else max(hp.kv_len),

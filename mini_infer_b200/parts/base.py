@@ -124,6 +124,13 @@ class StepContext:
     groups: list[GroupView] = field(default_factory=list)
     tiles: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = field(default_factory=dict)
     decode_only: bool = False          # every request brings exactly one token
+    # a mixed step: the requests that bring one token (their rows of q, their lengths, their rows
+    # of the block tables) and the query tiles of the other requests alone
+    n_single: int = 0
+    single_q_start: torch.Tensor | None = None
+    single_kv_len: torch.Tensor | None = None
+    single_rows: torch.Tensor | None = None
+    tiles_multi: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = field(default_factory=dict)
     max_kv_len: int = 0
     # per cache group: (triples, count, capacity) of the page ids the step scatters into the
     # block tables before its first kernel (the step runner's business, not a part's)

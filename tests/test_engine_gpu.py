@@ -127,6 +127,30 @@ def test_decode_lookahead_gives_the_same_tokens(model_dirs, cuda_graph):
     assert "stop" in ahead_why and sched.wasted_tokens >= 1
 
 
+def test_decode_steps_of_every_batch_size_are_captured_ahead(model_dirs):
+    """``capture_decode_steps`` leaves a graph per batch size and an empty cache behind, and what
+    is generated afterwards (replaying those graphs from the first decode step on) is what the
+    uncaptured engine generates."""
+    from mini_infer_b200.engine import ContinuousScheduler, ModelRunner, Request
+    from mini_infer_b200.sampling import SamplingParams
+
+    prompts = [prompt_ids("C", n, salt=70 + i) for i, n in enumerate([9, 33, 5])]
+    plain = ModelRunner.from_pretrained(model_dirs["C"], dtype="bfloat16", num_blocks=32, block_size=16, max_requests=4)
+    want = [r.tokens for r in ContinuousScheduler(plain).generate([Request(p, SamplingParams(), 12) for p in prompts])]
+    runner = ModelRunner.from_pretrained(model_dirs["C"], dtype="bfloat16", num_blocks=32, block_size=16, max_requests=4,
+                                         cuda_graph=True)
+    free = runner.cache.num_free_pages()
+    assert runner.capture_decode_steps(4) == 4
+    assert sorted(runner.stepper._graphs) == [(1,), (2,), (3,), (4,)]
+    assert runner.cache.num_requests == 0 and runner.cache.num_free_pages() == free
+    assert runner.capture_decode_steps(4) == 0          # nothing left to capture
+    replays = sum(slot.replays for slot in runner.stepper._graphs.values())
+    got = [r.tokens for r in ContinuousScheduler(runner).generate([Request(p, SamplingParams(), 12) for p in prompts])]
+    assert got == want
+    assert sum(slot.replays for slot in runner.stepper._graphs.values()) > replays
+    runner.cache.check()
+
+
 def test_engine_thread_streams_the_same_tokens(model_dirs):
     """The engine loop on a thread of its own (``start`` / ``stop``): requests submitted from
     this thread while it runs, tokens streamed through callbacks, the runner's health word read
