@@ -68,10 +68,22 @@ def test_layout_of_a_mixed_step_and_of_a_captured_one():
     assert view(hp, "update_count0") == [4] and hp.update_capacity == [4]      # three pages for a, one for b
     # tiles with the most keys first: a's last tile sees 37 keys, then 32, 16, and b's one key
     assert view(hp, "tile_req16") == [0, 0, 0, 1] and view(hp, "tile_tok16") == [32, 16, 0, 0]
+    # the request that brings one token is listed for the decode kernel (its row of q, its length,
+    # its row of the block tables), and the tiles are listed once more without it
+    assert hp.n_single == 1
+    assert view(hp, "single_q_start") == [37] and view(hp, "single_kv_len") == [1]
+    assert view(hp, "single_rows") == [cache.slot("b")]
+    assert view(hp, "multi_req16") == [0, 0, 0] and view(hp, "multi_tok16") == [32, 16, 0] and hp.multi_counts[16] == 3
     # a captured step: fixed room for one new page per request; what is unused is marked -1
     hp = runner.host_plan([StepEntry("a", [3], [0]), StepEntry("b", [4], [0])], graphed=True)
     assert hp.decode_only and hp.update_capacity == [2] and view(hp, "update_count0") == [0]
     assert view(hp, "updates0") == [-1] * 6
+    assert hp.n_single == 0 and not hp.multi_counts and view(hp, "single_q_start") == []
+    # a step of prompt portions only has nobody for the decode kernel
+    cache.add_request("d")
+    hp = runner.host_plan([StepEntry("d", [1, 2, 3], [2])])
+    assert hp.n_single == 0 and not hp.multi_counts
+    cache.free_request("d")
     # pages handed out outside a step that do not fit that room travel separately
     cache.add_request("c")
     cache.plan_append([("c", 16 * 5)])
