@@ -613,24 +613,40 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 // counter to the unit's chunk count merges the stretches in block order.  The copy warp runs
 // ahead across unit boundaries, so the ring of stages never drains inside a block.
 //
+// Taking up a unit costs a block about as much as `unit_cost` chunks (its queries, the merge of
+// the four warps' shares, the output), so in the row every unit is that many positions longer
+// than its chunks: the first `unit_cost` positions of a unit stand for no chunk.  A block whose
+// stretch holds a hundred requests of one chunk then gets fewer chunks than one in the middle
+// of a long request, and both end at about the same time.
+//
 // Scratch: slot (unit + block) is unique and increases along the row, so part_o holds
 // (units + G) * 8 * d floats, part_ml (units + G) * 8 * 2, counters one int per unit (zero
 // between calls).  No host-side plan: the blocks work the stretches out from kv_len themselves.
 
-// Position i of the row -> request b, unit u within the request, chunk c_rel within the unit.
-__device__ __forceinline__ void balanced_locate(long long i, const int* cum, int B, int U, int& b, int& u,
-                                                int& c_rel, int& n_b) {
+// The row: request after request, each with U units of (ov + its chunks) positions; request b
+// starts at position (cum[b] + ov * b) * U.  The part of the row's stretch [i, i1) that lies in
+// the unit holding position i: request b, unit u within it, `seg` chunks from chunk c_rel of the
+// unit on (seg is 0 when the part covers only positions that stand for no chunk).  Returns the
+// number of positions of the part.
+__device__ __forceinline__ int balanced_part(long long i, long long i1, const int* cum, int B, int U, int ov,
+                                             int& b, int& u, int& c_rel, int& seg, int& n_b) {
   int lo = 0, hi = B - 1;
-  while (lo < hi) {   // the largest b with cum[b] * U <= i (requests without chunks are passed over)
+  while (lo < hi) {   // the largest b whose first position is <= i
     const int mid = (lo + hi + 1) >> 1;
-    if ((long long)cum[mid] * U <= i) lo = mid;
+    if ((long long)(cum[mid] + ov * mid) * U <= i) lo = mid;
     else hi = mid - 1;
   }
   b = lo;
   n_b = cum[b + 1] - cum[b];
-  const long long r = i - (long long)cum[b] * U;
-  u = (int)(r / n_b);
-  c_rel = (int)(r - (long long)u * n_b);
+  const int nv = n_b + ov;
+  const long long r = i - (long long)(cum[b] + ov * b) * U;
+  u = (int)(r / nv);
+  const int p = (int)(r - (long long)u * nv);
+  const int len = (int)min((long long)(nv - p), i1 - i);
+  const int first = max(p, ov);
+  c_rel = first - ov;
+  seg = max(0, p + len - first);
+  return len;
 }
 
 // The stretches g_first .. g_last of one unit into its output row (head r of the unit's group,
@@ -711,7 +727,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
                                  const int* __restrict__ block_table, int bt_stride,
                                  const int* __restrict__ table_rows, int page_size, int page_shift,
                                  const int* __restrict__ q_start, const int* __restrict__ kv_len, int B, int nq,
-                                 int nkv, int d, float scale, int window, int min_chunks,
+                                 int nkv, int d, float scale, int window, int min_chunks, int unit_cost,
                                  float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                                  int* __restrict__ status, const float* __restrict__ rope_cs, int store_kv) {
   // ROPE (the head size is then DMAX exactly): rope_cs holds per query token [d / 2] sines then
@@ -760,18 +776,26 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
     if (lane == 0) cum[0] = 0;
   }
   __syncthreads();
-  const long long W = (long long)cum[B] * U;
-  // a stretch shorter than min_chunks costs more in set-up and merging than it spreads
-  int G = (int)min((long long)gridDim.x, max((long long)1, W / max(1, min_chunks)));
-  // Requests of one length, and fewer units than blocks: a block count that is a multiple of
-  // the unit count makes every stretch a whole fraction of one unit (no block straddles two
-  // units, every unit has the same number of stretches), which costs fewer partial results
-  // than the last few blocks would bring.
+  int ov = max(0, unit_cost);
+  int G;
   {
-    const long long units = (long long)B * U;
+    // Requests of one length, and fewer units than blocks: a block count that is a multiple of
+    // the unit count makes every stretch a whole fraction of one unit (no block straddles two
+    // units, every unit has the same number of stretches), which costs fewer partial results
+    // than the last few blocks would bring.  Every block then takes up one unit: nothing to weigh.
+    const long long units = (long long)B * U, chunks = (long long)cum[B] * U;
     const int n0 = cum[1];
-    if (units < G && W == units * n0) G = (int)(units * (G / units));
+    // a stretch shorter than min_chunks costs more in set-up and merging than it spreads
+    const int g_plain = (int)min((long long)gridDim.x, max((long long)1, chunks / max(1, min_chunks)));
+    if (units < g_plain && chunks == units * n0) {
+      ov = 0;
+      G = (int)(units * (g_plain / units));
+    } else {
+      G = (int)min((long long)gridDim.x, max((long long)1, (chunks + units * ov) / max(1, min_chunks)));
+    }
   }
+  const long long W = (long long)(cum[B] + ov * B) * U;
+  if (W == 0) G = 1;
   if ((int)blockIdx.x >= G) return;
   if (status && *reinterpret_cast<volatile int*>(status)) return;   // an earlier block gave up waiting
   const long long i0 = W * blockIdx.x / G, i1 = W * (blockIdx.x + 1) / G;
@@ -794,9 +818,8 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
     bool ok = true, waited = false, stored_seen = false;
     int it = 0;
     for (long long i = i0; i < i1 && ok;) {
-      int b, u, c_rel, n_b;
-      balanced_locate(i, cum, B, U, b, u, c_rel, n_b);
-      const int seg = (int)min((long long)(n_b - c_rel), i1 - i);
+      int b, u, c_rel, seg, n_b;
+      const int len = balanced_part(i, i1, cum, B, U, ov, b, u, c_rel, seg, n_b);
       const int kvh = u / hblocks;
       const int kl = kv_len[b];
       const int lo = window > 0 ? max(0, kl - window) : 0;
@@ -828,7 +851,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
                        d, &bars[st]);
         }
       }
-      i += seg;
+      i += len;
     }
     return;
   }
@@ -842,10 +865,9 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
     mi_pdl_wait();
     const int half = d >> 1, n_rot = half >> 3, cpr = d >> 3, per_unit = n_rot + cpr;
     for (long long i = i0; i < i1;) {
-      int b, u, c_rel, n_b;
-      balanced_locate(i, cum, B, U, b, u, c_rel, n_b);
-      const int seg = (int)min((long long)(n_b - c_rel), i1 - i);
-      if (c_rel + seg == n_b) {
+      int b, u, c_rel, seg, n_b;
+      const int len = balanced_part(i, i1, cum, B, U, ov, b, u, c_rel, seg, n_b);
+      if (seg > 0 && c_rel + seg == n_b) {
         const int kvh = u / hblocks, kl = kv_len[b], tok = q_start[b], pos = kl - 1;
         const int* table = block_table + (size_t)(table_rows ? table_rows[b] : b) * bt_stride;
         const int page = table[page_shift >= 0 ? (pos >> page_shift) : (pos / page_size)];
@@ -874,7 +896,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
           }
         }
       }
-      i += seg;
+      i += len;
     }
     fence_proxy_async_all();   // a bulk copy reads these plain stores next
     __syncwarp();
@@ -891,9 +913,12 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
   int it = 0;
   bool warp_dead = false;   // this warp's wait ran out: it keeps in step with the others but computes nothing more
   for (long long i = i0; i < i1;) {
-    int b, u, c_rel, n_b;
-    balanced_locate(i, cum, B, U, b, u, c_rel, n_b);
-    const int seg = (int)min((long long)(n_b - c_rel), i1 - i);
+    int b, u, c_rel, seg, n_b;
+    const int len = balanced_part(i, i1, cum, B, U, ov, b, u, c_rel, seg, n_b);
+    if (seg == 0) {   // only positions that stand for no chunk
+      i += len;
+      continue;
+    }
     const int unit = b * U + u;
     const int kvh = u / hblocks, hb = u - kvh * hblocks;
     const int heads_here = min(DEC_HEADS, g - hb * DEC_HEADS);
@@ -1084,7 +1109,8 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
       consumer_barrier(NTHREADS);
       if (is_last) {
         __threadfence();
-        const long long start = (long long)cum[b] * U + (long long)u * n_b;
+        // the blocks whose stretches hold the unit's chunks: its positions from `ov` on
+        const long long start = (long long)(cum[b] + ov * b) * U + (long long)u * (n_b + ov) + ov;
         const int g_first = (int)(((start + 1) * G - 1) / W), g_last = (int)(((start + n_b) * G - 1) / W);
         if (r < heads_here)
           balanced_merge_unit<DMAX>(part_o, part_ml, unit, g_first, g_last, r, cgrp, d,
@@ -1093,7 +1119,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
       }
     }
     consumer_barrier(NTHREADS);   // merge_o, merge_m and is_last may be written again
-    i += seg;
+    i += len;
   }
   // a request that holds no key at all has no chunk in the row: its output rows are zero
   if (blockIdx.x == 0)
@@ -1522,6 +1548,15 @@ extern "C" int mi_attention_decode(const void* q, int q_stride, void* out, int o
                                     part_ml, counters, stream);
 }
 
+// What taking up a unit costs a block, in chunks (attention_decode_balanced_kernel's unit_cost): measured, a unit
+// costs about as much as two chunks; times stop falling between three and four.  A negative argument only reads.
+static int g_unit_cost = 3;
+extern "C" int mi_attention_decode_balanced_unit_cost(int chunks) {
+  const int before = g_unit_cost;
+  if (chunks >= 0) g_unit_cost = chunks;
+  return before;
+}
+
 static size_t balanced_smem_bytes(int B, int d) {   // the ring, the warps' merge buffer, the running sum of chunks
   return (size_t)(2 * DEC_STAGES * KCHUNK) * d * sizeof(bf16) + (size_t)4 * DEC_HEADS * d * sizeof(float) +
          (size_t)(B + 1) * sizeof(int);
@@ -1570,8 +1605,8 @@ extern "C" int mi_attention_decode_balanced(const void* q, int q_stride, void* o
     }                                                                                                     \
     MI_LAUNCH((kern), grid, ROPE ? BAL_THREADS : DEC_THREADS, smem, stream, (const bf16*)q, q_stride,     \
               (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, block_table, bt_stride,   \
-              table_rows, page_size, page_shift, q_start, kv_len, B, nq, nkv, d, scale, window, 4, part_o, \
-              part_ml, counters, wait_status_ptr(), rope_cs, store_kv);                                   \
+              table_rows, page_size, page_shift, q_start, kv_len, B, nq, nkv, d, scale, window, 4,        \
+              g_unit_cost, part_o, part_ml, counters, wait_status_ptr(), rope_cs, store_kv);              \
   } while (0)
   if (rope_cs) {
     if (d == 64) MI_DECODE_BAL(64, true);

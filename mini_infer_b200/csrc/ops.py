@@ -167,6 +167,7 @@ def _sig_attention_mma(lib: ctypes.CDLL) -> None:
     lib.mi_attention_decode_balanced.argtypes = [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
         c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+    lib.mi_attention_decode_balanced_unit_cost.argtypes = [c_int]
     lib.mi_attention_wait_status.argtypes = [c_int]
     lib.mi_set_status_word.argtypes = [c_void_p]
     lib.mi_attention_prefill.argtypes = [
@@ -639,6 +640,14 @@ def attention_decode_balanced(q, q_stride, out, kcache, vcache, block_table, pag
         head_dim, float(scale), int(window), int(grid.value), _ptr(part_o), _ptr(part_ml), _ptr(count),
         _ptr(rope_table), 1 if store_kv else 0, _stream())
     _finish(lib, rc, "attention_decode")
+
+
+def decode_unit_cost(chunks: int | None = None) -> int:
+    """What the balanced decode kernel reckons a block pays for taking up one (request, head
+    group) unit, in 64-key chunks, when it cuts the requests' keys into equal stretches (so that a
+    block with many short requests gets fewer keys than one inside a long request).  Sets it when
+    given; returns the value that was in force before."""
+    return int(_lib("attention_mma").mi_attention_decode_balanced_unit_cost(-1 if chunks is None else int(chunks)))
 
 
 def attention_wait_status(reset: bool = True) -> int:

@@ -499,6 +499,28 @@ def test_attention_decode_balanced(nq, nkv, d, page):
         assert (got - want).abs().max().item() <= BF16_BOUND
 
 
+@pytest.mark.parametrize("unit_cost", [0, 1, 2, 5, 40])
+def test_attention_decode_balanced_whatever_a_unit_is_reckoned_to_cost(unit_cost):
+    """The balanced kernel lengthens every unit by a number of positions that stand for no chunk
+    before it cuts the row into stretches.  Whatever that number is, every chunk is read exactly
+    once: many requests of one chunk beside a long one (stretches that begin and end inside the
+    added positions, blocks that find no chunk in theirs), a window."""
+    before = ops().decode_unit_cost(unit_cost)
+    try:
+        assert ops().decode_unit_cost() == unit_cost
+        for seed, (nq, nkv, d, page), lens, window in (
+                (1, (32, 8, 128, 16), [3000] + [5, 64, 1, 17, 63, 65, 2, 128] * 6 + [700], 0),
+                (2, (8, 2, 64, 8), [1] * 40 + [9000] + [1] * 23, 0),
+                (3, (6, 2, 48, 8), [130, 1, 200, 64, 7, 1000, 3], 100),
+                (4, (4, 4, 64, 16), [2, 2, 2], 0)):
+            got, want = run_attention([1] * len(lens), lens, nq, nkv, d, page, torch.bfloat16, seed=seed, window=window,
+                                      kernel="balanced")
+            assert torch.isfinite(got).all()
+            assert (got - want).abs().max().item() <= BF16_BOUND
+    finally:
+        ops().decode_unit_cost(before)
+
+
 @pytest.mark.parametrize("nq,nkv,d,page", [(32, 8, 128, 16), (8, 2, 64, 8), (6, 3, 128, 16), (5, 1, 256, 32), (4, 4, 64, 16),
                                             (24, 1, 128, 32)])
 def test_attention_decode_rotates_and_stores_by_itself(nq, nkv, d, page):
