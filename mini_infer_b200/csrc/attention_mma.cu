@@ -84,6 +84,21 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32
                "l"(src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
+// The same copy for data that is read once per step (a decode step reads every key and value of a
+// request exactly once, and all layers' caches together are far larger than the L2): marked to be
+// evicted first, so that what the step's kernels hand to one another stays in the L2 meanwhile.
+// MINI_INFER_L2_HINTS=0 in the environment switches the mark off (for comparisons).
+static __device__ int g_stream_once_hint = 1;
+__device__ __forceinline__ void bulk_copy_g2s_once(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  if (!g_stream_once_hint) return bulk_copy_g2s(dst, src, bytes, bar);
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(policy));
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;\n" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -163,6 +178,8 @@ struct PageLoader {
     return (uint32_t)cnt * (uint32_t)rows * (uint32_t)d * 4u;   // keys and values, 2 bytes each
   }
 
+  // kOnce: nobody else reads these keys and values in this step (decode), see bulk_copy_g2s_once
+  template <bool kOnce = false>
   __device__ __forceinline__ void issue(bf16* kdst, bf16* vdst, const bf16* __restrict__ kcache,
                                         const bf16* __restrict__ vcache, int page_size, int page_shift, int chunk,
                                         int nkv, int kvh, int d, uint64_t* bar) const {
@@ -172,8 +189,12 @@ struct PageLoader {
     const bool is_v = t >= n;
     const int j0 = chunk * KCHUNK + piece * rows;
     const size_t off = (((size_t)pg * nkv + kvh) * page_size + inpage_of(j0, page_size, page_shift)) * d;
-    bulk_copy_g2s((is_v ? vdst : kdst) + (size_t)piece * rows * d, (is_v ? vcache : kcache) + off,
-                  (uint32_t)rows * (uint32_t)d * 2u, bar);
+    if (kOnce)
+      bulk_copy_g2s_once((is_v ? vdst : kdst) + (size_t)piece * rows * d, (is_v ? vcache : kcache) + off,
+                         (uint32_t)rows * (uint32_t)d * 2u, bar);
+    else
+      bulk_copy_g2s((is_v ? vdst : kdst) + (size_t)piece * rows * d, (is_v ? vcache : kcache) + off,
+                    (uint32_t)rows * (uint32_t)d * 2u, bar);
   }
 };
 
@@ -410,7 +431,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
       for (int t0 = 0; t0 < pieces; t0 += 32) {   // more than 32 copies only with odd page sizes
         loader.t = t0 + lane;
         loader.fetch(table, page_size, page_shift, c, lo, kl);
-        loader.issue(Ks + st * KCHUNK * d, Vs + st * KCHUNK * d, kcache, vcache, page_size, page_shift, c, nkv, kvh,
+        loader.issue<true>(Ks + st * KCHUNK * d, Vs + st * KCHUNK * d, kcache, vcache, page_size, page_shift, c, nkv, kvh,
                      d, &bars[st]);
       }
     }
@@ -847,7 +868,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
         for (int t0 = 0; t0 < pieces; t0 += 32) {
           loader.t = t0 + lane;
           loader.fetch(table, page_size, page_shift, c, lo, kl);
-          loader.issue(Ks + st * KCHUNK * d, Vs + st * KCHUNK * d, kcache, vcache, page_size, page_shift, c, nkv, kvh,
+          loader.issue<true>(Ks + st * KCHUNK * d, Vs + st * KCHUNK * d, kcache, vcache, page_size, page_shift, c, nkv, kvh,
                        d, &bars[st]);
         }
       }
@@ -1428,6 +1449,14 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 
 static int check_common(const void* q, int q_stride, const void* out, int out_stride, const void* kcache,
                         const void* vcache, int nq, int nkv, int d, int page_size, int window) {
+  if (!mi_l2_hints_enabled()) {   // once per device: tell the kernels
+    static bool told[64];
+    int dev = -1;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !told[dev]) {
+      const int off = 0;
+      if (cudaMemcpyToSymbol(g_stream_once_hint, &off, sizeof(int)) == cudaSuccess) told[dev] = true;
+    }
+  }
   if (d <= 0 || d % 16 != 0 || d > 256) MI_REFUSE("attention: head size %d is not a multiple of 16 in [16, 256]", d);
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0) MI_REFUSE("attention: %d query heads cannot share %d key/value heads", nq, nkv);
   if (page_size <= 0 || window < 0) MI_REFUSE("attention: bad page size %d or window %d", page_size, window);

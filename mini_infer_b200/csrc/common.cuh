@@ -64,6 +64,16 @@ __device__ __forceinline__ void mi_pdl_enter() {
 
 #ifdef __CUDACC__
 #include <stdlib.h>
+// MINI_INFER_L2_HINTS=0 in the environment leaves out the evict-first marks on data that a step
+// reads once (the weights of the streaming product, the keys and values of decode attention).
+static inline bool mi_l2_hints_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("MINI_INFER_L2_HINTS");
+    enabled = (e && e[0] == '0' && e[1] == 0) ? 0 : 1;
+  }
+  return enabled != 0;
+}
 // MINI_INFER_PDL=0 in the environment launches kernels the ordinary way (for comparisons).
 static inline bool mi_pdl_enabled() {
   static int enabled = -1;

@@ -95,6 +95,31 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
       : "memory");
 }
 
+// The same loads with an L2 eviction policy.  Weights are read once per step and are far larger
+// than the L2, so they are marked to be evicted first: what the step's kernels hand to one another
+// (activations, the residual stream, partial tiles) then stays resident between them.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_2d_hint(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, "
+      "%4}], [%2], %5;\n" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_hint(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, "
+      "%4, %5}], [%2], %6;\n" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "l"(policy)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the
 // 128-byte swizzle in groups of 8 rows (1024 bytes apart).
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
@@ -163,19 +188,41 @@ struct Segments {
   }
 };
 
-template <typename OutT>
+// What the epilogue may do beside storing the product, for a decoder block whose additions and
+// norms ride on its products (at most 16 tokens).  Two halves that do not depend on each other:
+//
+//   stats_in   the input x was multiplied by the norm's gain but not yet divided by the root mean
+//              square of its row: stats_in[t][token] are the sums of squares over 128 features
+//              each, written by the product before; every accumulator of a token is scaled by
+//              rsqrt(sum_t stats_in[t][token] / width + eps) before anything else happens to it
+//   residual   the product is a branch's output: h = product + residual is stored back to the fp32
+//              stream, y becomes h * gain[feature] (bf16, the next product's input), and
+//              stats_out[tile][token] the sum of h^2 over the tile's features, added in a fixed
+//              order (lanes by butterfly, then the four warps)
+struct EpilogueFusion {
+  const float* stats_in;
+  int n_stat_tiles;
+  float inv_width, eps;
+  float* residual;
+  const float* gain;
+  float* stats_out;
+};
+#define FUSED_MAX_TOKENS 16
+
+template <typename OutT, bool kFused>
 __global__ void __launch_bounds__(GT_THREADS, 1)
 gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                 OutT* __restrict__ y, int ldy, int M, int N, int K, int n_tok, int stages, int kb, int chunked, int swiglu,
-                float* __restrict__ partials, int* __restrict__ counters) {
+                float* __restrict__ partials, int* __restrict__ counters, const EpilogueFusion fus, int w_evict_first) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // stage s: kb W boxes [128][64] bf16 (16 KB each), then kb x boxes [n_tok][64] bf16
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t w_bytes = TILE_ROWS * TILE_K * 2, x_bytes = (uint32_t)n_tok * TILE_K * 2;
   const uint32_t stage_bytes = (w_bytes + x_bytes) * kb;
-  __shared__ __align__(8) uint64_t full[MAX_STAGES], empty[MAX_STAGES], acc_full, acc_empty;
+  __shared__ __align__(8) uint64_t full[MAX_STAGES], empty[MAX_STAGES], acc_full, acc_empty, inputs_ready;
   __shared__ uint32_t tmem_base_holder;
   __shared__ int give_up, is_last, epilogue_stop;
+  __shared__ float row_scale[FUSED_MAX_TOKENS], square_sums[4][FUSED_MAX_TOKENS];
 
   // The kernel that follows in the stream may start its blocks now; it waits for this grid's
   // results itself before it touches them.
@@ -202,6 +249,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       }
       mbar_init(&acc_full, 1);
       mbar_init(&acc_empty, 4);
+      mbar_init(&inputs_ready, 1);
       give_up = 0;
       epilogue_stop = 0;
       asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -221,6 +269,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       };
       int st = 0, round = 0, issued = 0;
       bool waited = false, ok = true;
+      const uint64_t w_policy = l2_policy_evict_first();
       for (int i = 0; i < segs.nseg && ok; ++i) {
         int natural, tile, kc0, len;
         segs.get(i, natural, tile, kc0, len);
@@ -228,6 +277,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           if (!waited && issued == stages) {
             // the ring is full of weights: now the kernel before this one must be done
             mi_pdl_wait();
+            if (kFused) mbar_arrive(&inputs_ready);   // the epilogue warps may read the kernels' before results
             waited = true;
             int st2 = 0, i2 = 0, kc2 = 0, nat2, tile2, kc02, len2 = 0;
             for (int n = 0; n < issued; ++n) {   // x for the stages already under way
@@ -241,11 +291,18 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           if (round > 0 && !mbar_wait(&empty[st], (round - 1) & 1, gu)) { ok = false; break; }
           unsigned char* dst = smem + (size_t)st * stage_bytes;
           mbar_expect_tx(&full[st], stage_bytes);
-          if (chunked) {
-            tma_load_3d(dst, &map_w, 0, tile * TILE_ROWS, kc * kb, &full[st]);
+          if (!w_evict_first) {
+            if (chunked) {
+              tma_load_3d(dst, &map_w, 0, tile * TILE_ROWS, kc * kb, &full[st]);
+            } else {
+              for (int b = 0; b < kb; ++b)
+                tma_load_2d(dst + b * w_bytes, &map_w, (kc * kb + b) * TILE_K, tile * TILE_ROWS, &full[st]);
+            }
+          } else if (chunked) {
+            tma_load_3d_hint(dst, &map_w, 0, tile * TILE_ROWS, kc * kb, &full[st], w_policy);
           } else {
             for (int b = 0; b < kb; ++b)
-              tma_load_2d(dst + b * w_bytes, &map_w, (kc * kb + b) * TILE_K, tile * TILE_ROWS, &full[st]);
+              tma_load_2d_hint(dst + b * w_bytes, &map_w, (kc * kb + b) * TILE_K, tile * TILE_ROWS, &full[st], w_policy);
           }
           if (waited) load_x(dst + kb * w_bytes, kc, &full[st]);
           ++issued;
@@ -254,6 +311,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       }
       if (!waited && ok) {   // fewer units than stages: everything is under way, x still to come
         mi_pdl_wait();
+        if (kFused) mbar_arrive(&inputs_ready);
         int st2 = 0, i2 = 0, kc2 = 0, nat2, tile2, kc02, len2 = 0;
         for (int n = 0; n < issued; ++n) {
           while (kc2 == len2) { segs.get(i2++, nat2, tile2, kc02, len2); kc2 = 0; }
@@ -309,6 +367,63 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     // epilogue: TMEM lane quarter (warp & 3), one row of W per thread
     const int quarter = warp & 3, row = quarter * 32 + lane;
     const int etid = (warp - 2) * 32 + lane;   // 0..127 among the epilogue threads
+    // The last word on a tile's values v (16 tokens from c0, this thread's row n of W): scale, add
+    // to the stream, store.  `res` holds the stream's values where fus.residual is set.
+    auto store_final = [&](float (&v)[16], const float (&res)[16], float g, int c0, int tile, int n) {
+      if (kFused && fus.stats_in) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] *= row_scale[j];
+      }
+      if (kFused && fus.residual) {
+        float sq[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float h = 0.f;
+          if (n < N && c0 + j < M) {
+            h = v[j] + res[j];
+            fus.residual[(size_t)(c0 + j) * N + n] = h;
+            y[(size_t)(c0 + j) * ldy + n] = mi_from_float<OutT>(h * g);
+          }
+          sq[j] = h * h;
+        }
+        // Sixteen sums over the warp's 32 rows in 16 shuffles: at every step a lane passes on the
+        // half of its values that its partner keeps, so lane l ends with the sum of token (l >> 1) & 15.
+#pragma unroll
+        for (int half = 8, off = 16; half >= 1; half >>= 1, off >>= 1) {
+          const bool upper = (lane & off) != 0;
+#pragma unroll
+          for (int j = 0; j < half; ++j) {
+            const float give = upper ? sq[j] : sq[j + half];
+            const float keep = upper ? sq[j + half] : sq[j];
+            sq[j] = keep + __shfl_xor_sync(0xffffffffu, give, off);
+          }
+        }
+        sq[0] += __shfl_xor_sync(0xffffffffu, sq[0], 1);
+        if (!(lane & 1)) square_sums[quarter][(lane >> 1) & 15] = sq[0];
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        if (etid < FUSED_MAX_TOKENS)
+          fus.stats_out[tile * FUSED_MAX_TOKENS + etid] =
+              (square_sums[0][etid] + square_sums[1][etid]) + (square_sums[2][etid] + square_sums[3][etid]);
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");   // the sums are read before the next tile writes them
+      } else if (swiglu) {
+        // rows alternate gate, up: the even lane of a pair has the gate, its neighbour the up
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
+          if (!(row & 1) && n < N && c0 + j < M)
+            y[(size_t)(c0 + j) * ldy + (n >> 1)] = mi_from_float<OutT>((v[j] / (1.f + expf(-v[j]))) * other);
+        }
+      } else if (n < N) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (c0 + j < M) y[(size_t)(c0 + j) * ldy + n] = mi_from_float<OutT>(v[j]);
+      }
+    };
+    auto load_stream = [&](float (&res)[16], int c0, int n) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        res[j] = (kFused && fus.residual && n < N && c0 + j < M) ? __ldcg(fus.residual + (size_t)(c0 + j) * N + n) : 0.f;
+    };
     for (int i = 0; i < segs.nseg; ++i) {
       int natural, tile, kc0, len;
       segs.get(i, natural, tile, kc0, len);
@@ -324,6 +439,22 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // first segment (slot 0); the first block's is slot 0 only if it begins with the tile.
         first_slot = c_first * 2 + (first_unit(total, c_first, G) == t0 ? 0 : 1);
       }
+      float stream_vals[16] = {};
+      const float gain_n = (kFused && fus.residual && n < N) ? __ldg(fus.gain + n) : 0.f;   // needed last, asked for first
+      if (kFused && i == 0) {
+        // What the kernels before this one wrote may be read once the copy thread's wait for them is
+        // over (these warps do not wait for the grids themselves: that wait wakes up late).
+        // (a wait that gives up here makes the wait for the accumulator below give up as well)
+        const bool ready = mbar_wait(&inputs_ready, 0, gu);
+        if (fus.stats_in && ready && etid < FUSED_MAX_TOKENS) {
+          // every token's scale from the sums the product before left, tile by tile
+          float sum = 0.f;
+          for (int t = 0; t < fus.n_stat_tiles; ++t) sum += __ldcg(fus.stats_in + t * FUSED_MAX_TOKENS + etid);
+          row_scale[etid] = rsqrtf(sum * fus.inv_width + fus.eps);
+        }
+        // row_scale is read after the barrier that follows the wait for the accumulator
+      }
+      if (kFused && whole) load_stream(stream_vals, 0, n);   // asked for while the MMAs still run
       // the four warps leave together or not at all (they meet at named barriers below)
       if (!mbar_wait(&acc_full, i & 1, gu)) epilogue_stop = 1;
       asm volatile("bar.sync 1, 128;\n" ::: "memory");
@@ -336,19 +467,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         float v[16];
         tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
         if (whole) {
-          if (swiglu) {
-            // rows alternate gate, up: the even lane of a pair has the gate, its neighbour the up
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
-              if (!(row & 1) && n < N && c0 + j < M)
-                y[(size_t)(c0 + j) * ldy + (n >> 1)] = mi_from_float<OutT>((v[j] / (1.f + expf(-v[j]))) * other);
-            }
-          } else if (n < N) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (c0 + j < M) y[(size_t)(c0 + j) * ldy + n] = mi_from_float<OutT>(v[j]);
-          }
+          store_final(v, stream_vals, gain_n, c0, tile, n);
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
@@ -371,6 +490,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             // flight per thread; the additions still run in block order
             for (int j0 = 0; j0 < M; j0 += 16) {
               float acc[16];
+              if (kFused) load_stream(stream_vals, j0, n);   // in flight beside the partial tiles
 #pragma unroll
               for (int j = 0; j < 16; ++j) acc[j] = 0.f;
               for (int cb = c_first; cb <= c_last; cb += 4) {
@@ -389,19 +509,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                   for (int j = 0; j < 16; ++j) acc[j] += v[cc][j];
               }
-              if (swiglu) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  const float other = __shfl_xor_sync(0xffffffffu, acc[j], 1);
-                  if (!(row & 1) && n < N && j0 + j < M)
-                    y[(size_t)(j0 + j) * ldy + (n >> 1)] =
-                        mi_from_float<OutT>((acc[j] / (1.f + expf(-acc[j]))) * other);
-                }
-              } else if (n < N) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                  if (j0 + j < M) y[(size_t)(j0 + j) * ldy + n] = mi_from_float<OutT>(acc[j]);
-              }
+              store_final(acc, stream_vals, gain_n, j0, tile, n);
             }
           }
           if (etid == 0) counters[tile] = 0;   // ready for the next call
@@ -500,8 +608,26 @@ extern "C" int mi_gemm_tma_workspace(int M, int N, int blocks, long long* partia
 // y[m, i] = silu(x w[2i]) * (x w[2i+1]), computed on the fp32 accumulators.  `blocks` is the number of persistent blocks (the number of SMs); `partials` and
 // `counters` (zero before the first call; the kernel leaves them zero) as mi_gemm_tma_workspace
 // says.
-extern "C" int mi_gemm_tma(const void* x, long long ldx, const void* w, void* y, long long ldy, int M, int N, int K,
-                           int out_dtype, int swiglu, int blocks, float* partials, int* counters, cudaStream_t stream) {
+//
+// The fused forms (at most 16 rows of x), see EpilogueFusion: with `stats_in` ([stat_tiles][16] sums
+// of squares, `width` features in all) every row of the product is scaled by
+// rsqrt(sum / width + eps) first; with `residual` ([M, N] fp32, updated in place) the product is
+// added to it, y = (product + residual) * gain[n], and `stats_out` ([ceil(N / 128)][16]) receives
+// the sums of squares of the new residual per 128 features.  Null pointers switch a half off.
+extern "C" int mi_gemm_tma_fused(const void* x, long long ldx, const void* w, void* y, long long ldy, int M, int N,
+                                 int K, int out_dtype, int swiglu, int blocks, float* partials, int* counters,
+                                 const float* stats_in, int stat_tiles, int width, float eps, float* residual,
+                                 const float* gain, float* stats_out, cudaStream_t stream) {
+  EpilogueFusion fus = {stats_in, stat_tiles, width > 0 ? 1.f / (float)width : 0.f, eps, residual, gain, stats_out};
+  if (stats_in || residual) {
+    if (M > FUSED_MAX_TOKENS)
+      MI_REFUSE("gemm_tma: the fused epilogues take at most %d rows of x, got %d", FUSED_MAX_TOKENS, M);
+    if (stats_in && (stat_tiles <= 0 || width <= 0))
+      MI_REFUSE("gemm_tma: row statistics need their tile count and width (%d, %d)", stat_tiles, width);
+    if (residual && (!gain || !stats_out || swiglu))
+      MI_REFUSE("gemm_tma: the residual epilogue needs a gain and room for its statistics, and no gate/up pairs");
+    if (residual && !mi_aligned(residual, 4)) MI_REFUSE("gemm_tma: misaligned residual stream");
+  }
   if (swiglu && (N % 2)) MI_REFUSE("gemm_tma: the gate/up epilogue needs an even number of rows of W, got %d", N);
   if (M <= 0 || N <= 0) return 0;
   if (M > MAX_TOKENS) MI_REFUSE("gemm_tma: %d rows of x; this kernel takes at most %d", M, MAX_TOKENS);
@@ -538,16 +664,27 @@ extern "C" int mi_gemm_tma(const void* x, long long ldx, const void* w, void* y,
   if (!maps_ok)
     MI_REFUSE("gemm_tma: the driver refused a tensor map (N %d, K %d, M %d)", N, K, M);
   cudaError_t e;
-  if (out_dtype == MI_DTYPE_BF16) {
-    auto kern = gemm_tma_kernel<bf16>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    MI_LAUNCH((kern), grid, GT_THREADS, smem, stream, map_w, map_x, (bf16*)y, (int)ldy, M, N, K, n_tok, stages, kb, chunked, swiglu ? 1 : 0, partials, counters);
-  } else {
-    auto kern = gemm_tma_kernel<float>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    MI_LAUNCH((kern), grid, GT_THREADS, smem, stream, map_w, map_x, (float*)y, (int)ldy, M, N, K, n_tok, stages, kb, chunked, swiglu ? 1 : 0, partials, counters);
+#define GT_LAUNCH(T, FUSED)                                                                                        \
+  {                                                                                                                \
+    auto kern = gemm_tma_kernel<T, FUSED>;                                                                         \
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                        \
+    if (e != cudaSuccess) return (int)e;                                                                           \
+    MI_LAUNCH((kern), grid, GT_THREADS, smem, stream, map_w, map_x, (T*)y, (int)ldy, M, N, K, n_tok, stages, kb,   \
+              chunked, swiglu ? 1 : 0, partials, counters, fus, w_evict_first);                                                   \
   }
+  const bool fused = stats_in || residual;
+  const int w_evict_first = mi_l2_hints_enabled() ? 1 : 0;
+  if (out_dtype == MI_DTYPE_BF16) {
+    if (fused) GT_LAUNCH(bf16, true) else GT_LAUNCH(bf16, false)
+  } else {
+    if (fused) GT_LAUNCH(float, true) else GT_LAUNCH(float, false)
+  }
+#undef GT_LAUNCH
   MI_RETURN_LAUNCH_STATUS();
+}
+
+extern "C" int mi_gemm_tma(const void* x, long long ldx, const void* w, void* y, long long ldy, int M, int N, int K,
+                           int out_dtype, int swiglu, int blocks, float* partials, int* counters, cudaStream_t stream) {
+  return mi_gemm_tma_fused(x, ldx, w, y, ldy, M, N, K, out_dtype, swiglu, blocks, partials, counters, nullptr, 0, 0,
+                           0.f, nullptr, nullptr, nullptr, stream);
 }

@@ -181,6 +181,9 @@ def _sig_attention_mma(lib: ctypes.CDLL) -> None:
 def _sig_gemm_tma(lib: ctypes.CDLL) -> None:
     lib.mi_gemm_tma.argtypes = [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int,
                                 c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
+    lib.mi_gemm_tma_fused.argtypes = [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int,
+                                      c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+                                      c_void_p, c_void_p, c_void_p, c_void_p]
     lib.mi_gemm_tma_workspace.argtypes = [c_int, c_int, c_int, ctypes.POINTER(ctypes.c_longlong),
                                           ctypes.POINTER(c_int)]
     lib.mi_gemm_tma_status.argtypes = [c_int]
@@ -803,11 +806,11 @@ def sample(
 
 TMA_GEMM_MAX_ROWS = 128            # what gemm_tma.cu takes
 # ``linear`` routes inputs of up to this many rows to gemm_tma.  Measured on a B200 inside a
-# captured decode step (Llama 3.1 8B sizes) the two products are within run-to-run noise of
-# each other up to 16 rows (batch 8: 3.97 vs 3.96 ms per step; batch 12: 4.10 vs 4.02 to
-# 4.18; batch 16: 4.35 vs 4.37) and the library product is ahead from 32 rows on (5.32 vs
-# 5.20; 64 rows: 7.65 vs 6.70).
-TMA_GEMM_DISPATCH_ROWS = 8
+# captured decode step (Llama 3.1 8B sizes, milliseconds per step, own product against the
+# library's): up to 16 rows the own product is ahead, because it marks the weights to leave the
+# L2 first and does the block's additions and norms in its epilogues (batch 8: 3.74 vs 4.05;
+# batch 16: 4.17 vs 4.42); from 32 rows on the library is (5.23 vs 5.15; 64 rows: 7.34 vs 6.63).
+TMA_GEMM_DISPATCH_ROWS = 16
 USE_TMA_GEMM = os.environ.get("MINI_INFER_TMA_GEMM", "1") != "0"
 _tma_ws: dict[int, list[tuple[torch.Tensor, torch.Tensor]]] = {}
 
@@ -832,12 +835,36 @@ def gemm_tma_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+TMA_GEMM_FUSED_ROWS = 16    # the fused epilogues of gemm_tma take one group of 16 token columns
+TMA_GEMM_STAT_TOKENS = 16   # columns of a statistics table
+TMA_GEMM_TILE_ROWS = 128    # rows of W per tile: one row of a statistics table
+
+
+class RowStats:
+    """Sums of squares of the rows of an fp32 stream ``[M, width]``, 128 features at a time
+    (``sums [ceil(width / 128), 16]``, column = row of the stream), as the residual epilogue of
+    ``gemm_tma`` leaves them, with the ``eps`` of the norm they are meant for."""
+
+    __slots__ = ("sums", "width", "eps")
+
+    def __init__(self, sums: torch.Tensor, width: int, eps: float) -> None:
+        self.sums, self.width, self.eps = sums, int(width), float(eps)
+
+
 def gemm_tma(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-             swiglu: bool = False) -> torch.Tensor:
+             swiglu: bool = False, row_stats: RowStats | None = None,
+             residual: torch.Tensor | None = None, gain: torch.Tensor | None = None,
+             eps: float = 0.0):
     """``x [M <= 128, K] @ w [N, K]^T`` for bfloat16 operands on the tcgen05 tensor cores,
     streaming ``w`` once through TMA (gemm_tma.cu); the result is bfloat16 or float32.  With
     ``swiglu`` the rows of ``w`` alternate gate, up and the result is ``[M, N / 2]``:
-    ``silu(gate) * up`` computed on the fp32 accumulators in the product's epilogue."""
+    ``silu(gate) * up`` computed on the fp32 accumulators in the product's epilogue.
+
+    Two fused forms for at most 16 rows.  ``row_stats``: every row of the product is first
+    scaled by ``rsqrt(sum of its squares / width + eps)`` (the input was multiplied by a norm's
+    gain, not yet divided by its root mean square).  ``residual [M, N]`` fp32 with ``gain [N]``
+    fp32: the product is added to ``residual`` in place, the result is ``residual * gain`` and a
+    second value is returned, the ``RowStats`` of the new residual for a norm with ``eps``."""
     _cuda(x, w)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tma: operands must be bfloat16")
@@ -854,9 +881,28 @@ def gemm_tma(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bf
         raise KernelError("gemm_tma: the gate/up epilogue needs an even number of rows")
     n_out = N // 2 if swiglu else N
     out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
-    rc = lib.mi_gemm_tma(_ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), n_out, M, N, K,
-                         _code(out_dtype), 1 if swiglu else 0, blocks, _ptr(partial), _ptr(count), _stream())
+    sums_in = tiles_in = width = None
+    if row_stats is not None:
+        sums_in, width = row_stats.sums, row_stats.width
+        tiles_in = -(-width // TMA_GEMM_TILE_ROWS)
+        if (width != K or sums_in.dtype != torch.float32 or not sums_in.is_contiguous()
+                or tuple(sums_in.shape) != (tiles_in, TMA_GEMM_STAT_TOKENS)):
+            raise KernelError(f"gemm_tma: row statistics {tuple(sums_in.shape)} of width {width} do not fit K = {K}")
+    stats_out = None
+    if residual is not None:
+        if (gain is None or gain.dtype != torch.float32 or gain.numel() != N or not gain.is_contiguous()
+                or residual.dtype != torch.float32 or tuple(residual.shape) != (M, N) or not residual.is_contiguous()):
+            raise KernelError("gemm_tma: the residual epilogue needs a contiguous fp32 stream [M, N] and an fp32 gain [N]")
+        _cuda(residual, gain)
+        stats_out = torch.empty((-(-N // TMA_GEMM_TILE_ROWS), TMA_GEMM_STAT_TOKENS), dtype=torch.float32,
+                                device=x.device)
+    rc = lib.mi_gemm_tma_fused(_ptr(x), x.stride(0) if M > 1 else K, _ptr(w), _ptr(out), n_out, M, N, K,
+                               _code(out_dtype), 1 if swiglu else 0, blocks, _ptr(partial), _ptr(count),
+                               _ptr(sums_in), tiles_in or 0, width or 0, row_stats.eps if row_stats else 0.0,
+                               _ptr(residual), _ptr(gain), _ptr(stats_out), _stream())
     _finish(lib, rc, "gemm_tma")
+    if residual is not None:
+        return out, RowStats(stats_out, N, eps)
     return out
 
 
@@ -866,21 +912,47 @@ def gemm_tma_status(reset: bool = True) -> int:
     return int(_lib("gemm_tma").mi_gemm_tma_status(1 if reset else 0))
 
 
-def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor) -> torch.Tensor:
+def fused_norms_enabled() -> bool:
+    """Whether additions and norms may ride on the streaming product's epilogues
+    (``MINI_INFER_FUSED_NORMS=0`` keeps them as kernels of their own, for comparisons)."""
+    return USE_TMA_GEMM and os.environ.get("MINI_INFER_FUSED_NORMS", "1") != "0"
+
+
+def linear_fusable(n_rows: int, w: torch.Tensor) -> bool:
+    """Whether a product of ``n_rows`` rows with ``w`` has the fused forms of ``gemm_tma``
+    (``row_stats`` on its input side, ``linear_into_stream`` on its output side)."""
+    return (fused_norms_enabled() and 0 < n_rows <= min(TMA_GEMM_DISPATCH_ROWS, TMA_GEMM_FUSED_ROWS)
+            and w.is_cuda and w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_contiguous()
+            and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0)
+
+
+def linear_into_stream(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, gain: torch.Tensor,
+                       eps: float) -> tuple[torch.Tensor, "RowStats"]:
+    """``residual += x w^T`` in place (fp32); returns ``residual * gain`` in bfloat16 and the row
+    statistics a product with ``row_stats`` needs to finish an RMS norm with ``eps``."""
+    if not linear_fusable(x.shape[0], w) or not gemm_tma_ok(x, w):
+        raise KernelError("linear_into_stream: these operands have no fused form (ask linear_fusable first)")
+    return gemm_tma(x, w, torch.bfloat16, residual=residual, gain=gain, eps=eps)
+
+
+def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, row_stats: "RowStats | None" = None) -> torch.Tensor:
     """``silu(x Wg^T) * (x Wu^T)`` for a merged projection whose rows alternate gate, up
     (``w_pairs [2 I, K]``).  Decode-sized bfloat16 inputs run the product and the activation
     as one kernel (gemm_tma with its gate/up epilogue); everything else runs ``linear`` and
-    the SiLU-multiply kernel on the interleaved result."""
+    the SiLU-multiply kernel on the interleaved result.  ``row_stats``: see ``gemm_tma``."""
     if (x.dtype == torch.bfloat16 and USE_TMA_GEMM and x.shape[0] <= TMA_GEMM_DISPATCH_ROWS
             and w_pairs.dtype == torch.bfloat16 and gemm_tma_ok(x, w_pairs)):
-        return gemm_tma(x, w_pairs, torch.bfloat16, swiglu=True)
+        return gemm_tma(x, w_pairs, torch.bfloat16, swiglu=True, row_stats=row_stats)
+    if row_stats is not None:
+        raise KernelError("linear_swiglu: row statistics need the streaming product (ask linear_fusable first)")
     return silu_mul(linear(x, w_pairs), pairs=True)
 
 
 _MM_OUT_DTYPE: bool | None = None
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
+           row_stats: "RowStats | None" = None) -> torch.Tensor:
     """``x [M, K] @ w [N, K]^T``.
 
     float32 operands run the true-fp32 CUDA-core kernel (never a library product, which
@@ -889,8 +961,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     kernel before it still runs; other bfloat16 operands use the library product with fp32
     accumulation, as the reference does for every linear layer (``distributed/linear.py:167``).
     ``out_dtype=float32`` keeps the accumulator's precision in the result (used for logits).
+    ``row_stats`` (streaming product only): see ``gemm_tma``.
     """
     global _MM_OUT_DTYPE, launch_count
+    if row_stats is not None:
+        if not linear_fusable(x.shape[0], w) or not gemm_tma_ok(x, w):
+            raise KernelError("linear: row statistics need the streaming product (ask linear_fusable first)")
+        return gemm_tma(x, w, out_dtype or torch.bfloat16, row_stats=row_stats)
     if x.dtype == torch.float32:
         if w.dtype != torch.float32:
             raise KernelError("linear: fp32 activations need fp32 weights")

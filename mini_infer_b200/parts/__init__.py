@@ -2,6 +2,7 @@
 
 from .base import (  # noqa: F401
     Arrangement,
+    DeferredNorm,
     FeedForward,
     GroupView,
     KVNeed,
@@ -14,6 +15,7 @@ from .base import (  # noqa: F401
     Position,
     StateNeed,
     StepContext,
+    StreamSink,
     build_part,
     lookup,
     register_arrangement,

@@ -210,14 +210,58 @@ class Position(Part):
                            kcache=cache.k, vcache=cache.v)
 
 
+class StreamSink:
+    """Where a branch's last product may put its result instead of returning it: added to the
+    fp32 ``residual`` stream in place, with what ``norm`` (the norm that follows) needs to do the
+    rest without a kernel of its own.  Made by ``Norm.stream_sink``; ``payload`` is the norm's
+    own business (an RMS norm keeps its gain in fp32 and its eps there)."""
+
+    __slots__ = ("norm", "residual", "payload")
+
+    def __init__(self, norm: "Norm", residual: torch.Tensor, payload: Any) -> None:
+        self.norm, self.residual, self.payload = norm, residual, payload
+
+
+class DeferredNorm:
+    """A norm's input whose addition to the stream has happened and whose normalisation is left
+    to the product that reads it: ``x`` (the stream times the norm's gain, in the compute dtype),
+    ``stats`` (what that product needs to finish the norm, e.g. sums of squares per row) and the
+    updated ``residual`` stream.  The norm it was made for hands it on untouched; a part takes it
+    only if it said so (``takes_deferred_norm``)."""
+
+    __slots__ = ("norm", "x", "stats", "residual")
+
+    def __init__(self, norm: "Norm", x: torch.Tensor, stats: Any, residual: torch.Tensor) -> None:
+        self.norm, self.x, self.stats, self.residual = norm, x, stats, residual
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.x.dtype
+
+    @property
+    def device(self) -> torch.device:
+        return self.x.device
+
+    @property
+    def shape(self) -> torch.Size:
+        return self.x.shape
+
+
 class Norm(Part):
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None,
                 rows: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
         """``(normed, new_residual)``; ``residual`` is the fp32 stream or None (first norm).
 
         With ``rows`` (int32 indices) only those rows are normalised and no residual is
-        returned."""
+        returned.  A norm that hands out sinks (below) is given back what was made from them, a
+        ``DeferredNorm``, as ``x``, and returns it with its residual, launching nothing."""
         raise NotImplementedError
+
+    def stream_sink(self, residual: torch.Tensor, n_rows: int) -> StreamSink | None:
+        """A sink for the branch before this norm, or None when this norm (or this step: its
+        dtype, its number of rows) has no fused form; the branch then returns its output and
+        ``forward`` adds and normalises as usual."""
+        return None
 
 
 class Mixer(Part):
@@ -234,10 +278,26 @@ class Mixer(Part):
                 position: Position | None) -> torch.Tensor:
         raise NotImplementedError
 
+    # Optional, for arrangements that let additions and norms ride on a branch's products.  A
+    # part that answers True to the first is called with ``x`` a ``DeferredNorm``; one that
+    # answers True to the second is called with ``into=sink`` and returns a ``DeferredNorm``.
+    # Parts that know nothing of this inherit False and are called as above.
+    def takes_deferred_norm(self, n_rows: int) -> bool:
+        return False
+
+    def adds_to_stream(self, n_rows: int) -> bool:
+        return False
+
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
+
+    def takes_deferred_norm(self, n_rows: int) -> bool:
+        return False
+
+    def adds_to_stream(self, n_rows: int) -> bool:
+        return False
 
 
 class Arrangement:
@@ -266,6 +326,13 @@ class Arrangement:
 
     def forward(self, x, residual, ctx: StepContext, cache: LayerCache):
         raise NotImplementedError
+
+    def entry(self) -> tuple[Norm, Part] | None:
+        """The norm a layer begins with and the part that reads it, for the layer before (which
+        may then add its last branch to the stream itself and leave the norm to that part,
+        ``forward(..., following=entry)``), or None: the layer wants a plain ``(x, residual)``.
+        An arrangement that returns an entry also takes the ``following`` argument."""
+        return None
 
 
 # ----------------------------------------------------------------------------- registries

@@ -14,6 +14,7 @@ import torch
 from ..csrc import ops
 from .base import (
     Arrangement,
+    DeferredNorm,
     FeedForward,
     KVNeed,
     LayerCache,
@@ -24,6 +25,7 @@ from .base import (
     PlanNeeds,
     Position,
     StepContext,
+    StreamSink,
     register_arrangement,
     register_embedding,
     register_feed_forward,
@@ -40,15 +42,29 @@ def _as_compute(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 
 
 class Linear:
-    """``y = x W^T`` with ``W [out, in]`` kept in the compute dtype."""
+    """``y = x W^T`` with ``W [out, in]`` kept in the compute dtype.
+
+    ``x`` may be a ``DeferredNorm`` whose statistics are row sums of squares (the product then
+    finishes the norm in its epilogue), and ``into_stream`` adds the product to a sink's stream;
+    ``fusable`` says whether this matrix and row count have those forms."""
 
     def __init__(self, weight: torch.Tensor) -> None:
         if weight.dim() != 2 or not weight.is_contiguous():
             raise ValueError("Linear needs a contiguous [out, in] matrix")
         self.weight = weight
 
-    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    def __call__(self, x, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        if isinstance(x, DeferredNorm):
+            return ops.linear(x.x, self.weight, out_dtype, row_stats=x.stats)
         return ops.linear(x, self.weight, out_dtype)
+
+    def fusable(self, n_rows: int) -> bool:
+        return ops.linear_fusable(n_rows, self.weight)
+
+    def into_stream(self, x: torch.Tensor, sink: StreamSink) -> DeferredNorm:
+        gain, eps = sink.payload
+        y, stats = ops.linear_into_stream(x, self.weight, sink.residual, gain, eps)
+        return DeferredNorm(sink.norm, y, stats, sink.residual)
 
 
 # ----------------------------------------------------------------------------- norm
@@ -71,7 +87,19 @@ class RMSNorm(Norm):
         self.weight = w if w.dtype == torch.float32 else w.to(dtype)
         self.eps = float(self.param("eps"))
 
+    def stream_sink(self, residual, n_rows):
+        if (not ops.fused_norms_enabled() or residual is None
+                or n_rows > ops.TMA_GEMM_FUSED_ROWS or not residual.is_cuda):
+            return None
+        if getattr(self, "_gain32", None) is None:
+            self._gain32 = self.weight.to(torch.float32).contiguous()   # the products' epilogues read fp32
+        return StreamSink(self, residual, (self._gain32, self.eps))
+
     def forward(self, x, residual, rows=None):
+        if isinstance(x, DeferredNorm):
+            if x.norm is not self or rows is not None:
+                raise ValueError("a deferred norm was handed to another norm than the one it was made for")
+            return x, x.residual
         if rows is not None:
             return ops.add_rmsnorm(x, self.weight, self.eps, residual_in=residual, rows=rows), None
         new_residual = torch.empty(x.shape, dtype=torch.float32, device=x.device)
@@ -208,7 +236,13 @@ class GroupedQueryAttention(Mixer):
         self.qkv_proj = Linear(qkv)
         self.o_proj = Linear(_as_compute(tensors["o_proj.weight"], dtype).contiguous())
 
-    def forward(self, x, ctx: StepContext, cache: LayerCache, position):
+    def takes_deferred_norm(self, n_rows):
+        return self.qkv_proj.fusable(n_rows)
+
+    def adds_to_stream(self, n_rows):
+        return self.o_proj.fusable(n_rows)
+
+    def forward(self, x, ctx: StepContext, cache: LayerCache, position, into=None):
         nq, nkv, d = self.nq, self.nkv, self.d
         qkv = self.qkv_proj(x)
         table = None
@@ -225,7 +259,7 @@ class GroupedQueryAttention(Mixer):
         out = torch.empty((ctx.n_tokens, nq * d), dtype=x.dtype, device=x.device)
         ops.attention(qkv, qkv.stride(0), out, cache, ctx, nq, nkv, d, self.scale, self.window or 0,
                       rope_table=table)
-        return self.o_proj(out)
+        return self.o_proj(out) if into is None else self.o_proj.into_stream(out, into)
 
 
 # ----------------------------------------------------------------------------- feed-forward
@@ -256,8 +290,18 @@ class SwiGLU(FeedForward):
         self.gate_up_proj = Linear(gate_up)
         self.down_proj = Linear(_as_compute(tensors["down_proj.weight"], dtype).contiguous())
 
-    def forward(self, x, ctx):
-        return self.down_proj(ops.linear_swiglu(x, self.gate_up_proj.weight))
+    def takes_deferred_norm(self, n_rows):
+        return self.gate_up_proj.fusable(n_rows)
+
+    def adds_to_stream(self, n_rows):
+        return self.down_proj.fusable(n_rows)
+
+    def forward(self, x, ctx, into=None):
+        if isinstance(x, DeferredNorm):
+            h = ops.linear_swiglu(x.x, self.gate_up_proj.weight, row_stats=x.stats)
+        else:
+            h = ops.linear_swiglu(x, self.gate_up_proj.weight)
+        return self.down_proj(h) if into is None else self.down_proj.into_stream(h, into)
 
 
 # ----------------------------------------------------------------------------- embedding / head
@@ -315,13 +359,36 @@ class PreNormBlock(Arrangement):
     following norm (reference ``models/blocks/transformer_block.py:107-120,140-153``): the
     block receives the previous branch output ``x`` and the fp32 stream ``residual``, and
     returns its feed-forward output with the stream that does not yet include it.
+
+    Where the parts on both sides of a norm say they can (few rows, bfloat16), the branch's last
+    product adds its result to the stream itself and the product after the norm finishes the
+    norm in its epilogue, so that the norm launches nothing: within the block for the second
+    norm, and across blocks when the layer that follows gave its ``entry``.
     """
 
-    def forward(self, x, residual, ctx, cache):
+    def entry(self):
+        return self.mixer_norm, self.mixer
+
+    @staticmethod
+    def _sink(producer, norm, consumer, residual, n_rows):
+        if residual is None or not producer.adds_to_stream(n_rows) or not consumer.takes_deferred_norm(n_rows):
+            return None
+        return norm.stream_sink(residual, n_rows)
+
+    def forward(self, x, residual, ctx, cache, following=None):
+        n = ctx.n_tokens
         a, residual = self.mixer_norm.forward(x, residual)
-        h = self.mixer.forward(a, ctx, cache, self.position)
+        sink = self._sink(self.mixer, self.feed_forward_norm, self.feed_forward, residual, n)
+        if sink is None:
+            h = self.mixer.forward(a, ctx, cache, self.position)
+        else:
+            h = self.mixer.forward(a, ctx, cache, self.position, into=sink)
         b, residual = self.feed_forward_norm.forward(h, residual)
-        f = self.feed_forward.forward(b, ctx)
+        sink = self._sink(self.feed_forward, following[0], following[1], residual, n) if following else None
+        if sink is None:
+            f = self.feed_forward.forward(b, ctx)
+        else:
+            f = self.feed_forward.forward(b, ctx, into=sink)
         return f, residual
 
 

@@ -155,8 +155,14 @@ class DecoderModel:
             raise RuntimeError("the model has no weights yet")
         x = self.embedding.forward(ctx)
         residual = None
-        for entry, cache in zip(self.schedule, caches):
-            x, residual = self.blocks[entry.layer].forward(x, residual, ctx, cache)
+        for i, (entry, cache) in enumerate(zip(self.schedule, caches)):
+            block = self.blocks[entry.layer]
+            if block.entry() is None:
+                x, residual = block.forward(x, residual, ctx, cache)
+                continue
+            # a layer that takes part in the hand-over of norms is told how the next one begins
+            after = self.blocks[self.schedule[i + 1].layer].entry() if i + 1 < len(self.schedule) else None
+            x, residual = block.forward(x, residual, ctx, cache, following=after)
         if n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
         z, _ = self.final_norm.forward(x, residual, rows=want_rows)

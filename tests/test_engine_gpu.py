@@ -127,6 +127,54 @@ def test_decode_lookahead_gives_the_same_tokens(model_dirs, cuda_graph):
     assert "stop" in ahead_why and sched.wasted_tokens >= 1
 
 
+@pytest.mark.parametrize("which", ["B", "C"])
+def test_norms_ride_on_the_products_in_small_steps(which, model_dirs, monkeypatch):
+    """In a bfloat16 step of a few tokens the blocks' additions and norms are done by the
+    products around them: only the first norm and the final norm launch a kernel.  The logits
+    agree with the route that launches every norm, and with the plain implementation."""
+    from mini_infer_b200.csrc import ops
+    from mini_infer_b200.engine import ModelRunner, StepEntry
+
+    cfg = TINY[which]
+    layers = cfg["num_hidden_layers"]
+    prompt = prompt_ids(which, 37, salt=91)
+    tail = prompt_ids(which, 6, salt=92)
+    calls = []
+    real = ops.add_rmsnorm
+
+    def counting(*args, **kwargs):
+        calls.append(1)
+        return real(*args, **kwargs)
+
+    monkeypatch.setattr(ops, "add_rmsnorm", counting)
+
+    def run(fused):
+        monkeypatch.setenv("MINI_INFER_FUSED_NORMS", "1" if fused else "0")
+        runner = ModelRunner.from_pretrained(model_dirs[which], dtype="bfloat16", block_size=PAGE_SIZE[which],
+                                             num_blocks=64, max_requests=2, cuda_graph=False)
+        runner.add_request("r")
+        runner.step([StepEntry("r", prompt, [])])
+        rows, counts = [], []
+        for tok in tail[:3]:
+            del calls[:]
+            rows.append(runner.step([StepEntry("r", [tok], [0])]).logits[0].float().cpu())
+            counts.append(len(calls))
+        del calls[:]
+        rows.extend(runner.step([StepEntry("r", tail[3:], [0, 1, 2])]).logits.float().cpu())   # a portion of three
+        counts.append(len(calls))
+        return torch.stack(rows), counts
+
+    fused, n_fused = run(True)
+    unfused, n_unfused = run(False)
+    assert n_unfused == [2 * layers + 1] * 4
+    assert n_fused == [2] * 4
+    want = P.llama_logits(load_state(model_dirs[which]), cfg, prompt + tail, dtype=torch.float64)[len(prompt):]
+    bound = T.tolerance("bfloat16", float(want.abs().max()))
+    for got in (fused, unfused):
+        assert T.first_bad(got.double().numpy(), want.numpy(), bound) is None
+    assert ops.gemm_tma_status() == 0
+
+
 def test_decode_steps_of_every_batch_size_are_captured_ahead(model_dirs):
     """``capture_decode_steps`` leaves a graph per batch size and an empty cache behind, and what
     is generated afterwards (replaying those graphs from the first decode step on) is what the

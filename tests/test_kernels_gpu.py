@@ -220,6 +220,66 @@ def test_gemm_tma(M, N, K, out_dtype):
     assert ops().gemm_tma_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 256, 64), (8, 4096, 4096), (5, 320, 176), (8, 192, 14336), (16, 1000, 520),
+                                   (3, 4104, 1032)])
+def test_gemm_tma_adds_to_the_stream_and_leaves_statistics(M, N, K):
+    """The residual epilogue: the fp32 stream takes the product in place, the output is the new
+    stream times the gain, and the sums of squares per 128 features add up to each row's; then
+    the product that takes those statistics finishes an RMS norm.  Against float64; widths with
+    a ragged last tile and k ranges cut across blocks."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=50)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=51, scale=0.1)
+    res = rnd(M, N, seed=52)
+    gain = 1 + 0.1 * rnd(N, seed=53)
+    eps = 1e-5
+    stream = res.clone().to(DEV)
+    y, stats = ops().gemm_tma(x.to(DEV), w.to(DEV), torch.bfloat16, residual=stream, gain=gain.to(DEV), eps=eps)
+    want_stream = res.double() + x.double() @ w.double().T
+    scale = max(1.0, want_stream.abs().max().item())
+    assert (stream.cpu().double() - want_stream).abs().max().item() <= 1e-5 * scale
+    want_y = want_stream * gain.double()
+    assert (y.cpu().double() - want_y).abs().max().item() <= 1 / 128 * max(1.0, want_y.abs().max().item())
+    assert stats.width == N and stats.eps == eps and stats.sums.shape == (-(-N // 128), 16)
+    sums = stats.sums.cpu().double()
+    want_sq = (want_stream ** 2).sum(dim=1)
+    assert ((sums[:, :M].sum(dim=0) - want_sq).abs() <= 1e-5 * want_sq).all()
+    for t in range(sums.shape[0]):      # tile by tile, so that no tile's share lands in another's slot
+        part = (want_stream[:, t * 128:(t + 1) * 128] ** 2).sum(dim=1)
+        assert ((sums[t, :M] - part).abs() <= 1e-5 * part + 1e-9).all()
+    # the consumer: a product of the gained stream, scaled row by row in its epilogue
+    w2 = rnd(264, N, dtype=torch.bfloat16, seed=54, scale=0.1)
+    out = ops().gemm_tma(y, w2.to(DEV), torch.float32, row_stats=stats)
+    rstd = 1.0 / torch.sqrt(want_sq / N + eps)
+    want_out = (y.cpu().double() * rstd[:, None]) @ w2.double().T
+    assert (out.cpu().double() - want_out).abs().max().item() <= 1e-5 * max(1.0, want_out.abs().max().item())
+    # against the norm itself: gain * h * rstd, rounded once more on this route (y is bfloat16)
+    normed = (want_stream * rstd[:, None] * gain.double()) @ w2.double().T
+    assert (out.cpu().double() - normed).abs().max().item() <= 1 / 128 * max(1.0, normed.abs().max().item())
+    # and with the gate/up epilogue behind the scaling
+    wg, wu = rnd(100, N, dtype=torch.bfloat16, seed=55, scale=0.1), rnd(100, N, dtype=torch.bfloat16, seed=56, scale=0.1)
+    pairs = torch.stack([wg, wu], dim=1).reshape(200, N).contiguous()
+    act = ops().gemm_tma(y, pairs.to(DEV), torch.bfloat16, swiglu=True, row_stats=stats)
+    xn = y.cpu().double() * rstd[:, None]
+    want_act = P.silu(xn @ wg.double().T) * (xn @ wu.double().T)
+    assert (act.cpu().double() - want_act).abs().max().item() <= 1 / 128 * max(1.0, want_act.abs().max().item())
+    assert ops().gemm_tma_status() == 0
+
+
+def test_gemm_tma_fused_forms_refuse_what_they_cannot_take():
+    w = rnd(256, 64, dtype=torch.bfloat16, seed=57).to(DEV)
+    x = rnd(17, 64, dtype=torch.bfloat16, seed=58).to(DEV)
+    with pytest.raises(ops().KernelError, match="at most 16"):
+        ops().gemm_tma(x, w, torch.bfloat16, residual=torch.zeros(17, 256, device=DEV),
+                       gain=torch.ones(256, device=DEV), eps=1e-5)
+    with pytest.raises(ops().KernelError, match="fp32"):
+        ops().gemm_tma(x[:4].contiguous(), w, torch.bfloat16, residual=torch.zeros(4, 256, device=DEV),
+                       gain=torch.ones(256, device=DEV, dtype=torch.bfloat16), eps=1e-5)
+    stats = ops().RowStats(torch.zeros(2, 16, device=DEV), 200, 1e-5)
+    with pytest.raises(ops().KernelError, match="do not fit"):
+        ops().gemm_tma(x[:4].contiguous(), w, torch.bfloat16, row_stats=stats)
+    assert not ops().linear_fusable(17, w) and ops().linear_fusable(16, w)
+
+
 def test_gemm_tma_is_deterministic_and_independent_of_other_rows():
     """Partial tiles are added in block order whatever the arrival order, and a row of x gives
     the same result alone as among other rows."""
