@@ -304,6 +304,9 @@ def long_mixed(runner, args, num_blocks: int) -> dict:
                                 decode_headroom_blocks=8)
     # Warm-up: one short request end to end, so that kernels are built and loaded.
     sched.generate([Request(prompts[0][:64], SamplingParams(), max_tokens=4)])
+    # ... and the decode steps of every batch size are captured, as the engine thread does before
+    # it serves (ContinuousScheduler.start): a size met for the first time costs some 40 ms otherwise
+    captured = runner.capture_decode_steps(args.requests)
     clocks = ClockSampler()
     clocks.start()
     torch.cuda.synchronize()
@@ -343,7 +346,7 @@ def long_mixed(runner, args, num_blocks: int) -> dict:
         "decode_step_ms_p50": round(decode_ms[len(decode_ms) // 2], 3) if decode_ms else None,
         "pool_high_water": round(high_water, 4), "pool_in_use_after": runner.cache.usage(),
         "preemptions": sched.preemptions, "tokens_computed_in_vain": sched.wasted_tokens,
-        "clocks": clock_summary,
+        "decode_graphs_captured_ahead": captured, "clocks": clock_summary,
     }
     return line
 

@@ -2,7 +2,7 @@
 
     python -m mini_infer_b200.microbench attention_decode --batch 8 --context 2048
     python -m mini_infer_b200.microbench attention_prefill --tokens 2048 [--impl mma]
-    python -m mini_infer_b200.microbench gemm_tma --rows 8 --n 28672 --k 4096
+    python -m mini_infer_b200.microbench gemm_tma --rows 8 --n 28672 --k 4096 [--epilogue stream|stats]
     python -m mini_infer_b200.microbench add_rmsnorm --rows 8 --width 4096
     python -m mini_infer_b200.microbench rope_write --rows 2048
     python -m mini_infer_b200.microbench silu_mul --rows 2048 --width 14336
@@ -175,9 +175,20 @@ def attention_prefill(args, ops, device, flush) -> tuple[float, str]:
 def gemm_tma(args, ops, device, flush) -> tuple[float, str]:
     x = torch.randn(args.rows, args.k, device=device, dtype=torch.bfloat16)
     w = torch.randn(args.n, args.k, device=device, dtype=torch.bfloat16)
+    if args.epilogue == "stream":      # the product added to the fp32 stream, gain and statistics for the next norm
+        stream = torch.randn(args.rows, args.n, device=device)
+        gain = torch.ones(args.n, device=device)
 
-    def run():
-        ops.gemm_tma(x, w)
+        def run():
+            ops.gemm_tma(x, w, residual=stream, gain=gain, eps=1e-5)
+    elif args.epilogue == "stats":     # every row scaled by the statistics the product before left
+        stats = ops.RowStats(torch.rand(-(-args.k // 128), 16, device=device) * 128, args.k, 1e-5)
+
+        def run():
+            ops.gemm_tma(x, w, row_stats=stats)
+    else:
+        def run():
+            ops.gemm_tma(x, w)
 
     us = _time(run, args.iters, args.warmup, flush)
     status = ops.gemm_tma_status()
@@ -273,6 +284,8 @@ def main(argv=None) -> int:
                     help="attention_prefill: the tcgen05 kernel (default) or the mma.sync kernel; attention_decode: "
                          "keys spread evenly over persistent blocks (default) or equal slices per request; "
                          "library: FlashInfer's paged prefill wrapper on the same shapes, for comparison")
+    ap.add_argument("--epilogue", choices=["plain", "stream", "stats"], default="plain",
+                    help="gemm_tma: the plain product, or one of its fused forms for up to 16 rows")
     ap.add_argument("--rope", action="store_true",
                     help="attention_decode: give the kernel un-rotated q, k, v and the rotary table (it rotates and stores itself)")
     ap.add_argument("--skew", type=float, default=0.0,
