@@ -21,6 +21,11 @@
 // tile; the block that arrives last at a tile (a counter per tile) adds the partials in block
 // order and stores the result, so the sum's order is fixed and nobody waits for anybody.
 //
+// The weights are read with an evict-first mark (they pass once per step and are far larger than
+// the L2), so that the small tensors the step's kernels hand to one another stay there.  For up to
+// 16 tokens the kernel has a second instance whose epilogue also does a decoder block's additions
+// and norms (EpilogueFusion below): the plain instance keeps its registers.
+//
 // Every mbarrier wait is bounded: a wait that gives up sets a status word, the block leaves
 // its loops, frees its tensor memory and returns (the output is then wrong and the host finds
 // the status set).
