@@ -213,26 +213,26 @@ class Position(Part):
 class StreamSink:
     """Where a branch's last product may put its result instead of returning it: added to the
     fp32 ``residual`` stream in place, with what ``norm`` (the norm that follows) needs to do the
-    rest without a kernel of its own.  Made by ``Norm.stream_sink``; ``payload`` is the norm's
-    own business (an RMS norm keeps its gain in fp32 and its eps there)."""
+    rest without a kernel of its own.  Made by ``Norm.stream_sink``; ``kind`` is the norm's
+    ``deferred_kind`` and says what ``payload`` holds (``"rms"``: the gain in fp32 and eps)."""
 
-    __slots__ = ("norm", "residual", "payload")
+    __slots__ = ("norm", "kind", "residual", "payload")
 
-    def __init__(self, norm: "Norm", residual: torch.Tensor, payload: Any) -> None:
-        self.norm, self.residual, self.payload = norm, residual, payload
+    def __init__(self, norm: "Norm", kind: str, residual: torch.Tensor, payload: Any) -> None:
+        self.norm, self.kind, self.residual, self.payload = norm, kind, residual, payload
 
 
 class DeferredNorm:
     """A norm's input whose addition to the stream has happened and whose normalisation is left
     to the product that reads it: ``x`` (the stream times the norm's gain, in the compute dtype),
-    ``stats`` (what that product needs to finish the norm, e.g. sums of squares per row) and the
-    updated ``residual`` stream.  The norm it was made for hands it on untouched; a part takes it
-    only if it said so (``takes_deferred_norm``)."""
+    ``stats`` (what that product needs to finish the norm; for kind ``"rms"`` the sums of squares
+    per row) and the updated ``residual`` stream.  The norm it was made for hands it on untouched;
+    a part takes it only if it said so (``takes_deferred_norm``)."""
 
-    __slots__ = ("norm", "x", "stats", "residual")
+    __slots__ = ("norm", "kind", "x", "stats", "residual")
 
-    def __init__(self, norm: "Norm", x: torch.Tensor, stats: Any, residual: torch.Tensor) -> None:
-        self.norm, self.x, self.stats, self.residual = norm, x, stats, residual
+    def __init__(self, norm: "Norm", kind: str, x: torch.Tensor, stats: Any, residual: torch.Tensor) -> None:
+        self.norm, self.kind, self.x, self.stats, self.residual = norm, kind, x, stats, residual
 
     @property
     def dtype(self) -> torch.dtype:
@@ -248,6 +248,11 @@ class DeferredNorm:
 
 
 class Norm(Part):
+    # What kind of unfinished norm this class can leave to the products around it (``"rms"``: the
+    # product before adds to the stream, multiplies by the gain and leaves sums of squares; the
+    # product after divides by the root mean square), or None: the norm always runs by itself.
+    deferred_kind: ClassVar[str | None] = None
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None,
                 rows: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
         """``(normed, new_residual)``; ``residual`` is the fp32 stream or None (first norm).
@@ -279,13 +284,14 @@ class Mixer(Part):
         raise NotImplementedError
 
     # Optional, for arrangements that let additions and norms ride on a branch's products.  A
-    # part that answers True to the first is called with ``x`` a ``DeferredNorm``; one that
-    # answers True to the second is called with ``into=sink`` and returns a ``DeferredNorm``.
-    # Parts that know nothing of this inherit False and are called as above.
-    def takes_deferred_norm(self, n_rows: int) -> bool:
+    # part that answers True to the first is called with ``x`` a ``DeferredNorm`` of that kind;
+    # one that answers True to the second is called with ``into=sink`` (a sink of that kind) and
+    # returns a ``DeferredNorm``.  Parts that know nothing of this inherit False and are called
+    # as above.
+    def takes_deferred_norm(self, n_rows: int, kind: str) -> bool:
         return False
 
-    def adds_to_stream(self, n_rows: int) -> bool:
+    def adds_to_stream(self, n_rows: int, kind: str) -> bool:
         return False
 
 
@@ -293,10 +299,10 @@ class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
-    def takes_deferred_norm(self, n_rows: int) -> bool:
+    def takes_deferred_norm(self, n_rows: int, kind: str) -> bool:
         return False
 
-    def adds_to_stream(self, n_rows: int) -> bool:
+    def adds_to_stream(self, n_rows: int, kind: str) -> bool:
         return False
 
 

@@ -55,16 +55,20 @@ class Linear:
 
     def __call__(self, x, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         if isinstance(x, DeferredNorm):
+            if x.kind != "rms":
+                raise ValueError(f"this product cannot finish a norm of kind {x.kind!r}")
             return ops.linear(x.x, self.weight, out_dtype, row_stats=x.stats)
         return ops.linear(x, self.weight, out_dtype)
 
-    def fusable(self, n_rows: int) -> bool:
-        return ops.linear_fusable(n_rows, self.weight)
+    def fusable(self, n_rows: int, kind: str = "rms") -> bool:
+        return kind == "rms" and ops.linear_fusable(n_rows, self.weight)
 
     def into_stream(self, x: torch.Tensor, sink: StreamSink) -> DeferredNorm:
+        if sink.kind != "rms":
+            raise ValueError(f"this product cannot finish a norm of kind {sink.kind!r}")
         gain, eps = sink.payload
         y, stats = ops.linear_into_stream(x, self.weight, sink.residual, gain, eps)
-        return DeferredNorm(sink.norm, y, stats, sink.residual)
+        return DeferredNorm(sink.norm, sink.kind, y, stats, sink.residual)
 
 
 # ----------------------------------------------------------------------------- norm
@@ -77,6 +81,8 @@ class RMSNorm(Norm):
 
     params: ``hidden_size``, ``eps``.  tensors: ``weight [hidden_size]``.
     """
+
+    deferred_kind = "rms"
 
     def param_decls(self):
         return {"weight": ParamDecl((int(self.param("hidden_size")),), "gain")}
@@ -93,7 +99,7 @@ class RMSNorm(Norm):
             return None
         if getattr(self, "_gain32", None) is None:
             self._gain32 = self.weight.to(torch.float32).contiguous()   # the products' epilogues read fp32
-        return StreamSink(self, residual, (self._gain32, self.eps))
+        return StreamSink(self, self.deferred_kind, residual, (self._gain32, self.eps))
 
     def forward(self, x, residual, rows=None):
         if isinstance(x, DeferredNorm):
@@ -236,11 +242,11 @@ class GroupedQueryAttention(Mixer):
         self.qkv_proj = Linear(qkv)
         self.o_proj = Linear(_as_compute(tensors["o_proj.weight"], dtype).contiguous())
 
-    def takes_deferred_norm(self, n_rows):
-        return self.qkv_proj.fusable(n_rows)
+    def takes_deferred_norm(self, n_rows, kind):
+        return self.qkv_proj.fusable(n_rows, kind)
 
-    def adds_to_stream(self, n_rows):
-        return self.o_proj.fusable(n_rows)
+    def adds_to_stream(self, n_rows, kind):
+        return self.o_proj.fusable(n_rows, kind)
 
     def forward(self, x, ctx: StepContext, cache: LayerCache, position, into=None):
         nq, nkv, d = self.nq, self.nkv, self.d
@@ -290,14 +296,16 @@ class SwiGLU(FeedForward):
         self.gate_up_proj = Linear(gate_up)
         self.down_proj = Linear(_as_compute(tensors["down_proj.weight"], dtype).contiguous())
 
-    def takes_deferred_norm(self, n_rows):
-        return self.gate_up_proj.fusable(n_rows)
+    def takes_deferred_norm(self, n_rows, kind):
+        return self.gate_up_proj.fusable(n_rows, kind)
 
-    def adds_to_stream(self, n_rows):
-        return self.down_proj.fusable(n_rows)
+    def adds_to_stream(self, n_rows, kind):
+        return self.down_proj.fusable(n_rows, kind)
 
     def forward(self, x, ctx, into=None):
         if isinstance(x, DeferredNorm):
+            if x.kind != "rms":
+                raise ValueError(f"this product cannot finish a norm of kind {x.kind!r}")
             h = ops.linear_swiglu(x.x, self.gate_up_proj.weight, row_stats=x.stats)
         else:
             h = ops.linear_swiglu(x, self.gate_up_proj.weight)
@@ -371,7 +379,9 @@ class PreNormBlock(Arrangement):
 
     @staticmethod
     def _sink(producer, norm, consumer, residual, n_rows):
-        if residual is None or not producer.adds_to_stream(n_rows) or not consumer.takes_deferred_norm(n_rows):
+        kind = norm.deferred_kind
+        if (kind is None or residual is None or not producer.adds_to_stream(n_rows, kind)
+                or not consumer.takes_deferred_norm(n_rows, kind)):
             return None
         return norm.stream_sink(residual, n_rows)
 

@@ -27,9 +27,9 @@ def test_parts_say_no_unless_they_know_better():
 
     m, f, n = ToyMixer(_spec("toy")), ToyFeedForward(_spec("toy")), ToyNorm(_spec("toy"))
     for rows in (1, 8, 16, 4096):
-        assert not m.takes_deferred_norm(rows) and not m.adds_to_stream(rows)
-        assert not f.takes_deferred_norm(rows) and not f.adds_to_stream(rows)
-        assert n.stream_sink(torch.zeros(rows, 8), rows) is None
+        assert not m.takes_deferred_norm(rows, "rms") and not m.adds_to_stream(rows, "rms")
+        assert not f.takes_deferred_norm(rows, "rms") and not f.adds_to_stream(rows, "rms")
+        assert n.stream_sink(torch.zeros(rows, 8), rows) is None and n.deferred_kind is None
     assert ToyBlock(m, f, n, n, None).entry() is None
 
 
@@ -51,10 +51,11 @@ def test_a_norm_takes_back_only_what_was_made_for_it():
     a = build_part("norm", _spec("rmsnorm", hidden_size=16, eps=1e-5))
     b = build_part("norm", _spec("rmsnorm", hidden_size=16, eps=1e-5))
     stream = torch.zeros(2, 16)
-    handed = DeferredNorm(a, torch.zeros(2, 16), object(), stream)
+    handed = DeferredNorm(a, "rms", torch.zeros(2, 16), object(), stream)
     x, residual = a.forward(handed, None)
     assert x is handed and residual is stream
     with pytest.raises(ValueError, match="another norm"):
         b.forward(handed, None)
-    sink = StreamSink(a, stream, ("gain", 1e-5))
+    sink = StreamSink(a, "rms", stream, ("gain", 1e-5))
+    assert a.deferred_kind == "rms" and sink.kind == "rms"
     assert sink.norm is a and sink.residual is stream and handed.shape == (2, 16) and handed.dtype == torch.float32
