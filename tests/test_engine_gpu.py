@@ -168,6 +168,12 @@ def test_norms_ride_on_the_products_in_small_steps(which, model_dirs, monkeypatc
     unfused, n_unfused = run(False)
     assert n_unfused == [2 * layers + 1] * 4
     assert n_fused == [2] * 4
+    # a norm of a kind the products do not know keeps its kernel, whatever the switch says
+    from mini_infer_b200.parts.builtin import RMSNorm
+    monkeypatch.setattr(RMSNorm, "deferred_kind", "a kind of its own")
+    other, n_other = run(True)
+    monkeypatch.undo()
+    assert n_other == [2 * layers + 1] * 4 and torch.equal(other, unfused)
     want = P.llama_logits(load_state(model_dirs[which]), cfg, prompt + tail, dtype=torch.float64)[len(prompt):]
     bound = T.tolerance("bfloat16", float(want.abs().max()))
     for got in (fused, unfused):
