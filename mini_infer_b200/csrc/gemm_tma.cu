@@ -448,7 +448,8 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       const float gain_n = (kFused && fus.residual && n < N) ? __ldg(fus.gain + n) : 0.f;   // needed last, asked for first
       if (kFused && i == 0) {
         // What the kernels before this one wrote may be read once the copy thread's wait for them is
-        // over (these warps do not wait for the grids themselves: that wait wakes up late).
+        // over: it says so through a barrier of the block, which orders these warps' loads behind it
+        // (measured: no faster and no slower than every warp waiting for the grids itself).
         // (a wait that gives up here makes the wait for the accumulator below give up as well)
         const bool ready = mbar_wait(&inputs_ready, 0, gu);
         if (fus.stats_in && ready && etid < FUSED_MAX_TOKENS) {
