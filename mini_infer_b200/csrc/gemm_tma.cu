@@ -43,6 +43,8 @@ MI_DEFINE_ERROR_API()
 #define SMEM_BUDGET (200 * 1024)   // ring of stages; about 100 KB per SM must be in flight to keep memory busy
 #define ALIGNED_GRID_MIN_PCT 85     // use a block count that divides into the tiles if it keeps this share of the SMs
 #define BOXES_PER_STAGE 2          // k boxes per stage: one box per stage leaves the issuing threads behind
+#define WIDE_BOXES_PER_STAGE 4     // ... and four where they fit (see mi_gemm_tma_fused)
+#define SMEM_BUDGET_WIDE (221 * 1024)
 #define MAX_STAGES 12
 #define SPIN_LIMIT (1 << 22)
 
@@ -643,8 +645,16 @@ extern "C" int mi_gemm_tma_fused(const void* x, long long ldx, const void* w, vo
   if (blocks <= 0) MI_REFUSE("gemm_tma: bad block count %d", blocks);
   if (out_dtype != MI_DTYPE_BF16 && out_dtype != MI_DTYPE_F32) MI_REFUSE("gemm_tma: unknown output dtype %d", out_dtype);
   const int n_tok = (M + 15) / 16 * 16;
-  const int kb = BOXES_PER_STAGE;
-  const int budget = SMEM_BUDGET;
+  // Four boxes along k per stage where three such stages fit (up to 16 tokens) and K is a whole
+  // number of them: every row of W then contributes 512 contiguous bytes to a copy instead of 256
+  // (inside a captured decode step of Llama 3.1 8B sizes: 3.762 -> 3.733 ms; three boxes: 3.736).
+  int kb = BOXES_PER_STAGE;
+  int budget = SMEM_BUDGET;
+  if (K >= 2048 && K % (TILE_K * WIDE_BOXES_PER_STAGE) == 0 &&
+      (TILE_ROWS * TILE_K * 2 + n_tok * TILE_K * 2) * WIDE_BOXES_PER_STAGE * 3 <= SMEM_BUDGET_WIDE) {
+    kb = WIDE_BOXES_PER_STAGE;
+    budget = SMEM_BUDGET_WIDE;
+  }
   const long long total = (long long)((N + TILE_ROWS - 1) / TILE_ROWS) * ((K + TILE_K * kb - 1) / (TILE_K * kb));
   int grid = (int)(total < blocks ? total : blocks);
   {
